@@ -1,0 +1,160 @@
+/*
+ * awq_b200.h — C ABI of the B200 (sm_100a) AWQ W4A16 quantized-linear kernels.
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes and a CUDA stream,
+ * returns an int status (0 = ok) and never throws, exits or allocates: the
+ * caller owns all memory, including repacked weights and workspaces.  The
+ * library keeps no state between calls apart from a per-device cache of
+ * immutable device properties.
+ *
+ * Tensor formats (the reference's on-disk AWQ tensors, group size G):
+ *   qweight int32 [K, N/8]   bits 4i..4i+3 of word c hold channel 8c+ORDER[i],
+ *                            ORDER = {0,2,4,6,1,3,5,7}
+ *   qzeros  int32 [K/G, N/8] same nibble rule
+ *   scales  fp16  [K/G, N]
+ *   bias    fp16  [N] or NULL
+ *   W[k,n]  = fp16_rn( fp16(q[k,n] - z[k/G,n]) * scales[k/G,n] )
+ *   y[m,n]  = fp16( sum_k x[m,k] * W[k,n] )  then  y = fp16(y + bias[n])
+ *
+ * Kernel-side weight layout ("packed", produced once at load by
+ * awq_b200_repack, same byte count as qweight): [K/128][N][16] uint32, where
+ * word j of (block b, column n) holds q[128b + 8j + e, n] for e = 0..7 at
+ * nibble position (e >> 1) + 4 * (e & 1).  qzeros and scales are used as they
+ * are on disk.
+ *
+ * Shape rules for every compute entry point: K % 128 == 0, N % 8 == 0,
+ * G % 128 == 0 and K % G == 0; all pointers 16-byte aligned.
+ */
+#ifndef AWQ_B200_H_
+#define AWQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AWQ_B200_API __attribute__((visibility("default")))
+#else
+#define AWQ_B200_API
+#endif
+
+/* A cudaStream_t, spelled without the CUDA headers. */
+typedef void* awq_b200_stream_t;
+
+enum awq_b200_status {
+  AWQ_B200_OK = 0,
+  AWQ_B200_ERR_NULL = 1,      /* a required pointer is NULL                       */
+  AWQ_B200_ERR_SHAPE = 2,     /* M/K/N violate the shape rules above              */
+  AWQ_B200_ERR_ALIGN = 3,     /* a pointer is not 16-byte aligned                 */
+  AWQ_B200_ERR_GROUP = 4,     /* unsupported group size                           */
+  AWQ_B200_ERR_WORKSPACE = 5, /* workspace missing or smaller than *_workspace_bytes */
+  AWQ_B200_ERR_CUDA = 6,      /* a CUDA call failed; see awq_b200_last_cuda_error  */
+  AWQ_B200_ERR_ARCH = 7,      /* current device is not compute capability 10.x    */
+  AWQ_B200_ERR_TOO_LARGE = 8  /* size beyond what an entry point supports         */
+};
+
+/* Library version, major * 1000 + minor.  No reference counterpart (the
+ * reference extension is unversioned, LLMQRT/runtime_refact/csrc/bindings.cpp:9-47). */
+AWQ_B200_API int awq_b200_version(void);
+
+/* Static, human-readable name of a status code. */
+AWQ_B200_API const char* awq_b200_status_string(int status);
+
+/* cudaError_t value of the last failed CUDA call on the calling thread (0 if none). */
+AWQ_B200_API int awq_b200_last_cuda_error(void);
+
+/* Make `device` current for the calling thread inside this library's CUDA
+ * runtime instance.  Replaces the `at::cuda::OptionalCUDAGuard` the reference
+ * installs in its GEMM entry points (LLMQRT/runtime_refact/csrc/awq/gemm_db.cu:683). */
+AWQ_B200_API int awq_b200_set_device(int device);
+
+/* ---- load-time repack --------------------------------------------------- */
+
+/* Bytes of the packed weight for a K x N linear (= K * N / 2). */
+AWQ_B200_API size_t awq_b200_packed_bytes(int K, int N);
+
+/* qweight [K, N/8] -> packed.  Load-time step with no reference counterpart:
+ * the reference kernels read the on-disk layout directly
+ * (LLMQRT/runtime_refact/csrc/awq/gemv.cu:132-135). */
+AWQ_B200_API int awq_b200_repack(const int32_t* qweight, void* packed, int K, int N,
+                    awq_b200_stream_t stream);
+
+/* packed -> qweight [K, N/8]; exact inverse of awq_b200_repack, so a module's
+ * state_dict can always be produced in the on-disk format. */
+AWQ_B200_API int awq_b200_unpack(const void* packed, int32_t* qweight, int K, int N,
+                    awq_b200_stream_t stream);
+
+/* ---- dequantisation (parity aid and fp16 fallback for callers) ---------- */
+
+/* On-disk tensors -> W fp16 [K, N], bit-for-bit the reference's
+ * dequantize_gemm (LLMQRT/runtime_refact/utils/packing_utils.py:65-80). */
+AWQ_B200_API int awq_b200_dequant(const int32_t* qweight, const int32_t* qzeros, const void* scales,
+                     void* W, int K, int N, int group_size, awq_b200_stream_t stream);
+
+/* Packed weight -> W fp16 [K, N] through the very device function the GEMV and
+ * GEMM kernels dequantise with; must equal awq_b200_dequant bit-for-bit. */
+AWQ_B200_API int awq_b200_dequant_packed(const void* packed, const int32_t* qzeros, const void* scales,
+                            void* W, int K, int N, int group_size, awq_b200_stream_t stream);
+
+/* ---- decode: split-K GEMV, M <= 16 -------------------------------------- */
+
+/* Bytes of scratch awq_b200_gemv needs for (M, K, N).  The first
+ * awq_b200_gemv_counter_bytes(N) bytes hold arrival counters that must be zero
+ * before the first call and are left zero by every completed call. */
+AWQ_B200_API size_t awq_b200_gemv_workspace_bytes(int M, int K, int N);
+AWQ_B200_API size_t awq_b200_gemv_counter_bytes(int N);
+
+/* y[M, N] = x[M, K] . W (+ bias), 1 <= M <= 16, one pass over the weights for
+ * all rows.  Replaces awq_gemv / awq_gemv_coalesced
+ * (LLMQRT/runtime_refact/csrc/awq/gemv.cu:171-208, gemv_coalesced.cu:263-303).
+ * A row's result does not depend on M or on the other rows, and repeated calls
+ * give identical bits.  Calls sharing one workspace must not overlap on the GPU. */
+AWQ_B200_API int awq_b200_gemv(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                  const void* bias, void* y, int M, int K, int N, int group_size,
+                  void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {1,2,4} column
+ * tiles per warp, bps in 1..16 k-blocks of 128 per split, 0 = planner's choice.
+ * Its workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N).  No
+ * reference counterpart. */
+AWQ_B200_API size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N);
+AWQ_B200_API int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales,
+                       const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
+                       int group_size, void* workspace, size_t workspace_bytes,
+                       awq_b200_stream_t stream, int ntw, int bps);
+
+/* ---- prefill: TMA + tcgen05/TMEM GEMM, any M >= 1 ----------------------- */
+
+AWQ_B200_API size_t awq_b200_gemm_workspace_bytes(int M, int K, int N);
+
+/* Y[M, N] = X[M, K] . W (+ bias) with fp32 accumulation in tensor memory.
+ * Replaces awq_gemm / awq_gemm_db / awq_gemm_cutlass
+ * (LLMQRT/runtime_refact/csrc/awq/gemm.cu:407-467, gemm_db.cu:670-732,
+ * gemm_cutlass.cu:314-374); the reference's split_k_iters argument has no
+ * equivalent because partial sums never leave tensor memory. */
+AWQ_B200_API int awq_b200_gemm(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                  const void* bias, void* y, int M, int K, int N, int group_size,
+                  void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* ---- dispatch ------------------------------------------------------------ */
+
+/* Largest M routed to the GEMV kernel by awq_b200_linear (16). */
+AWQ_B200_API int awq_b200_gemv_max_rows(void);
+
+AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
+
+/* M <= 16 -> awq_b200_gemv, else awq_b200_gemm.  Mirrors the row-count switch
+ * in AWQLinearMMFunction.forward
+ * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), with
+ * the threshold moved from 8 to 16 rows. */
+AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                    const void* bias, void* y, int M, int K, int N, int group_size,
+                    void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AWQ_B200_H_ */

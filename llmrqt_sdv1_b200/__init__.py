@@ -1,0 +1,10 @@
+"""B200 (sm_100a) implementation of the AWQ W4A16 quantized-linear hot path.
+
+Public surface:
+  AWQLinear_GEMM, AWQLinearMMFunction   module API of the reference runtime
+  sq_fp8_kernels                        function API of the reference extension
+  kernels                               torch wrappers over the C ABI (include/awq_b200.h)
+"""
+from .linear_awq import AWQLinear_GEMM, AWQLinearMMFunction, WQLinear_GEMM, WQLinearMMFunction, pack_awq_int4
+
+__all__ = ["AWQLinear_GEMM", "AWQLinearMMFunction", "WQLinear_GEMM", "WQLinearMMFunction", "pack_awq_int4"]

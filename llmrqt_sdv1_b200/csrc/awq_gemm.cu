@@ -1,0 +1,500 @@
+// Prefill path: W4A16 GEMM on 5th-generation tensor cores.
+//
+// Persistent, warp-specialised kernel, one CTA per SM, CTA tile (128*MH) x 256,
+// k-stage of 64:
+//   warp 0      TMA producer: activations [128 x 64] fp16 per row half (128-byte
+//               swizzle) and the packed int4 weights [256 columns x 32 bytes].
+//   warp 1      allocates tensor memory and issues tcgen05.mma (M=128, N=256,
+//               K=16, fp16 inputs, fp32 accumulators in TMEM), one thread.
+//   warps 2-9   read the packed nibbles from shared memory, dequantise them to
+//               the exact reference fp16 weight and store them as the K-major,
+//               128-byte-swizzled B operand; after the last k-stage the same
+//               warps drain the accumulators (tcgen05.ld), round to fp16, add
+//               the bias and store Y.
+// Stages are handed over with mbarriers.  Every wait is bounded: on expiry the
+// kernel raises an abort flag, all roles fall through, tensor memory is freed
+// and a non-zero status word is left in the workspace.
+#include <cuda.h>
+
+#include "awq_common.cuh"
+
+namespace awq {
+
+constexpr int kGemmThreads = 320;
+constexpr int kDequantThreads = 256;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kABytesHalf = 128 * kBK * 2;   // 16 KiB: 128 rows x 128 B
+constexpr int kBBytes = kBN * kBK * 2;       // 32 KiB: 256 columns x 128 B
+constexpr int kRawBytes = kBN * (kBK / 2);   // 8 KiB: 256 columns x 32 B of nibbles
+constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // ~2 s at 2 GHz
+
+template <int MH> struct GemmCfg {
+  static constexpr int kStages = (MH == 2) ? 3 : 4;
+  static constexpr int kStageBytes = MH * kABytesHalf + kBBytes + kRawBytes;
+  static constexpr int kTmemCols = 256 * MH;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+  const uint16_t* scales;
+  const uint32_t* qzeros;
+  const uint16_t* bias;
+  uint16_t* y;
+  unsigned* status;  // workspace word: 0 = ok, else which wait expired
+  int M, K, N;
+  int group_size;
+  int mtiles, ntiles;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *abort_flag) if the phase did not
+// complete in time or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  unsigned spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        atomicCAS(const_cast<int*>(abort_flag), 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset: next 8-row group
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+                                (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cvt_pack_bias(float a, float b, uint32_t bias2, bool has_bias) {
+  __half2 h = __floats2half2_rn(a, b);
+  uint32_t v = *reinterpret_cast<uint32_t*>(&h);
+  if (has_bias) asm("add.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(bias2));
+  return v;
+}
+
+template <int MH>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+            const GemmParams p) {
+  using Cfg = GemmCfg<MH>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ uint32_t s_tmem_base;
+
+  // 1024-byte aligned carve-up: [stage: A halves | B | raw] x kStages, then barriers.
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  auto a_addr = [&](int st, int h) { return base + st * Cfg::kStageBytes + h * kABytesHalf; };
+  auto b_addr = [&](int st) { return base + st * Cfg::kStageBytes + MH * kABytesHalf; };
+  auto raw_addr = [&](int st) { return base + st * Cfg::kStageBytes + MH * kABytesHalf + kBBytes; };
+  const uint32_t bar_base = base + kStages * Cfg::kStageBytes;
+  auto bar_full_tma = [&](int st) { return bar_base + 8u * st; };
+  auto bar_full_b = [&](int st) { return bar_base + 8u * (kStages + st); };
+  auto bar_empty = [&](int st) { return bar_base + 8u * (2 * kStages + st); };
+  const uint32_t bar_acc_full = bar_base + 8u * (3 * kStages);
+  const uint32_t bar_acc_empty = bar_base + 8u * (3 * kStages + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int st = 0; st < kStages; ++st) {
+      mbar_init(bar_full_tma(st), 1);
+      mbar_init(bar_full_b(st), kDequantThreads / 32);
+      mbar_init(bar_empty(st), 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, kDequantThreads / 32);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  const int nks = p.K / kBK;
+  const int num_tiles = p.mtiles * p.ntiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.mtiles) * (128 * MH);
+        const int n0 = (tile / p.mtiles) * kBN;
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int st = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(bar_empty(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+          mbar_expect_tx(bar_full_tma(st), MH * kABytesHalf + kRawBytes);
+#pragma unroll
+          for (int h = 0; h < MH; ++h) tma_load_2d(a_addr(st, h), &map_x, ks * kBK, m0 + h * 128, bar_full_tma(st));
+          tma_load_3d(raw_addr(st), &map_w, (ks & 1) * 32, n0, ks >> 1, bar_full_tma(st));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+        if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int st = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 3)) { ok = false; break; }
+          if (!mbar_wait(bar_full_b(st), ph, abort_flag, 4)) { ok = false; break; }
+          tcgen05_fence_after();
+#pragma unroll
+          for (int h = 0; h < MH; ++h) {
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk) {
+              const uint64_t da = make_sw128_desc(a_addr(st, h) + kk * 32);
+              const uint64_t db = make_sw128_desc(b_addr(st) + kk * 32);
+              tcgen05_mma_f16(tmem_base + h * 256, da, db, kInstrDesc, (ks | kk) != 0 ? 1u : 0u);
+            }
+          }
+          tcgen05_commit(bar_empty(st));   // stage reusable once these MMAs have read it
+        }
+        if (ok) tcgen05_commit(bar_acc_full);
+      }
+    }
+  } else {
+    // ---------------------- dequantise, then drain accumulators ---------------
+    const int id = tid - 64;                 // 0..255
+    const int dq_warp = id >> 5;             // 0..7
+    const int col_local = id >> 1;           // 0..127 (second pass: +128)
+    const int hh = id & 1;                   // which 16-byte half of the column's 32 raw bytes
+    const int lane_q = warp & 3;             // TMEM lane quarter this warp may read
+    const int col_half = dq_warp >> 2;       // epilogue: columns [128*col_half, +128)
+    // B-operand byte offsets of the four 16-byte chunks this thread writes per pass
+    uint32_t boff[4];
+    {
+      const int r8 = col_local & 7;
+      const uint32_t row_off = static_cast<uint32_t>(col_local >> 3) * 1024u + static_cast<uint32_t>(r8) * 128u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) boff[i] = row_off + static_cast<uint32_t>(((4 * hh + i) ^ r8) << 4);
+    }
+    const int zcols = p.N >> 3;
+    uint32_t it = 0, tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      const int m0 = (tile % p.mtiles) * (128 * MH);
+      const int n0 = (tile / p.mtiles) * kBN;
+      const int nA = n0 + col_local, nB = nA + 128;
+      const bool vA = nA < p.N, vB = nB < p.N;
+      const uint32_t zshift = awq_slot_shift(static_cast<uint32_t>(nA & 7));  // nB & 7 == nA & 7
+
+      auto load_sz = [&](int ks, uint32_t& sA, uint32_t& sB, uint32_t& zA, uint32_t& zB) {
+        const int grp = (ks * kBK) / p.group_size;
+        sA = vA ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + nA) : 0u;
+        sB = vB ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + nB) : 0u;
+        zA = vA ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (nA >> 3)) : 0u;
+        zB = vB ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (nB >> 3)) : 0u;
+      };
+      uint32_t sA, sB, zA, zB, sA_n = 0, sB_n = 0, zA_n = 0, zB_n = 0;
+      load_sz(0, sA, sB, zA, zB);
+
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        const int st = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        const bool group_changes = (ks + 1 < nks) && (((ks + 1) * kBK) % p.group_size == 0);
+        if (group_changes) load_sz(ks + 1, sA_n, sB_n, zA_n, zB_n);
+        if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 5)) { ok = false; break; }
+
+        const unsigned char* raw = base_ptr + (raw_addr(st) - base);
+        unsigned char* bst = base_ptr + (b_addr(st) - base);
+        const uint4 r0 = *reinterpret_cast<const uint4*>(raw + id * 16);
+        const uint4 r1 = *reinterpret_cast<const uint4*>(raw + 4096 + id * 16);
+        {
+          const ZeroPair zp = make_zero_pair((zA >> zshift) & 0xFu);
+          const uint32_t s2 = sA * 0x00010001u;
+          const uint32_t w[4] = {r0.x, r0.y, r0.z, r0.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[4];
+            dequant_word(w[i], zp, s2, o);
+            *reinterpret_cast<uint4*>(bst + boff[i]) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        {
+          const ZeroPair zp = make_zero_pair((zB >> zshift) & 0xFu);
+          const uint32_t s2 = sB * 0x00010001u;
+          const uint32_t w[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[4];
+            dequant_word(w[i], zp, s2, o);
+            *reinterpret_cast<uint4*>(bst + 16384 + boff[i]) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full_b(st));
+        if (group_changes) { sA = sA_n; sB = sB_n; zA = zA_n; zB = zB_n; }
+      }
+      if (!ok) break;
+
+      // ------------------------------ epilogue --------------------------------
+      if (!mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) { ok = false; break; }
+      tcgen05_fence_after();
+      const bool has_bias = p.bias != nullptr;
+#pragma unroll 1
+      for (int h = 0; h < MH; ++h) {
+        const int row = m0 + h * 128 + lane_q * 32 + lane;
+#pragma unroll 1
+        for (int chunk = 0; chunk < 4; ++chunk) {
+          const int col0 = n0 + col_half * 128 + chunk * 32;
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_q * 32) << 16) +
+                                 static_cast<uint32_t>(h * 256 + col_half * 128 + chunk * 32);
+          tcgen05_ld_32x32b_x32(taddr, v);   // whole warp, even if its rows are past M
+          tcgen05_wait_ld();
+          if (row < p.M) {
+            uint16_t* yrow = p.y + static_cast<size_t>(row) * p.N;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int col = col0 + q * 8;
+              if (col < p.N) {
+                uint32_t b2[4] = {0u, 0u, 0u, 0u};
+                if (has_bias) {
+                  const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                  b2[0] = bv.x; b2[1] = bv.y; b2[2] = bv.z; b2[3] = bv.w;
+                }
+                uint4 out;
+                out.x = cvt_pack_bias(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]), b2[0], has_bias);
+                out.y = cvt_pack_bias(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), b2[1], has_bias);
+                out.z = cvt_pack_bias(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), b2[2], has_bias);
+                out.w = cvt_pack_bias(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), b2[3], has_bias);
+                *reinterpret_cast<uint4*>(yrow + col) = out;
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+  if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, static_cast<unsigned>(s_abort));
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encode(EncodeTiledFn* out) {
+  EncodeTiledFn fn = __atomic_load_n(&g_encode, __ATOMIC_ACQUIRE);
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    AWQ_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !sym) return cuda_fail(cudaErrorNotSupported);
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    __atomic_store_n(&g_encode, fn, __ATOMIC_RELEASE);
+  }
+  *out = fn;
+  return AWQ_B200_OK;
+}
+
+template <int MH>
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int sm_count,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<MH>;
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  const int tiles = p.mtiles * p.ntiles;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  gemm_kernel<MH><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
+  AWQ_CUDA_TRY(cudaGetLastError());
+  return AWQ_B200_OK;
+}
+
+int gemm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                  cudaStream_t stream) {
+  if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
+  if (int st = check_shape(K, N, group_size)) return st;
+  if (M < 1) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y) ||
+      (bias && !aligned16(bias)))
+    return AWQ_B200_ERR_ALIGN;
+  if (!workspace || workspace_bytes < 16) return AWQ_B200_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
+  EncodeTiledFn encode;
+  if (int st = get_encode(&encode)) return st;
+
+  // Row halves per CTA tile: two when that does not cost an extra wave.
+  const int ntiles = (N + kBN - 1) / kBN;
+  const long long t1 = static_cast<long long>((M + 127) / 128) * ntiles;
+  const long long t2 = static_cast<long long>((M + 255) / 256) * ntiles;
+  const long long w1 = (t1 + di.sm_count - 1) / di.sm_count, w2 = (t2 + di.sm_count - 1) / di.sm_count;
+  const int MH = (M > 128 && 2 * w2 <= w1) ? 2 : 1;
+
+  CUtensorMap mx, mw;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {kBK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  }
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / kBlockK)};
+    const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(N) * 64};
+    const cuuint32_t box[3] = {32, kBN, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(packed), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  }
+
+  GemmParams p;
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
+  p.bias = static_cast<const uint16_t*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.status = static_cast<unsigned*>(workspace);
+  p.M = M; p.K = K; p.N = N;
+  p.group_size = group_size;
+  p.ntiles = ntiles;
+  p.mtiles = (M + 128 * MH - 1) / (128 * MH);
+  return MH == 2 ? launch_gemm<2>(mx, mw, p, di.sm_count, stream) : launch_gemm<1>(mx, mw, p, di.sm_count, stream);
+}
+
+}  // namespace awq
+
+using namespace awq;
+
+extern "C" {
+
+size_t awq_b200_gemm_workspace_bytes(int M, int K, int N) {
+  (void)M; (void)K; (void)N;
+  return 256;  // one status word, padded
+}
+
+int awq_b200_gemm(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                  awq_b200_stream_t stream) {
+  return gemm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+                       static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,389 @@
+// Decode path: split-K W4A16 GEMV for 1 <= M <= 16 rows.
+//
+// One pass over the packed weights serves all rows.  Work unit = one 128-k
+// block x one tile of 8 output columns = 512 contiguous bytes, read by a warp
+// as one 128-bit load per lane.  Lane (g = lane / 4, c = lane % 4) owns column
+// 8*tile + g and the four words 4c..4c+3 of that column (32 consecutive k),
+// dequantises them in registers to fp16 (the exact reference weight) and feeds
+// them to mma.sync m16n8k16 as the B operand, with the activations as A and
+// fp32 accumulators.  k is split over gridDim.y; each split writes fp32
+// partials to the workspace and the last CTA to arrive for a column range adds
+// them in split order, so results are deterministic and a row's value does not
+// depend on how many rows the call has.
+#include "awq_common.cuh"
+
+namespace awq {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvMaxBps = 16;   // 128-k blocks per split (bounds the activation slice in smem)
+constexpr int kGemvMaxRows = 16;
+
+struct GemvParams {
+  const uint16_t* x;
+  const uint4* wp;
+  const uint16_t* scales;
+  const uint32_t* qzeros;
+  const uint16_t* bias;
+  uint16_t* y;
+  float* partial;
+  unsigned* counters;
+  int M, K, N;
+  int group_blocks;  // group_size / 128
+  int nblk;          // K / 128
+  int bps;           // blocks per split
+  int S;             // number of splits
+  int ntiles;        // N / 8
+};
+
+__device__ __forceinline__ void mma_16816(float acc[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// y = fp16(acc) then, with a bias, fp16(y + bias): the two roundings of the
+// reference's `out + bias` on an fp16 tensor.
+__device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, size_t row_off, int col,
+                                           float a, float b) {
+  uint32_t v = pack_half2(a, b);
+  if (bias != nullptr) {
+    const uint32_t bv = *reinterpret_cast<const uint32_t*>(bias + col);
+    asm("add.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(bv));
+  }
+  *reinterpret_cast<uint32_t*>(y + row_off + col) = v;
+}
+
+template <int NTW, int MT>
+__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int split = blockIdx.y;
+  const int b0 = split * p.bps;
+  const int nb = min(p.bps, p.nblk - b0);
+  const int row_stride = p.bps * 256 + 64;  // bytes; +64 keeps rows g and g+1 on disjoint banks
+
+  const int tile0 = (blockIdx.x * kGemvWarps + warp) * NTW;
+  int tile[NTW];
+#pragma unroll
+  for (int t = 0; t < NTW; ++t) tile[t] = min(tile0 + t, p.ntiles - 1);  // clamp: loads stay in range
+
+  const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;  // uint4 per 128-k block
+  const int zcols = p.N >> 3;
+
+  uint4 wcur[NTW];
+  uint32_t scur[NTW], zcur[NTW];
+  auto issue_loads = [&](int bl, uint4 (&w)[NTW], uint32_t (&s)[NTW], uint32_t (&z)[NTW]) {
+    const int b = b0 + bl;
+    const int grp = b / p.group_blocks;
+    const uint4* wb = p.wp + static_cast<size_t>(b) * block_stride_u4 + lane;
+#pragma unroll
+    for (int t = 0; t < NTW; ++t) w[t] = ldg_stream(wb + static_cast<size_t>(tile[t]) * 32);
+#pragma unroll
+    for (int t = 0; t < NTW; ++t) {
+      s[t] = __ldg(p.scales + static_cast<size_t>(grp) * p.N + tile[t] * 8 + g);
+      z[t] = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tile[t]);
+    }
+  };
+  issue_loads(0, wcur, scur, zcur);
+
+  // Stage this split's activation slice.  Chunk j (8 halves) of a block lands at
+  // slot (j % 4) * 4 + j / 4 so that lane c's i-th 128-bit read (chunk 4c + i)
+  // is conflict free.
+  {
+    const int chunks_per_row = nb * 16;
+    const int total = MT * chunks_per_row;
+    for (int i = tid; i < total; i += kGemvThreads) {
+      const int r = i / chunks_per_row;
+      const int cj = i - r * chunks_per_row;
+      const int bl = cj >> 4, j = cj & 15;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < p.M)
+        v = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.K +
+                                                 static_cast<size_t>(b0 + bl) * kBlockK + j * 8));
+      const int slot = (j & 3) * 4 + (j >> 2);
+      *reinterpret_cast<uint4*>(smem + r * row_stride + bl * 256 + slot * 16) = v;
+    }
+  }
+  __syncthreads();
+
+  float acc[NTW][4];
+#pragma unroll
+  for (int t = 0; t < NTW; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+
+  const unsigned char* xrow = smem + g * row_stride + c * 16;
+
+  for (int bl = 0; bl < nb; ++bl) {
+    uint4 wnext[NTW];
+    uint32_t snext[NTW], znext[NTW];
+    if (bl + 1 < nb) issue_loads(bl + 1, wnext, snext, znext);
+
+    uint4 xa[4], xb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xa[i] = *reinterpret_cast<const uint4*>(xrow + bl * 256 + i * 64);
+      if (MT == 16) xb[i] = *reinterpret_cast<const uint4*>(xrow + 8 * row_stride + bl * 256 + i * 64);
+      else xb[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+
+#pragma unroll
+    for (int t = 0; t < NTW; ++t) {
+      const ZeroPair zp = make_zero_pair((zcur[t] >> awq_slot_shift(g)) & 0xFu);
+      const uint32_t s2 = scur[t] * 0x00010001u;
+      const uint32_t w[4] = {wcur[t].x, wcur[t].y, wcur[t].z, wcur[t].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t o[4];
+        dequant_word(w[i], zp, s2, o);
+        mma_16816(acc[t], xa[i].x, xb[i].x, xa[i].y, xb[i].y, o[0], o[1]);
+        mma_16816(acc[t], xa[i].z, xb[i].z, xa[i].w, xb[i].w, o[2], o[3]);
+      }
+    }
+
+    if (bl + 1 < nb) {
+#pragma unroll
+      for (int t = 0; t < NTW; ++t) { wcur[t] = wnext[t]; scur[t] = snext[t]; zcur[t] = znext[t]; }
+    }
+  }
+
+  // ---- epilogue -----------------------------------------------------------
+  if (p.S == 1) {
+#pragma unroll
+    for (int t = 0; t < NTW; ++t) {
+      if (tile0 + t >= p.ntiles) continue;
+      const int col = (tile0 + t) * 8 + 2 * c;
+      if (g < p.M) store_out2(p.y, p.bias, static_cast<size_t>(g) * p.N, col, acc[t][0], acc[t][1]);
+      if (MT == 16 && g + 8 < p.M)
+        store_out2(p.y, p.bias, static_cast<size_t>(g + 8) * p.N, col, acc[t][2], acc[t][3]);
+    }
+    return;
+  }
+
+#pragma unroll
+  for (int t = 0; t < NTW; ++t) {
+    if (tile0 + t >= p.ntiles) continue;
+    const int col = (tile0 + t) * 8 + 2 * c;
+    if (g < p.M)
+      __stcg(reinterpret_cast<float2*>(p.partial + (static_cast<size_t>(split) * p.M + g) * p.N + col),
+             make_float2(acc[t][0], acc[t][1]));
+    if (MT == 16 && g + 8 < p.M)
+      __stcg(reinterpret_cast<float2*>(p.partial + (static_cast<size_t>(split) * p.M + g + 8) * p.N + col),
+             make_float2(acc[t][2], acc[t][3]));
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+    const int last = (prev == static_cast<unsigned>(p.S - 1));
+    if (last) p.counters[blockIdx.x] = 0u;  // every split has arrived: leave the counter clean
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // The last CTA of this column range adds the S partials in split order.
+  const int col0 = blockIdx.x * (kGemvWarps * NTW * 8);
+  const int ncols = min(kGemvWarps * NTW * 8, p.N - col0);
+  const int pairs = ncols >> 1;
+  for (int i = tid; i < p.M * pairs; i += kGemvThreads) {
+    const int row = i / pairs;
+    const int col = col0 + 2 * (i - row * pairs);
+    const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
+    const size_t split_stride = static_cast<size_t>(p.M) * p.N;
+    float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
+    for (int s = 1; s < p.S; ++s) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * split_stride));
+      sum.x += v.x;
+      sum.y += v.y;
+    }
+    store_out2(p.y, p.bias, static_cast<size_t>(row) * p.N, col, sum.x, sum.y);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host: decomposition chosen from (K, N) only, never from M.
+// ---------------------------------------------------------------------------
+struct GemvPlan {
+  int ntw;
+  int bps;
+  int S;
+  int ncol;
+};
+
+static GemvPlan plan_gemv(int K, int N, int sm_count) {
+  const int nblk = K / kBlockK, ntiles = N / 8;
+  const int slots = sm_count * 2;
+  // Cost model in microseconds: a CTA streams bps*ntw units of 4 KiB; two CTAs
+  // share one SM's slice of HBM bandwidth (~44 KB/us).
+  const double t_fix = 1.2, t_unit = 0.19, t_red = 0.4, t_red_split = 0.04;
+  GemvPlan best{1, 1, nblk, 0};
+  double best_t = 1e30;
+  const int ntws[3] = {4, 2, 1};
+  for (int ntw : ntws) {
+    const int ncol = (ntiles + kGemvWarps * ntw - 1) / (kGemvWarps * ntw);
+    int prev_S = -1;
+    for (int bps = kGemvMaxBps; bps >= 1; --bps) {
+      const int S = (nblk + bps - 1) / bps;
+      if (S == prev_S) continue;
+      prev_S = S;
+      const int bps_eff = (nblk + S - 1) / S;  // even split
+      const long long nctas = static_cast<long long>(ncol) * S;
+      const long long waves = (nctas + slots - 1) / slots;
+      double t = waves * (t_fix + bps_eff * ntw * t_unit);
+      if (S > 1) t += t_red + S * t_red_split;
+      if (t < best_t) {
+        best_t = t;
+        best = GemvPlan{ntw, bps_eff, S, ncol};
+      }
+    }
+  }
+  best.S = (nblk + best.bps - 1) / best.bps;
+  return best;
+}
+
+static size_t counter_bytes(int N) {
+  const size_t ncol_max = (static_cast<size_t>(N) / 8 + kGemvWarps - 1) / kGemvWarps;  // ntw = 1
+  return (ncol_max * sizeof(unsigned) + 255) / 256 * 256;
+}
+
+template <int NTW, int MT>
+static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64);
+  if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
+  if (smem > 48 * 1024) {
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+  }
+  dim3 grid(plan.ncol, plan.S);
+  gemv_kernel<NTW, MT><<<grid, kGemvThreads, smem, stream>>>(p);
+  AWQ_CUDA_TRY(cudaGetLastError());
+  return AWQ_B200_OK;
+}
+
+int gemv_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                  const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_bps) {
+  if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
+  if (int st = check_shape(K, N, group_size)) return st;
+  if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) ||
+      !aligned16(y) || (bias && !aligned16(bias)))
+    return AWQ_B200_ERR_ALIGN;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
+
+  GemvPlan plan = plan_gemv(K, N, di.sm_count);
+  if (force_ntw == 1 || force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
+  if (force_bps >= 1 && force_bps <= kGemvMaxBps) plan.bps = force_bps;
+  const int nblk = K / kBlockK, ntiles = N / 8;
+  plan.S = (nblk + plan.bps - 1) / plan.bps;
+  plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
+  if (plan.S > 65535) return AWQ_B200_ERR_TOO_LARGE;
+
+  GemvParams p;
+  p.x = static_cast<const uint16_t*>(x);
+  p.wp = static_cast<const uint4*>(packed);
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
+  p.bias = static_cast<const uint16_t*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.partial = nullptr;
+  p.counters = nullptr;
+  p.M = M; p.K = K; p.N = N;
+  p.group_blocks = group_size / kBlockK;
+  p.nblk = nblk;
+  p.bps = plan.bps;
+  p.S = plan.S;
+  p.ntiles = ntiles;
+  if (plan.S > 1) {
+    const size_t cb = counter_bytes(N);
+    const size_t need = cb + static_cast<size_t>(plan.S) * M * N * sizeof(float);
+    if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
+    p.counters = static_cast<unsigned*>(workspace);
+    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + cb);
+  }
+
+  const bool wide = M > 8;
+#define AWQ_GEMV_CASE(NTW_)                                                                  \
+  case NTW_:                                                                                 \
+    return wide ? launch_gemv<NTW_, 16>(p, plan, di.max_smem_optin, stream)                  \
+                : launch_gemv<NTW_, 8>(p, plan, di.max_smem_optin, stream);
+  switch (plan.ntw) {
+    AWQ_GEMV_CASE(1)
+    AWQ_GEMV_CASE(2)
+    AWQ_GEMV_CASE(4)
+    default: return AWQ_B200_ERR_SHAPE;
+  }
+#undef AWQ_GEMV_CASE
+}
+
+size_t gemv_workspace_bytes(int M, int K, int N) {
+  if (M < 1 || K < kBlockK || N < 8) return 0;
+  // Worst case over every decomposition the planner or a forced plan can pick: bps = 1.
+  const size_t S_max = static_cast<size_t>(K / kBlockK);
+  return counter_bytes(N) + S_max * static_cast<size_t>(M) * N * sizeof(float);
+}
+
+}  // namespace awq
+
+using namespace awq;
+
+extern "C" {
+
+size_t awq_b200_gemv_counter_bytes(int N) { return N > 0 ? counter_bytes(N) : 0; }
+
+size_t awq_b200_gemv_workspace_bytes(int M, int K, int N) {
+  if (M < 1 || K < kBlockK || N < 8) return 0;
+  DeviceInfo di;
+  int sm = 148;
+  if (device_info(&di) == AWQ_B200_OK) sm = di.sm_count;
+  const GemvPlan plan = plan_gemv(K, N, sm);
+  return counter_bytes(N) + static_cast<size_t>(plan.S) * M * N * sizeof(float);
+}
+
+int awq_b200_gemv(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                  const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                  size_t workspace_bytes, awq_b200_stream_t stream) {
+  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0);
+}
+
+// Tuning hook: same as awq_b200_gemv with the decomposition forced
+// (ntw in {1,2,4} column tiles per warp, bps in 1..16 k-blocks per split; 0 = planner's choice).
+// The workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N) bytes.
+size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N) { return gemv_workspace_bytes(M, K, N); }
+
+int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                       const void* bias, void* y, int M, int K, int N, int group_size,
+                       void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
+                       int bps) {
+  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps);
+}
+
+int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }
+
+}  // extern "C"

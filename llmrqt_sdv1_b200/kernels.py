@@ -1,0 +1,161 @@
+"""Torch-level wrappers over the C ABI: they allocate outputs and workspaces
+with torch, pass raw device pointers plus the current stream, and turn status
+codes into exceptions.  No arithmetic happens here."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+GEMV_MAX_ROWS = lib.awq_b200_gemv_max_rows()
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _prep(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    if dev.type != "cuda":
+        raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
+    for t in tensors:
+        if t is not None and t.device != dev:
+            raise RuntimeError("all tensors of one call must be on the same device")
+    _lib.set_device(dev.index if dev.index is not None else torch.cuda.current_device())
+    return dev
+
+
+def _kn(qweight: torch.Tensor) -> tuple[int, int]:
+    if qweight.dtype != torch.int32 or qweight.dim() != 2:
+        raise ValueError("qweight must be int32 [K, N/8]")
+    return qweight.shape[0], qweight.shape[1] * 8
+
+
+class PackedWeight:
+    """Kernel-layout weight of one linear: packed nibbles plus the on-disk
+    scales / qzeros it is used with."""
+    __slots__ = ("packed", "qzeros", "scales", "K", "N", "group_size")
+
+    def __init__(self, packed, qzeros, scales, K, N, group_size):
+        self.packed, self.qzeros, self.scales = packed, qzeros, scales
+        self.K, self.N, self.group_size = K, N, group_size
+
+
+def repack(qweight: torch.Tensor) -> torch.Tensor:
+    """On-disk qweight int32 [K, N/8] -> packed int32 [K/128, N, 16] (same bytes)."""
+    K, N = _kn(qweight)
+    qweight = qweight.contiguous()
+    _prep(qweight)
+    if K % 128 != 0:
+        raise ValueError(f"in_features must be a multiple of 128, got {K}")
+    packed = torch.empty((K // 128, N, 16), dtype=torch.int32, device=qweight.device)
+    check(lib.awq_b200_repack(qweight.data_ptr(), packed.data_ptr(), K, N, _stream(qweight)), "awq_b200_repack")
+    return packed
+
+
+def unpack(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of `repack`."""
+    nblk, N, _ = packed.shape
+    K = nblk * 128
+    _prep(packed)
+    qweight = torch.empty((K, N // 8), dtype=torch.int32, device=packed.device)
+    check(lib.awq_b200_unpack(packed.data_ptr(), qweight.data_ptr(), K, N, _stream(packed)), "awq_b200_unpack")
+    return qweight
+
+
+def make_packed(qweight, qzeros, scales, group_size) -> PackedWeight:
+    K, N = _kn(qweight)
+    G = K if group_size == -1 else group_size
+    if scales.dtype != torch.float16 or tuple(scales.shape) != (K // G, N):
+        raise ValueError("scales must be fp16 [K/G, N]")
+    if qzeros.dtype != torch.int32 or tuple(qzeros.shape) != (K // G, N // 8):
+        raise ValueError("qzeros must be int32 [K/G, N/8]")
+    return PackedWeight(repack(qweight), qzeros.contiguous(), scales.contiguous(), K, N, G)
+
+
+def dequantize(qweight, qzeros, scales, group_size) -> torch.Tensor:
+    """fp16 [K, N], bit-identical to the reference's dequantize_gemm."""
+    K, N = _kn(qweight)
+    qweight, qzeros, scales = qweight.contiguous(), qzeros.contiguous(), scales.contiguous()
+    _prep(qweight, qzeros, scales)
+    W = torch.empty((K, N), dtype=torch.float16, device=qweight.device)
+    check(lib.awq_b200_dequant(qweight.data_ptr(), qzeros.data_ptr(), scales.data_ptr(), W.data_ptr(), K, N,
+                               K if group_size == -1 else group_size, _stream(W)), "awq_b200_dequant")
+    return W
+
+
+def dequantize_packed(pw: PackedWeight) -> torch.Tensor:
+    _prep(pw.packed, pw.qzeros, pw.scales)
+    W = torch.empty((pw.K, pw.N), dtype=torch.float16, device=pw.packed.device)
+    check(lib.awq_b200_dequant_packed(pw.packed.data_ptr(), pw.qzeros.data_ptr(), pw.scales.data_ptr(),
+                                      W.data_ptr(), pw.K, pw.N, pw.group_size, _stream(W)),
+          "awq_b200_dequant_packed")
+    return W
+
+
+# One zero-initialised workspace per (device, stream): calls that share a
+# workspace must not overlap on the GPU, and calls on one stream never do.
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(dev: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (dev.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_x(x: torch.Tensor, pw: PackedWeight) -> torch.Tensor:
+    if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != pw.K:
+        raise ValueError(f"x must be fp16 [M, {pw.K}], got {x.dtype} {tuple(x.shape)}")
+    return x.contiguous()
+
+
+def _run(fn, name, x, pw, bias, ws_bytes, out=None, extra=()):
+    x = _check_x(x, pw)
+    dev = _prep(x, pw.packed, pw.qzeros, pw.scales, bias)
+    M = x.shape[0]
+    y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
+    stream = _stream(x)
+    ws = _workspace(dev, stream, ws_bytes)
+    check(fn(x.data_ptr(), pw.packed.data_ptr(), pw.scales.data_ptr(), pw.qzeros.data_ptr(),
+             bias.data_ptr() if bias is not None else None, y.data_ptr(), M, pw.K, pw.N, pw.group_size,
+             ws.data_ptr(), ws.numel(), stream, *extra), name)
+    return y
+
+
+def gemv(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
+    """Decode kernel, 1 <= M <= 16."""
+    return _run(lib.awq_b200_gemv, "awq_b200_gemv", x, pw, bias,
+                lib.awq_b200_gemv_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out)
+
+
+def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None) -> torch.Tensor:
+    """Decode kernel with a forced decomposition (tuning and tests)."""
+    return _run(lib.awq_b200_gemv_plan, "awq_b200_gemv_plan", x, pw, bias,
+                lib.awq_b200_gemv_workspace_bytes_max(max(x.shape[0], 1), pw.K, pw.N), out, (ntw, bps))
+
+
+def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
+    """Prefill kernel (tcgen05), any M >= 1."""
+    return _run(lib.awq_b200_gemm, "awq_b200_gemm", x, pw, bias,
+                lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out)
+
+
+def linear(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
+    """M <= 16 -> GEMV, else GEMM (dispatch inside the library)."""
+    return _run(lib.awq_b200_linear, "awq_b200_linear", x, pw, bias,
+                lib.awq_b200_linear_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out)
+
+
+def gemm_status(dev: torch.device | None = None) -> int:
+    """Status word the GEMM kernel leaves in this stream's workspace (0 = every
+    device-side wait completed).  Synchronises."""
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    ws = _workspaces.get((dev.index, torch.cuda.current_stream(dev).cuda_stream))
+    if ws is None:
+        return 0
+    return int(ws[:4].view(torch.int32).item())

@@ -1,0 +1,138 @@
+"""`AWQLinear_GEMM`: the reference runtime's AWQ W4A16 linear module
+(LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:216-414) with the
+same constructor, buffer names / shapes / dtypes, `from_linear`, `impl_mode`
+and forward conventions, so reference checkpoints, `load_state_dict`, and the
+q/k/v fusion that concatenates buffers along N work unchanged.  The forward
+runs the sm_100a kernels; the kernel-layout repack of `qweight` happens lazily
+on the first forward after the buffers last changed (or eagerly via `prepare`).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch.autograd import Function
+
+AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
+
+
+def _kernels():
+    # Imported on first use so that host-only helpers (packing, sharding plans)
+    # stay importable for inspection; any compute call still fails loudly
+    # without the CUDA library.
+    from . import kernels, sq_fp8_kernels
+    return kernels, sq_fp8_kernels
+
+
+def pack_awq_int4(values: torch.Tensor) -> torch.Tensor:
+    """int tensor [R, C] with entries 0..15 -> int32 [R, C/8]; slot i of a word holds
+    column 8c + AWQ_ORDER[i] (linear_awq.py:333-346, vectorised)."""
+    R, Cc = values.shape
+    v = values.to(torch.int32).reshape(R, Cc // 8, 8)
+    out = torch.zeros((R, Cc // 8), dtype=torch.int32, device=values.device)
+    for slot, logical in enumerate(AWQ_ORDER):
+        out |= v[:, :, logical] << (4 * slot)
+    return out
+
+
+class AWQLinearMMFunction(Function):
+    """Same positional signature as the reference function (linear_awq.py:128-212)."""
+
+    @staticmethod
+    def forward(ctx, x, qweight, qzeros, scales, w_bit=4, group_size=128, bias=None, out_features=0,
+                impl_mode="auto"):
+        out_shape = x.shape[:-1] + (out_features,)
+        if x.shape[0] == 0 or x.numel() == 0:
+            return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
+        if impl_mode not in {"auto", "dequant_matmul"}:
+            raise ValueError(f"AWQ impl_mode must be 'auto' or 'dequant_matmul', got {impl_mode!r}")
+        kernels, ext = _kernels()
+        if impl_mode == "dequant_matmul":
+            # Explicit reference path: materialise the fp16 weight, then a library matmul.
+            out = torch.matmul(x, kernels.dequantize(qweight, qzeros, scales, group_size))
+        else:
+            pw = ext.packed_for(qweight, qzeros, scales, group_size)
+            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw).reshape(out_shape)
+        out = out + bias if bias is not None else out
+        if out.dim() == 2:          # the reference always hands back a 3-D tensor
+            out = out.unsqueeze(0)
+        return out
+
+
+class AWQLinear_GEMM(nn.Module):
+    def __init__(self, w_bit, group_size, in_features, out_features, bias, dev, training=False):
+        super().__init__()
+        if w_bit not in [4]:
+            raise NotImplementedError("Only 4-bit are supported for now.")
+        self.in_features = in_features
+        self.out_features = out_features
+        self.w_bit = w_bit
+        self.group_size = group_size if group_size != -1 else in_features
+        self.training = training
+        self.impl_mode = "auto"     # or "dequant_matmul"
+        assert self.in_features % self.group_size == 0
+        assert out_features % (32 // self.w_bit) == 0
+        pack = 32 // self.w_bit
+        self.register_buffer("qweight", torch.zeros((in_features, out_features // pack), dtype=torch.int32, device=dev))
+        self.register_buffer("qzeros", torch.zeros((in_features // self.group_size, out_features // pack),
+                                                   dtype=torch.int32, device=dev))
+        self.register_buffer("scales", torch.zeros((in_features // self.group_size, out_features),
+                                                   dtype=torch.float16, device=dev))
+        if bias:
+            self.register_buffer("bias", torch.zeros((out_features,), dtype=torch.float16, device=dev))
+        else:
+            self.bias = None
+
+    @classmethod
+    def from_linear(cls, linear, w_bit, group_size, init_only=False, dtype=torch.bfloat16, scales=None,
+                    zeros=None, per_tensor=False):
+        """Build from an nn.Linear holding the fake-quantised fp16 weight plus its
+        `scales` / `zeros` [K/G, N] (linear_awq.py:274-363).  Same arithmetic as the
+        reference's per-column loop, done on whole tensors."""
+        awq_linear = cls(w_bit, group_size, linear.in_features, linear.out_features,
+                         linear.bias is not None, linear.weight.device)
+        if init_only:
+            return awq_linear
+        assert scales is not None and zeros is not None
+        G = awq_linear.group_size
+        scale_zeros = zeros * scales
+        awq_linear.scales = scales.clone().half()
+        if linear.bias is not None:
+            awq_linear.bias = linear.bias.clone().half()
+        w_t = linear.weight.data.t()                                             # [K, N]
+        intweight = torch.round((w_t + scale_zeros.repeat_interleave(G, dim=0))
+                                / awq_linear.scales.repeat_interleave(G, dim=0)).to(torch.int32)
+        awq_linear.qweight = pack_awq_int4(intweight.contiguous())
+        awq_linear.qzeros = pack_awq_int4(zeros.to(torch.int32))
+        return awq_linear
+
+    def prepare(self):
+        """Repack now instead of on the first forward (call after any buffer surgery)."""
+        _, ext = _kernels()
+        ext.packed_for(self.qweight, self.qzeros, self.scales, self.group_size)
+        return self
+
+    def forward(self, x):
+        assert x.device == self.qweight.device, "when awq linear fwd, input and qweight must be same device!"
+        assert self.qzeros.device == self.qweight.device, "when awq linear fwd, qzeros and qweight must be same device!"
+        assert self.scales.device == self.qweight.device, "when awq linear fwd, scales and qweight must be same device!"
+        out_shape = x.shape[:-1] + (self.out_features,)
+        if x.shape[0] == 0:
+            return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
+        input_dtype = x.dtype
+        if input_dtype != torch.float16:
+            x = x.to(torch.float16)
+        with torch.no_grad():
+            out = AWQLinearMMFunction.apply(x, self.qweight, self.qzeros, self.scales, self.w_bit,
+                                            self.group_size, self.bias, self.out_features, self.impl_mode)
+        if input_dtype != torch.float16:
+            out = out.to(dtype=input_dtype)
+        return out
+
+    def extra_repr(self) -> str:
+        return "in_features={}, out_features={}, bias={}, w_bit={}, group_size={}".format(
+            self.in_features, self.out_features, self.bias is not None, self.w_bit, self.group_size)
+
+
+# Older names kept by the reference (linear_awq.py:412-414).
+WQLinear_GEMM = AWQLinear_GEMM
+WQLinearMMFunction = AWQLinearMMFunction

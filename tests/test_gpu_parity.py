@@ -1,0 +1,248 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the
+reference-generated golden fixtures.  Needs a B200."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import awq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3   # max|y - ref| / max|ref|, the layer-output bound of the parity contract
+
+
+@pytest.fixture(scope="module")
+def K_():
+    from llmrqt_sdv1_b200 import kernels
+    assert torch.cuda.is_available()
+    return kernels
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+_cache = {}
+
+
+def tensors(K, N, G=128, seed=0):
+    key = (K, N, G, seed)
+    if key not in _cache:
+        _cache[key] = orc.make_awq_tensors(K, N, G, seed)
+    return _cache[key]
+
+
+# --------------------------------------------------------------------------- dequant
+def test_dequant_golden_all_pairs(K_, golden_dir):
+    g = np.load(os.path.join(golden_dir, "awq_all_pairs.npz"))
+    G = int(g["group_size"])
+    W = K_.dequantize(dev(g["qweight"]), dev(g["qzeros"]), dev(g["scales"]), G)
+    assert np.array_equal(bits(W), g["W_bits"])            # incl. subnormals, inf, -0
+    pw = K_.make_packed(dev(g["qweight"]), dev(g["qzeros"]), dev(g["scales"]), G)
+    assert np.array_equal(bits(K_.dequantize_packed(pw)), g["W_bits"])
+
+
+def test_dequant_golden_small(K_, golden_dir):
+    g = np.load(os.path.join(golden_dir, "awq_small.npz"))
+    W = K_.dequantize(dev(g["qweight"]), dev(g["qzeros"]), dev(g["scales"]), int(g["group_size"]))
+    assert np.array_equal(bits(W), g["W"].view(np.uint16))
+
+
+@pytest.mark.parametrize("K,N,G", [(128, 8, 128), (256, 72, 128), (512, 128, 256), (2048, 6144, 128),
+                                   (384, 64, 384)])
+def test_dequant_and_repack_vs_oracle(K_, K, N, G):
+    qw, qz, sc = tensors(K, N, G, seed=5)
+    ref = orc.dequantize(qw, qz, sc, G).view(np.uint16)
+    dqw, dqz, dsc = dev(qw), dev(qz), dev(sc)
+    assert np.array_equal(bits(K_.dequantize(dqw, dqz, dsc, G)), ref)
+    pw = K_.make_packed(dqw, dqz, dsc, G)
+    assert pw.packed.numel() * 4 == K * N // 2
+    assert np.array_equal(bits(K_.dequantize_packed(pw)), ref)
+    assert torch.equal(K_.unpack(pw.packed), dqw)          # exact inverse
+
+
+def test_dequant_random_bits(K_):
+    """Arbitrary int32 patterns (sign bit set, all nibble values) and random fp16 scale bits."""
+    rng = np.random.default_rng(11)
+    K, N, G = 256, 256, 128
+    qw = rng.integers(-2**31, 2**31, size=(K, N // 8), dtype=np.int64).astype(np.int32)
+    qz = rng.integers(-2**31, 2**31, size=(K // G, N // 8), dtype=np.int64).astype(np.int32)
+    sb = rng.integers(0, 2**16, size=(K // G, N), dtype=np.int64).astype(np.uint16)
+    sb[(sb & 0x7C00) == 0x7C00] &= 0x83FF        # no inf/nan scales (nan payloads are not pinned)
+    sc = sb.view(np.float16)
+    ref = orc.dequantize(qw, qz, sc, G)
+    got = K_.dequantize(dev(qw), dev(qz), dev(sc), G)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    got_p = K_.dequantize_packed(pw)
+    finite = np.isfinite(ref)
+    assert np.array_equal(bits(got)[finite], ref.view(np.uint16)[finite])
+    assert np.array_equal(bits(got_p), bits(got))
+    assert np.array_equal(np.isinf(got.cpu().numpy()), np.isinf(ref))
+
+
+# --------------------------------------------------------------------------- GEMV
+GEMV_SHAPES = [(128, 8), (256, 72), (2048, 2048), (2048, 6144), (6144, 2048), (1024, 1000 * 8)]
+
+
+@pytest.mark.parametrize("K,N", GEMV_SHAPES)
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+def test_gemv_vs_oracle(K_, K, N, M):
+    qw, qz, sc = tensors(K, N, 128, seed=1)
+    x = orc.make_activations(M, K, seed=M)
+    ref = orc.linear_forward(x, qw, qz, sc, 128)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    y = K_.gemv(dev(x), pw)
+    assert y.shape == (M, N) and y.dtype == torch.float16
+    assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+
+
+def test_gemv_config1_golden(K_, golden_dir):
+    """Config 1 (M=1, K=2048, N=6144, seed 0) against the reference's own forward output."""
+    g = np.load(os.path.join(golden_dir, "awq_config1_slice.npz"))
+    K, N, G = int(g["K"]), int(g["N"]), int(g["group_size"])
+    qw, qz, sc = orc.make_awq_tensors(K, N, G, seed=0)
+    x = orc.make_activations(1, K, seed=0)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    y = K_.linear(dev(x), pw).cpu().numpy()
+    assert orc.max_normalised_error(y, g["y"][0]) <= TOL
+    W = K_.dequantize_packed(pw)
+    assert np.array_equal(bits(W[:, :64]), g["W_cols_0_64"].view(np.uint16))
+
+
+@pytest.mark.parametrize("ntw", [1, 2, 4])
+@pytest.mark.parametrize("bps", [1, 3, 16])
+def test_gemv_every_decomposition(K_, ntw, bps):
+    K, N, M = 2048, 1096, 5                       # N/8 = 137 tiles: ragged for every ntw
+    qw, qz, sc = tensors(K, N, 128, seed=2)
+    x = orc.make_activations(M, K, seed=3)
+    ref = orc.linear_forward(x, qw, qz, sc, 128)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    y = K_.gemv_plan(dev(x), pw, ntw, bps)
+    assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+    y2 = K_.gemv_plan(dev(x), pw, ntw, bps)      # counters were left clean: second call identical
+    assert torch.equal(y, y2)
+
+
+def test_gemv_row_result_independent_of_batch(K_):
+    """A row's bits must not depend on M (decode q_len=1 and verify q_len=2 must agree,
+    LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:161-166) nor on the run."""
+    K, N = 2048, 4096
+    qw, qz, sc = tensors(K, N, 128, seed=4)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    x16 = dev(orc.make_activations(16, K, seed=9))
+    y16 = K_.gemv(x16, pw)
+    for M in (1, 2, 7, 8, 9, 15):
+        yM = K_.gemv(x16[:M].contiguous(), pw)
+        assert torch.equal(yM, y16[:M]), f"rows differ between M={M} and M=16"
+    for r in (3, 12):
+        assert torch.equal(K_.gemv(x16[r:r + 1].contiguous(), pw)[0], y16[r])
+    for _ in range(50):
+        assert torch.equal(K_.gemv(x16, pw), y16)
+
+
+def test_gemv_bias_group256_and_linearity(K_):
+    K, N, G = 1024, 512, 256
+    qw, qz, sc = tensors(K, N, G, seed=6)
+    rng = np.random.default_rng(0)
+    bias = rng.standard_normal(N).astype(np.float16)
+    x = orc.make_activations(4, K, seed=1)
+    ref = orc.linear_forward(x, qw, qz, sc, G, bias)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    y = K_.gemv(dev(x), pw, bias=dev(bias))
+    assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+    # y(2x) == 2 y(x) exactly in binary floating point (no bias)
+    y1 = K_.gemv(dev(x), pw)
+    y2 = K_.gemv(dev((x * np.float16(2)).astype(np.float16)), pw)
+    assert torch.equal(y2, y1 * 2)
+
+
+def test_gemv_rejects_bad_arguments(K_):
+    qw, qz, sc = tensors(256, 72, 128, seed=5)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    with pytest.raises(ValueError):
+        K_.gemv(torch.zeros(17, 256, dtype=torch.float16, device="cuda"), pw)
+    with pytest.raises(ValueError):
+        K_.gemv(torch.zeros(1, 128, dtype=torch.float16, device="cuda"), pw)
+    with pytest.raises(ValueError):
+        K_.make_packed(dev(qw), dev(qz), dev(sc), 64)
+
+
+# --------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,K,N", [(17, 128, 128), (64, 256, 256), (128, 512, 384), (200, 1024, 72),
+                                   (256, 4096, 256), (300, 2048, 1000 * 8), (512, 4096, 4096),
+                                   (1000, 1024, 640)])
+def test_gemm_vs_oracle(K_, M, K, N):
+    qw, qz, sc = tensors(K, N, 128, seed=7)
+    x = orc.make_activations(M, K, seed=M)
+    ref = orc.linear_forward(x, qw, qz, sc, 128)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    y = K_.gemm(dev(x), pw)
+    torch.cuda.synchronize()
+    assert K_.gemm_status() == 0
+    assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+
+
+def test_gemm_bias_group_and_small_m(K_):
+    K, N, G = 1024, 512, 512
+    qw, qz, sc = tensors(K, N, G, seed=8)
+    rng = np.random.default_rng(1)
+    bias = rng.standard_normal(N).astype(np.float16)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    for M in (1, 16, 33, 129):
+        x = orc.make_activations(M, K, seed=M)
+        ref = orc.linear_forward(x, qw, qz, sc, G, bias)
+        y = K_.gemm(dev(x), pw, bias=dev(bias))
+        assert K_.gemm_status() == 0
+        assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+
+
+def test_gemm_matches_gemv_rows(K_):
+    """The two kernels multiply the same fp16 weights with fp32 accumulation."""
+    K, N = 2048, 2048
+    qw, qz, sc = tensors(K, N, 128, seed=1)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    x = dev(orc.make_activations(16, K, seed=2))
+    a, b = K_.gemv(x, pw).float(), K_.gemm(x, pw).float()
+    assert (a - b).abs().max() / b.abs().max() <= 1e-3
+
+
+# --------------------------------------------------------------------------- full-size properties
+def _random_packed_inputs(K, N, G, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    qw = torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
+    qz = torch.randint(-2**31, 2**31 - 1, (K // G, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
+    sc = (torch.rand((K // G, N), device="cuda", generator=g) * 0.004 + 0.001).half()
+    return qw, qz, sc
+
+
+@pytest.mark.parametrize("K,N,M", [(8192, 57344, 1), (28672, 8192, 16), (2048, 12288, 4)])
+def test_gemv_full_size_vs_device_dequant_matmul(K_, K, N, M):
+    """BASELINE-size decode linears: the kernel against dequant (proved bit-exact above)
+    followed by a library fp16 matmul on the same device, plus the unpack round trip."""
+    qw, qz, sc = _random_packed_inputs(K, N, 128, seed=K + N)
+    pw = K_.make_packed(qw, qz, sc, 128)
+    assert torch.equal(K_.unpack(pw.packed), qw)
+    x = torch.randn((M, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)).half()
+    W = K_.dequantize(qw, qz, sc, 128)
+    ref = torch.matmul(x.float(), W.float())
+    y = K_.gemv(x, pw).float()
+    assert (y - ref).abs().max() / ref.abs().max() <= TOL
+    assert torch.equal(K_.dequantize_packed(pw), W)
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 28672, 2048), (14336, 4096, 2048), (4096, 6144, 8192)])
+def test_gemm_full_size_vs_device_dequant_matmul(K_, K, N, M):
+    qw, qz, sc = _random_packed_inputs(K, N, 128, seed=K + N + M)
+    pw = K_.make_packed(qw, qz, sc, 128)
+    x = torch.randn((M, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(2)).half()
+    W = K_.dequantize(qw, qz, sc, 128)
+    ref = torch.matmul(x, W).float()
+    y = K_.gemm(x, pw)
+    assert K_.gemm_status() == 0
+    assert (y.float() - ref).abs().max() / ref.abs().max() <= TOL

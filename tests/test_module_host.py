@@ -1,0 +1,49 @@
+"""Host-side logic of the module mirror (packing, construction, conventions).  CPU only."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from llmrqt_sdv1_b200 import AWQLinear_GEMM, WQLinear_GEMM, pack_awq_int4
+
+
+def test_constructor_buffers():
+    m = AWQLinear_GEMM(4, 128, 256, 64, True, "cpu")
+    assert m.qweight.shape == (256, 8) and m.qweight.dtype == torch.int32
+    assert m.qzeros.shape == (2, 8) and m.scales.shape == (2, 64) and m.scales.dtype == torch.float16
+    assert m.bias.shape == (64,) and m.impl_mode == "auto"
+    assert set(m.state_dict()) == {"qweight", "qzeros", "scales", "bias"}
+    assert AWQLinear_GEMM(4, -1, 256, 64, False, "cpu").group_size == 256
+    assert WQLinear_GEMM is AWQLinear_GEMM
+    with pytest.raises(NotImplementedError):
+        AWQLinear_GEMM(8, 128, 256, 64, False, "cpu")
+
+
+def test_from_linear_matches_reference_packing(golden_dir):
+    g = np.load(os.path.join(golden_dir, "awq_small.npz"))
+    G = int(g["group_size"])
+    N, K = g["w_fake"].shape
+    lin = torch.nn.Linear(K, N, bias=False).half()
+    lin.weight.data = torch.from_numpy(g["w_fake"])
+    q = AWQLinear_GEMM.from_linear(lin, 4, G, scales=torch.from_numpy(g["scales_kn"]),
+                                   zeros=torch.from_numpy(g["zeros_kn"]))
+    assert np.array_equal(q.qweight.numpy(), g["qweight"])
+    assert np.array_equal(q.qzeros.numpy(), g["qzeros"])
+    assert np.array_equal(q.scales.numpy().view(np.uint16), g["scales"].view(np.uint16))
+
+
+def test_pack_order():
+    v = torch.arange(8).reshape(1, 8)
+    w = int(pack_awq_int4(v)[0, 0]) & 0xFFFFFFFF
+    assert [(w >> (4 * i)) & 0xF for i in range(8)] == [0, 2, 4, 6, 1, 3, 5, 7]
+
+
+def test_empty_batch_and_no_cpu_fallback():
+    m = AWQLinear_GEMM(4, 128, 128, 64, False, "cpu")
+    assert m(torch.zeros(0, 128, dtype=torch.float16)).shape == (0, 64)
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(2, 128, dtype=torch.float16))     # CPU tensors: the kernels refuse, nothing falls back
+    m.impl_mode = "bogus"
+    with pytest.raises(ValueError):
+        m(torch.zeros(2, 128, dtype=torch.float16))
