@@ -1,0 +1,529 @@
+#!/usr/bin/env python
+"""Benchmark of the AWQ W4A16 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  Workloads:
+
+  qwen3_decode  (default at N=1)  the Qwen3-1.7B-shaped decode linears, M=1: one step =
+                28 layers x {qkv 2048->4096, o 2048->2048, gate_up 2048->12288,
+                down 6144->2048}, every layer with its own weights (734 MB per step,
+                larger than the 126 MB L2, so no flush is needed between steps).
+  ffn70b_tp     (default at N>1)  the 70B-class FFN linears, M=1, tensor-parallel over
+                the N ranks: gate_up 8192->57344 column-sharded, down 28672->8192
+                row-sharded + one NCCL all-reduce; one step = 8 layers.
+
+`value` times the kernels alone (inputs resident in HBM, one CUDA graph per step);
+`e2e` times the module API (`AWQLinear_GEMM.forward`) with the activations starting in
+pinned host memory and the result read back to the host every step.  `--impl reference`
+times the CPU dequant+matmul path (the oracle's C restatement, all host threads) on
+a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GROUP = 128
+QWEN3_LAYERS = 28
+QWEN3_LINEARS = [("qkv", 2048, 4096), ("o", 2048, 2048), ("gate_up", 2048, 12288), ("down", 6144, 2048)]
+FFN70B_LAYERS = 8
+FFN70B = {"gate_up": (8192, 57344), "down": (28672, 8192)}
+PREFILL_SHAPES = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu
+# capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"gemv_2048x12288_m1": None}
+
+
+def gemv_bytes(M, K, N, G=GROUP):
+    """Algorithmic bytes of one decode linear: packed weights + scales + zeros + x + y."""
+    return K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2 + 2 * M * K + 2 * M * N
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]),
+                "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index):
+        self.ok = False
+        self.sm, self.bits = [], 0
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_sm = None
+
+    def sample(self):
+        if not self.ok:
+            return
+        try:
+            self.sm.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            fn = getattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                self.nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.bits |= int(fn(self.h))
+        except Exception:
+            pass
+
+    def wait_and_sample(self, end_event):
+        self.sample()
+        while not end_event.query():
+            self.sample()
+            time.sleep(0.001)
+
+    def summary(self):
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_sm, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.max_sm,
+                "reasons": [n for b, n in self.REASONS.items() if self.bits & b], "samples": len(self.sm)}
+
+
+# ----------------------------------------------------------------------------- reference / CPU arm
+def cpu_layer_tensors(shapes, seed=0):
+    from oracle import awq_oracle as orc
+    out = []
+    for i, (_, K, N) in enumerate(shapes):
+        qw, qz, sc = orc.make_awq_tensors(K, N, GROUP, seed=seed + i)
+        out.append((K, N, qw, qz, sc, orc.make_activations(1, K, seed=seed + i)))
+    return out
+
+
+def cpu_time_decode_layers(layer, repeats):
+    """Seconds per pass of the reference CPU path (dequant + matmul, C restatement) over `layer`."""
+    from oracle import c_oracle
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for (K, N, qw, qz, sc, x) in layer:
+            c_oracle.linear_forward(x, qw, qz, sc, GROUP)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args, rank):
+    """`--impl reference`: the CPU dequant+matmul path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    from oracle import c_oracle
+    if args.workload == "ffn70b_tp":
+        shapes = [("gate_up", *FFN70B["gate_up"]), ("down", *FFN70B["down"])]
+        layers, sample = FFN70B_LAYERS, "one 70B FFN layer (gate_up 8192x57344, down 28672x8192) at M=1 per step"
+    else:
+        shapes, layers = QWEN3_LINEARS, QWEN3_LAYERS
+        sample = "one Qwen3-1.7B layer's four decode linears at M=1 per step (1/28 of the GPU arm's step)"
+    layer = cpu_layer_tensors(shapes)
+    nbytes = sum(gemv_bytes(1, K, N) for (K, N, *_r) in layer)
+    cpu_time_decode_layers(layer, max(args.warmup, 1))
+    times = cpu_time_decode_layers(layer, args.steps)
+    sec = sum(times) / len(times)
+    gbs = nbytes / sec / 1e9
+    line = {
+        "impl": "reference", "metric": "W4A16 GEMV HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "ffn70b_tp" else "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": {"workload": args.workload, "M": 1, "group_size": GROUP,
+                                        "layers_per_step": 1, "layers_in_gpu_step": layers},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": c_oracle.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm helpers
+def time_graph(torch, fn, iters, warmup=3, reps=3):
+    """Median ms per call of `fn` (a sequence of launches on the current stream), graph-replayed."""
+    for _ in range(warmup):
+        fn()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / iters)
+    return statistics.median(out)
+
+
+def decode_detail(torch, kernels, quantize, peaks):
+    """Per-shape decode table: GB/s at M in {1,4,8,16}, weights rotated over > 2x L2."""
+    rows = []
+    shapes = [(n, K, N) for (n, K, N) in QWEN3_LINEARS] + [("gate", 2048, 6144)] + \
+             [("70b_gate_up", *FFN70B["gate_up"]), ("70b_down", *FFN70B["down"])]
+    for name, K, N in shapes:
+        per = K * N // 2
+        copies = max(2, min(64, (300 << 20) // per + 1))
+        qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=K + N, device="cuda")
+        base = kernels.make_packed(qw, qz, sc, GROUP)
+        pws = [base] + [kernels.PackedWeight(base.packed.clone(), qz.clone(), sc.clone(), K, N, GROUP)
+                        for _ in range(copies - 1)]
+        for M in (1, 4, 8, 16):
+            x = torch.randn((M, K), device="cuda").half()
+            ys = [torch.empty((M, N), dtype=torch.float16, device="cuda") for _ in range(copies)]
+
+            def fn():
+                for pw, y in zip(pws, ys):
+                    kernels.gemv(x, pw, out=y)
+            ms = time_graph(torch, fn, iters=5) / copies
+            gbs = gemv_bytes(M, K, N) / (ms * 1e-3) / 1e9
+            rows.append({"linear": name, "K": K, "N": N, "M": M, "us": round(ms * 1e3, 3), "gbs": round(gbs, 1),
+                         "frac_measured": round(gbs / peaks["hbm_gbs"], 4), "frac_nominal_8tbs": round(gbs / 8000.0, 4)})
+        del pws, base
+    return rows
+
+
+def prefill_detail(torch, kernels, quantize, peaks):
+    rows = []
+    for K, N in PREFILL_SHAPES:
+        qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=K + N, device="cuda")
+        pw = kernels.make_packed(qw, qz, sc, GROUP)
+        for M in (512, 2048, 8192):
+            x = torch.randn((M, K), device="cuda").half()
+            y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            ms = time_graph(torch, lambda: kernels.gemm(x, pw, out=y), iters=10)
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            rows.append({"K": K, "N": N, "M": M, "us": round(ms * 1e3, 2), "tflops": round(tf, 1),
+                         "frac_measured": round(tf / peaks["tflops"], 4), "frac_nominal_2250": round(tf / 2250.0, 4)})
+        assert kernels.gemm_status() == 0, "a device-side wait expired in the GEMM"
+    return rows
+
+
+def run_qwen3_decode(args, torch, peaks):
+    from llmrqt_sdv1_b200 import AWQLinear_GEMM, kernels, quantize
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M = 1
+    modules, pws, xs, ys = [], [], {}, []
+    for K in (2048, 6144):
+        xs[K] = torch.randn((M, K), device=dev).half()
+    for layer in range(QWEN3_LAYERS):
+        for i, (name, K, N) in enumerate(QWEN3_LINEARS):
+            qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=layer * 16 + i, device=dev)
+            m = AWQLinear_GEMM(4, GROUP, K, N, False, dev)
+            m.qweight, m.qzeros, m.scales = qw, qz, sc
+            m.prepare()
+            modules.append(m)
+            from llmrqt_sdv1_b200.sq_fp8_kernels import packed_for
+            pws.append(packed_for(m.qweight, m.qzeros, m.scales, GROUP))
+            ys.append(torch.empty((M, N), dtype=torch.float16, device=dev))
+    step_bytes = sum(gemv_bytes(M, pw.K, pw.N) for pw in pws)
+    launches_per_step = len(pws)
+
+    def step():
+        for pw, y in zip(pws, ys):
+            kernels.gemv(xs[pw.K], pw, out=y)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        graph.replay()
+    b.record()
+    sampler.wait_and_sample(b)
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    value = step_bytes / (ms * 1e-3) / 1e9
+
+    # ---- end to end through the module API, host buffers ---------------------------------
+    hx = {K: torch.randn((1, M, K)).half().pin_memory() for K in (2048, 6144)}
+    dx = {K: torch.empty((1, M, K), dtype=torch.float16, device=dev) for K in (2048, 6144)}
+    hy = torch.empty((1, M, QWEN3_LINEARS[-1][2]), dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        for K in dx:
+            dx[K].copy_(hx[K], non_blocking=True)
+        y = None
+        for m in modules:
+            y = m(dx[m.in_features])
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        e2e_step()
+    a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a2.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b2.record()
+    torch.cuda.synchronize()
+    e2e_ms = a2.elapsed_time(b2) / args.steps
+    e2e = {"value": step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": sum(t.numel() * 2 for t in hx.values()), "d2h_bytes_per_step": hy.numel() * 2,
+           "api": "AWQLinear_GEMM.forward x 112 per step"}
+
+    # ---- parity of what was just timed, against dequant + library matmul on the device ----
+    pw0, m0 = pws[2], modules[2]
+    W = kernels.dequantize(m0.qweight, m0.qzeros, m0.scales, GROUP)
+    ref = torch.matmul(xs[pw0.K].float(), W.float())
+    err = float((ys[2].float() - ref).abs().max() / ref.abs().max())
+    parity = {"dequant_bit_exact": bool(torch.equal(kernels.dequantize_packed(pw0), W)), "max_norm_err": err,
+              "tolerance": 2e-3}
+
+    line = {
+        "metric": "W4A16 GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "qwen3_decode: Qwen3-1.7B decode linears (qkv, o, gate_up, down) x 28 layers, M=1, "
+                               "W4A16 g128", "M": M, "group_size": GROUP, "launches_per_step": launches_per_step,
+                   "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (734 MB of weights per step, no flush)",
+                   "timing": "one CUDA graph per step, CUDA events on the launching stream"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["gemv_2048x12288_m1"],
+                     "peak_source": peaks["source"], "kernel": "awq::gemv_kernel",
+                     "avg_launch_us": ms * 1e3 / launches_per_step, "frac_of_nominal_8tbs": value / 8000.0},
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": sampler.summary(), "parity": parity,
+    }
+    if not args.no_detail:
+        line["decode_detail"] = decode_detail(torch, kernels, quantize, peaks)
+        line["prefill_detail"] = prefill_detail(torch, kernels, quantize, peaks)
+        best = max(line["prefill_detail"], key=lambda r: r["tflops"])
+        line["roofline_gemm"] = {"bound": "tensor", "achieved": best["tflops"], "peak": peaks["tflops"],
+                                 "unit": "TFLOP/s", "frac": best["tflops"] / peaks["tflops"], "traffic": None,
+                                 "peak_source": peaks["source"], "kernel": "awq::gemm_kernel",
+                                 "shape": {k: best[k] for k in ("M", "K", "N")}}
+    if not args.no_cpu:
+        from oracle import c_oracle
+        layer = cpu_layer_tensors(QWEN3_LINEARS)
+        cpu_time_decode_layers(layer, 2)
+        t = cpu_time_decode_layers(layer, 28 * 3)
+        sec = sum(t) / len(t)
+        nbytes = sum(gemv_bytes(1, K, N) for (K, N, *_r) in layer)
+        line["cpu_baseline"] = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": c_oracle.threads(), "kind": "port",
+                                "sample": "one layer's four decode linears (26.2 MB) x 84 passes, C restatement of "
+                                          "dequant+matmul with OpenMP", "ms_per_layer": sec * 1e3}
+    print(json.dumps(line), flush=True)
+
+
+def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
+    import torch.distributed as dist
+    from llmrqt_sdv1_b200 import kernels, quantize
+    from llmrqt_sdv1_b200.sharded import ColumnParallelAWQLinear, RowParallelAWQLinear
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    M = 1
+    Kg, Ng = FFN70B["gate_up"]
+    Kd, Nd = FFN70B["down"]
+    ng_local, kd_local = Ng // world, Kd // world
+    gate_up, down, y_g, y_d = [], [], [], []
+    for layer in range(FFN70B_LAYERS):
+        # A rank's shard of a seeded full matrix is itself a seeded matrix (RTN groups never straddle a
+        # shard boundary), so the shards are generated directly.
+        qw, qz, sc = quantize.random_awq_tensors(Kg, ng_local, GROUP, seed=1000 * layer + rank, device=dev)
+        gate_up.append(ColumnParallelAWQLinear.from_local(qw, qz, sc, None, GROUP))
+        qw, qz, sc = quantize.random_awq_tensors(kd_local, Nd, GROUP, seed=1000 * layer + 500 + rank, device=dev)
+        down.append(RowParallelAWQLinear.from_local(qw, qz, sc, None, GROUP))
+        y_g.append(torch.empty((M, ng_local), dtype=torch.float16, device=dev))
+        y_d.append(torch.empty((M, Nd), dtype=torch.float16, device=dev))
+    x_g = torch.randn((M, Kg), device=dev).half()
+    x_d = torch.randn((M, kd_local), device=dev).half()
+    pw_g = [m.packed() for m in gate_up]
+    pw_d = [m.packed() for m in down]
+    step_bytes_total = FFN70B_LAYERS * (gemv_bytes(M, Kg, Ng) + gemv_bytes(M, Kd, Nd))
+
+    def step():
+        for i in range(FFN70B_LAYERS):
+            kernels.gemv(x_g, pw_g[i], out=y_g[i])
+            kernels.gemv(x_d, pw_d[i], out=y_d[i])
+            if world > 1:
+                dist.all_reduce(y_d[i])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    graphed = True
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+    except Exception:
+        graphed, run = False, step
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        run()
+    b.record()
+    sampler.wait_and_sample(b)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    # end to end: module API, activations from pinned host memory, result read back
+    hxg, hxd = torch.randn((1, M, Kg)).half().pin_memory(), torch.randn((1, M, kd_local)).half().pin_memory()
+    dxg, dxd = torch.empty_like(hxg, device=dev), torch.empty_like(hxd, device=dev)
+    hy = torch.empty((1, M, Nd), dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        dxg.copy_(hxg, non_blocking=True)
+        dxd.copy_(hxd, non_blocking=True)
+        y = None
+        for i in range(FFN70B_LAYERS):
+            gate_up[i](dxg)
+            y = down[i](dxd)
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a2.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b2.record()
+    torch.cuda.synchronize()
+    t2 = torch.tensor([a2.elapsed_time(b2) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item())
+    if rank != 0:
+        return
+    value = step_bytes_total / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+    line = {
+        "metric": "W4A16 GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "ffn70b_tp: 70B-class FFN linears, gate_up 8192->57344 column-sharded, down "
+                               "28672->8192 row-sharded + NCCL all-reduce, M=1, W4A16 g128, 8 layers per step",
+                   "M": M, "tp": world, "group_size": GROUP, "bytes_per_step_all_ranks": step_bytes_total,
+                   "l2": "inputs larger than L2 (8 distinct layers per step)", "cuda_graph": graphed},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "awq::gemv_kernel (+ncclAllReduce in the step)", "per_gpu": True},
+        "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
+                "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
+        "gpu_launches": 2 * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_profile_case(args, torch):
+    """Small, self-terminating cases for `ncu` captures (a few launches, a few hundred MB)."""
+    from llmrqt_sdv1_b200 import kernels, quantize
+    torch.cuda.set_device(0)
+    if args.profile_case.startswith("gemv"):
+        # gemv / gemv16: 24 distinct 2048x12288 weights (13 MB each, 314 MB > L2), two passes
+        # gemv70b: one 8192x57344 weight (235 MB > L2), three launches
+        M = 16 if args.profile_case == "gemv16" else 1
+        K, N, copies, passes = (8192, 57344, 1, 3) if args.profile_case == "gemv70b" else (2048, 12288, 24, 2)
+        qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
+        base = kernels.make_packed(qw, qz, sc, GROUP)
+        pws = [base] + [kernels.PackedWeight(base.packed.clone(), qz, sc, K, N, GROUP) for _ in range(copies - 1)]
+        x = torch.randn((M, K), device="cuda").half()
+        y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        for _ in range(passes):
+            for pw in pws:
+                kernels.gemv(x, pw, out=y)
+    else:
+        M, K, N = (8192, 4096, 28672) if args.profile_case == "gemm_large" else (2048, 4096, 6144)
+        qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
+        pw = kernels.make_packed(qw, qz, sc, GROUP)
+        x = torch.randn((M, K), device="cuda").half()
+        y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        for _ in range(4):
+            kernels.gemm(x, pw, out=y)
+        torch.cuda.synchronize()
+        assert kernels.gemm_status() == 0
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": args.profile_case, "ok": True}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp"])
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "gemm", "gemm_large"],
+                    help="run a small fixed case of one kernel (for ncu) and exit")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload is None:
+        args.workload = "qwen3_decode" if max(world, args.gpus) == 1 else "ffn70b_tp"
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    if args.profile_case:
+        run_profile_case(args, torch)
+        return
+    peaks = load_peaks()
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        if args.workload == "qwen3_decode":
+            if rank == 0:
+                run_qwen3_decode(args, torch, peaks)
+        else:
+            run_ffn70b_tp(args, torch, peaks, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -102,8 +102,11 @@ AWQ_B200_API int awq_b200_dequant_packed(const void* packed, const int32_t* qzer
 /* ---- decode: split-K GEMV, M <= 16 -------------------------------------- */
 
 /* Bytes of scratch awq_b200_gemv needs for (M, K, N).  The first
- * awq_b200_gemv_counter_bytes(N) bytes hold arrival counters that must be zero
- * before the first call and are left zero by every completed call. */
+ * awq_b200_gemv_counter_bytes(N) bytes (a constant, 16 KiB) hold arrival
+ * counters that must be zero before the first call and are left zero by every
+ * completed call; the rest holds fp32 partial sums and needs no initialisation.
+ * One workspace may serve linears of any shape, but awq_b200_gemv and
+ * awq_b200_linear lay it out differently: do not hand the same buffer to both. */
 AWQ_B200_API size_t awq_b200_gemv_workspace_bytes(int M, int K, int N);
 AWQ_B200_API size_t awq_b200_gemv_counter_bytes(int N);
 

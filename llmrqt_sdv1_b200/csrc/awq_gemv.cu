@@ -262,10 +262,12 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
   return best;
 }
 
-static size_t counter_bytes(int N) {
-  const size_t ncol_max = (static_cast<size_t>(N) / 8 + kGemvWarps - 1) / kGemvWarps;  // ntw = 1
-  return (ncol_max * sizeof(unsigned) + 255) / 256 * 256;
-}
+// The arrival counters sit in a fixed-size slot at the start of the workspace,
+// independent of the problem shape, so that one workspace can serve linears of
+// different sizes: partial sums of one call can then never land where another
+// call expects clean counters.
+constexpr int kGemvMaxCounters = 4096;
+static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
 template <int NTW, int MT>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream) {
@@ -300,7 +302,11 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   const int nblk = K / kBlockK, ntiles = N / 8;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
   plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
-  if (plan.S > 65535) return AWQ_B200_ERR_TOO_LARGE;
+  while (plan.ncol > kGemvMaxCounters && plan.ntw < 4) {
+    plan.ntw *= 2;
+    plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
+  }
+  if (plan.S > 65535 || plan.ncol > kGemvMaxCounters) return AWQ_B200_ERR_TOO_LARGE;
 
   GemvParams p;
   p.x = static_cast<const uint16_t*>(x);

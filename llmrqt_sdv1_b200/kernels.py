@@ -94,13 +94,14 @@ def dequantize_packed(pw: PackedWeight) -> torch.Tensor:
     return W
 
 
-# One zero-initialised workspace per (device, stream): calls that share a
-# workspace must not overlap on the GPU, and calls on one stream never do.
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# One zero-initialised workspace per (device, stream, entry point): calls that
+# share a workspace must not overlap on the GPU (calls on one stream never do),
+# and the entry points lay their workspace out differently.
+_workspaces: dict[tuple[int, int, str], torch.Tensor] = {}
 
 
-def _workspace(dev: torch.device, stream: int, nbytes: int) -> torch.Tensor:
-    key = (dev.index, stream)
+def _workspace(dev: torch.device, stream: int, nbytes: int, kind: str) -> torch.Tensor:
+    key = (dev.index, stream, kind)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
@@ -120,7 +121,7 @@ def _run(fn, name, x, pw, bias, ws_bytes, out=None, extra=()):
     M = x.shape[0]
     y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
     stream = _stream(x)
-    ws = _workspace(dev, stream, ws_bytes)
+    ws = _workspace(dev, stream, ws_bytes, name)
     check(fn(x.data_ptr(), pw.packed.data_ptr(), pw.scales.data_ptr(), pw.qzeros.data_ptr(),
              bias.data_ptr() if bias is not None else None, y.data_ptr(), M, pw.K, pw.N, pw.group_size,
              ws.data_ptr(), ws.numel(), stream, *extra), name)
@@ -155,7 +156,10 @@ def gemm_status(dev: torch.device | None = None) -> int:
     """Status word the GEMM kernel leaves in this stream's workspace (0 = every
     device-side wait completed).  Synchronises."""
     dev = dev or torch.device("cuda", torch.cuda.current_device())
-    ws = _workspaces.get((dev.index, torch.cuda.current_stream(dev).cuda_stream))
-    if ws is None:
-        return 0
-    return int(ws[:4].view(torch.int32).item())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = 0
+    for kind in ("awq_b200_gemm", "awq_b200_linear"):
+        ws = _workspaces.get((dev.index, stream, kind))
+        if ws is not None:
+            status |= int(ws[:4].view(torch.int32).item())
+    return status

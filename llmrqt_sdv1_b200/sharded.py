@@ -1,0 +1,169 @@
+"""Tensor-parallel AWQ linears for weights too large for one GPU.
+
+The reference runtime is single-GPU (LLMQRT/runtime_refact/core/base.py:44 pins
+CUDA_VISIBLE_DEVICES=0); the only tensor-parallel precedent in its repository
+is the fp16 Column/Merged/Row-parallel linears of
+spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:68-199, whose slicing
+rules these classes follow for the AWQ tensors:
+
+* column-sharded (gate/up/qkv): rank r keeps output columns
+  [r*N/tp, (r+1)*N/tp) of qweight / qzeros / scales (for a fused tensor, that
+  slice of EACH fused part); activations are replicated; no collective.
+* row-sharded (down/o): rank r keeps input rows [r*K/tp, (r+1)*K/tp) of
+  qweight and the matching group rows of qzeros / scales; the input is the
+  matching K-slice; outputs are summed with ONE all-reduce; bias is added on
+  rank 0 only, before the reduction.
+
+One process per GPU; `torch.distributed` (NCCL over NVLink on GPUs, gloo on CPU
+for the host-logic tests) provides the collective.  The all-reduce runs on the
+fp16 outputs; each rank's fp16 partial was rounded once from an fp32
+accumulator, so tp roundings plus tp-1 fp16 additions enter the result (within
+the 2e-3 layer-output bound for tp <= 8 at the tested shapes).
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .linear_awq import AWQLinear_GEMM
+
+PACK = 8
+
+
+def column_shard(qweight, qzeros, scales, bias, rank: int, world: int, parts: Sequence[int] | None = None):
+    """Slice the on-disk tensors along N.  `parts` lists the widths of fused
+    sub-matrices (e.g. [gate, up] or [q, k, v]); each is sliced separately and
+    the slices are concatenated, so every rank holds matching pieces of all."""
+    N = scales.shape[1]
+    parts = list(parts) if parts else [N]
+    if sum(parts) != N:
+        raise ValueError(f"parts {parts} do not add up to out_features {N}")
+    qw, qz, sc, bs = [], [], [], []
+    start = 0
+    for width in parts:
+        if width % (world * PACK) != 0:
+            raise ValueError(f"fused part of width {width} cannot be split {world} ways on an 8-column boundary")
+        w = width // world
+        lo = start + rank * w
+        qw.append(qweight[:, lo // PACK:(lo + w) // PACK])
+        qz.append(qzeros[:, lo // PACK:(lo + w) // PACK])
+        sc.append(scales[:, lo:lo + w])
+        if bias is not None:
+            bs.append(bias[lo:lo + w])
+        start += width
+    cat = lambda xs, d: torch.cat(xs, dim=d).contiguous()
+    return cat(qw, 1), cat(qz, 1), cat(sc, 1), (cat(bs, 0) if bias is not None else None)
+
+
+def row_shard(qweight, qzeros, scales, group_size: int, rank: int, world: int):
+    """Slice the on-disk tensors along K on a group (and 128-row) boundary."""
+    K = qweight.shape[0]
+    if K % world != 0 or (K // world) % group_size != 0 or (K // world) % 128 != 0:
+        raise ValueError(f"in_features {K} cannot be split {world} ways on a group / 128-row boundary")
+    k = K // world
+    g = k // group_size
+    return (qweight[rank * k:(rank + 1) * k].contiguous(), qzeros[rank * g:(rank + 1) * g].contiguous(),
+            scales[rank * g:(rank + 1) * g].contiguous())
+
+
+def _world(group):
+    if not dist.is_available() or not dist.is_initialized():
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+def _local_linear(qw, qz, sc, bias, group_size, device) -> AWQLinear_GEMM:
+    K, n = qw.shape[0], sc.shape[1]
+    lin = AWQLinear_GEMM(4, group_size, K, n, bias is not None, device)
+    lin.qweight.copy_(qw)
+    lin.qzeros.copy_(qz)
+    lin.scales.copy_(sc)
+    if bias is not None:
+        lin.bias.copy_(bias)
+    return lin
+
+
+def _packed(lin: AWQLinear_GEMM):
+    from .sq_fp8_kernels import packed_for
+    return packed_for(lin.qweight, lin.qzeros, lin.scales, lin.group_size)
+
+
+class ColumnParallelAWQLinear(nn.Module):
+    """y_local = x . W[:, shard]; optionally all-gathers the shards along N."""
+
+    def __init__(self, qweight, qzeros, scales, bias, group_size: int, parts: Sequence[int] | None = None,
+                 gather_output: bool = False, group=None, device=None):
+        super().__init__()
+        self.group = group
+        self.rank, self.world = _world(group)
+        self.gather_output = gather_output
+        qw, qz, sc, b = column_shard(qweight, qzeros, scales, bias, self.rank, self.world, parts)
+        self.linear = _local_linear(qw, qz, sc, b, group_size, device if device is not None else qweight.device)
+        self.out_features = scales.shape[1]
+
+    @classmethod
+    def from_local(cls, qweight, qzeros, scales, bias, group_size: int, gather_output: bool = False, group=None):
+        """Wrap tensors that already are this rank's column shard."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        self.group, self.gather_output = group, gather_output
+        self.rank, self.world = _world(group)
+        self.linear = _local_linear(qweight, qzeros, scales, bias, group_size, qweight.device)
+        self.out_features = scales.shape[1] * self.world
+        return self
+
+    def packed(self):
+        return _packed(self.linear)
+
+    def forward(self, x):
+        y = self.linear(x)
+        if self.gather_output and self.world > 1:
+            parts = [torch.empty_like(y) for _ in range(self.world)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=-1)
+        return y
+
+
+class RowParallelAWQLinear(nn.Module):
+    """y = all_reduce_sum( x[..., shard] . W[shard, :] ) (+ bias on rank 0)."""
+
+    def __init__(self, qweight, qzeros, scales, bias, group_size: int, input_is_parallel: bool = True,
+                 group=None, device=None):
+        super().__init__()
+        self.group = group
+        self.rank, self.world = _world(group)
+        self.input_is_parallel = input_is_parallel
+        G = qweight.shape[0] if group_size == -1 else group_size
+        qw, qz, sc = row_shard(qweight, qzeros, scales, G, self.rank, self.world)
+        self.linear = _local_linear(qw, qz, sc, bias if self.rank == 0 else None, G,
+                                    device if device is not None else qweight.device)
+        self.in_features = qweight.shape[0]
+        self.k_local = qw.shape[0]
+
+    @classmethod
+    def from_local(cls, qweight, qzeros, scales, bias, group_size: int, input_is_parallel: bool = True, group=None):
+        """Wrap tensors that already are this rank's row shard (bias is kept on rank 0 only)."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        self.group, self.input_is_parallel = group, input_is_parallel
+        self.rank, self.world = _world(group)
+        G = qweight.shape[0] if group_size == -1 else group_size
+        self.linear = _local_linear(qweight, qzeros, scales, bias if self.rank == 0 else None, G, qweight.device)
+        self.k_local = qweight.shape[0]
+        self.in_features = self.k_local * self.world
+        return self
+
+    def packed(self):
+        return _packed(self.linear)
+
+    def forward(self, x):
+        if not self.input_is_parallel:
+            x = x[..., self.rank * self.k_local:(self.rank + 1) * self.k_local]
+        y = self.linear(x)
+        if self.world > 1:
+            y = y.contiguous()
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y

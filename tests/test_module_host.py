@@ -47,3 +47,15 @@ def test_empty_batch_and_no_cpu_fallback():
     m.impl_mode = "bogus"
     with pytest.raises(ValueError):
         m(torch.zeros(2, 128, dtype=torch.float16))
+
+
+def test_torch_quantizer_matches_reference(golden_dir):
+    from llmrqt_sdv1_b200.quantize import quantize_weight, rtn_quantize
+    g = np.load(os.path.join(golden_dir, "awq_small.npz"))
+    G = int(g["group_size"])
+    w = torch.from_numpy(g["w"])
+    fake, s, z = rtn_quantize(w, G)
+    assert np.array_equal(fake.numpy().view(np.uint16), g["w_fake"].view(np.uint16))
+    qw, qz, sc = quantize_weight(w, G)
+    assert np.array_equal(qw.numpy(), g["qweight"]) and np.array_equal(qz.numpy(), g["qzeros"])
+    assert np.array_equal(sc.numpy().view(np.uint16), g["scales"].view(np.uint16))

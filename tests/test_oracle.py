@@ -93,3 +93,21 @@ def test_config1_generator_and_forward(golden_dir):
     x = orc.make_activations(M, K, seed=int(g["seed"]))
     y = orc.linear_forward(x, qw, qz, sc, G)
     assert orc.max_normalised_error(y, g["y"][0]) <= 1e-3
+
+
+# ---- the C restatement (used as the timed CPU baseline) ----------------------------------
+def test_c_oracle_matches_goldens(golden_dir):
+    from oracle import c_oracle
+    g = _load(golden_dir, "awq_all_pairs.npz")
+    W = c_oracle.dequantize(g["qweight"], g["qzeros"], g["scales"], int(g["group_size"]))
+    assert np.array_equal(W.view(np.uint16), g["W_bits"])
+    g = _load(golden_dir, "awq_small.npz")
+    G = int(g["group_size"])
+    assert np.array_equal(c_oracle.dequantize(g["qweight"], g["qzeros"], g["scales"], G).view(np.uint16),
+                          g["W"].view(np.uint16))
+    y = c_oracle.linear_forward(g["x"], g["qweight"], g["qzeros"], g["scales"], G)
+    assert orc.max_normalised_error(y, g["y"][0]) <= 1e-3
+    g = _load(golden_dir, "awq_bias_3d.npz")
+    y3 = c_oracle.linear_forward(g["x3"], g["qweight"], g["qzeros"], g["scales"], int(g["group_size"]), g["bias"])
+    assert orc.max_normalised_error(y3, g["y3"]) <= 1e-3
+    assert c_oracle.threads() >= 1
