@@ -18,6 +18,7 @@ constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = 8;
 constexpr int kGemvMaxBps = 16;   // 128-k blocks per split (bounds the activation slice in smem)
 constexpr int kGemvMaxRows = 16;
+constexpr int kGemvUnitsInFlight = 8;  // 128-bit weight loads in flight per thread
 
 struct GemvParams {
   const uint16_t* x;
@@ -91,21 +92,24 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;  // uint4 per 128-k block
   const int zcols = p.N >> 3;
 
-  uint4 wcur[NTW];
-  uint32_t scur[NTW], zcur[NTW];
-  auto issue_loads = [&](int bl, uint4 (&w)[NTW], uint32_t (&s)[NTW], uint32_t (&z)[NTW]) {
+  // Register ring of D = NTW * PB work units (one 128-bit weight load, its scale
+  // and its zero word each): PB k-blocks are in flight per thread at all times,
+  // so the memory pipe stays full without relying on occupancy.
+  constexpr int PB = kGemvUnitsInFlight / NTW;
+  constexpr int D = NTW * PB;
+  uint4 wr[D];
+  uint32_t sr[D], zr[D];
+  auto issue_loads = [&](int bl, int t, uint4& w, uint32_t& sc, uint32_t& z) {
     const int b = b0 + bl;
     const int grp = b / p.group_blocks;
-    const uint4* wb = p.wp + static_cast<size_t>(b) * block_stride_u4 + lane;
-#pragma unroll
-    for (int t = 0; t < NTW; ++t) w[t] = ldg_stream(wb + static_cast<size_t>(tile[t]) * 32);
-#pragma unroll
-    for (int t = 0; t < NTW; ++t) {
-      s[t] = __ldg(p.scales + static_cast<size_t>(grp) * p.N + tile[t] * 8 + g);
-      z[t] = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tile[t]);
-    }
+    w = ldg_stream(p.wp + static_cast<size_t>(b) * block_stride_u4 + static_cast<size_t>(tile[t]) * 32 + lane);
+    sc = __ldg(p.scales + static_cast<size_t>(grp) * p.N + tile[t] * 8 + g);
+    z = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tile[t]);
   };
-  issue_loads(0, wcur, scur, zcur);
+#pragma unroll
+  for (int j = 0; j < D; ++j) {
+    if (j / NTW < nb) issue_loads(j / NTW, j % NTW, wr[j], sr[j], zr[j]);
+  }
 
   // Stage this split's activation slice.  Chunk j (8 halves) of a block lands at
   // slot (j % 4) * 4 + j / 4 so that lane c's i-th 128-bit read (chunk 4c + i)
@@ -133,36 +137,34 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
 
   const unsigned char* xrow = smem + g * row_stride + c * 16;
 
-  for (int bl = 0; bl < nb; ++bl) {
-    uint4 wnext[NTW];
-    uint32_t snext[NTW], znext[NTW];
-    if (bl + 1 < nb) issue_loads(bl + 1, wnext, snext, znext);
-
-    uint4 xa[4], xb[4];
+  for (int bl0 = 0; bl0 < nb; bl0 += PB) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      xa[i] = *reinterpret_cast<const uint4*>(xrow + bl * 256 + i * 64);
-      if (MT == 16) xb[i] = *reinterpret_cast<const uint4*>(xrow + 8 * row_stride + bl * 256 + i * 64);
-      else xb[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-
+    for (int pb = 0; pb < PB; ++pb) {
+      const int bl = bl0 + pb;
+      if (bl < nb) {
+        uint4 xa[4], xb[4];
 #pragma unroll
-    for (int t = 0; t < NTW; ++t) {
-      const ZeroPair zp = make_zero_pair((zcur[t] >> awq_slot_shift(g)) & 0xFu);
-      const uint32_t s2 = scur[t] * 0x00010001u;
-      const uint32_t w[4] = {wcur[t].x, wcur[t].y, wcur[t].z, wcur[t].w};
+        for (int i = 0; i < 4; ++i) {
+          xa[i] = *reinterpret_cast<const uint4*>(xrow + bl * 256 + i * 64);
+          if (MT == 16) xb[i] = *reinterpret_cast<const uint4*>(xrow + 8 * row_stride + bl * 256 + i * 64);
+          else xb[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t o[4];
-        dequant_word(w[i], zp, s2, o);
-        mma_16816(acc[t], xa[i].x, xb[i].x, xa[i].y, xb[i].y, o[0], o[1]);
-        mma_16816(acc[t], xa[i].z, xb[i].z, xa[i].w, xb[i].w, o[2], o[3]);
+        for (int t = 0; t < NTW; ++t) {
+          const int j = pb * NTW + t;
+          const ZeroPair zp = make_zero_pair((zr[j] >> awq_slot_shift(g)) & 0xFu);
+          const uint32_t s2 = sr[j] * 0x00010001u;
+          const uint32_t w[4] = {wr[j].x, wr[j].y, wr[j].z, wr[j].w};
+          if (bl + PB < nb) issue_loads(bl + PB, t, wr[j], sr[j], zr[j]);   // refill the slot just read
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[4];
+            dequant_word(w[i], zp, s2, o);
+            mma_16816(acc[t], xa[i].x, xb[i].x, xa[i].y, xb[i].y, o[0], o[1]);
+            mma_16816(acc[t], xa[i].z, xb[i].z, xa[i].w, xb[i].w, o[2], o[3]);
+          }
+        }
       }
-    }
-
-    if (bl + 1 < nb) {
-#pragma unroll
-      for (int t = 0; t < NTW; ++t) { wcur[t] = wnext[t]; scur[t] = snext[t]; zcur[t] = znext[t]; }
     }
   }
 

@@ -37,7 +37,7 @@ def test_stateless_queries():
     assert b"128" in lib.awq_b200_status_string(4)
     assert lib.awq_b200_packed_bytes(2048, 6144) == 2048 * 6144 // 2
     assert lib.awq_b200_gemv_max_rows() == 16
-    assert lib.awq_b200_gemv_counter_bytes(6144) % 256 == 0
+    assert lib.awq_b200_gemv_counter_bytes(6144) == lib.awq_b200_gemv_counter_bytes(57344) == 16384
     ws1 = lib.awq_b200_gemv_workspace_bytes(1, 2048, 6144)
     ws16 = lib.awq_b200_gemv_workspace_bytes(16, 2048, 6144)
     assert 0 < ws1 <= ws16 <= lib.awq_b200_gemv_workspace_bytes_max(16, 2048, 6144)
