@@ -119,7 +119,7 @@ AWQ_B200_API int awq_b200_gemv(const void* x, const void* packed, const void* sc
                   const void* bias, void* y, int M, int K, int N, int group_size,
                   void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
 
-/* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {1,2,4} column
+/* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {2,4} column
  * tiles per warp, bps in 1..16 k-blocks of 128 per split, 0 = planner's choice.
  * Its workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N).  No
  * reference counterpart. */

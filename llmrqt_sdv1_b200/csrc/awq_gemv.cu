@@ -3,13 +3,15 @@
 // One pass over the packed weights serves all rows.  Work unit = one 128-k
 // block x one tile of 8 output columns = 512 contiguous bytes, read by a warp
 // as one 128-bit load per lane.  Lane (g = lane / 4, c = lane % 4) owns column
-// 8*tile + g and the four words 4c..4c+3 of that column (32 consecutive k),
-// dequantises them in registers to fp16 (the exact reference weight) and feeds
-// them to mma.sync m16n8k16 as the B operand, with the activations as A and
-// fp32 accumulators.  k is split over gridDim.y; each split writes fp32
-// partials to the workspace and the last CTA to arrive for a column range adds
-// them in split order, so results are deterministic and a row's value does not
-// depend on how many rows the call has.
+// 8*tile + g and the four words 4c..4c+3 of that column (32 consecutive k).
+// Two adjacent tiles form the 16 rows of an mma.sync m16n8k16 A operand; the
+// nibbles go to the tensor core as unscaled codes and scale / zero point are
+// applied in fp32 once per 128-k block, which keeps the instruction count per
+// byte low enough for the kernel to be bound by HBM rather than by issue slots.
+// k is split over gridDim.y; each split writes fp32 partials to the workspace
+// and the last CTA to arrive for a column range adds them in split order, so
+// results are deterministic and a row's value does not depend on how many rows
+// the call has.
 #include "awq_common.cuh"
 
 namespace awq {
@@ -71,8 +73,43 @@ __device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, si
   *reinterpret_cast<uint32_t*>(y + row_off + col) = v;
 }
 
+// One packed word (8 nibbles) -> four half2 for the tensor core, without scaling:
+// out[0], out[2] hold the exact codes q (nibbles 0/4 and 2/6: (q | 0x6400) - 1024);
+// out[1], out[3] hold 64 + q (nibbles 1/5 and 3/7 or-ed into the mantissa of 2^6),
+// whose constant 64 is removed afterwards through the per-block activation sums.
+__device__ __forceinline__ void unpack_codes(uint32_t w, uint32_t out[4]) {
+  constexpr uint32_t kLoMask = 0x000f000fu, kHiMask = 0x00f000f0u;
+  constexpr uint32_t k1024 = 0x64006400u, k64 = 0x54005400u;
+  const uint32_t w8 = w >> 8;
+  out[0] = h2_sub(lop3_and_or(w, kLoMask, k1024), k1024);
+  out[1] = lop3_and_or(w, kHiMask, k64);
+  out[2] = h2_sub(lop3_and_or(w8, kLoMask, k1024), k1024);
+  out[3] = lop3_and_or(w8, kHiMask, k64);
+}
+
+__device__ __forceinline__ float small_uint_to_float(uint32_t v) {   // exact for v < 2^23, no I2F
+  return __uint_as_float(0x4B000000u | v) - 8388608.0f;
+}
+
+// NTW (2 or 4) column tiles per warp, handled as NTW/2 pairs of 16 columns; MT = 8 or 16 rows.
+//
+// Arithmetic per 128-k block b, column n, row m (all fp32 after the tensor core):
+//   y[m,n] += s[b,n] * ( sum_k x[m,k] * code[k,n]  -  z[b,n] * sum_k x[m,k] )
+// The 16 columns of a pair are the rows of the mma A operand (the weights), the
+// activations are the B operand (8 rows of x per mma), so one m16n8k16 covers
+// 16 columns x 16 k.  The two activation sums per block and row (all k, and 64x
+// the k fed as "64 + q") come from the tensor core as well, once per CTA.
+__device__ __forceinline__ void store_out1(uint16_t* y, const uint16_t* bias, size_t row_off, int col, float a) {
+  __half h = __float2half_rn(a);
+  if (bias != nullptr) h = __hadd(h, __ushort_as_half(bias[col]));
+  y[row_off + col] = __half_as_ushort(h);
+}
+
 template <int NTW, int MT>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams p) {
+  static_assert(NTW == 2 || NTW == 4, "column tiles are processed in pairs");
+  constexpr int NP = NTW / 2;    // pairs per warp
+  constexpr int MH = MT / 8;     // row halves
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_last;
 
@@ -83,6 +120,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const int b0 = split * p.bps;
   const int nb = min(p.bps, p.nblk - b0);
   const int row_stride = p.bps * 256 + 64;  // bytes; +64 keeps rows g and g+1 on disjoint banks
+  unsigned char* tsm = smem + MT * row_stride;   // [bps][MH][4 lanes c] x float4 {S(2c), S(2c+1), H(2c), H(2c+1)}
 
   const int tile0 = (blockIdx.x * kGemvWarps + warp) * NTW;
   int tile[NTW];
@@ -93,8 +131,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const int zcols = p.N >> 3;
 
   // Register ring of D = NTW * PB work units (one 128-bit weight load, its scale
-  // and its zero word each): PB k-blocks are in flight per thread at all times,
-  // so the memory pipe stays full without relying on occupancy.
+  // and its zero word each): PB k-blocks are in flight per thread at all times.
   constexpr int PB = kGemvUnitsInFlight / NTW;
   constexpr int D = NTW * PB;
   uint4 wr[D];
@@ -131,67 +168,113 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   }
   __syncthreads();
 
-  float acc[NTW][4];
-#pragma unroll
-  for (int t = 0; t < NTW; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-
   const unsigned char* xrow = smem + g * row_stride + c * 16;
+
+  // Per-block activation sums, through the tensor core: S[m] = sum_k x[m,k] and
+  // H[m] = 64 * sum over the k that are fed as (64 + q).
+  for (int bl = warp; bl < nb; bl += kGemvWarps) {
+#pragma unroll
+    for (int mh = 0; mh < MH; ++mh) {
+      float S[4] = {0.f, 0.f, 0.f, 0.f}, H[4] = {0.f, 0.f, 0.f, 0.f};
+      constexpr uint32_t kOne = 0x3C003C00u, k64 = 0x54005400u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xrow + mh * 8 * row_stride + bl * 256 + i * 64);
+        mma_16816(S, kOne, kOne, kOne, kOne, xv.x, xv.y);
+        mma_16816(S, kOne, kOne, kOne, kOne, xv.z, xv.w);
+        mma_16816(H, 0u, 0u, k64, k64, xv.x, xv.y);
+        mma_16816(H, 0u, 0u, k64, k64, xv.z, xv.w);
+      }
+      if (g == 0)
+        *reinterpret_cast<float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16) = make_float4(S[0], S[1], H[0], H[1]);
+    }
+  }
+  __syncthreads();
+
+  float acc[MH][NP][4];
+#pragma unroll
+  for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+    for (int q = 0; q < NP; ++q) acc[mh][q][0] = acc[mh][q][1] = acc[mh][q][2] = acc[mh][q][3] = 0.f;
 
   for (int bl0 = 0; bl0 < nb; bl0 += PB) {
 #pragma unroll
     for (int pb = 0; pb < PB; ++pb) {
       const int bl = bl0 + pb;
       if (bl < nb) {
-        uint4 xa[4], xb[4];
+        uint4 xv[MH][4];
+        float4 T[MH];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          xa[i] = *reinterpret_cast<const uint4*>(xrow + bl * 256 + i * 64);
-          if (MT == 16) xb[i] = *reinterpret_cast<const uint4*>(xrow + 8 * row_stride + bl * 256 + i * 64);
-          else xb[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int mh = 0; mh < MH; ++mh) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            xv[mh][i] = *reinterpret_cast<const uint4*>(xrow + mh * 8 * row_stride + bl * 256 + i * 64);
+          T[mh] = *reinterpret_cast<const float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16);
         }
 #pragma unroll
-        for (int t = 0; t < NTW; ++t) {
-          const int j = pb * NTW + t;
-          const ZeroPair zp = make_zero_pair((zr[j] >> awq_slot_shift(g)) & 0xFu);
-          const uint32_t s2 = sr[j] * 0x00010001u;
-          const uint32_t w[4] = {wr[j].x, wr[j].y, wr[j].z, wr[j].w};
-          if (bl + PB < nb) issue_loads(bl + PB, t, wr[j], sr[j], zr[j]);   // refill the slot just read
+        for (int q = 0; q < NP; ++q) {
+          const int ja = pb * NTW + 2 * q, jb = ja + 1;
+          const uint32_t wa[4] = {wr[ja].x, wr[ja].y, wr[ja].z, wr[ja].w};
+          const uint32_t wb[4] = {wr[jb].x, wr[jb].y, wr[jb].z, wr[jb].w};
+          const float sa = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[ja])));
+          const float sb = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[jb])));
+          const float za = small_uint_to_float((zr[ja] >> awq_slot_shift(g)) & 0xFu);
+          const float zb = small_uint_to_float((zr[jb] >> awq_slot_shift(g)) & 0xFu);
+          if (bl + PB < nb) {   // refill the two slots just read
+            issue_loads(bl + PB, 2 * q, wr[ja], sr[ja], zr[ja]);
+            issue_loads(bl + PB, 2 * q + 1, wr[jb], sr[jb], zr[jb]);
+          }
+          float blk[MH][4];
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {   // start from -H so the "+64" terms cancel inside the chain
+            blk[mh][0] = -T[mh].z; blk[mh][1] = -T[mh].w; blk[mh][2] = -T[mh].z; blk[mh][3] = -T[mh].w;
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint32_t o[4];
-            dequant_word(w[i], zp, s2, o);
-            mma_16816(acc[t], xa[i].x, xb[i].x, xa[i].y, xb[i].y, o[0], o[1]);
-            mma_16816(acc[t], xa[i].z, xb[i].z, xa[i].w, xb[i].w, o[2], o[3]);
+            uint32_t qa[4], qb[4];
+            unpack_codes(wa[i], qa);
+            unpack_codes(wb[i], qb);
+#pragma unroll
+            for (int mh = 0; mh < MH; ++mh) {
+              mma_16816(blk[mh], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
+              mma_16816(blk[mh], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
+            }
+          }
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {
+            acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, blk[mh][0]), acc[mh][q][0]);
+            acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, blk[mh][1]), acc[mh][q][1]);
+            acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, blk[mh][2]), acc[mh][q][2]);
+            acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, blk[mh][3]), acc[mh][q][3]);
           }
         }
       }
     }
   }
 
-  // ---- epilogue -----------------------------------------------------------
-  if (p.S == 1) {
+  // ---- epilogue: this thread holds rows m = 8*mh + 2c, +1 of columns n and n + 8 ------------
+  const bool direct = (p.S == 1);
 #pragma unroll
-    for (int t = 0; t < NTW; ++t) {
-      if (tile0 + t >= p.ntiles) continue;
-      const int col = (tile0 + t) * 8 + 2 * c;
-      if (g < p.M) store_out2(p.y, p.bias, static_cast<size_t>(g) * p.N, col, acc[t][0], acc[t][1]);
-      if (MT == 16 && g + 8 < p.M)
-        store_out2(p.y, p.bias, static_cast<size_t>(g + 8) * p.N, col, acc[t][2], acc[t][3]);
+  for (int q = 0; q < NP; ++q) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (tile0 + 2 * q + half >= p.ntiles) continue;
+      const int n = (tile0 + 2 * q + half) * 8 + g;
+#pragma unroll
+      for (int mh = 0; mh < MH; ++mh) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int m = mh * 8 + 2 * c + e;
+          if (m >= p.M) continue;
+          const float v = acc[mh][q][half * 2 + e];
+          if (direct) store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, n, v);
+          else __stcg(p.partial + (static_cast<size_t>(split) * p.M + m) * p.N + n, v);
+        }
+      }
     }
-    return;
   }
+  if (direct) return;
 
-#pragma unroll
-  for (int t = 0; t < NTW; ++t) {
-    if (tile0 + t >= p.ntiles) continue;
-    const int col = (tile0 + t) * 8 + 2 * c;
-    if (g < p.M)
-      __stcg(reinterpret_cast<float2*>(p.partial + (static_cast<size_t>(split) * p.M + g) * p.N + col),
-             make_float2(acc[t][0], acc[t][1]));
-    if (MT == 16 && g + 8 < p.M)
-      __stcg(reinterpret_cast<float2*>(p.partial + (static_cast<size_t>(split) * p.M + g + 8) * p.N + col),
-             make_float2(acc[t][2], acc[t][3]));
-  }
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -239,9 +322,9 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
   // Cost model in microseconds: a CTA streams bps*ntw units of 4 KiB; two CTAs
   // share one SM's slice of HBM bandwidth (~44 KB/us).
   const double t_fix = 1.2, t_unit = 0.19, t_red = 0.4, t_red_split = 0.04;
-  GemvPlan best{1, 1, nblk, 0};
+  GemvPlan best{2, 1, nblk, 0};
   double best_t = 1e30;
-  const int ntws[3] = {4, 2, 1};
+  const int ntws[2] = {4, 2};
   for (int ntw : ntws) {
     const int ncol = (ntiles + kGemvWarps * ntw - 1) / (kGemvWarps * ntw);
     int prev_S = -1;
@@ -273,7 +356,7 @@ static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsign
 
 template <int NTW, int MT>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64);
+  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
     AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -299,8 +382,11 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
 
   GemvPlan plan = plan_gemv(K, N, di.sm_count);
-  if (force_ntw == 1 || force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
+  if (force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
   if (force_bps >= 1 && force_bps <= kGemvMaxBps) plan.bps = force_bps;
+  // The 16-row variant keeps twice the accumulators: run it with two tiles per warp.  Only the
+  // k-split decides the order of additions, so this cannot change a row's result.
+  if (M > 8 && force_ntw == 0) plan.ntw = 2;
   const int nblk = K / kBlockK, ntiles = N / 8;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
   plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
@@ -340,7 +426,6 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
     return wide ? launch_gemv<NTW_, 16>(p, plan, di.max_smem_optin, stream)                  \
                 : launch_gemv<NTW_, 8>(p, plan, di.max_smem_optin, stream);
   switch (plan.ntw) {
-    AWQ_GEMV_CASE(1)
     AWQ_GEMV_CASE(2)
     AWQ_GEMV_CASE(4)
     default: return AWQ_B200_ERR_SHAPE;
@@ -380,7 +465,7 @@ int awq_b200_gemv(const void* x, const void* packed, const void* scales, const i
 }
 
 // Tuning hook: same as awq_b200_gemv with the decomposition forced
-// (ntw in {1,2,4} column tiles per warp, bps in 1..16 k-blocks per split; 0 = planner's choice).
+// (ntw in {2,4} column tiles per warp, bps in 1..16 k-blocks per split; 0 = planner's choice).
 // The workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N) bytes.
 size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N) { return gemv_workspace_bytes(M, K, N); }
 
