@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const int nb = min(p.bps, p.nblk - b0);
   const int row_stride = p.bps * 256 + 64;  // bytes; +64 keeps rows g and g+1 on disjoint banks
   unsigned char* tsm = smem + MT * row_stride;   // [bps][MH][4 lanes c] x float4 {S(2c), S(2c+1), H(2c), H(2c+1)}
+  unsigned char* szsm = tsm + p.bps * MH * 64;   // [bps][8 * NTW tiles][8 columns] x float2 {scale, zero}
 
   const int tile0 = (blockIdx.x * kGemvWarps + warp) * NTW;
   int tile[NTW];
@@ -130,22 +131,48 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;  // uint4 per 128-k block
   const int zcols = p.N >> 3;
 
-  // Register ring of D = NTW * PB work units (one 128-bit weight load, its scale
-  // and its zero word each): PB k-blocks are in flight per thread at all times.
+  // Register ring of D = NTW * PB 128-bit weight loads: PB k-blocks are in flight
+  // per thread at all times.  One base pointer per tile; the block offset is a
+  // widening multiply-add.
   constexpr int PB = kGemvUnitsInFlight / NTW;
   constexpr int D = NTW * PB;
   uint4 wr[D];
-  uint32_t sr[D], zr[D];
-  auto issue_loads = [&](int bl, int t, uint4& w, uint32_t& sc, uint32_t& z) {
-    const int b = b0 + bl;
-    const int grp = b / p.group_blocks;
-    w = ldg_stream(p.wp + static_cast<size_t>(b) * block_stride_u4 + static_cast<size_t>(tile[t]) * 32 + lane);
-    sc = __ldg(p.scales + static_cast<size_t>(grp) * p.N + tile[t] * 8 + g);
-    z = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tile[t]);
+  const uint4* wbase[NTW];
+#pragma unroll
+  for (int t = 0; t < NTW; ++t)
+    wbase[t] = p.wp + static_cast<size_t>(b0) * block_stride_u4 + static_cast<size_t>(tile[t]) * 32 + lane;
+  const unsigned block_stride32 = static_cast<unsigned>(p.N) * 4u;
+  auto issue_load = [&](int bl, int t, uint4& w) {
+    w = ldg_stream(wbase[t] + static_cast<unsigned long long>(static_cast<unsigned>(bl)) * block_stride32);
   };
 #pragma unroll
   for (int j = 0; j < D; ++j) {
-    if (j / NTW < nb) issue_loads(j / NTW, j % NTW, wr[j], sr[j], zr[j]);
+    if (j / NTW < nb) issue_load(j / NTW, j % NTW, wr[j]);
+  }
+
+  // Scale and zero point of every (block, column) of this CTA go to shared memory
+  // once, already as fp32 pairs {s, z}; the main loop then needs no global loads
+  // besides the weights.  One item = 8 columns (one qzeros word, 8 scales).
+  {
+    constexpr int kCtaTiles = kGemvWarps * NTW;
+    const int cta_tile0 = blockIdx.x * kCtaTiles;
+    for (int i = tid; i < nb * kCtaTiles; i += kGemvThreads) {
+      const int bl = i / kCtaTiles, tt = i - bl * kCtaTiles;
+      const int tl = min(cta_tile0 + tt, p.ntiles - 1);
+      const int grp = (b0 + bl) / p.group_blocks;
+      const uint32_t zw = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tl);
+      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(p.scales + static_cast<size_t>(grp) * p.N + tl * 8));
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+      float4* dst = reinterpret_cast<float4*>(szsm + (static_cast<size_t>(bl) * kCtaTiles + tt) * 64);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float s0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw[h] & 0xFFFFu)));
+        const float s1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw[h] >> 16)));
+        const float z0 = small_uint_to_float((zw >> awq_slot_shift(2 * h)) & 0xFu);
+        const float z1 = small_uint_to_float((zw >> awq_slot_shift(2 * h + 1)) & 0xFu);
+        dst[h] = make_float4(s0, z0, s1, z1);
+      }
+    }
   }
 
   // Stage this split's activation slice.  Chunk j (8 halves) of a block lands at
@@ -216,13 +243,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
           const int ja = pb * NTW + 2 * q, jb = ja + 1;
           const uint32_t wa[4] = {wr[ja].x, wr[ja].y, wr[ja].z, wr[ja].w};
           const uint32_t wb[4] = {wr[jb].x, wr[jb].y, wr[jb].z, wr[jb].w};
-          const float sa = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[ja])));
-          const float sb = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[jb])));
-          const float za = small_uint_to_float((zr[ja] >> awq_slot_shift(g)) & 0xFu);
-          const float zb = small_uint_to_float((zr[jb] >> awq_slot_shift(g)) & 0xFu);
+          const float2* szp = reinterpret_cast<const float2*>(
+              szsm + ((static_cast<size_t>(bl) * (kGemvWarps * NTW) + warp * NTW + 2 * q) * 8 + g) * 8);
+          const float2 sza = szp[0], szb = szp[8];
+          const float sa = sza.x, za = sza.y, sb = szb.x, zb = szb.y;
           if (bl + PB < nb) {   // refill the two slots just read
-            issue_loads(bl + PB, 2 * q, wr[ja], sr[ja], zr[ja]);
-            issue_loads(bl + PB, 2 * q + 1, wr[jb], sr[jb], zr[jb]);
+            issue_load(bl + PB, 2 * q, wr[ja]);
+            issue_load(bl + PB, 2 * q + 1, wr[jb]);
           }
           float blk[MH][4];
 #pragma unroll
@@ -356,7 +383,8 @@ static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsign
 
 template <int NTW, int MT>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64;
+  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64 +
+                      static_cast<size_t>(p.bps) * kGemvWarps * NTW * 64;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
     AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
