@@ -193,7 +193,7 @@ def decode_detail(torch, kernels, quantize, peaks):
 
             def fn():
                 for pw, y in zip(pws, ys):
-                    kernels.gemv(x, pw, out=y)
+                    kernels.gemv(x, pw, out=y, overlap=True)
             ms = time_graph(torch, fn, iters=5) / copies
             gbs = gemv_bytes(M, K, N) / (ms * 1e-3) / 1e9
             rows.append({"linear": name, "K": K, "N": N, "M": M, "us": round(ms * 1e3, 3), "gbs": round(gbs, 1),
@@ -241,7 +241,7 @@ def run_qwen3_decode(args, torch, peaks):
 
     def step():
         for pw, y in zip(pws, ys):
-            kernels.gemv(xs[pw.K], pw, out=y)
+            kernels.gemv(xs[pw.K], pw, out=y, overlap=True)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -360,8 +360,8 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
 
     def step():
         for i in range(FFN70B_LAYERS):
-            kernels.gemv(x_g, pw_g[i], out=y_g[i])
-            kernels.gemv(x_d, pw_d[i], out=y_d[i])
+            kernels.gemv(x_g, pw_g[i], out=y_g[i], overlap=True)
+            kernels.gemv(x_d, pw_d[i], out=y_d[i], overlap=True)
             if world > 1:
                 dist.all_reduce(y_d[i])
 

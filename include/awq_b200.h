@@ -119,6 +119,22 @@ AWQ_B200_API int awq_b200_gemv(const void* x, const void* packed, const void* sc
                   const void* bias, void* y, int M, int K, int N, int group_size,
                   void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
 
+/* Call flags for the *_ex entry points. */
+enum awq_b200_flags {
+  /* The packed weights, scales and zeros are not being written by work still pending on the
+   * stream.  The kernel may then be launched with programmatic dependent launch: it fetches
+   * those constants while the previous kernel of the stream drains, and waits for that kernel
+   * before it reads x or writes y / the workspace. */
+  AWQ_B200_OVERLAP_PREVIOUS = 1
+};
+
+/* awq_b200_gemv with call flags.  No reference counterpart (the reference launches on the
+ * legacy default stream with no overlap, LLMQRT/runtime_refact/csrc/awq/gemv.cu:196-201). */
+AWQ_B200_API int awq_b200_gemv_ex(const void* x, const void* packed, const void* scales,
+                     const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
+                     int group_size, void* workspace, size_t workspace_bytes,
+                     awq_b200_stream_t stream, unsigned flags);
+
 /* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {2,4} column
  * tiles per warp, bps in 1..16 k-blocks of 128 per split, 0 = planner's choice.
  * Its workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N).  No
@@ -156,6 +172,12 @@ AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* awq_b200_linear with call flags (the flags only affect the GEMV branch). */
+AWQ_B200_API int awq_b200_linear_ex(const void* x, const void* packed, const void* scales,
+                       const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
+                       int group_size, void* workspace, size_t workspace_bytes,
+                       awq_b200_stream_t stream, unsigned flags);
 
 #ifdef __cplusplus
 }

@@ -28,6 +28,8 @@ SIGNATURES = {
     "awq_b200_gemv_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_gemv_counter_bytes": (_Z, [_I]),
     "awq_b200_gemv": (_I, _COMPUTE),
+    "awq_b200_gemv_ex": (_I, _COMPUTE + [C.c_uint]),
+    "awq_b200_linear_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_gemv_workspace_bytes_max": (_Z, [_I, _I, _I]),
     "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I]),
     "awq_b200_gemm_workspace_bytes": (_Z, [_I, _I, _I]),
@@ -57,6 +59,7 @@ def _load() -> C.CDLL:
 
 lib = _load()
 
+OVERLAP_PREVIOUS = 1
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(1, 9)
 _VALUE_ERRORS = {ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_TOO_LARGE}
 

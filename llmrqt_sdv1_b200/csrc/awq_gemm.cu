@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include "awq_common.cuh"
+#include "awq_ptx.cuh"
 
 namespace awq {
 
@@ -27,7 +28,6 @@ constexpr int kBK = 64;
 constexpr int kABytesHalf = 128 * kBK * 2;   // 16 KiB: 128 rows x 128 B
 constexpr int kBBytes = kBN * kBK * 2;       // 32 KiB: 256 columns x 128 B
 constexpr int kRawBytes = kBN * (kBK / 2);   // 8 KiB: 256 columns x 32 B of nibbles
-constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // ~2 s at 2 GHz
 
 template <int MH> struct GemmCfg {
   static constexpr int kStages = (MH == 2) ? 3 : 4;
@@ -47,47 +47,7 @@ struct GemmParams {
   int mtiles, ntiles;
 };
 
-// ---- PTX wrappers -----------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises *abort_flag) if the phase did not
-// complete in time or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = clock64();
-  unsigned spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        atomicCAS(const_cast<int*>(abort_flag), 0, code);
-        return false;
-      }
-    }
-  }
-}
+// ---- PTX wrappers (mbarrier / bulk copy ones live in awq_ptx.cuh) -----------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -103,7 +63,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -189,7 +148,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, kDequantThreads / 32);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),

@@ -13,14 +13,15 @@
 // results are deterministic and a row's value does not depend on how many rows
 // the call has.
 #include "awq_common.cuh"
+#include "awq_ptx.cuh"
 
 namespace awq {
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = 8;
-constexpr int kGemvMaxBps = 16;   // 128-k blocks per split (bounds the activation slice in smem)
+constexpr int kGemvMaxBps = 16;  // 128-k blocks per split (bounds the activation slice in smem)
 constexpr int kGemvMaxRows = 16;
-constexpr int kGemvUnitsInFlight = 8;  // 128-bit weight loads in flight per thread
+constexpr int kGemvStages = 4;         // 128-k blocks of packed weights in flight per CTA (bulk copies)
 
 struct GemvParams {
   const uint16_t* x;
@@ -31,6 +32,7 @@ struct GemvParams {
   uint16_t* y;
   float* partial;
   unsigned* counters;
+  unsigned* status;    // last counter slot: 0, or the code of a device-side wait that expired
   int M, K, N;
   int group_blocks;  // group_size / 128
   int nblk;          // K / 128
@@ -112,6 +114,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   constexpr int MH = MT / 8;     // row halves
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_last;
+  __shared__ int s_abort;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -119,61 +122,67 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const int split = blockIdx.y;
   const int b0 = split * p.bps;
   const int nb = min(p.bps, p.nblk - b0);
+  constexpr int kCtaTiles = kGemvWarps * NTW;
+  constexpr int kWeightBytes = kCtaTiles * 512;         // one 128-k block of this CTA's columns
+  constexpr int kScaleOff = kWeightBytes;               // then kCtaTiles * 8 fp16 scales
+  constexpr int kZeroOff = kScaleOff + kCtaTiles * 16;  // then kCtaTiles qzeros words
+  constexpr int kStageBytes = kWeightBytes + kCtaTiles * 32;
+  constexpr int ST = kGemvStages;
+  // Shared memory: [ring: ST stages of {weights, scales, zeros}][x slice][activation sums][mbarriers]
+  unsigned char* ring = smem;
+  unsigned char* xsm = ring + ST * kStageBytes;
   const int row_stride = p.bps * 256 + 64;  // bytes; +64 keeps rows g and g+1 on disjoint banks
-  unsigned char* tsm = smem + MT * row_stride;   // [bps][MH][4 lanes c] x float4 {S(2c), S(2c+1), H(2c), H(2c+1)}
-  unsigned char* szsm = tsm + p.bps * MH * 64;   // [bps][8 * NTW tiles][8 columns] x float2 {scale, zero}
+  unsigned char* tsm = xsm + MT * row_stride;    // [bps][MH][4 lanes c] x float4 {S(2c), S(2c+1), H(2c), H(2c+1)}
+  const uint32_t bar_base = smem_u32(tsm + p.bps * MH * 64);
+  auto bar_full = [&](int st) { return bar_base + 8u * st; };
+  auto bar_empty = [&](int st) { return bar_base + 8u * (ST + st); };
+  volatile int* abort_flag = &s_abort;
 
-  const int tile0 = (blockIdx.x * kGemvWarps + warp) * NTW;
-  int tile[NTW];
-#pragma unroll
-  for (int t = 0; t < NTW; ++t) tile[t] = min(tile0 + t, p.ntiles - 1);  // clamp: loads stay in range
-
-  const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;  // uint4 per 128-k block
+  const int cta_tile0 = blockIdx.x * kCtaTiles;
+  const int tile0 = cta_tile0 + warp * NTW;
   const int zcols = p.N >> 3;
-
-  // Register ring of D = NTW * PB 128-bit weight loads: PB k-blocks are in flight
-  // per thread at all times.  One base pointer per tile; the block offset is a
-  // widening multiply-add.
-  constexpr int PB = kGemvUnitsInFlight / NTW;
-  constexpr int D = NTW * PB;
-  uint4 wr[D];
-  const uint4* wbase[NTW];
-#pragma unroll
-  for (int t = 0; t < NTW; ++t)
-    wbase[t] = p.wp + static_cast<size_t>(b0) * block_stride_u4 + static_cast<size_t>(tile[t]) * 32 + lane;
-  const unsigned block_stride32 = static_cast<unsigned>(p.N) * 4u;
-  auto issue_load = [&](int bl, int t, uint4& w) {
-    w = ldg_stream(wbase[t] + static_cast<unsigned long long>(static_cast<unsigned>(bl)) * block_stride32);
+  // The CTA's columns of one block are contiguous in the packed layout: one bulk copy per block.
+  const uint32_t valid_tiles = static_cast<uint32_t>(min(kCtaTiles, p.ntiles - cta_tile0));
+  const uint4* wsrc = p.wp + (static_cast<size_t>(b0) * p.N) * 4 + static_cast<size_t>(cta_tile0) * 32;
+  const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;
+  // qzeros rows can be bulk-copied only if every row segment is 16-byte aligned and sized.
+  const bool zeros_by_copy = (p.N & 31) == 0;
+  const uint32_t stage_tx = valid_tiles * (512u + 16u + (zeros_by_copy ? 4u : 0u));
+  // One stage = the packed weights, scales and zero words of one 128-k block: up to three bulk copies.
+  auto issue_stage = [&](int bl) {
+    const int st = bl % ST;
+    const uint32_t dst = smem_u32(ring + st * kStageBytes);
+    const int grp = (b0 + bl) / p.group_blocks;
+    mbar_expect_tx(bar_full(st), stage_tx);
+    bulk_load(dst, wsrc + static_cast<size_t>(bl) * block_stride_u4, valid_tiles * 512u, bar_full(st));
+    bulk_load(dst + kScaleOff, p.scales + static_cast<size_t>(grp) * p.N + static_cast<size_t>(cta_tile0) * 8,
+              valid_tiles * 16u, bar_full(st));
+    if (zeros_by_copy)
+      bulk_load(dst + kZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u, bar_full(st));
   };
-#pragma unroll
-  for (int j = 0; j < D; ++j) {
-    if (j / NTW < nb) issue_load(j / NTW, j % NTW, wr[j]);
-  }
 
-  // Scale and zero point of every (block, column) of this CTA go to shared memory
-  // once, already as fp32 pairs {s, z}; the main loop then needs no global loads
-  // besides the weights.  One item = 8 columns (one qzeros word, 8 scales).
-  {
-    constexpr int kCtaTiles = kGemvWarps * NTW;
-    const int cta_tile0 = blockIdx.x * kCtaTiles;
-    for (int i = tid; i < nb * kCtaTiles; i += kGemvThreads) {
-      const int bl = i / kCtaTiles, tt = i - bl * kCtaTiles;
-      const int tl = min(cta_tile0 + tt, p.ntiles - 1);
-      const int grp = (b0 + bl) / p.group_blocks;
-      const uint32_t zw = __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + tl);
-      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(p.scales + static_cast<size_t>(grp) * p.N + tl * 8));
-      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-      float4* dst = reinterpret_cast<float4*>(szsm + (static_cast<size_t>(bl) * kCtaTiles + tt) * 64);
+  int issued = 0;   // blocks whose copy has been started (meaningful in thread 0 only)
+  if (tid == 0) {
+    s_abort = 0;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float s0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw[h] & 0xFFFFu)));
-        const float s1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sw[h] >> 16)));
-        const float z0 = small_uint_to_float((zw >> awq_slot_shift(2 * h)) & 0xFu);
-        const float z1 = small_uint_to_float((zw >> awq_slot_shift(2 * h + 1)) & 0xFu);
-        dst[h] = make_float4(s0, z0, s1, z1);
+    for (int st = 0; st < ST; ++st) {
+      mbar_init(bar_full(st), 1);
+      mbar_init(bar_empty(st), kGemvWarps);
+    }
+    mbar_fence_init();
+#pragma unroll
+    for (int st = 0; st < ST; ++st) {
+      if (st < nb) {
+        issue_stage(st);
+        issued = st + 1;
       }
     }
   }
+  // Everything requested so far is constant data.  Let the next kernel of the stream start its own
+  // prefetch, and wait for the previous one before touching activations, outputs or the workspace
+  // (both are no-ops unless the launch asked for programmatic dependent launch).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // Stage this split's activation slice.  Chunk j (8 halves) of a block lands at
   // slot (j % 4) * 4 + j / 4 so that lane c's i-th 128-bit read (chunk 4c + i)
@@ -190,30 +199,29 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
         v = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.K +
                                                  static_cast<size_t>(b0 + bl) * kBlockK + j * 8));
       const int slot = (j & 3) * 4 + (j >> 2);
-      *reinterpret_cast<uint4*>(smem + r * row_stride + bl * 256 + slot * 16) = v;
+      *reinterpret_cast<uint4*>(xsm + r * row_stride + bl * 256 + slot * 16) = v;
     }
   }
   __syncthreads();
 
-  const unsigned char* xrow = smem + g * row_stride + c * 16;
+  const unsigned char* xrow = xsm + g * row_stride + c * 16;
 
   // Per-block activation sums, through the tensor core: S[m] = sum_k x[m,k] and
   // H[m] = 64 * sum over the k that are fed as (64 + q).
   for (int bl = warp; bl < nb; bl += kGemvWarps) {
 #pragma unroll
     for (int mh = 0; mh < MH; ++mh) {
-      float S[4] = {0.f, 0.f, 0.f, 0.f}, H[4] = {0.f, 0.f, 0.f, 0.f};
+      // A rows 0..7 are all ones (-> S), rows 8..15 are 0 for the exact-code k and 64 for the others (-> H).
+      float SH[4] = {0.f, 0.f, 0.f, 0.f};
       constexpr uint32_t kOne = 0x3C003C00u, k64 = 0x54005400u;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint4 xv = *reinterpret_cast<const uint4*>(xrow + mh * 8 * row_stride + bl * 256 + i * 64);
-        mma_16816(S, kOne, kOne, kOne, kOne, xv.x, xv.y);
-        mma_16816(S, kOne, kOne, kOne, kOne, xv.z, xv.w);
-        mma_16816(H, 0u, 0u, k64, k64, xv.x, xv.y);
-        mma_16816(H, 0u, 0u, k64, k64, xv.z, xv.w);
+        mma_16816(SH, kOne, 0u, kOne, k64, xv.x, xv.y);
+        mma_16816(SH, kOne, 0u, kOne, k64, xv.z, xv.w);
       }
       if (g == 0)
-        *reinterpret_cast<float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16) = make_float4(S[0], S[1], H[0], H[1]);
+        *reinterpret_cast<float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16) = make_float4(SH[0], SH[1], SH[2], SH[3]);
     }
   }
   __syncthreads();
@@ -224,11 +232,44 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
 #pragma unroll
     for (int q = 0; q < NP; ++q) acc[mh][q][0] = acc[mh][q][1] = acc[mh][q][2] = acc[mh][q][3] = 0.f;
 
-  for (int bl0 = 0; bl0 < nb; bl0 += PB) {
+  bool ok = true;
+  for (int bl = 0; bl < nb; ++bl) {
+    const int st = bl % ST;
+    const uint32_t ph = static_cast<uint32_t>(bl / ST) & 1u;
+    if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) { ok = false; break; }
+    uint4 wv[NTW];
+    float sc[NTW], zp[NTW];
+    {
+      const unsigned char* stage = ring + st * kStageBytes;
+      const unsigned char* src = stage + (warp * NTW) * 512 + lane * 16;
 #pragma unroll
-    for (int pb = 0; pb < PB; ++pb) {
-      const int bl = bl0 + pb;
-      if (bl < nb) {
+      for (int t = 0; t < NTW; ++t) wv[t] = *reinterpret_cast<const uint4*>(src + t * 512);
+      const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(stage + kScaleOff) + (warp * NTW) * 8 + g;
+      const uint32_t* zsrc = reinterpret_cast<const uint32_t*>(stage + kZeroOff) + warp * NTW;
+#pragma unroll
+      for (int t = 0; t < NTW; ++t) {
+        sc[t] = __half2float(__ushort_as_half(ssrc[t * 8]));
+        uint32_t zw;
+        if (zeros_by_copy) zw = zsrc[t];
+        else zw = __ldg(p.qzeros + static_cast<size_t>((b0 + bl) / p.group_blocks) * zcols +
+                        min(tile0 + t, p.ntiles - 1));
+        zp[t] = small_uint_to_float((zw >> awq_slot_shift(g)) & 0xFu);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty(st));
+    // Refill one block late (the stage read in the previous iteration), so that the producer
+    // thread almost never waits for the other warps.
+    if (tid == 0 && bl >= 1 && bl - 1 + ST < nb) {
+      const int pst = (bl - 1) % ST;
+      const uint32_t pph = static_cast<uint32_t>((bl - 1) / ST) & 1u;
+      if (mbar_wait(bar_empty(pst), pph, abort_flag, 2)) {
+        issue_stage(bl - 1 + ST);
+        issued = bl + ST;
+      }
+    }
+    {
+      {
         uint4 xv[MH][4];
         float4 T[MH];
 #pragma unroll
@@ -240,17 +281,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
         }
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
-          const int ja = pb * NTW + 2 * q, jb = ja + 1;
-          const uint32_t wa[4] = {wr[ja].x, wr[ja].y, wr[ja].z, wr[ja].w};
-          const uint32_t wb[4] = {wr[jb].x, wr[jb].y, wr[jb].z, wr[jb].w};
-          const float2* szp = reinterpret_cast<const float2*>(
-              szsm + ((static_cast<size_t>(bl) * (kGemvWarps * NTW) + warp * NTW + 2 * q) * 8 + g) * 8);
-          const float2 sza = szp[0], szb = szp[8];
-          const float sa = sza.x, za = sza.y, sb = szb.x, zb = szb.y;
-          if (bl + PB < nb) {   // refill the two slots just read
-            issue_load(bl + PB, 2 * q, wr[ja]);
-            issue_load(bl + PB, 2 * q + 1, wr[jb]);
-          }
+          const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
+          const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
+          const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
           float blk[MH][4];
 #pragma unroll
           for (int mh = 0; mh < MH; ++mh) {   // start from -H so the "+64" terms cancel inside the chain
@@ -276,6 +309,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
           }
         }
       }
+    }
+  }
+  if (!ok) {
+    // A wait expired.  Let this CTA's outstanding copies land (bounded) before shared memory is
+    // released, record the failure, and fall through: the output of this call is invalid.
+    if (tid == 0) {
+      for (int bl = max(0, issued - ST); bl < issued; ++bl)
+        mbar_wait_timed(bar_full(bl % ST), static_cast<uint32_t>(bl / ST) & 1u);
+      if (p.status != nullptr) atomicCAS(p.status, 0u, static_cast<unsigned>(s_abort));
     }
   }
 
@@ -382,23 +424,33 @@ constexpr int kGemvMaxCounters = 4096;
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
 template <int NTW, int MT>
-static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64 +
-                      static_cast<size_t>(p.bps) * kGemvWarps * NTW * 64;
+static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream,
+                       bool overlap_previous) {
+  const size_t smem = static_cast<size_t>(kGemvStages) * kGemvWarps * NTW * (512 + 32) +
+                      static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64 +
+                      2 * kGemvStages * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
     AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
-  dim3 grid(plan.ncol, plan.S);
-  gemv_kernel<NTW, MT><<<grid, kGemvThreads, smem, stream>>>(p);
-  AWQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan.ncol, plan.S);
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_previous ? 1 : 0;
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT>, p));
   return AWQ_B200_OK;
 }
 
 int gemv_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
-                  size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_bps) {
+                  size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_bps, unsigned flags) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
@@ -418,11 +470,14 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   const int nblk = K / kBlockK, ntiles = N / 8;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
   plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
-  while (plan.ncol > kGemvMaxCounters && plan.ntw < 4) {
+  unsigned* p_status = nullptr;
+  while (plan.ncol > kGemvMaxCounters - 1 && plan.ntw < 4) {
     plan.ntw *= 2;
     plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
   }
-  if (plan.S > 65535 || plan.ncol > kGemvMaxCounters) return AWQ_B200_ERR_TOO_LARGE;
+  if (plan.S > 65535 || plan.ncol > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
+  if (workspace && workspace_bytes >= counter_bytes(N) && aligned16(workspace))
+    p_status = static_cast<unsigned*>(workspace) + (kGemvMaxCounters - 1);
 
   GemvParams p;
   p.x = static_cast<const uint16_t*>(x);
@@ -433,6 +488,7 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   p.y = static_cast<uint16_t*>(y);
   p.partial = nullptr;
   p.counters = nullptr;
+  p.status = p_status;
   p.M = M; p.K = K; p.N = N;
   p.group_blocks = group_size / kBlockK;
   p.nblk = nblk;
@@ -449,10 +505,11 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   }
 
   const bool wide = M > 8;
+  const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
 #define AWQ_GEMV_CASE(NTW_)                                                                  \
   case NTW_:                                                                                 \
-    return wide ? launch_gemv<NTW_, 16>(p, plan, di.max_smem_optin, stream)                  \
-                : launch_gemv<NTW_, 8>(p, plan, di.max_smem_optin, stream);
+    return wide ? launch_gemv<NTW_, 16>(p, plan, di.max_smem_optin, stream, overlap)         \
+                : launch_gemv<NTW_, 8>(p, plan, di.max_smem_optin, stream, overlap);
   switch (plan.ntw) {
     AWQ_GEMV_CASE(2)
     AWQ_GEMV_CASE(4)
@@ -489,7 +546,14 @@ int awq_b200_gemv(const void* x, const void* packed, const void* scales, const i
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                   size_t workspace_bytes, awq_b200_stream_t stream) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0u);
+}
+
+int awq_b200_gemv_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                     const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                     size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
+  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, flags);
 }
 
 // Tuning hook: same as awq_b200_gemv with the decomposition forced
@@ -502,7 +566,7 @@ int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, co
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
                        int bps) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps, 0u);
 }
 
 int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }

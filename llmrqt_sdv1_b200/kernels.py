@@ -35,11 +35,14 @@ def _kn(qweight: torch.Tensor) -> tuple[int, int]:
 class PackedWeight:
     """Kernel-layout weight of one linear: packed nibbles plus the on-disk
     scales / qzeros it is used with."""
-    __slots__ = ("packed", "qzeros", "scales", "K", "N", "group_size")
+    __slots__ = ("packed", "qzeros", "scales", "K", "N", "group_size", "fresh")
 
-    def __init__(self, packed, qzeros, scales, K, N, group_size):
+    def __init__(self, packed, qzeros, scales, K, N, group_size, fresh=False):
         self.packed, self.qzeros, self.scales = packed, qzeros, scales
         self.K, self.N, self.group_size = K, N, group_size
+        # True while the repack kernel that produced `packed` may still be queued: the first
+        # compute call must then not prefetch the weights ahead of the previous kernel.
+        self.fresh = fresh
 
 
 def repack(qweight: torch.Tensor) -> torch.Tensor:
@@ -71,7 +74,7 @@ def make_packed(qweight, qzeros, scales, group_size) -> PackedWeight:
         raise ValueError("scales must be fp16 [K/G, N]")
     if qzeros.dtype != torch.int32 or tuple(qzeros.shape) != (K // G, N // 8):
         raise ValueError("qzeros must be int32 [K/G, N/8]")
-    return PackedWeight(repack(qweight), qzeros.contiguous(), scales.contiguous(), K, N, G)
+    return PackedWeight(repack(qweight), qzeros.contiguous(), scales.contiguous(), K, N, G, fresh=True)
 
 
 def dequantize(qweight, qzeros, scales, group_size) -> torch.Tensor:
@@ -128,10 +131,13 @@ def _run(fn, name, x, pw, bias, ws_bytes, out=None, extra=()):
     return y
 
 
-def gemv(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
-    """Decode kernel, 1 <= M <= 16."""
-    return _run(lib.awq_b200_gemv, "awq_b200_gemv", x, pw, bias,
-                lib.awq_b200_gemv_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out)
+def gemv(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """Decode kernel, 1 <= M <= 16.  `overlap=True` lets the kernel prefetch its weights while the
+    previous kernel of the stream drains; pass it only when the weights are not being written by
+    work still queued on that stream (i.e. not right after `repack`)."""
+    return _run(lib.awq_b200_gemv_ex, "awq_b200_gemv", x, pw, bias,
+                lib.awq_b200_gemv_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
+                (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
 
 def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None) -> torch.Tensor:
@@ -146,10 +152,24 @@ def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
                 lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out)
 
 
-def linear(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
-    """M <= 16 -> GEMV, else GEMM (dispatch inside the library)."""
-    return _run(lib.awq_b200_linear, "awq_b200_linear", x, pw, bias,
-                lib.awq_b200_linear_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out)
+def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """M <= 16 -> GEMV, else GEMM (dispatch inside the library).  `overlap` as in `gemv`."""
+    return _run(lib.awq_b200_linear_ex, "awq_b200_linear", x, pw, bias,
+                lib.awq_b200_linear_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
+                (_lib.OVERLAP_PREVIOUS if overlap else 0,))
+
+
+def gemv_status(dev: torch.device | None = None) -> int:
+    """Status word of the decode kernel in this stream's workspaces (0 = no device-side wait expired).
+    Synchronises."""
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = 0
+    for kind, off in (("awq_b200_gemv", 0), ("awq_b200_gemv_plan", 0), ("awq_b200_linear", 256)):
+        ws = _workspaces.get((dev.index, stream, kind))
+        if ws is not None:
+            status |= int(ws[off + 4095 * 4: off + 4096 * 4].view(torch.int32).item())
+    return status
 
 
 def gemm_status(dev: torch.device | None = None) -> int:

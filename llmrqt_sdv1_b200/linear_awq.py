@@ -51,7 +51,8 @@ class AWQLinearMMFunction(Function):
             out = torch.matmul(x, kernels.dequantize(qweight, qzeros, scales, group_size))
         else:
             pw = ext.packed_for(qweight, qzeros, scales, group_size)
-            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw).reshape(out_shape)
+            overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
+            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw, overlap=overlap).reshape(out_shape)
         out = out + bias if bias is not None else out
         if out.dim() == 2:          # the reference always hands back a 3-D tensor
             out = out.unsqueeze(0)

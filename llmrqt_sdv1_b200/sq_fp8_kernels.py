@@ -43,6 +43,11 @@ def packed_for(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor
     return pw
 
 
+def _linear(in_feats, pw):
+    overlap, pw.fresh = not pw.fresh, False   # the call right after a repack must not prefetch weights
+    return kernels.linear(in_feats, pw, overlap=overlap)
+
+
 def _infer_group(kernel: torch.Tensor, scaling_factors: torch.Tensor) -> int:
     return kernel.shape[0] // scaling_factors.shape[0]
 
@@ -52,7 +57,7 @@ def awq_gemv(in_feats, kernel, scaling_factors, zeros, group_size):
     unless group_size == 128 and returns uninitialised memory; here any multiple of 128 works
     and anything else raises ValueError."""
     pw = packed_for(kernel, zeros, scaling_factors, group_size)
-    return kernels.linear(in_feats, pw)
+    return _linear(in_feats, pw)
 
 
 def awq_gemv_coalesced(in_feats, kernel, scaling_factors, zeros, group_size, version=2):
@@ -67,7 +72,7 @@ def awq_gemm(in_feats, kernel, scaling_factors, zeros, split_k_iters=8):
     Rows <= 16 are routed to the decode kernel inside the library, because the reference's own
     dispatch sends 8 <= M <= 16 here (linear_awq.py:167-185)."""
     pw = packed_for(kernel, zeros, scaling_factors, _infer_group(kernel, scaling_factors))
-    return kernels.linear(in_feats, pw)
+    return _linear(in_feats, pw)
 
 
 def awq_gemm_db(in_feats, kernel, scaling_factors, zeros, split_k_iters=8):
