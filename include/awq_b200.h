@@ -143,7 +143,7 @@ AWQ_B200_API size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N);
 AWQ_B200_API int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales,
                        const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
                        int group_size, void* workspace, size_t workspace_bytes,
-                       awq_b200_stream_t stream, int ntw, int bps);
+                       awq_b200_stream_t stream, int ntw, int bps, unsigned flags);
 
 /* ---- prefill: TMA + tcgen05/TMEM GEMM, any M >= 1 ----------------------- */
 

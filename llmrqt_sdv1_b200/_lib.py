@@ -31,7 +31,7 @@ SIGNATURES = {
     "awq_b200_gemv_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_linear_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_gemv_workspace_bytes_max": (_Z, [_I, _I, _I]),
-    "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I]),
+    "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I, C.c_uint]),
     "awq_b200_gemm_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_gemm": (_I, _COMPUTE),
     "awq_b200_gemv_max_rows": (_I, []),

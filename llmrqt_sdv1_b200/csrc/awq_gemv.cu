@@ -17,11 +17,12 @@
 
 namespace awq {
 
-constexpr int kGemvThreads = 256;
-constexpr int kGemvWarps = 8;
-constexpr int kGemvMaxBps = 16;  // 128-k blocks per split (bounds the activation slice in smem)
+constexpr int kGemvWarps = 8;                       // compute warps; one more warp only issues bulk copies
+constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
+constexpr int kGemvMaxBps = 32;  // 128-k blocks per split (bounds the activation slice in smem)
 constexpr int kGemvMaxRows = 16;
-constexpr int kGemvStages = 4;         // 128-k blocks of packed weights in flight per CTA (bulk copies)
+// 128-k blocks in flight per CTA (bulk copies): 5 x 17 KiB or 6 x 8.5 KiB of shared memory.
+__host__ __device__ constexpr int gemv_stages(int ntw) { return ntw == 4 ? 5 : 6; }
 
 struct GemvParams {
   const uint16_t* x;
@@ -82,7 +83,7 @@ __device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, si
 __device__ __forceinline__ void unpack_codes(uint32_t w, uint32_t out[4]) {
   constexpr uint32_t kLoMask = 0x000f000fu, kHiMask = 0x00f000f0u;
   constexpr uint32_t k1024 = 0x64006400u, k64 = 0x54005400u;
-  const uint32_t w8 = w >> 8;
+  const uint32_t w8 = __umulhi(w, 0x01000000u);   // w >> 8 on the multiplier pipe; the logic pipe is the busy one
   out[0] = h2_sub(lop3_and_or(w, kLoMask, k1024), k1024);
   out[1] = lop3_and_or(w, kHiMask, k64);
   out[2] = h2_sub(lop3_and_or(w8, kLoMask, k1024), k1024);
@@ -127,13 +128,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   constexpr int kScaleOff = kWeightBytes;               // then kCtaTiles * 8 fp16 scales
   constexpr int kZeroOff = kScaleOff + kCtaTiles * 16;  // then kCtaTiles qzeros words
   constexpr int kStageBytes = kWeightBytes + kCtaTiles * 32;
-  constexpr int ST = kGemvStages;
-  // Shared memory: [ring: ST stages of {weights, scales, zeros}][x slice][activation sums][mbarriers]
+  constexpr int ST = gemv_stages(NTW);
+  const bool is_producer = (warp == kGemvWarps);
+  // Shared memory: [ring: ST stages of {weights, scales, zeros}][mbarriers]
   unsigned char* ring = smem;
-  unsigned char* xsm = ring + ST * kStageBytes;
-  const int row_stride = p.bps * 256 + 64;  // bytes; +64 keeps rows g and g+1 on disjoint banks
-  unsigned char* tsm = xsm + MT * row_stride;    // [bps][MH][4 lanes c] x float4 {S(2c), S(2c+1), H(2c), H(2c+1)}
-  const uint32_t bar_base = smem_u32(tsm + p.bps * MH * 64);
+  unsigned char* szsm = ring + ST * kStageBytes;            // [warp][2][32] float2 {scale, zero}
+  const uint32_t bar_base = smem_u32(szsm + kGemvWarps * 2 * 32 * 8);
   auto bar_full = [&](int st) { return bar_base + 8u * st; };
   auto bar_empty = [&](int st) { return bar_base + 8u * (ST + st); };
   volatile int* abort_flag = &s_abort;
@@ -161,8 +161,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
       bulk_load(dst + kZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u, bar_full(st));
   };
 
-  int issued = 0;   // blocks whose copy has been started (meaningful in thread 0 only)
-  if (tid == 0) {
+  int issued = 0;   // blocks whose copy has been started (meaningful in the producer thread only)
+  if (is_producer && lane == 0) {
     s_abort = 0;
 #pragma unroll
     for (int st = 0; st < ST; ++st) {
@@ -184,47 +184,31 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Stage this split's activation slice.  Chunk j (8 halves) of a block lands at
-  // slot (j % 4) * 4 + j / 4 so that lane c's i-th 128-bit read (chunk 4c + i)
-  // is conflict free.
-  {
-    const int chunks_per_row = nb * 16;
-    const int total = MT * chunks_per_row;
-    for (int i = tid; i < total; i += kGemvThreads) {
-      const int r = i / chunks_per_row;
-      const int cj = i - r * chunks_per_row;
-      const int bl = cj >> 4, j = cj & 15;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < p.M)
-        v = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r) * p.K +
-                                                 static_cast<size_t>(b0 + bl) * kBlockK + j * 8));
-      const int slot = (j & 3) * 4 + (j >> 2);
-      *reinterpret_cast<uint4*>(xsm + r * row_stride + bl * 256 + slot * 16) = v;
-    }
+  __syncthreads();   // mbarrier initialisation visible to every warp
+
+  // Activations go straight from global memory (L1/L2 resident) to the mma B fragments: lane
+  // (g, c) needs row 8*mh + g, k = 32c .. 32c+31 of each block, i.e. 64 contiguous bytes.
+  const uint16_t* xlane[MH];
+  bool xvalid[MH];
+#pragma unroll
+  for (int mh = 0; mh < MH; ++mh) {
+    const int m = mh * 8 + g;
+    xvalid[mh] = m < p.M;
+    xlane[mh] = p.x + static_cast<size_t>(xvalid[mh] ? m : 0) * p.K + static_cast<size_t>(b0) * kBlockK + c * 32;
   }
-  __syncthreads();
-
-  const unsigned char* xrow = xsm + g * row_stride + c * 16;
-
-  // Per-block activation sums, through the tensor core: S[m] = sum_k x[m,k] and
-  // H[m] = 64 * sum over the k that are fed as (64 + q).
-  for (int bl = warp; bl < nb; bl += kGemvWarps) {
+  auto load_x = [&](int bl, uint4 (&xv)[MH][4]) {
 #pragma unroll
     for (int mh = 0; mh < MH; ++mh) {
-      // A rows 0..7 are all ones (-> S), rows 8..15 are 0 for the exact-code k and 64 for the others (-> H).
-      float SH[4] = {0.f, 0.f, 0.f, 0.f};
-      constexpr uint32_t kOne = 0x3C003C00u, k64 = 0x54005400u;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xrow + mh * 8 * row_stride + bl * 256 + i * 64);
-        mma_16816(SH, kOne, 0u, kOne, k64, xv.x, xv.y);
-        mma_16816(SH, kOne, 0u, kOne, k64, xv.z, xv.w);
+        xv[mh][i] = make_uint4(0u, 0u, 0u, 0u);
+        if (xvalid[mh]) xv[mh][i] = __ldg(reinterpret_cast<const uint4*>(xlane[mh] + bl * kBlockK + i * 8));
       }
-      if (g == 0)
-        *reinterpret_cast<float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16) = make_float4(SH[0], SH[1], SH[2], SH[3]);
     }
-  }
-  __syncthreads();
+  };
+  constexpr bool kPrefetchX = (MH == 1);   // double-buffer the fragments when registers allow
+  uint4 xnext[MH][4];
+  if (!is_producer && kPrefetchX) load_x(0, xnext);
 
   float acc[MH][NP][4];
 #pragma unroll
@@ -232,11 +216,20 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
 #pragma unroll
     for (int q = 0; q < NP; ++q) acc[mh][q][0] = acc[mh][q][1] = acc[mh][q][2] = acc[mh][q][3] = 0.f;
 
-  bool ok = true;
+  if (is_producer) {
+    // Producer warp: refill a stage as soon as all compute warps have released it.
+    if (lane == 0) {
+      for (int bl = ST; bl < nb; ++bl) {
+        if (!mbar_wait(bar_empty(bl % ST), static_cast<uint32_t>(bl / ST - 1) & 1u, abort_flag, 2)) break;
+        issue_stage(bl);
+        issued = bl + 1;
+      }
+    }
+  } else
   for (int bl = 0; bl < nb; ++bl) {
     const int st = bl % ST;
     const uint32_t ph = static_cast<uint32_t>(bl / ST) & 1u;
-    if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) { ok = false; break; }
+    if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) break;
     uint4 wv[NTW];
     float sc[NTW], zp[NTW];
     {
@@ -244,50 +237,67 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
       const unsigned char* src = stage + (warp * NTW) * 512 + lane * 16;
 #pragma unroll
       for (int t = 0; t < NTW; ++t) wv[t] = *reinterpret_cast<const uint4*>(src + t * 512);
-      const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(stage + kScaleOff) + (warp * NTW) * 8 + g;
-      const uint32_t* zsrc = reinterpret_cast<const uint32_t*>(stage + kZeroOff) + warp * NTW;
+      // Each lane converts ONE {scale, zero} pair of the warp's 8*NTW columns to fp32 and parks it
+      // in a warp-private slot; every lane then picks up the NTW pairs of its own columns.
+      float2* slot = reinterpret_cast<float2*>(szsm) + (warp * 2 + (bl & 1)) * 32;
+      if (lane < NTW * 8) {
+        const int tl = lane >> 3, cl = lane & 7;
+        const unsigned short sraw = reinterpret_cast<const unsigned short*>(stage + kScaleOff)[(warp * NTW + tl) * 8 + cl];
+        uint32_t zw;
+        if (zeros_by_copy) zw = reinterpret_cast<const uint32_t*>(stage + kZeroOff)[warp * NTW + tl];
+        else zw = __ldg(p.qzeros + static_cast<size_t>((b0 + bl) / p.group_blocks) * zcols +
+                        min(tile0 + tl, p.ntiles - 1));
+        slot[lane] = make_float2(__half2float(__ushort_as_half(sraw)),
+                                 small_uint_to_float((zw >> awq_slot_shift(static_cast<uint32_t>(cl))) & 0xFu));
+      }
+      __syncwarp();
 #pragma unroll
       for (int t = 0; t < NTW; ++t) {
-        sc[t] = __half2float(__ushort_as_half(ssrc[t * 8]));
-        uint32_t zw;
-        if (zeros_by_copy) zw = zsrc[t];
-        else zw = __ldg(p.qzeros + static_cast<size_t>((b0 + bl) / p.group_blocks) * zcols +
-                        min(tile0 + t, p.ntiles - 1));
-        zp[t] = small_uint_to_float((zw >> awq_slot_shift(g)) & 0xFu);
+        const float2 v = slot[t * 8 + g];
+        sc[t] = v.x;
+        zp[t] = v.y;
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_empty(st));
-    // Refill one block late (the stage read in the previous iteration), so that the producer
-    // thread almost never waits for the other warps.
-    if (tid == 0 && bl >= 1 && bl - 1 + ST < nb) {
-      const int pst = (bl - 1) % ST;
-      const uint32_t pph = static_cast<uint32_t>((bl - 1) / ST) & 1u;
-      if (mbar_wait(bar_empty(pst), pph, abort_flag, 2)) {
-        issue_stage(bl - 1 + ST);
-        issued = bl + ST;
-      }
-    }
     {
       {
         uint4 xv[MH][4];
         float4 T[MH];
+        if (kPrefetchX) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) xv[0][i] = xnext[0][i];
+          if (bl + 1 < nb) load_x(bl + 1, xnext);
+        } else {
+          load_x(bl, xv);
+        }
+        // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
+        // x[m,k]), rows 8..15 are 0 for the exact-code k and 64 for the k fed as 64 + q (-> H[m]).
 #pragma unroll
         for (int mh = 0; mh < MH; ++mh) {
+          float SH[4] = {0.f, 0.f, 0.f, 0.f};
+          constexpr uint32_t kOne = 0x3C003C00u, k64h = 0x54005400u;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            xv[mh][i] = *reinterpret_cast<const uint4*>(xrow + mh * 8 * row_stride + bl * 256 + i * 64);
-          T[mh] = *reinterpret_cast<const float4*>(tsm + ((bl * MH + mh) * 4 + c) * 16);
+          for (int i = 0; i < 4; ++i) {
+            mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
+            mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
+          }
+          T[mh] = make_float4(SH[0], SH[1], SH[2], SH[3]);
         }
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
           const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
           const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
           const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
-          float blk[MH][4];
+          // kChains independent accumulation chains per block keep the tensor-core latency off the
+          // critical path; chain 0 starts from -H so that the "+64" terms cancel.
+          constexpr int kChains = 2;
+          float blk[MH][kChains][4];
 #pragma unroll
-          for (int mh = 0; mh < MH; ++mh) {   // start from -H so the "+64" terms cancel inside the chain
-            blk[mh][0] = -T[mh].z; blk[mh][1] = -T[mh].w; blk[mh][2] = -T[mh].z; blk[mh][3] = -T[mh].w;
+          for (int mh = 0; mh < MH; ++mh) {
+            blk[mh][0][0] = -T[mh].z; blk[mh][0][1] = -T[mh].w; blk[mh][0][2] = -T[mh].z; blk[mh][0][3] = -T[mh].w;
+#pragma unroll
+            for (int ch = 1; ch < kChains; ++ch) blk[mh][ch][0] = blk[mh][ch][1] = blk[mh][ch][2] = blk[mh][ch][3] = 0.f;
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -296,25 +306,34 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
             unpack_codes(wb[i], qb);
 #pragma unroll
             for (int mh = 0; mh < MH; ++mh) {
-              mma_16816(blk[mh], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
-              mma_16816(blk[mh], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
+              mma_16816(blk[mh][(2 * i) % kChains], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
+              mma_16816(blk[mh][(2 * i + 1) % kChains], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
             }
           }
 #pragma unroll
           for (int mh = 0; mh < MH; ++mh) {
-            acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, blk[mh][0]), acc[mh][q][0]);
-            acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, blk[mh][1]), acc[mh][q][1]);
-            acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, blk[mh][2]), acc[mh][q][2]);
-            acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, blk[mh][3]), acc[mh][q][3]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (kChains == 4) blk[mh][0][e] = (blk[mh][0][e] + blk[mh][1][e]) + (blk[mh][2][e] + blk[mh][3][e]);
+              else blk[mh][0][e] = blk[mh][0][e] + blk[mh][1][e];
+            }
+          }
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {
+            acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, blk[mh][0][0]), acc[mh][q][0]);
+            acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, blk[mh][0][1]), acc[mh][q][1]);
+            acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, blk[mh][0][2]), acc[mh][q][2]);
+            acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, blk[mh][0][3]), acc[mh][q][3]);
           }
         }
       }
     }
   }
-  if (!ok) {
+  __syncthreads();
+  if (s_abort != 0) {
     // A wait expired.  Let this CTA's outstanding copies land (bounded) before shared memory is
     // released, record the failure, and fall through: the output of this call is invalid.
-    if (tid == 0) {
+    if (is_producer && lane == 0) {
       for (int bl = max(0, issued - ST); bl < issued; ++bl)
         mbar_wait_timed(bar_full(bl % ST), static_cast<uint32_t>(bl / ST) & 1u);
       if (p.status != nullptr) atomicCAS(p.status, 0u, static_cast<unsigned>(s_abort));
@@ -327,7 +346,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   for (int q = 0; q < NP; ++q) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      if (tile0 + 2 * q + half >= p.ntiles) continue;
+      if (is_producer || tile0 + 2 * q + half >= p.ntiles) continue;
       const int n = (tile0 + 2 * q + half) * 8 + g;
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh) {
@@ -426,9 +445,8 @@ static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsign
 template <int NTW, int MT>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream,
                        bool overlap_previous) {
-  const size_t smem = static_cast<size_t>(kGemvStages) * kGemvWarps * NTW * (512 + 32) +
-                      static_cast<size_t>(MT) * (p.bps * 256 + 64) + static_cast<size_t>(p.bps) * (MT / 8) * 64 +
-                      2 * kGemvStages * 8;
+  const size_t smem = static_cast<size_t>(gemv_stages(NTW)) * kGemvWarps * NTW * (512 + 32) + kGemvWarps * 2 * 32 * 8 +
+                      2 * gemv_stages(NTW) * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
     AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -564,9 +582,9 @@ size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N) { return gemv_work
 int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                        const void* bias, void* y, int M, int K, int N, int group_size,
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
-                       int bps) {
+                       int bps, unsigned flags) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps, 0u);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps, flags);
 }
 
 int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }

@@ -140,10 +140,11 @@ def gemv(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> tor
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
 
-def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None) -> torch.Tensor:
+def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
     """Decode kernel with a forced decomposition (tuning and tests)."""
     return _run(lib.awq_b200_gemv_plan, "awq_b200_gemv_plan", x, pw, bias,
-                lib.awq_b200_gemv_workspace_bytes_max(max(x.shape[0], 1), pw.K, pw.N), out, (ntw, bps))
+                lib.awq_b200_gemv_workspace_bytes_max(max(x.shape[0], 1), pw.K, pw.N), out,
+                (ntw, bps, _lib.OVERLAP_PREVIOUS if overlap else 0))
 
 
 def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
