@@ -125,7 +125,11 @@ enum awq_b200_flags {
    * stream.  The kernel may then be launched with programmatic dependent launch: it fetches
    * those constants while the previous kernel of the stream drains, and waits for that kernel
    * before it reads x or writes y / the workspace. */
-  AWQ_B200_OVERLAP_PREVIOUS = 1
+  AWQ_B200_OVERLAP_PREVIOUS = 1,
+  /* Decode kernel: add the split-k partial sums through the global workspace even where the
+   * splits could form a thread-block cluster (2..8 splits) and add them over distributed shared
+   * memory.  Both ways add in the same order and give identical bits; this flag exists for tests. */
+  AWQ_B200_NO_CLUSTER = 2
 };
 
 /* awq_b200_gemv with call flags.  No reference counterpart (the reference launches on the
@@ -136,14 +140,15 @@ AWQ_B200_API int awq_b200_gemv_ex(const void* x, const void* packed, const void*
                      awq_b200_stream_t stream, unsigned flags);
 
 /* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {2,4} column
- * tiles per warp, bps in 1..16 k-blocks of 128 per split, 0 = planner's choice.
+ * tiles per warp, kw in {1,2,4,8} warps that split k inside a CTA, bps k-blocks of
+ * 128 per grid-level split; 0 = planner's choice.
  * Its workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N).  No
  * reference counterpart. */
 AWQ_B200_API size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N);
 AWQ_B200_API int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales,
                        const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
                        int group_size, void* workspace, size_t workspace_bytes,
-                       awq_b200_stream_t stream, int ntw, int bps, unsigned flags);
+                       awq_b200_stream_t stream, int ntw, int kw, int bps, unsigned flags);
 
 /* ---- prefill: TMA + tcgen05/TMEM GEMM, any M >= 1 ----------------------- */
 

@@ -10,7 +10,8 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libawq_b200.so")
+# AWQ_B200_LIBRARY points the binding at another build of the same ABI (e.g. a diagnostic build).
+LIB_PATH = os.environ.get("AWQ_B200_LIBRARY") or os.path.join(_HERE, "libawq_b200.so")
 
 # name -> (restype, argtypes); mirrors include/awq_b200.h one to one.
 _P, _I, _Z = C.c_void_p, C.c_int, C.c_size_t
@@ -31,7 +32,7 @@ SIGNATURES = {
     "awq_b200_gemv_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_linear_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_gemv_workspace_bytes_max": (_Z, [_I, _I, _I]),
-    "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I, C.c_uint]),
+    "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I, _I, C.c_uint]),
     "awq_b200_gemm_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_gemm": (_I, _COMPUTE),
     "awq_b200_gemv_max_rows": (_I, []),
@@ -60,6 +61,7 @@ def _load() -> C.CDLL:
 lib = _load()
 
 OVERLAP_PREVIOUS = 1
+NO_CLUSTER = 2
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(1, 9)
 _VALUE_ERRORS = {ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_TOO_LARGE}
 

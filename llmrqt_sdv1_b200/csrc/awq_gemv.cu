@@ -15,11 +15,31 @@
 #include "awq_common.cuh"
 #include "awq_ptx.cuh"
 
+#ifdef AWQ_GEMV_TRACE
+// Diagnostic build only: per-CTA phase timestamps (ns) into a caller-provided buffer.
+__device__ unsigned long long* g_gemv_trace = nullptr;
+__device__ __forceinline__ unsigned long long gemv_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define GEMV_TRACE(i)                                                                              \
+  do {                                                                                             \
+    if ((threadIdx.x & 31) == 0 && threadIdx.x < 64 && g_gemv_trace)                               \
+      g_gemv_trace[((blockIdx.y * gridDim.x + blockIdx.x) * 2 + (threadIdx.x >> 5)) * 8 + (i)] = gemv_now(); \
+  } while (0)
+extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_gemv_trace(void* buf) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_gemv_trace, &buf, sizeof(buf)));
+}
+#else
+#define GEMV_TRACE(i) do { } while (0)
+#endif
+
 namespace awq {
 
 constexpr int kGemvWarps = 8;                       // compute warps; one more warp only issues bulk copies
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
-constexpr int kGemvMaxBps = 32;  // 128-k blocks per split (bounds the activation slice in smem)
+constexpr int kGemvMaxBps = 32;   // per warp  // 128-k blocks per split (bounds the activation slice in smem)
 constexpr int kGemvMaxRows = 16;
 // 128-k blocks in flight per CTA (bulk copies): 5 x 17 KiB or 6 x 8.5 KiB of shared memory.
 __host__ __device__ constexpr int gemv_stages(int ntw) { return ntw == 4 ? 5 : 6; }
@@ -40,6 +60,7 @@ struct GemvParams {
   int bps;           // blocks per split
   int S;             // number of splits
   int ntiles;        // N / 8
+  int cluster;       // 1: the S splits of a column range form one thread-block cluster and reduce over DSMEM
 };
 
 __device__ __forceinline__ void mma_16816(float acc[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -83,7 +104,7 @@ __device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, si
 __device__ __forceinline__ void unpack_codes(uint32_t w, uint32_t out[4]) {
   constexpr uint32_t kLoMask = 0x000f000fu, kHiMask = 0x00f000f0u;
   constexpr uint32_t k1024 = 0x64006400u, k64 = 0x54005400u;
-  const uint32_t w8 = __umulhi(w, 0x01000000u);   // w >> 8 on the multiplier pipe; the logic pipe is the busy one
+  const uint32_t w8 = w >> 8;
   out[0] = h2_sub(lop3_and_or(w, kLoMask, k1024), k1024);
   out[1] = lop3_and_or(w, kHiMask, k64);
   out[2] = h2_sub(lop3_and_or(w8, kLoMask, k1024), k1024);
@@ -94,25 +115,49 @@ __device__ __forceinline__ float small_uint_to_float(uint32_t v) {   // exact fo
   return __uint_as_float(0x4B000000u | v) - 8388608.0f;
 }
 
-// NTW (2 or 4) column tiles per warp, handled as NTW/2 pairs of 16 columns; MT = 8 or 16 rows.
-//
-// Arithmetic per 128-k block b, column n, row m (all fp32 after the tensor core):
-//   y[m,n] += s[b,n] * ( sum_k x[m,k] * code[k,n]  -  z[b,n] * sum_k x[m,k] )
-// The 16 columns of a pair are the rows of the mma A operand (the weights), the
-// activations are the B operand (8 rows of x per mma), so one m16n8k16 covers
-// 16 columns x 16 k.  The two activation sums per block and row (all k, and 64x
-// the k fed as "64 + q") come from the tensor core as well, once per CTA.
 __device__ __forceinline__ void store_out1(uint16_t* y, const uint16_t* bias, size_t row_off, int col, float a) {
   __half h = __float2half_rn(a);
   if (bias != nullptr) h = __hadd(h, __ushort_as_half(bias[col]));
   y[row_off + col] = __half_as_ushort(h);
 }
 
-template <int NTW, int MT>
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float2 ld_dsmem_f2(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+  return v;
+}
+
+// Compute warps form a CW x KW grid (CW * KW = 8): warp (cw, kw) owns NTW column tiles
+// (NTW/2 pairs of 16 columns) and every KW-th 128-k block of this CTA's k-range.  MT = 8 or 16 rows.
+//
+// Arithmetic per 128-k block b, column n, row m (all fp32 after the tensor core):
+//   y[m,n] += s[b,n] * ( sum_k x[m,k] * code[k,n]  -  z[b,n] * sum_k x[m,k] )
+// The 16 columns of a pair are the rows of the mma A operand (the weights), the activations are the
+// B operand (8 rows of x per mma), so one m16n8k16 covers 16 columns x 16 k.  The activation sums
+// per block and row come from the tensor core as well.  Sums are added in a fixed order: a warp's
+// blocks in k order, then the KW warps of a column group in kw order (shared memory), then the
+// grid-level splits in split order (cluster shared memory or the global workspace).
+template <int NTW, int MT, int KW>
 __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams p) {
   static_assert(NTW == 2 || NTW == 4, "column tiles are processed in pairs");
-  constexpr int NP = NTW / 2;    // pairs per warp
-  constexpr int MH = MT / 8;     // row halves
+  static_assert(KW == 1 || KW == 2 || KW == 4 || KW == 8, "KW divides the 8 compute warps");
+  constexpr int NP = NTW / 2;              // pairs per warp
+  constexpr int MH = MT / 8;               // row halves
+  constexpr int CW = kGemvWarps / KW;      // column groups per CTA
+  constexpr int kCtaTiles = CW * NTW;      // 8-column tiles per CTA
+  constexpr int kCtaCols = kCtaTiles * 8;
+  constexpr int kSubWeights = kCtaTiles * 512;            // one block of this CTA's columns
+  constexpr int kSubScaleOff = kSubWeights;               // then kCtaTiles * 8 fp16 scales
+  constexpr int kSubZeroOff = kSubScaleOff + kCtaTiles * 16;
+  constexpr int kSubBytes = kSubWeights + kCtaTiles * 32; // one block: weights, scales, zero words (padded)
+  constexpr int kStageBytes = KW * kSubBytes;             // one pipeline stage: KW consecutive blocks
+  constexpr int ST = gemv_stages(NTW);
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_last;
   __shared__ int s_abort;
@@ -121,47 +166,48 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = blockIdx.y;
-  const int b0 = split * p.bps;
-  const int nb = min(p.bps, p.nblk - b0);
-  constexpr int kCtaTiles = kGemvWarps * NTW;
-  constexpr int kWeightBytes = kCtaTiles * 512;         // one 128-k block of this CTA's columns
-  constexpr int kScaleOff = kWeightBytes;               // then kCtaTiles * 8 fp16 scales
-  constexpr int kZeroOff = kScaleOff + kCtaTiles * 16;  // then kCtaTiles qzeros words
-  constexpr int kStageBytes = kWeightBytes + kCtaTiles * 32;
-  constexpr int ST = gemv_stages(NTW);
+  GEMV_TRACE(0);
   const bool is_producer = (warp == kGemvWarps);
-  // Shared memory: [ring: ST stages of {weights, scales, zeros}][mbarriers]
+  const int cw = warp % CW, kw = (warp / CW) % KW;
+  const int b0 = split * p.bps;
+  const int nb = min(p.bps, p.nblk - b0);        // blocks of this split
+  const int nit = (nb + KW - 1) / KW;            // pipeline iterations (KW blocks each)
+
+  // Shared memory: [ring: ST stages][mbarriers]; the ring is reused for the reductions at the end.
   unsigned char* ring = smem;
-  unsigned char* szsm = ring + ST * kStageBytes;            // [warp][2][32] float2 {scale, zero}
-  const uint32_t bar_base = smem_u32(szsm + kGemvWarps * 2 * 32 * 8);
+  const uint32_t bar_base = smem_u32(ring + ST * kStageBytes);
   auto bar_full = [&](int st) { return bar_base + 8u * st; };
   auto bar_empty = [&](int st) { return bar_base + 8u * (ST + st); };
   volatile int* abort_flag = &s_abort;
 
   const int cta_tile0 = blockIdx.x * kCtaTiles;
-  const int tile0 = cta_tile0 + warp * NTW;
+  const int tile0 = cta_tile0 + cw * NTW;
   const int zcols = p.N >> 3;
-  // The CTA's columns of one block are contiguous in the packed layout: one bulk copy per block.
   const uint32_t valid_tiles = static_cast<uint32_t>(min(kCtaTiles, p.ntiles - cta_tile0));
   const uint4* wsrc = p.wp + (static_cast<size_t>(b0) * p.N) * 4 + static_cast<size_t>(cta_tile0) * 32;
   const size_t block_stride_u4 = static_cast<size_t>(p.N) * 4;
   // qzeros rows can be bulk-copied only if every row segment is 16-byte aligned and sized.
-  const bool zeros_by_copy = (p.N & 31) == 0;
-  const uint32_t stage_tx = valid_tiles * (512u + 16u + (zeros_by_copy ? 4u : 0u));
-  // One stage = the packed weights, scales and zero words of one 128-k block: up to three bulk copies.
-  auto issue_stage = [&](int bl) {
-    const int st = bl % ST;
-    const uint32_t dst = smem_u32(ring + st * kStageBytes);
-    const int grp = (b0 + bl) / p.group_blocks;
-    mbar_expect_tx(bar_full(st), stage_tx);
-    bulk_load(dst, wsrc + static_cast<size_t>(bl) * block_stride_u4, valid_tiles * 512u, bar_full(st));
-    bulk_load(dst + kScaleOff, p.scales + static_cast<size_t>(grp) * p.N + static_cast<size_t>(cta_tile0) * 8,
-              valid_tiles * 16u, bar_full(st));
-    if (zeros_by_copy)
-      bulk_load(dst + kZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u, bar_full(st));
+  const bool zeros_by_copy = ((p.N & 31) == 0) && ((valid_tiles & 3u) == 0u);
+  const uint32_t sub_tx = valid_tiles * (512u + 16u + (zeros_by_copy ? 4u : 0u));
+  // One stage = the packed weights, scales and zero words of KW consecutive blocks.
+  auto issue_stage = [&](int it) {
+    const int st = it % ST;
+    const int nblocks = min(KW, nb - it * KW);
+    mbar_expect_tx(bar_full(st), sub_tx * static_cast<uint32_t>(nblocks));
+    for (int j = 0; j < nblocks; ++j) {
+      const int bl = it * KW + j;
+      const uint32_t dst = smem_u32(ring + st * kStageBytes + j * kSubBytes);
+      const int grp = (b0 + bl) / p.group_blocks;
+      bulk_load(dst, wsrc + static_cast<size_t>(bl) * block_stride_u4, valid_tiles * 512u, bar_full(st));
+      bulk_load(dst + kSubScaleOff, p.scales + static_cast<size_t>(grp) * p.N + static_cast<size_t>(cta_tile0) * 8,
+                valid_tiles * 16u, bar_full(st));
+      if (zeros_by_copy)
+        bulk_load(dst + kSubZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u,
+                  bar_full(st));
+    }
   };
 
-  int issued = 0;   // blocks whose copy has been started (meaningful in the producer thread only)
+  int issued = 0;   // stages whose copies have been started (meaningful in the producer thread only)
   if (is_producer && lane == 0) {
     s_abort = 0;
 #pragma unroll
@@ -172,7 +218,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
     mbar_fence_init();
 #pragma unroll
     for (int st = 0; st < ST; ++st) {
-      if (st < nb) {
+      if (st < nit) {
         issue_stage(st);
         issued = st + 1;
       }
@@ -183,7 +229,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   // (both are no-ops unless the launch asked for programmatic dependent launch).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-
+  GEMV_TRACE(1);
   __syncthreads();   // mbarrier initialisation visible to every warp
 
   // Activations go straight from global memory (L1/L2 resident) to the mma B fragments: lane
@@ -202,13 +248,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         xv[mh][i] = make_uint4(0u, 0u, 0u, 0u);
-        if (xvalid[mh]) xv[mh][i] = __ldg(reinterpret_cast<const uint4*>(xlane[mh] + bl * kBlockK + i * 8));
+        if (xvalid[mh] && bl < nb) xv[mh][i] = __ldg(reinterpret_cast<const uint4*>(xlane[mh] + bl * kBlockK + i * 8));
       }
     }
   };
   constexpr bool kPrefetchX = (MH == 1);   // double-buffer the fragments when registers allow
   uint4 xnext[MH][4];
-  if (!is_producer && kPrefetchX) load_x(0, xnext);
+  if (!is_producer && kPrefetchX) load_x(kw, xnext);
 
   float acc[MH][NP][4];
 #pragma unroll
@@ -219,151 +265,194 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   if (is_producer) {
     // Producer warp: refill a stage as soon as all compute warps have released it.
     if (lane == 0) {
-      for (int bl = ST; bl < nb; ++bl) {
-        if (!mbar_wait(bar_empty(bl % ST), static_cast<uint32_t>(bl / ST - 1) & 1u, abort_flag, 2)) break;
-        issue_stage(bl);
-        issued = bl + 1;
+      for (int it = ST; it < nit; ++it) {
+        if (!mbar_wait(bar_empty(it % ST), static_cast<uint32_t>(it / ST - 1) & 1u, abort_flag, 2)) break;
+        issue_stage(it);
+        issued = it + 1;
       }
     }
-  } else
-  for (int bl = 0; bl < nb; ++bl) {
-    const int st = bl % ST;
-    const uint32_t ph = static_cast<uint32_t>(bl / ST) & 1u;
-    if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) break;
-    uint4 wv[NTW];
-    float sc[NTW], zp[NTW];
-    {
-      const unsigned char* stage = ring + st * kStageBytes;
-      const unsigned char* src = stage + (warp * NTW) * 512 + lane * 16;
+  } else {
+    for (int it = 0; it < nit; ++it) {
+      const int st = it % ST;
+      const uint32_t ph = static_cast<uint32_t>(it / ST) & 1u;
+      const int bl = it * KW + kw;               // this warp's block in this iteration
+      if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) break;
+      if (it == 0) GEMV_TRACE(2);
+      uint4 wv[NTW];
+      float sc[NTW], zp[NTW];
+      if (bl < nb) {
+        const unsigned char* sub = ring + st * kStageBytes + kw * kSubBytes;
+        const unsigned char* src = sub + (cw * NTW) * 512 + lane * 16;
 #pragma unroll
-      for (int t = 0; t < NTW; ++t) wv[t] = *reinterpret_cast<const uint4*>(src + t * 512);
-      // Each lane converts ONE {scale, zero} pair of the warp's 8*NTW columns to fp32 and parks it
-      // in a warp-private slot; every lane then picks up the NTW pairs of its own columns.
-      float2* slot = reinterpret_cast<float2*>(szsm) + (warp * 2 + (bl & 1)) * 32;
-      if (lane < NTW * 8) {
-        const int tl = lane >> 3, cl = lane & 7;
-        const unsigned short sraw = reinterpret_cast<const unsigned short*>(stage + kScaleOff)[(warp * NTW + tl) * 8 + cl];
-        uint32_t zw;
-        if (zeros_by_copy) zw = reinterpret_cast<const uint32_t*>(stage + kZeroOff)[warp * NTW + tl];
-        else zw = __ldg(p.qzeros + static_cast<size_t>((b0 + bl) / p.group_blocks) * zcols +
-                        min(tile0 + tl, p.ntiles - 1));
-        slot[lane] = make_float2(__half2float(__ushort_as_half(sraw)),
-                                 small_uint_to_float((zw >> awq_slot_shift(static_cast<uint32_t>(cl))) & 0xFu));
+        for (int t = 0; t < NTW; ++t) wv[t] = *reinterpret_cast<const uint4*>(src + t * 512);
+        const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(sub + kSubScaleOff) + (cw * NTW) * 8 + g;
+        const uint32_t* zsrc = reinterpret_cast<const uint32_t*>(sub + kSubZeroOff) + cw * NTW;
+#pragma unroll
+        for (int t = 0; t < NTW; ++t) {
+          sc[t] = __half2float(__ushort_as_half(ssrc[t * 8]));
+          uint32_t zw;
+          if (zeros_by_copy) zw = zsrc[t];
+          else zw = __ldg(p.qzeros + static_cast<size_t>((b0 + bl) / p.group_blocks) * zcols +
+                          min(tile0 + t, p.ntiles - 1));
+          zp[t] = small_uint_to_float((zw >> awq_slot_shift(g)) & 0xFu);
+        }
       }
       __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty(st));
+      if (bl >= nb) continue;
+
+      uint4 xv[MH][4];
+      float4 T[MH];
+      if (kPrefetchX) {
 #pragma unroll
-      for (int t = 0; t < NTW; ++t) {
-        const float2 v = slot[t * 8 + g];
-        sc[t] = v.x;
-        zp[t] = v.y;
+        for (int i = 0; i < 4; ++i) xv[0][i] = xnext[0][i];
+        load_x(bl + KW, xnext);
+      } else {
+        load_x(bl, xv);
       }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_empty(st));
-    {
-      {
-        uint4 xv[MH][4];
-        float4 T[MH];
-        if (kPrefetchX) {
+      // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
+      // x[m,k]), rows 8..15 are 0 for the exact-code k and 64 for the k fed as 64 + q (-> H[m]).
 #pragma unroll
-          for (int i = 0; i < 4; ++i) xv[0][i] = xnext[0][i];
-          if (bl + 1 < nb) load_x(bl + 1, xnext);
-        } else {
-          load_x(bl, xv);
+      for (int mh = 0; mh < MH; ++mh) {
+        float SH[4] = {0.f, 0.f, 0.f, 0.f};
+        constexpr uint32_t kOne = 0x3C003C00u, k64h = 0x54005400u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
+          mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
         }
-        // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
-        // x[m,k]), rows 8..15 are 0 for the exact-code k and 64 for the k fed as 64 + q (-> H[m]).
+        T[mh] = make_float4(SH[0], SH[1], SH[2], SH[3]);
+      }
+#pragma unroll
+      for (int q = 0; q < NP; ++q) {
+        const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
+        const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
+        const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
+        // Two independent accumulation chains per block; chain 0 starts from -H so that the
+        // "+64" terms cancel.
+        float blk[MH][2][4];
 #pragma unroll
         for (int mh = 0; mh < MH; ++mh) {
-          float SH[4] = {0.f, 0.f, 0.f, 0.f};
-          constexpr uint32_t kOne = 0x3C003C00u, k64h = 0x54005400u;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
-            mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
-          }
-          T[mh] = make_float4(SH[0], SH[1], SH[2], SH[3]);
+          blk[mh][0][0] = -T[mh].z; blk[mh][0][1] = -T[mh].w; blk[mh][0][2] = -T[mh].z; blk[mh][0][3] = -T[mh].w;
+          blk[mh][1][0] = blk[mh][1][1] = blk[mh][1][2] = blk[mh][1][3] = 0.f;
         }
 #pragma unroll
-        for (int q = 0; q < NP; ++q) {
-          const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
-          const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
-          const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
-          // kChains independent accumulation chains per block keep the tensor-core latency off the
-          // critical path; chain 0 starts from -H so that the "+64" terms cancel.
-          constexpr int kChains = 2;
-          float blk[MH][kChains][4];
+        for (int i = 0; i < 4; ++i) {
+          uint32_t qa[4], qb[4];
+          unpack_codes(wa[i], qa);
+          unpack_codes(wb[i], qb);
 #pragma unroll
           for (int mh = 0; mh < MH; ++mh) {
-            blk[mh][0][0] = -T[mh].z; blk[mh][0][1] = -T[mh].w; blk[mh][0][2] = -T[mh].z; blk[mh][0][3] = -T[mh].w;
-#pragma unroll
-            for (int ch = 1; ch < kChains; ++ch) blk[mh][ch][0] = blk[mh][ch][1] = blk[mh][ch][2] = blk[mh][ch][3] = 0.f;
+            mma_16816(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
+            mma_16816(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
           }
+        }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t qa[4], qb[4];
-            unpack_codes(wa[i], qa);
-            unpack_codes(wb[i], qb);
-#pragma unroll
-            for (int mh = 0; mh < MH; ++mh) {
-              mma_16816(blk[mh][(2 * i) % kChains], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
-              mma_16816(blk[mh][(2 * i + 1) % kChains], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
-            }
-          }
-#pragma unroll
-          for (int mh = 0; mh < MH; ++mh) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (kChains == 4) blk[mh][0][e] = (blk[mh][0][e] + blk[mh][1][e]) + (blk[mh][2][e] + blk[mh][3][e]);
-              else blk[mh][0][e] = blk[mh][0][e] + blk[mh][1][e];
-            }
-          }
-#pragma unroll
-          for (int mh = 0; mh < MH; ++mh) {
-            acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, blk[mh][0][0]), acc[mh][q][0]);
-            acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, blk[mh][0][1]), acc[mh][q][1]);
-            acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, blk[mh][0][2]), acc[mh][q][2]);
-            acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, blk[mh][0][3]), acc[mh][q][3]);
-          }
+        for (int mh = 0; mh < MH; ++mh) {
+          const float d0 = blk[mh][0][0] + blk[mh][1][0], d1 = blk[mh][0][1] + blk[mh][1][1];
+          const float d2 = blk[mh][0][2] + blk[mh][1][2], d3 = blk[mh][0][3] + blk[mh][1][3];
+          acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, d0), acc[mh][q][0]);
+          acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, d1), acc[mh][q][1]);
+          acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, d2), acc[mh][q][2]);
+          acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, d3), acc[mh][q][3]);
         }
       }
     }
   }
+  GEMV_TRACE(3);
   __syncthreads();
   if (s_abort != 0) {
     // A wait expired.  Let this CTA's outstanding copies land (bounded) before shared memory is
     // released, record the failure, and fall through: the output of this call is invalid.
     if (is_producer && lane == 0) {
-      for (int bl = max(0, issued - ST); bl < issued; ++bl)
-        mbar_wait_timed(bar_full(bl % ST), static_cast<uint32_t>(bl / ST) & 1u);
+      for (int it = max(0, issued - ST); it < issued; ++it)
+        mbar_wait_timed(bar_full(it % ST), static_cast<uint32_t>(it / ST) & 1u);
       if (p.status != nullptr) atomicCAS(p.status, 0u, static_cast<unsigned>(s_abort));
     }
+    __syncthreads();
   }
 
-  // ---- epilogue: this thread holds rows m = 8*mh + 2c, +1 of columns n and n + 8 ------------
+  // ---- epilogue -------------------------------------------------------------------------------
+  // A compute thread holds rows m = 8*mh + 2c, +1 of columns n and n + 8 of each of its pairs.
   const bool direct = (p.S == 1);
+  const bool via_cluster = (p.cluster != 0);
+  float* red_k = reinterpret_cast<float*>(ring);                 // [KW][M][kCtaCols]  (KW > 1 only)
+  float* red = red_k + (KW > 1 ? KW * p.M * kCtaCols : 0);       // [M][kCtaCols]      (cluster only)
+  // Where one finished element of this CTA goes: y, the cluster buffer, or the global partials.
+  auto emit = [&](int m, int nl, float v) {
+    const int n = cta_tile0 * 8 + nl;
+    if (n >= p.N) return;
+    if (direct) store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, n, v);
+    else if (via_cluster) red[m * kCtaCols + nl] = v;
+    else __stcg(p.partial + (static_cast<size_t>(split) * p.M + m) * p.N + n, v);
+  };
+  if (!is_producer) {
 #pragma unroll
-  for (int q = 0; q < NP; ++q) {
+    for (int q = 0; q < NP; ++q) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if (is_producer || tile0 + 2 * q + half >= p.ntiles) continue;
-      const int n = (tile0 + 2 * q + half) * 8 + g;
+      for (int half = 0; half < 2; ++half) {
+        const int nl = (cw * NTW + 2 * q + half) * 8 + g;
 #pragma unroll
-      for (int mh = 0; mh < MH; ++mh) {
+        for (int mh = 0; mh < MH; ++mh) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int m = mh * 8 + 2 * c + e;
-          if (m >= p.M) continue;
-          const float v = acc[mh][q][half * 2 + e];
-          if (direct) store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, n, v);
-          else __stcg(p.partial + (static_cast<size_t>(split) * p.M + m) * p.N + n, v);
+          for (int e = 0; e < 2; ++e) {
+            const int m = mh * 8 + 2 * c + e;
+            if (m >= p.M) continue;
+            const float v = acc[mh][q][half * 2 + e];
+            if (KW == 1) emit(m, nl, v);
+            else red_k[(kw * p.M + m) * kCtaCols + nl] = v;
+          }
         }
       }
     }
   }
-  if (direct) return;
+  if (KW > 1) {
+    // The KW warps of a column group add their sums in kw order.
+    __syncthreads();
+    for (int e = tid; e < p.M * kCtaCols; e += kGemvThreads) {
+      float v = red_k[e];
+#pragma unroll
+      for (int j = 1; j < KW; ++j) v += red_k[j * p.M * kCtaCols + e];
+      emit(e / kCtaCols, e % kCtaCols, v);
+    }
+  }
+  if (direct) {
+    GEMV_TRACE(6);
+    return;
+  }
+
+  if (via_cluster) {
+    // The S splits of this column range are the CTAs of one cluster (rank = split).  Each rank
+    // adds, in split order, the S partials of its own slice of the [M x columns] tile, read from
+    // the other CTAs' shared memory, and writes that slice of y.
+    cluster_sync_all();
+    const int ncols = min(kCtaCols, p.N - cta_tile0 * 8);
+    const int total_pairs = (p.M * kCtaCols) >> 1;
+    const int per_rank = (total_pairs + p.S - 1) / p.S;
+    const int first = split * per_rank;
+    const int last_pair = min(first + per_rank, total_pairs);
+    for (int i = first + tid; i < last_pair; i += kGemvThreads) {
+      const int e = 2 * i;
+      const int m = e / kCtaCols, nl = e - m * kCtaCols;
+      if (nl >= ncols) continue;
+      const uint32_t laddr = smem_u32(red + e);
+      float2 v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) v[r] = (r < p.S) ? ld_dsmem_f2(laddr, static_cast<uint32_t>(r)) : make_float2(0.f, 0.f);
+      float2 sum = v[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) {
+        if (r < p.S) { sum.x += v[r].x; sum.y += v[r].y; }
+      }
+      store_out2(p.y, p.bias, static_cast<size_t>(m) * p.N, cta_tile0 * 8 + nl, sum.x, sum.y);
+    }
+    cluster_sync_all();   // nobody leaves while its shared memory may still be read
+    GEMV_TRACE(6);
+    return;
+  }
 
   __threadfence();
+  GEMV_TRACE(4);
   __syncthreads();
   if (tid == 0) {
     const unsigned prev = atomicAdd(&p.counters[blockIdx.x], 1u);
@@ -372,62 +461,92 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
     s_last = last;
   }
   __syncthreads();
+  GEMV_TRACE(5);
   if (!s_last) return;
   __threadfence();
 
   // The last CTA of this column range adds the S partials in split order.
-  const int col0 = blockIdx.x * (kGemvWarps * NTW * 8);
-  const int ncols = min(kGemvWarps * NTW * 8, p.N - col0);
+  const int col0 = cta_tile0 * 8;
+  const int ncols = min(kCtaCols, p.N - col0);
   const int pairs = ncols >> 1;
   for (int i = tid; i < p.M * pairs; i += kGemvThreads) {
     const int row = i / pairs;
     const int col = col0 + 2 * (i - row * pairs);
     const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
     const size_t split_stride = static_cast<size_t>(p.M) * p.N;
-    float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
-    for (int s = 1; s < p.S; ++s) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * split_stride));
-      sum.x += v.x;
-      sum.y += v.y;
+    // Loads are issued eight at a time (independent), the additions stay in split order.
+    float2 sum = make_float2(0.f, 0.f);
+    for (int s0 = 0; s0 < p.S; s0 += 8) {
+      float2 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = (s0 + j < p.S) ? __ldcg(reinterpret_cast<const float2*>(src + (s0 + j) * split_stride))
+                              : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (s0 + j < p.S) {
+          if (s0 + j == 0) sum = v[0];
+          else { sum.x += v[j].x; sum.y += v[j].y; }
+        }
+      }
     }
     store_out2(p.y, p.bias, static_cast<size_t>(row) * p.N, col, sum.x, sum.y);
   }
+  GEMV_TRACE(6);
 }
+
 
 // ---------------------------------------------------------------------------
 // host: decomposition chosen from (K, N) only, never from M.
 // ---------------------------------------------------------------------------
 struct GemvPlan {
-  int ntw;
-  int bps;
-  int S;
-  int ncol;
+  int ntw;   // column tiles per warp (2 or 4)
+  int kw;    // warps sharing a column group and splitting k inside the CTA (1, 2, 4, 8)
+  int bps;   // 128-k blocks per grid-level split
+  int S;     // grid-level splits
+  int ncol;  // CTAs along N
 };
 
+static int plan_ncol(int ntiles, int ntw, int kw) {
+  const int cta_tiles = (kGemvWarps / kw) * ntw;
+  return (ntiles + cta_tiles - 1) / cta_tiles;
+}
+
+// Cost model in microseconds, fitted to in-kernel phase timestamps on B200.  A warp needs about
+// t_blk per 128-k block of its own; the warps of a CTA that split k add their sums through shared
+// memory (cheap); grid-level splits add theirs through a cluster (only worth it for grids of at most
+// one CTA per SM) or through the global workspace, which costs a memory round trip and a serial tail.
 static GemvPlan plan_gemv(int K, int N, int sm_count) {
   const int nblk = K / kBlockK, ntiles = N / 8;
   const int slots = sm_count * 2;
-  // Cost model in microseconds: a CTA streams bps*ntw units of 4 KiB; two CTAs
-  // share one SM's slice of HBM bandwidth (~44 KB/us).
-  const double t_fix = 1.2, t_unit = 0.19, t_red = 0.4, t_red_split = 0.04;
-  GemvPlan best{2, 1, nblk, 0};
+  const double floor_us = (static_cast<double>(K) * N / 2.0) / 6.0e6;   // bytes / (6 TB/s), in us
+  GemvPlan best{2, 1, nblk, 1, plan_ncol(ntiles, 2, 1)};
   double best_t = 1e30;
   const int ntws[2] = {4, 2};
+  const int kws[4] = {8, 4, 2, 1};
   for (int ntw : ntws) {
-    const int ncol = (ntiles + kGemvWarps * ntw - 1) / (kGemvWarps * ntw);
-    int prev_S = -1;
-    for (int bps = kGemvMaxBps; bps >= 1; --bps) {
-      const int S = (nblk + bps - 1) / bps;
-      if (S == prev_S) continue;
-      prev_S = S;
-      const int bps_eff = (nblk + S - 1) / S;  // even split
-      const long long nctas = static_cast<long long>(ncol) * S;
-      const long long waves = (nctas + slots - 1) / slots;
-      double t = waves * (t_fix + bps_eff * ntw * t_unit);
-      if (S > 1) t += t_red + S * t_red_split;
-      if (t < best_t) {
-        best_t = t;
-        best = GemvPlan{ntw, bps_eff, S, ncol};
+    const double t_blk = (ntw == 4) ? 0.85 : 0.50;
+    for (int kw : kws) {
+      const int ncol = plan_ncol(ntiles, ntw, kw);
+      if (ncol > 4095) continue;
+      int prev_S = -1;
+      for (int bps = nblk; bps >= 1; --bps) {
+        const int S = (nblk + bps - 1) / bps;
+        if (S == prev_S) continue;
+        prev_S = S;
+        const int bps_eff = (nblk + S - 1) / S;   // even split
+        if (bps_eff > kGemvMaxBps * kw) continue;
+        const int bpw = (bps_eff + kw - 1) / kw;  // blocks per warp
+        const long long nctas = static_cast<long long>(ncol) * S;
+        const long long waves = (nctas + slots - 1) / slots;
+        double t = waves * (bpw * t_blk);
+        if (t < floor_us) t = floor_us;
+        if (kw > 1) t += 0.3;
+        if (S > 1) t += (S <= 8 && nctas <= sm_count) ? 1.8 : 2.8 + 0.08 * S;
+        if (t < best_t) {
+          best_t = t;
+          best = GemvPlan{ntw, kw, bps_eff, S, ncol};
+        }
       }
     }
   }
@@ -442,14 +561,13 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
 constexpr int kGemvMaxCounters = 4096;
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
-template <int NTW, int MT>
+template <int NTW, int MT, int KW>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream,
                        bool overlap_previous) {
-  const size_t smem = static_cast<size_t>(gemv_stages(NTW)) * kGemvWarps * NTW * (512 + 32) + kGemvWarps * 2 * 32 * 8 +
-                      2 * gemv_stages(NTW) * 8;
+  const size_t smem = static_cast<size_t>(gemv_stages(NTW)) * kGemvWarps * NTW * (512 + 32) + 2 * gemv_stages(NTW) * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
@@ -457,18 +575,30 @@ static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_o
   cfg.blockDim = dim3(kGemvThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (overlap_previous) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.cluster) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = static_cast<unsigned>(plan.S);
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = overlap_previous ? 1 : 0;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT>, p));
+  cfg.numAttrs = na;
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW>, p));
   return AWQ_B200_OK;
 }
 
 int gemv_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
-                  size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_bps, unsigned flags) {
+                  size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_kw, int force_bps,
+                  unsigned flags) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
@@ -480,18 +610,20 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
 
   GemvPlan plan = plan_gemv(K, N, di.sm_count);
-  if (force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
-  if (force_bps >= 1 && force_bps <= kGemvMaxBps) plan.bps = force_bps;
-  // The 16-row variant keeps twice the accumulators: run it with two tiles per warp.  Only the
-  // k-split decides the order of additions, so this cannot change a row's result.
-  if (M > 8 && force_ntw == 0) plan.ntw = 2;
   const int nblk = K / kBlockK, ntiles = N / 8;
+  if (force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
+  if (force_kw == 1 || force_kw == 2 || force_kw == 4 || force_kw == 8) plan.kw = force_kw;
+  if (force_bps >= 1) plan.bps = force_bps < nblk ? force_bps : nblk;
+  if (plan.bps > kGemvMaxBps * plan.kw) plan.bps = kGemvMaxBps * plan.kw;
+  // The 16-row variant keeps twice the accumulators: run it with two tiles per warp.  Only the
+  // k-splits (kw, bps) decide the order of additions, so this cannot change a row's result.
+  if (M > 8 && force_ntw == 0) plan.ntw = 2;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
-  plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
+  plan.ncol = plan_ncol(ntiles, plan.ntw, plan.kw);
   unsigned* p_status = nullptr;
   while (plan.ncol > kGemvMaxCounters - 1 && plan.ntw < 4) {
     plan.ntw *= 2;
-    plan.ncol = (ntiles + kGemvWarps * plan.ntw - 1) / (kGemvWarps * plan.ntw);
+    plan.ncol = plan_ncol(ntiles, plan.ntw, plan.kw);
   }
   if (plan.S > 65535 || plan.ncol > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
   if (workspace && workspace_bytes >= counter_bytes(N) && aligned16(workspace))
@@ -513,7 +645,11 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   p.bps = plan.bps;
   p.S = plan.S;
   p.ntiles = ntiles;
-  if (plan.S > 1) {
+  // A cluster needs its CTAs resident together; beyond one CTA per SM that costs more occupancy than the
+  // shared-memory reduction saves.
+  p.cluster = (plan.S >= 2 && plan.S <= 8 && static_cast<long long>(plan.ncol) * plan.S <= di.sm_count &&
+               !(flags & AWQ_B200_NO_CLUSTER)) ? 1 : 0;
+  if (plan.S > 1 && !p.cluster) {
     const size_t cb = counter_bytes(N);
     const size_t need = cb + static_cast<size_t>(plan.S) * M * N * sizeof(float);
     if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
@@ -524,15 +660,13 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
 
   const bool wide = M > 8;
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
-#define AWQ_GEMV_CASE(NTW_)                                                                  \
-  case NTW_:                                                                                 \
-    return wide ? launch_gemv<NTW_, 16>(p, plan, di.max_smem_optin, stream, overlap)         \
-                : launch_gemv<NTW_, 8>(p, plan, di.max_smem_optin, stream, overlap);
-  switch (plan.ntw) {
-    AWQ_GEMV_CASE(2)
-    AWQ_GEMV_CASE(4)
-    default: return AWQ_B200_ERR_SHAPE;
-  }
+#define AWQ_GEMV_CASE(NTW_, KW_)                                                              \
+  if (plan.ntw == NTW_ && plan.kw == KW_)                                                     \
+    return wide ? launch_gemv<NTW_, 16, KW_>(p, plan, di.max_smem_optin, stream, overlap)     \
+                : launch_gemv<NTW_, 8, KW_>(p, plan, di.max_smem_optin, stream, overlap);
+  AWQ_GEMV_CASE(2, 1) AWQ_GEMV_CASE(2, 2) AWQ_GEMV_CASE(2, 4) AWQ_GEMV_CASE(2, 8)
+  AWQ_GEMV_CASE(4, 1) AWQ_GEMV_CASE(4, 2) AWQ_GEMV_CASE(4, 4) AWQ_GEMV_CASE(4, 8)
+  return AWQ_B200_ERR_SHAPE;
 #undef AWQ_GEMV_CASE
 }
 
@@ -564,27 +698,28 @@ int awq_b200_gemv(const void* x, const void* packed, const void* scales, const i
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                   size_t workspace_bytes, awq_b200_stream_t stream) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0u);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0, 0u);
 }
 
 int awq_b200_gemv_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                      const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                      size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, flags);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0, flags);
 }
 
 // Tuning hook: same as awq_b200_gemv with the decomposition forced
-// (ntw in {2,4} column tiles per warp, bps in 1..16 k-blocks per split; 0 = planner's choice).
+// (ntw in {2,4} column tiles per warp, kw in {1,2,4,8} warps splitting k inside a CTA, bps k-blocks
+// per grid-level split; 0 = planner's choice).
 // The workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N) bytes.
 size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N) { return gemv_workspace_bytes(M, K, N); }
 
 int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                        const void* bias, void* y, int M, int K, int N, int group_size,
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
-                       int bps, unsigned flags) {
+                       int kw, int bps, unsigned flags) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, bps, flags);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, kw, bps, flags);
 }
 
 int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }

@@ -116,17 +116,23 @@ def test_gemv_config1_golden(K_, golden_dir):
 
 
 @pytest.mark.parametrize("ntw", [2, 4])
-@pytest.mark.parametrize("bps", [1, 3, 16])
-def test_gemv_every_decomposition(K_, ntw, bps):
+@pytest.mark.parametrize("kw", [1, 2, 4, 8])
+@pytest.mark.parametrize("bps", [1, 2, 3, 5, 16])
+def test_gemv_every_decomposition(K_, ntw, kw, bps):
     K, N, M = 2048, 1096, 5                       # N/8 = 137 tiles: ragged for every ntw
     qw, qz, sc = tensors(K, N, 128, seed=2)
     x = orc.make_activations(M, K, seed=3)
     ref = orc.linear_forward(x, qw, qz, sc, 128)
     pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
-    y = K_.gemv_plan(dev(x), pw, ntw, bps)
+    y = K_.gemv_plan(dev(x), pw, ntw, bps, kw=kw)
     assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
-    y2 = K_.gemv_plan(dev(x), pw, ntw, bps)      # counters were left clean: second call identical
+    y2 = K_.gemv_plan(dev(x), pw, ntw, bps, kw=kw)      # counters were left clean: second call identical
     assert torch.equal(y, y2)
+    # split partials added over distributed shared memory (cluster) or through the workspace: same bits
+    y3 = K_.gemv_plan(dev(x), pw, ntw, bps, kw=kw, no_cluster=True)
+    y4 = K_.gemv_plan(dev(x), pw, ntw, bps, kw=kw, overlap=True)
+    assert torch.equal(y, y3) and torch.equal(y, y4)
+    assert K_.gemv_status() == 0
 
 
 def test_gemv_row_result_independent_of_batch(K_):
