@@ -512,41 +512,37 @@ static int plan_ncol(int ntiles, int ntw, int kw) {
   return (ntiles + cta_tiles - 1) / cta_tiles;
 }
 
-// Cost model in microseconds, fitted to in-kernel phase timestamps on B200.  A warp needs about
-// t_blk per 128-k block of its own; the warps of a CTA that split k add their sums through shared
-// memory (cheap); grid-level splits add theirs through a cluster (only worth it for grids of at most
-// one CTA per SM) or through the global workspace, which costs a memory round trip and a serial tail.
+// Cost model in microseconds: a least-squares fit to a sweep of (kw, S) over the decode shapes on
+// B200 (148 SMs, two resident CTAs per SM).  Terms: waves of CTAs, the blocks each warp walks
+// through per wave, the way grid-level partials are added (global workspace or cluster), a per-CTA
+// scheduling cost, and the slowdown of a warp when the SM is shared.
 static GemvPlan plan_gemv(int K, int N, int sm_count) {
   const int nblk = K / kBlockK, ntiles = N / 8;
-  const int slots = sm_count * 2;
-  const double floor_us = (static_cast<double>(K) * N / 2.0) / 6.0e6;   // bytes / (6 TB/s), in us
-  GemvPlan best{2, 1, nblk, 1, plan_ncol(ntiles, 2, 1)};
+  const double slots = 2.0 * sm_count;
+  const int ntw = 4;   // the row count may lower this later; it does not affect the order of additions
+  GemvPlan best{ntw, 1, nblk, 1, plan_ncol(ntiles, ntw, 1)};
   double best_t = 1e30;
-  const int ntws[2] = {4, 2};
   const int kws[4] = {8, 4, 2, 1};
-  for (int ntw : ntws) {
-    const double t_blk = (ntw == 4) ? 0.85 : 0.50;
-    for (int kw : kws) {
-      const int ncol = plan_ncol(ntiles, ntw, kw);
-      if (ncol > 4095) continue;
-      int prev_S = -1;
-      for (int bps = nblk; bps >= 1; --bps) {
-        const int S = (nblk + bps - 1) / bps;
-        if (S == prev_S) continue;
-        prev_S = S;
-        const int bps_eff = (nblk + S - 1) / S;   // even split
-        if (bps_eff > kGemvMaxBps * kw) continue;
-        const int bpw = (bps_eff + kw - 1) / kw;  // blocks per warp
-        const long long nctas = static_cast<long long>(ncol) * S;
-        const long long waves = (nctas + slots - 1) / slots;
-        double t = waves * (bpw * t_blk);
-        if (t < floor_us) t = floor_us;
-        if (kw > 1) t += 0.3;
-        if (S > 1) t += (S <= 8 && nctas <= sm_count) ? 1.8 : 2.8 + 0.08 * S;
-        if (t < best_t) {
-          best_t = t;
-          best = GemvPlan{ntw, kw, bps_eff, S, ncol};
-        }
+  for (int kw : kws) {
+    const int ncol = plan_ncol(ntiles, ntw, kw);
+    if (ncol > 4095) continue;
+    int prev_S = -1;
+    for (int bps = nblk; bps >= 1; --bps) {
+      const int S = (nblk + bps - 1) / bps;
+      if (S == prev_S) continue;
+      prev_S = S;
+      const int bps_eff = (nblk + S - 1) / S;   // even split
+      if (bps_eff > kGemvMaxBps * kw) continue;
+      const double bpw = (bps_eff + kw - 1) / kw;  // blocks per warp
+      const double n = static_cast<double>(ncol) * S;
+      const double waves = static_cast<double>(static_cast<long long>((n + slots - 1) / slots));
+      const bool clus = S >= 2 && S <= 8 && n <= sm_count;
+      const bool glob = S > 1 && !clus;
+      const double t = -0.761 + 0.882 * waves + 0.927 * waves * bpw + (glob ? 1.729 : 0.0) + (clus ? 1.253 : 0.0) +
+                       1.918 * (n / slots) + 0.721 * ((n < slots ? n : slots) / slots) * bpw;
+      if (t < best_t) {
+        best_t = t;
+        best = GemvPlan{ntw, kw, bps_eff, S, ncol};
       }
     }
   }
