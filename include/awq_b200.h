@@ -139,6 +139,26 @@ AWQ_B200_API int awq_b200_gemv_ex(const void* x, const void* packed, const void*
                      int group_size, void* workspace, size_t workspace_bytes,
                      awq_b200_stream_t stream, unsigned flags);
 
+/* awq_b200_gemv for hosts that must not allocate device memory while serving: runtimes that size
+ * every device buffer at start-up and then forbid cudaMalloc (fixed-arena inference servers, plugin
+ * hosts that give the plugin no allocator), where there is nobody to hand this call a workspace.
+ * It has no counterpart in the reference.  The split-k scratch lives in a fixed 8 MiB array inside
+ * the library's device image (awq_b200_gemv_static_scratch_bytes()), present on every GPU that
+ * loads the library until the process exits; the caller passes only inputs and the output.
+ *   - Shapes whose planned scratch (awq_b200_gemv_workspace_bytes) exceeds the array return
+ *     AWQ_B200_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on a device resolves the array's device address and zeroes its counters on
+ *     `stream`; make that first call, with the device current, before starting any stream capture.
+ *   - No cudaMalloc / cudaFree or allocating library routine is called, on any call.
+ *   - All calls share the one array and it keeps the previous call's partial sums: calls that can
+ *     overlap on the GPU (different streams) race.  Serialise them, or use awq_b200_gemv with one
+ *     workspace per stream.
+ * Results are bit-identical to awq_b200_gemv. */
+AWQ_B200_API size_t awq_b200_gemv_static_scratch_bytes(void);
+AWQ_B200_API int awq_b200_gemv_static(const void* x, const void* packed, const void* scales,
+                         const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
+                         int group_size, awq_b200_stream_t stream);
+
 /* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {2,4} column
  * tiles per warp, kw in {1,2,4,8} warps that split k inside a CTA, bps k-blocks of
  * 128 per grid-level split; 0 = planner's choice.

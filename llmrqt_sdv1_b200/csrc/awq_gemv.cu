@@ -721,3 +721,54 @@ int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, co
 int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Decode GEMV for callers that cannot allocate device memory.
+// ---------------------------------------------------------------------------
+namespace awq {
+
+// Scratch for the split-k partial sums and their arrival counters, resident in every GPU that loads
+// this library until the process exits.  The name below is a host-side handle only: the device
+// address is looked up per device with cudaGetSymbolAddress and passed to the kernel like any
+// other workspace pointer.
+constexpr size_t kGemvStaticScratchBytes = 8u << 20;   // 8 MiB
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[kGemvStaticScratchBytes];
+
+static void* g_static_scratch_ptr[64];     // per device ordinal; written once, after set-up succeeded
+
+static int static_scratch_for_current_device(cudaStream_t stream, void** out) {
+  int dev = 0;
+  AWQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return AWQ_B200_ERR_TOO_LARGE;
+  void* ptr = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    // First call on this device: resolve the array's address on the device that is current now and
+    // zero the arrival counters (later calls leave them zero themselves).
+    AWQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_gemv_static_scratch));
+    AWQ_CUDA_TRY(cudaMemsetAsync(ptr, 0, counter_bytes(0), stream));
+    __atomic_store_n(&g_static_scratch_ptr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return AWQ_B200_OK;
+}
+
+}  // namespace awq
+
+extern "C" {
+
+size_t awq_b200_gemv_static_scratch_bytes(void) { return kGemvStaticScratchBytes; }
+
+int awq_b200_gemv_static(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                         const void* bias, void* y, int M, int K, int N, int group_size,
+                         awq_b200_stream_t stream) {
+  if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
+  if (int st = check_shape(K, N, group_size)) return st;
+  // Worst case the planner can ask for at this shape; refuse rather than overrun the fixed array.
+  if (awq_b200_gemv_workspace_bytes(M, K, N) > kGemvStaticScratchBytes) return AWQ_B200_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  if (int st = static_scratch_for_current_device(static_cast<cudaStream_t>(stream), &scratch)) return st;
+  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, scratch, kGemvStaticScratchBytes,
+                       static_cast<cudaStream_t>(stream), 0, 0, 0, 0u);
+}
+
+}  // extern "C"

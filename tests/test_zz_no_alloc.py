@@ -1,0 +1,70 @@
+"""The allocation-free decode entry point, called through the C ABI.
+
+Some hosts of this library may not allocate device memory once they are serving (they carve up the
+GPU at start-up and forbid cudaMalloc afterwards, or they load the library as a plugin and give it
+no allocator), so they cannot supply the workspace that `awq_b200_gemv` asks for.
+`awq_b200_gemv_static` keeps its split-k scratch in a fixed array inside the library instead.  This
+test checks that it gives exactly the bits of the ordinary entry point, twice in a row (the array is
+shared and keeps the previous call's contents), and that it refuses shapes that do not fit.
+
+Collected last on purpose: with `-x`, every other test has already run if this one fails.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import awq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def _static_gemv(lib, x, pw, bias=None):
+    y = torch.empty((x.shape[0], pw.N), dtype=torch.float16, device=x.device)
+    st = lib.awq_b200_gemv_static(_ptr(x), _ptr(pw.packed), _ptr(pw.scales), _ptr(pw.qzeros), _ptr(bias), _ptr(y),
+                                  x.shape[0], pw.K, pw.N, pw.group_size,
+                                  torch.cuda.current_stream().cuda_stream)
+    return st, y
+
+
+def test_static_scratch_entry_point_matches_workspace_entry_point():
+    from llmrqt_sdv1_b200 import _lib, kernels
+    lib = _lib.lib
+    torch.cuda.set_device(0)
+    _lib.set_device(0)
+    assert lib.awq_b200_gemv_static_scratch_bytes() == 8 << 20
+    # K = 6144, N = 2048 is planned with several grid-level k-splits, i.e. it really uses the scratch.
+    K, N, G = 6144, 2048, 128
+    qw, qz, sc = orc.make_awq_tensors(K, N, G, seed=11)
+    pw = kernels.make_packed(*(torch.from_numpy(t).cuda() for t in (qw, qz, sc)), G)
+    bias = torch.from_numpy(np.random.default_rng(5).standard_normal(N).astype(np.float16)).cuda()
+    assert lib.awq_b200_gemv_workspace_bytes(4, K, N) > lib.awq_b200_gemv_counter_bytes(N)   # partial sums needed
+    for call, M in enumerate((4, 4, 16, 1)):          # back-to-back calls share the array
+        x = torch.from_numpy(orc.make_activations(M, K, seed=call)).cuda()
+        ref = kernels.gemv(x, pw, bias=bias)
+        st, y = _static_gemv(lib, x, pw, bias)
+        assert st == 0, lib.awq_b200_status_string(st)
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref), f"call {call} (M={M}) differs from awq_b200_gemv"   # same tolerance as elsewhere: bit-equal
+        want = orc.linear_forward(x.cpu().numpy(), qw, qz, sc, G, bias.cpu().numpy())
+        assert orc.max_normalised_error(y.cpu().numpy(), want) <= 2e-3
+    assert kernels.gemv_status() == 0
+
+
+def test_static_scratch_entry_point_rejects_what_does_not_fit():
+    from llmrqt_sdv1_b200 import _lib
+    lib = _lib.lib
+    _lib.set_device(0)
+    # 70B-class gate_up at 16 rows plans more partial sums than the fixed array holds; nothing is launched
+    # (pointers are never dereferenced on this path, so small dummies suffice).
+    d = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    assert lib.awq_b200_gemv_workspace_bytes(16, 8192, 57344) > lib.awq_b200_gemv_static_scratch_bytes()
+    st = lib.awq_b200_gemv_static(d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(), None, d.data_ptr(),
+                                  16, 8192, 57344, 128, None)
+    assert st == _lib.ERR_TOO_LARGE
+    assert b"limit" in lib.awq_b200_status_string(st)
+    assert lib.awq_b200_gemv_static(d.data_ptr(), d.data_ptr(), d.data_ptr(), d.data_ptr(), None, d.data_ptr(),
+                                    17, 2048, 2048, 128, None) == _lib.ERR_SHAPE
