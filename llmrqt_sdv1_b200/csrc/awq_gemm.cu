@@ -396,12 +396,14 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
   EncodeTiledFn encode;
   if (int st = get_encode(&encode)) return st;
 
-  // Row halves per CTA tile: two when that does not cost an extra wave.
+  // Row halves per CTA tile.  A 256-row tile dequantises each weight once for twice the MMA work, so
+  // it keeps the tensor pipe fed where a 128-row tile is limited by the dequant warps; it is chosen
+  // unless the coarser tiles lose more to wave quantisation (tile time ratio measured ~1.7).
   const int ntiles = (N + kBN - 1) / kBN;
   const long long t1 = static_cast<long long>((M + 127) / 128) * ntiles;
   const long long t2 = static_cast<long long>((M + 255) / 256) * ntiles;
   const long long w1 = (t1 + di.sm_count - 1) / di.sm_count, w2 = (t2 + di.sm_count - 1) / di.sm_count;
-  const int MH = (M > 128 && 2 * w2 <= w1) ? 2 : 1;
+  const int MH = (M > 128 && 1.7 * static_cast<double>(w2) <= static_cast<double>(w1)) ? 2 : 1;
 
   CUtensorMap mx, mw;
   {
