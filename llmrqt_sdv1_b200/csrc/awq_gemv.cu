@@ -23,16 +23,19 @@ __device__ __forceinline__ unsigned long long gemv_now() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Slot base depends on N so that two different linears launched back to back land in separate regions.
 #define GEMV_TRACE(i)                                                                              \
   do {                                                                                             \
     if ((threadIdx.x & 31) == 0 && threadIdx.x < 64 && g_gemv_trace)                               \
-      g_gemv_trace[((blockIdx.y * gridDim.x + blockIdx.x) * 2 + (threadIdx.x >> 5)) * 8 + (i)] = gemv_now(); \
+      g_gemv_trace[(((p.N >> 10) & 3) * 8192 + (blockIdx.y * gridDim.x + blockIdx.x) * 2 + (threadIdx.x >> 5)) * 16 + (i)] = gemv_now(); \
   } while (0)
+#define GEMV_TRACE_IT(i) do { if (it == 0) GEMV_TRACE(i); else if (it == 1) GEMV_TRACE((i) + 4); } while (0)
 extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_gemv_trace(void* buf) {
   return static_cast<int>(cudaMemcpyToSymbol(g_gemv_trace, &buf, sizeof(buf)));
 }
 #else
 #define GEMV_TRACE(i) do { } while (0)
+#define GEMV_TRACE_IT(i) do { } while (0)
 #endif
 
 namespace awq {
@@ -278,6 +281,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
       const int bl = it * KW + kw;               // this warp's block in this iteration
       if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) break;
       if (it == 0) GEMV_TRACE(2);
+      GEMV_TRACE_IT(7);
       uint4 wv[NTW];
       float sc[NTW], zp[NTW];
       if (bl < nb) {
@@ -300,6 +304,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty(st));
       if (bl >= nb) continue;
+      GEMV_TRACE_IT(8);
 
       uint4 xv[MH][4];
       float4 T[MH];
@@ -312,29 +317,30 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
       }
       // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
       // x[m,k]), rows 8..15 are 0 for the exact-code k and 64 for the k fed as 64 + q (-> H[m]).
+      // Two short chains; nothing below waits for them until the very end of the block.
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh) {
-        float SH[4] = {0.f, 0.f, 0.f, 0.f};
+        float SH0[4] = {0.f, 0.f, 0.f, 0.f}, SH1[4] = {0.f, 0.f, 0.f, 0.f};
         constexpr uint32_t kOne = 0x3C003C00u, k64h = 0x54005400u;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
-          mma_16816(SH, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
+          mma_16816(SH0, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
+          mma_16816(SH1, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
         }
-        T[mh] = make_float4(SH[0], SH[1], SH[2], SH[3]);
+        T[mh] = make_float4(SH0[0] + SH1[0], SH0[1] + SH1[1], SH0[2] + SH1[2], SH0[3] + SH1[3]);
       }
+      GEMV_TRACE_IT(9);
 #pragma unroll
       for (int q = 0; q < NP; ++q) {
         const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
         const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
         const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
-        // Two independent accumulation chains per block; chain 0 starts from -H so that the
-        // "+64" terms cancel.
+        // Two independent accumulation chains per block, both starting from zero.
         float blk[MH][2][4];
 #pragma unroll
         for (int mh = 0; mh < MH; ++mh) {
-          blk[mh][0][0] = -T[mh].z; blk[mh][0][1] = -T[mh].w; blk[mh][0][2] = -T[mh].z; blk[mh][0][3] = -T[mh].w;
-          blk[mh][1][0] = blk[mh][1][1] = blk[mh][1][2] = blk[mh][1][3] = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) blk[mh][0][e] = blk[mh][1][e] = 0.f;
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -349,14 +355,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
         }
 #pragma unroll
         for (int mh = 0; mh < MH; ++mh) {
-          const float d0 = blk[mh][0][0] + blk[mh][1][0], d1 = blk[mh][0][1] + blk[mh][1][1];
-          const float d2 = blk[mh][0][2] + blk[mh][1][2], d3 = blk[mh][0][3] + blk[mh][1][3];
+          // sum_k x*code = chain0 + chain1 - H   (H removes the "+64" of the odd nibbles)
+          const float d0 = (blk[mh][0][0] + blk[mh][1][0]) - T[mh].z, d1 = (blk[mh][0][1] + blk[mh][1][1]) - T[mh].w;
+          const float d2 = (blk[mh][0][2] + blk[mh][1][2]) - T[mh].z, d3 = (blk[mh][0][3] + blk[mh][1][3]) - T[mh].w;
           acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, d0), acc[mh][q][0]);
           acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, d1), acc[mh][q][1]);
           acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, d2), acc[mh][q][2]);
           acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, d3), acc[mh][q][3]);
         }
       }
+      GEMV_TRACE_IT(10);
     }
   }
   GEMV_TRACE(3);
