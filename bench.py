@@ -450,6 +450,54 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_qwen3_e2e(args, torch, peaks):
+    """BASELINE config 5: random-init Qwen3-1.7B-architecture model, every decoder linear an AWQ W4A16
+    linear on the new kernels, Hugging Face attention; batch 1, 128-token prompt, 128 greedy tokens."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from llmrqt_sdv1_b200 import kernels
+    from llmrqt_sdv1_b200.hf_adapter import quantize_model_, set_impl_mode
+    torch.cuda.set_device(0)
+    # The cuDNN attention backend rebuilds its plan for every new KV length (milliseconds of host time per
+    # decode step); the flash / math backends do not.
+    torch.backends.cuda.enable_cudnn_sdp(False)
+    cfg = Qwen3Config(hidden_size=2048, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=6144, vocab_size=151936, max_position_embeddings=4096,
+                      tie_word_embeddings=False)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = Qwen3ForCausalLM(cfg).half().eval()
+    n_lin = quantize_model_(model, GROUP)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    prompt = torch.randint(0, 151936, (1, 128), device="cuda", generator=g)
+    res = {}
+    with torch.no_grad():
+        for mode in ("auto", "dequant_matmul"):
+            set_impl_mode(model, mode)
+            model.generate(prompt, max_new_tokens=8, do_sample=False)      # warm-up (also repacks once)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter(); out = model(prompt, use_cache=True); torch.cuda.synchronize()
+            prefill_ms = (time.perf_counter() - t0) * 1e3
+            t0 = time.perf_counter()
+            seq = model.generate(prompt, max_new_tokens=128, min_new_tokens=128, do_sample=False)
+            torch.cuda.synchronize()
+            total_ms = (time.perf_counter() - t0) * 1e3
+            res[mode] = {"prefill_ms": prefill_ms, "generate_128_ms": total_ms,
+                         "decode_tok_s": 128.0 / max((total_ms - prefill_ms) * 1e-3, 1e-9), "tokens": seq[0, 128:].tolist()}
+        set_impl_mode(model, "auto"); la = model(res["dequant_matmul_seq"] if False else seq).logits.float()
+        set_impl_mode(model, "dequant_matmul"); lr = model(seq).logits.float()
+    same = sum(int(a == b) for a, b in zip(res["auto"]["tokens"], res["dequant_matmul"]["tokens"]))
+    line = {"metric": "decode tokens/s (config 5)", "value": res["auto"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
+            "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "qwen3_e2e: random-init Qwen3-1.7B architecture, 28 layers, %d AWQ linears, "
+                                   "HF attention, bs=1, 128 prompt + 128 greedy tokens" % n_lin},
+            "auto": {k: v for k, v in res["auto"].items() if k != "tokens"},
+            "dequant_matmul": {k: v for k, v in res["dequant_matmul"].items() if k != "tokens"},
+            "parity": {"greedy_tokens_equal": same, "of": 128,
+                       "teacher_forced_logit_err": float((la - lr).abs().max() / lr.abs().max())},
+            "status": {"gemm": kernels.gemm_status(), "gemv": kernels.gemv_status()}}
+    print(json.dumps(line), flush=True)
+
+
 def run_profile_case(args, torch):
     """Small, self-terminating cases for `ncu` captures (a few launches, a few hundred MB)."""
     from llmrqt_sdv1_b200 import kernels, quantize
@@ -487,7 +535,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp"])
+    ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp", "qwen3_e2e"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "gemm", "gemm_large"],
@@ -513,7 +561,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        if args.workload == "qwen3_decode":
+        if args.workload == "qwen3_e2e":
+            if rank == 0:
+                run_qwen3_e2e(args, torch, peaks)
+        elif args.workload == "qwen3_decode":
             if rank == 0:
                 run_qwen3_decode(args, torch, peaks)
         else:
