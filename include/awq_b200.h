@@ -160,8 +160,9 @@ AWQ_B200_API int awq_b200_gemv_static(const void* x, const void* packed, const v
                          int group_size, awq_b200_stream_t stream);
 
 /* Tuning hook: awq_b200_gemv with the decomposition forced: ntw in {2,4} column
- * tiles per warp, kw in {1,2,4,8} warps that split k inside a CTA, bps k-blocks of
- * 128 per grid-level split; 0 = planner's choice.
+ * tiles per warp, kw warps that split k inside a CTA (1,2,4,8 with 8 compute warps per CTA;
+ * 104, 108, 116 select 16 compute warps with kw = 4, 8, 16), bps k-blocks of 128 per
+ * grid-level split; 0 = planner's choice.
  * Its workspace must hold awq_b200_gemv_workspace_bytes_max(M, K, N).  No
  * reference counterpart. */
 AWQ_B200_API size_t awq_b200_gemv_workspace_bytes_max(int M, int K, int N);

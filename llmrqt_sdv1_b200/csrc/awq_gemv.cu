@@ -40,12 +40,11 @@ extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_gemv_tr
 
 namespace awq {
 
-constexpr int kGemvWarps = 8;                       // compute warps; one more warp only issues bulk copies
-constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
+// A CTA has W compute warps (8 or 16) plus one warp that only issues bulk copies.
 constexpr int kGemvMaxBps = 32;   // per warp  // 128-k blocks per split (bounds the activation slice in smem)
 constexpr int kGemvMaxRows = 16;
 // 128-k blocks in flight per CTA (bulk copies): 5 x 17 KiB or 6 x 8.5 KiB of shared memory.
-__host__ __device__ constexpr int gemv_stages(int ntw) { return ntw == 4 ? 5 : 6; }
+__host__ __device__ constexpr int gemv_stages(int ntw, int w) { return w == 16 ? (ntw == 4 ? 3 : 4) : (ntw == 4 ? 5 : 6); }
 
 struct GemvParams {
   const uint16_t* x;
@@ -136,7 +135,7 @@ __device__ __forceinline__ float2 ld_dsmem_f2(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-// Compute warps form a CW x KW grid (CW * KW = 8): warp (cw, kw) owns NTW column tiles
+// The W compute warps form a CW x KW grid (CW * KW = W): warp (cw, kw) owns NTW column tiles
 // (NTW/2 pairs of 16 columns) and every KW-th 128-k block of this CTA's k-range.  MT = 8 or 16 rows.
 //
 // Arithmetic per 128-k block b, column n, row m (all fp32 after the tensor core):
@@ -146,10 +145,13 @@ __device__ __forceinline__ float2 ld_dsmem_f2(uint32_t local_addr, uint32_t rank
 // per block and row come from the tensor core as well.  Sums are added in a fixed order: a warp's
 // blocks in k order, then the KW warps of a column group in kw order (shared memory), then the
 // grid-level splits in split order (cluster shared memory or the global workspace).
-template <int NTW, int MT, int KW>
-__global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams p) {
+template <int NTW, int MT, int KW, int W>
+__global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(const GemvParams p) {
+  constexpr int kGemvWarps = W;
+  constexpr int kGemvThreads = (W + 1) * 32;
   static_assert(NTW == 2 || NTW == 4, "column tiles are processed in pairs");
-  static_assert(KW == 1 || KW == 2 || KW == 4 || KW == 8, "KW divides the 8 compute warps");
+  static_assert(W == 8 || W == 16, "8 or 16 compute warps");
+  static_assert(KW >= 1 && KW <= W && (W % KW) == 0 && (KW & (KW - 1)) == 0, "KW divides the compute warps");
   constexpr int NP = NTW / 2;              // pairs per warp
   constexpr int MH = MT / 8;               // row halves
   constexpr int CW = kGemvWarps / KW;      // column groups per CTA
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
   constexpr int kSubZeroOff = kSubScaleOff + kCtaTiles * 16;
   constexpr int kSubBytes = kSubWeights + kCtaTiles * 32; // one block: weights, scales, zero words (padded)
   constexpr int kStageBytes = KW * kSubBytes;             // one pipeline stage: KW consecutive blocks
-  constexpr int ST = gemv_stages(NTW);
+  constexpr int ST = gemv_stages(NTW, W);
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int s_last;
   __shared__ int s_abort;
@@ -509,14 +511,15 @@ __global__ void __launch_bounds__(kGemvThreads, 2) gemv_kernel(const GemvParams 
 // ---------------------------------------------------------------------------
 struct GemvPlan {
   int ntw;   // column tiles per warp (2 or 4)
-  int kw;    // warps sharing a column group and splitting k inside the CTA (1, 2, 4, 8)
+  int w;     // compute warps per CTA (8 or 16)
+  int kw;    // warps sharing a column group and splitting k inside the CTA (divides w)
   int bps;   // 128-k blocks per grid-level split
   int S;     // grid-level splits
   int ncol;  // CTAs along N
 };
 
-static int plan_ncol(int ntiles, int ntw, int kw) {
-  const int cta_tiles = (kGemvWarps / kw) * ntw;
+static int plan_ncol(int ntiles, int ntw, int w, int kw) {
+  const int cta_tiles = (w / kw) * ntw;
   return (ntiles + cta_tiles - 1) / cta_tiles;
 }
 
@@ -524,33 +527,40 @@ static int plan_ncol(int ntiles, int ntw, int kw) {
 // B200 (148 SMs, two resident CTAs per SM).  Terms: waves of CTAs, the blocks each warp walks
 // through per wave, the way grid-level partials are added (global workspace or cluster), a per-CTA
 // scheduling cost, and the slowdown of a warp when the SM is shared.
+// Fitted coefficients (microseconds); see the comment above.
+static const double kPlanC[8] = {-0.761, 0.882, 0.927, 1.729, 1.253, 1.918, 0.721, 0.45};
+
 static GemvPlan plan_gemv(int K, int N, int sm_count) {
   const int nblk = K / kBlockK, ntiles = N / 8;
-  const double slots = 2.0 * sm_count;
   const int ntw = 4;   // the row count may lower this later; it does not affect the order of additions
-  GemvPlan best{ntw, 1, nblk, 1, plan_ncol(ntiles, ntw, 1)};
+  GemvPlan best{ntw, 8, 1, nblk, 1, plan_ncol(ntiles, ntw, 8, 1)};
   double best_t = 1e30;
-  const int kws[4] = {8, 4, 2, 1};
-  for (int kw : kws) {
-    const int ncol = plan_ncol(ntiles, ntw, kw);
-    if (ncol > 4095) continue;
-    int prev_S = -1;
-    for (int bps = nblk; bps >= 1; --bps) {
-      const int S = (nblk + bps - 1) / bps;
-      if (S == prev_S) continue;
-      prev_S = S;
-      const int bps_eff = (nblk + S - 1) / S;   // even split
-      if (bps_eff > kGemvMaxBps * kw) continue;
-      const double bpw = (bps_eff + kw - 1) / kw;  // blocks per warp
-      const double n = static_cast<double>(ncol) * S;
-      const double waves = static_cast<double>(static_cast<long long>((n + slots - 1) / slots));
-      const bool clus = S >= 2 && S <= 8 && n <= sm_count;
-      const bool glob = S > 1 && !clus;
-      const double t = -0.761 + 0.882 * waves + 0.927 * waves * bpw + (glob ? 1.729 : 0.0) + (clus ? 1.253 : 0.0) +
-                       1.918 * (n / slots) + 0.721 * ((n < slots ? n : slots) / slots) * bpw;
-      if (t < best_t) {
-        best_t = t;
-        best = GemvPlan{ntw, kw, bps_eff, S, ncol};
+  const int ws[2] = {8, 16};
+  for (int w : ws) {
+    if (w == 16 && nblk > 16) continue;   // 16 warps only paid off for short k in the sweep
+    const double slots = (w == 8 ? 2.0 : 1.0) * sm_count;   // resident CTAs
+    for (int kw = w; kw >= (w == 8 ? 1 : 4); kw >>= 1) {
+      const int ncol = plan_ncol(ntiles, ntw, w, kw);
+      if (ncol > 4095) continue;
+      int prev_S = -1;
+      for (int bps = nblk; bps >= 1; --bps) {
+        const int S = (nblk + bps - 1) / bps;
+        if (S == prev_S) continue;
+        prev_S = S;
+        const int bps_eff = (nblk + S - 1) / S;   // even split
+        if (bps_eff > kGemvMaxBps * kw) continue;
+        const double bpw = (bps_eff + kw - 1) / kw;  // blocks per warp
+        const double n = static_cast<double>(ncol) * S;
+        const double waves = static_cast<double>(static_cast<long long>((n + slots - 1) / slots));
+        const bool clus = S >= 2 && S <= 8 && n <= sm_count;
+        const bool glob = S > 1 && !clus;
+        const double t = kPlanC[0] + kPlanC[1] * waves + kPlanC[2] * waves * bpw + (glob ? kPlanC[3] : 0.0) +
+                         (clus ? kPlanC[4] : 0.0) + kPlanC[5] * (n / slots) +
+                         kPlanC[6] * ((n < slots ? n : slots) / slots) * bpw + (w == 16 ? kPlanC[7] : 0.0);
+        if (t < best_t) {
+          best_t = t;
+          best = GemvPlan{ntw, w, kw, bps_eff, S, ncol};
+        }
       }
     }
   }
@@ -565,18 +575,18 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
 constexpr int kGemvMaxCounters = 4096;
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
-template <int NTW, int MT, int KW>
+template <int NTW, int MT, int KW, int W>
 static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream,
                        bool overlap_previous) {
-  const size_t smem = static_cast<size_t>(gemv_stages(NTW)) * kGemvWarps * NTW * (512 + 32) + 2 * gemv_stages(NTW) * 8;
+  const size_t smem = static_cast<size_t>(gemv_stages(NTW, W)) * W * NTW * (512 + 32) + 2 * gemv_stages(NTW, W) * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan.ncol, plan.S);
-  cfg.blockDim = dim3(kGemvThreads);
+  cfg.blockDim = dim3((W + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -595,14 +605,14 @@ static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_o
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW>, p));
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW, W>, p));
   return AWQ_B200_OK;
 }
 
 int gemv_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_kw, int force_bps,
-                  unsigned flags) {
+                  unsigned flags, int force_w = 0) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
@@ -616,18 +626,21 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   GemvPlan plan = plan_gemv(K, N, di.sm_count);
   const int nblk = K / kBlockK, ntiles = N / 8;
   if (force_ntw == 2 || force_ntw == 4) plan.ntw = force_ntw;
-  if (force_kw == 1 || force_kw == 2 || force_kw == 4 || force_kw == 8) plan.kw = force_kw;
+  if (force_w == 8 || force_w == 16) plan.w = force_w;
+  if (force_kw >= 1 && force_kw <= plan.w && (plan.w % force_kw) == 0) plan.kw = force_kw;
+  if (plan.kw > plan.w) plan.kw = plan.w;
+  if (plan.w == 16 && plan.kw < 4) plan.kw = 4;
   if (force_bps >= 1) plan.bps = force_bps < nblk ? force_bps : nblk;
   if (plan.bps > kGemvMaxBps * plan.kw) plan.bps = kGemvMaxBps * plan.kw;
   // The 16-row variant keeps twice the accumulators: run it with two tiles per warp.  Only the
   // k-splits (kw, bps) decide the order of additions, so this cannot change a row's result.
   if (M > 8 && force_ntw == 0) plan.ntw = 2;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
-  plan.ncol = plan_ncol(ntiles, plan.ntw, plan.kw);
+  plan.ncol = plan_ncol(ntiles, plan.ntw, plan.w, plan.kw);
   unsigned* p_status = nullptr;
   while (plan.ncol > kGemvMaxCounters - 1 && plan.ntw < 4) {
     plan.ntw *= 2;
-    plan.ncol = plan_ncol(ntiles, plan.ntw, plan.kw);
+    plan.ncol = plan_ncol(ntiles, plan.ntw, plan.w, plan.kw);
   }
   if (plan.S > 65535 || plan.ncol > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
   if (workspace && workspace_bytes >= counter_bytes(N) && aligned16(workspace))
@@ -664,12 +677,14 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
 
   const bool wide = M > 8;
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
-#define AWQ_GEMV_CASE(NTW_, KW_)                                                              \
-  if (plan.ntw == NTW_ && plan.kw == KW_)                                                     \
-    return wide ? launch_gemv<NTW_, 16, KW_>(p, plan, di.max_smem_optin, stream, overlap)     \
-                : launch_gemv<NTW_, 8, KW_>(p, plan, di.max_smem_optin, stream, overlap);
-  AWQ_GEMV_CASE(2, 1) AWQ_GEMV_CASE(2, 2) AWQ_GEMV_CASE(2, 4) AWQ_GEMV_CASE(2, 8)
-  AWQ_GEMV_CASE(4, 1) AWQ_GEMV_CASE(4, 2) AWQ_GEMV_CASE(4, 4) AWQ_GEMV_CASE(4, 8)
+#define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                             \
+  if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                        \
+    return wide ? launch_gemv<NTW_, 16, KW_, W_>(p, plan, di.max_smem_optin, stream, overlap)    \
+                : launch_gemv<NTW_, 8, KW_, W_>(p, plan, di.max_smem_optin, stream, overlap);
+  AWQ_GEMV_CASE(2, 1, 8) AWQ_GEMV_CASE(2, 2, 8) AWQ_GEMV_CASE(2, 4, 8) AWQ_GEMV_CASE(2, 8, 8)
+  AWQ_GEMV_CASE(4, 1, 8) AWQ_GEMV_CASE(4, 2, 8) AWQ_GEMV_CASE(4, 4, 8) AWQ_GEMV_CASE(4, 8, 8)
+  AWQ_GEMV_CASE(2, 4, 16) AWQ_GEMV_CASE(2, 8, 16) AWQ_GEMV_CASE(2, 16, 16)
+  AWQ_GEMV_CASE(4, 4, 16) AWQ_GEMV_CASE(4, 8, 16) AWQ_GEMV_CASE(4, 16, 16)
   return AWQ_B200_ERR_SHAPE;
 #undef AWQ_GEMV_CASE
 }
@@ -723,7 +738,8 @@ int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, co
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
                        int kw, int bps, unsigned flags) {
   return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, kw, bps, flags);
+                       workspace_bytes, static_cast<cudaStream_t>(stream), ntw, kw % 100, bps, flags,
+                       kw >= 100 ? 16 : (kw > 0 ? 8 : 0));
 }
 
 int awq_b200_gemv_max_rows(void) { return kGemvMaxRows; }

@@ -116,7 +116,7 @@ def test_gemv_config1_golden(K_, golden_dir):
 
 
 @pytest.mark.parametrize("ntw", [2, 4])
-@pytest.mark.parametrize("kw", [1, 2, 4, 8])
+@pytest.mark.parametrize("kw", [1, 2, 4, 8, 104, 108, 116])   # 1xx = 16 compute warps per CTA
 @pytest.mark.parametrize("bps", [1, 2, 3, 5, 16])
 def test_gemv_every_decomposition(K_, ntw, kw, bps):
     K, N, M = 2048, 1096, 5                       # N/8 = 137 tiles: ragged for every ntw
