@@ -6,7 +6,7 @@
 //               swizzle) and the packed int4 weights [256 columns x 32 bytes].
 //   warp 1      allocates tensor memory and issues tcgen05.mma (M=128, N=256,
 //               K=16, fp16 inputs, fp32 accumulators in TMEM), one thread.
-//   warps 2-9   read the packed nibbles from shared memory, dequantise them to
+//   warps 2-17  read the packed nibbles from shared memory, dequantise them to
 //               the exact reference fp16 weight and store them as the K-major,
 //               128-byte-swizzled B operand; after the last k-stage the same
 //               warps drain the accumulators (tcgen05.ld), round to fp16, add
@@ -21,8 +21,8 @@
 
 namespace awq {
 
-constexpr int kGemmThreads = 320;
-constexpr int kDequantThreads = 256;
+constexpr int kDequantThreads = 512;              // 16 warps: dequantise, then drain the accumulators
+constexpr int kGemmThreads = 64 + kDequantThreads;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kABytesHalf = 128 * kBK * 2;   // 16 KiB: 128 rows x 128 B
@@ -30,10 +30,14 @@ constexpr int kBBytes = kBN * kBK * 2;       // 32 KiB: 256 columns x 128 B
 constexpr int kRawBytes = kBN * (kBK / 2);   // 8 KiB: 256 columns x 32 B of nibbles
 
 template <int MH> struct GemmCfg {
-  static constexpr int kStages = (MH == 2) ? 3 : 4;
-  static constexpr int kStageBytes = MH * kABytesHalf + kBBytes + kRawBytes;
+  // Two rings.  The TMA ring (activations + packed weights) is deep enough to cover the copy
+  // latency; the B ring (dequantised operand) only has to let the dequantisation of stage s+1
+  // overlap the MMAs of stage s.
+  static constexpr int kTmaStages = (MH == 2) ? 4 : 5;
+  static constexpr int kBStages = (MH == 2) ? 2 : 3;
+  static constexpr int kTmaStageBytes = MH * kABytesHalf + kRawBytes;
   static constexpr int kTmemCols = 256 * MH;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kTmaStages * kTmaStageBytes + kBStages * kBBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct GemmParams {
@@ -118,33 +122,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
             const GemmParams p) {
   using Cfg = GemmCfg<MH>;
-  constexpr int kStages = Cfg::kStages;
+  constexpr int NT = Cfg::kTmaStages, NB = Cfg::kBStages;
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
   __shared__ uint32_t s_tmem_base;
 
-  // 1024-byte aligned carve-up: [stage: A halves | B | raw] x kStages, then barriers.
+  // 1024-byte aligned carve-up: [B operand] x NB, [A halves | raw] x NT, then barriers.
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  auto a_addr = [&](int st, int h) { return base + st * Cfg::kStageBytes + h * kABytesHalf; };
-  auto b_addr = [&](int st) { return base + st * Cfg::kStageBytes + MH * kABytesHalf; };
-  auto raw_addr = [&](int st) { return base + st * Cfg::kStageBytes + MH * kABytesHalf + kBBytes; };
-  const uint32_t bar_base = base + kStages * Cfg::kStageBytes;
-  auto bar_full_tma = [&](int st) { return bar_base + 8u * st; };
-  auto bar_full_b = [&](int st) { return bar_base + 8u * (kStages + st); };
-  auto bar_empty = [&](int st) { return bar_base + 8u * (2 * kStages + st); };
-  const uint32_t bar_acc_full = bar_base + 8u * (3 * kStages);
-  const uint32_t bar_acc_empty = bar_base + 8u * (3 * kStages + 1);
+  const uint32_t tma_base = base + NB * kBBytes;
+  auto b_addr = [&](int b) { return base + b * kBBytes; };
+  auto a_addr = [&](int t, int h) { return tma_base + t * Cfg::kTmaStageBytes + h * kABytesHalf; };
+  auto raw_addr = [&](int t) { return tma_base + t * Cfg::kTmaStageBytes + MH * kABytesHalf; };
+  const uint32_t bar_base = tma_base + NT * Cfg::kTmaStageBytes;
+  auto bar_full_tma = [&](int t) { return bar_base + 8u * t; };
+  auto bar_empty_tma = [&](int t) { return bar_base + 8u * (NT + t); };   // MMA commit + 8 dequant warps
+  auto bar_full_b = [&](int b) { return bar_base + 8u * (2 * NT + b); };
+  auto bar_empty_b = [&](int b) { return bar_base + 8u * (2 * NT + NB + b); };
+  const uint32_t bar_acc_full = bar_base + 8u * (2 * NT + 2 * NB);
+  const uint32_t bar_acc_empty = bar_base + 8u * (2 * NT + 2 * NB + 1);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
     s_abort = 0;
-    for (int st = 0; st < kStages; ++st) {
-      mbar_init(bar_full_tma(st), 1);
-      mbar_init(bar_full_b(st), kDequantThreads / 32);
-      mbar_init(bar_empty(st), 1);
+    for (int t = 0; t < NT; ++t) {
+      mbar_init(bar_full_tma(t), 1);
+      mbar_init(bar_empty_tma(t), 1 + kDequantThreads / 32);
+    }
+    for (int b = 0; b < NB; ++b) {
+      mbar_init(bar_full_b(b), kDequantThreads / 32);
+      mbar_init(bar_empty_b(b), 1);
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, kDequantThreads / 32);
@@ -176,9 +185,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         const int m0 = (tile % p.mtiles) * (128 * MH);
         const int n0 = (tile / p.mtiles) * kBN;
         for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int st = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
-          if (!mbar_wait(bar_empty(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+          const int st = it % NT;
+          const uint32_t ph = (it / NT) & 1u;
+          if (!mbar_wait(bar_empty_tma(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
           mbar_expect_tx(bar_full_tma(st), MH * kABytesHalf + kRawBytes);
 #pragma unroll
           for (int h = 0; h < MH; ++h) tma_load_2d(a_addr(st, h), &map_x, ks * kBK, m0 + h * 128, bar_full_tma(st));
@@ -195,34 +204,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
         tcgen05_fence_after();
         for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int st = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+          const int st = it % NT, sb = it % NB;
+          const uint32_t ph = (it / NT) & 1u, phb = (it / NB) & 1u;
           if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 3)) { ok = false; break; }
-          if (!mbar_wait(bar_full_b(st), ph, abort_flag, 4)) { ok = false; break; }
+          if (!mbar_wait(bar_full_b(sb), phb, abort_flag, 4)) { ok = false; break; }
           tcgen05_fence_after();
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {
               const uint64_t da = make_sw128_desc(a_addr(st, h) + kk * 32);
-              const uint64_t db = make_sw128_desc(b_addr(st) + kk * 32);
+              const uint64_t db = make_sw128_desc(b_addr(sb) + kk * 32);
               tcgen05_mma_f16(tmem_base + h * 256, da, db, kInstrDesc, (ks | kk) != 0 ? 1u : 0u);
             }
           }
-          tcgen05_commit(bar_empty(st));   // stage reusable once these MMAs have read it
+          tcgen05_commit(bar_empty_tma(st));   // activations of this stage consumed
+          tcgen05_commit(bar_empty_b(sb));     // B buffer reusable
         }
         if (ok) tcgen05_commit(bar_acc_full);
       }
     }
   } else {
     // ---------------------- dequantise, then drain accumulators ---------------
-    const int id = tid - 64;                 // 0..255
-    const int dq_warp = id >> 5;             // 0..7
-    const int col_local = id >> 1;           // 0..127 (second pass: +128)
+    const int id = tid - 64;                 // 0..511
+    const int dq_warp = id >> 5;             // 0..15
+    const int col_local = id >> 1;           // 0..255: the column this thread dequantises
     const int hh = id & 1;                   // which 16-byte half of the column's 32 raw bytes
     const int lane_q = warp & 3;             // TMEM lane quarter this warp may read
-    const int col_half = dq_warp >> 2;       // epilogue: columns [128*col_half, +128)
-    // B-operand byte offsets of the four 16-byte chunks this thread writes per pass
+    const int col_quarter = dq_warp >> 2;    // epilogue: columns [64*col_quarter, +64)
+    // B-operand byte offsets of the four 16-byte chunks this thread writes per stage
     uint32_t boff[4];
     {
       const int r8 = col_local & 7;
@@ -236,31 +246,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
       const int m0 = (tile % p.mtiles) * (128 * MH);
       const int n0 = (tile / p.mtiles) * kBN;
-      const int nA = n0 + col_local, nB = nA + 128;
-      const bool vA = nA < p.N, vB = nB < p.N;
-      const uint32_t zshift = awq_slot_shift(static_cast<uint32_t>(nA & 7));  // nB & 7 == nA & 7
+      const int nA = n0 + col_local;
+      const bool vA = nA < p.N;
+      const uint32_t zshift = awq_slot_shift(static_cast<uint32_t>(nA & 7));
 
-      auto load_sz = [&](int ks, uint32_t& sA, uint32_t& sB, uint32_t& zA, uint32_t& zB) {
+      auto load_sz = [&](int ks, uint32_t& sA, uint32_t& zA) {
         const int grp = (ks * kBK) / p.group_size;
         sA = vA ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + nA) : 0u;
-        sB = vB ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + nB) : 0u;
         zA = vA ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (nA >> 3)) : 0u;
-        zB = vB ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (nB >> 3)) : 0u;
       };
-      uint32_t sA, sB, zA, zB, sA_n = 0, sB_n = 0, zA_n = 0, zB_n = 0;
-      load_sz(0, sA, sB, zA, zB);
+      uint32_t sA, zA, sA_n = 0, zA_n = 0;
+      load_sz(0, sA, zA);
 
       for (int ks = 0; ks < nks; ++ks, ++it) {
-        const int st = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
+        const int st = it % NT, sb = it % NB;
+        const uint32_t ph = (it / NT) & 1u, phb = (it / NB) & 1u;
         const bool group_changes = (ks + 1 < nks) && (((ks + 1) * kBK) % p.group_size == 0);
-        if (group_changes) load_sz(ks + 1, sA_n, sB_n, zA_n, zB_n);
+        if (group_changes) load_sz(ks + 1, sA_n, zA_n);
         if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 5)) { ok = false; break; }
 
         const unsigned char* raw = base_ptr + (raw_addr(st) - base);
-        unsigned char* bst = base_ptr + (b_addr(st) - base);
+        unsigned char* bst = base_ptr + (b_addr(sb) - base);
         const uint4 r0 = *reinterpret_cast<const uint4*>(raw + id * 16);
-        const uint4 r1 = *reinterpret_cast<const uint4*>(raw + 4096 + id * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty_tma(st));          // packed weights of this stage are in registers
+        if (!mbar_wait(bar_empty_b(sb), phb ^ 1u, abort_flag, 7)) { ok = false; break; }
         {
           const ZeroPair zp = make_zero_pair((zA >> zshift) & 0xFu);
           const uint32_t s2 = sA * 0x00010001u;
@@ -272,21 +282,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             *reinterpret_cast<uint4*>(bst + boff[i]) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
-        {
-          const ZeroPair zp = make_zero_pair((zB >> zshift) & 0xFu);
-          const uint32_t s2 = sB * 0x00010001u;
-          const uint32_t w[4] = {r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t o[4];
-            dequant_word(w[i], zp, s2, o);
-            *reinterpret_cast<uint4*>(bst + 16384 + boff[i]) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        }
         fence_proxy_async();   // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_b(st));
-        if (group_changes) { sA = sA_n; sB = sB_n; zA = zA_n; zB = zB_n; }
+        if (lane == 0) mbar_arrive(bar_full_b(sb));
+        if (group_changes) { sA = sA_n; zA = zA_n; }
       }
       if (!ok) break;
 
@@ -298,11 +297,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       for (int h = 0; h < MH; ++h) {
         const int row = m0 + h * 128 + lane_q * 32 + lane;
 #pragma unroll 1
-        for (int chunk = 0; chunk < 4; ++chunk) {
-          const int col0 = n0 + col_half * 128 + chunk * 32;
+        for (int chunk = 0; chunk < 2; ++chunk) {
+          const int col0 = n0 + col_quarter * 64 + chunk * 32;
           uint32_t v[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_q * 32) << 16) +
-                                 static_cast<uint32_t>(h * 256 + col_half * 128 + chunk * 32);
+                                 static_cast<uint32_t>(h * 256 + col_quarter * 64 + chunk * 32);
           tcgen05_ld_32x32b_x32(taddr, v);   // whole warp, even if its rows are past M
           tcgen05_wait_ld();
           if (row < p.M) {
