@@ -176,6 +176,8 @@ AWQ_B200_API int awq_b200_gemv_plan(const void* x, const void* packed, const voi
 AWQ_B200_API size_t awq_b200_gemm_workspace_bytes(int M, int K, int N);
 
 /* Y[M, N] = X[M, K] . W (+ bias) with fp32 accumulation in tensor memory.
+ * Two tcgen05 kernels stand behind it (dequantised weights staged in shared memory as the B operand,
+ * or written to tensor memory as the A operand); the faster tile shape is picked per (M, N).
  * Replaces awq_gemm / awq_gemm_db / awq_gemm_cutlass
  * (LLMQRT/runtime_refact/csrc/awq/gemm.cu:407-467, gemm_db.cu:670-732,
  * gemm_cutlass.cu:314-374); the reference's split_k_iters argument has no
@@ -183,6 +185,25 @@ AWQ_B200_API size_t awq_b200_gemm_workspace_bytes(int M, int K, int N);
 AWQ_B200_API int awq_b200_gemm(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                   const void* bias, void* y, int M, int K, int N, int group_size,
                   void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* Tuning hook: awq_b200_gemm restricted to the kernel that stages the dequantised weights in
+ * shared memory (awq_b200_gemm itself picks per shape between that kernel and awq_b200_gemm_wtm;
+ * both produce identical bits). */
+AWQ_B200_API int awq_b200_gemm_smem(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                       const void* bias, void* y, int M, int K, int N, int group_size,
+                       void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* Same contract as awq_b200_gemm; the dequantised weights go to tensor memory (the MMA's A operand)
+ * instead of shared memory.  No reference counterpart beyond awq_gemm's. */
+AWQ_B200_API int awq_b200_gemm_wtm(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                      const void* bias, void* y, int M, int K, int N, int group_size,
+                      void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
+
+/* Tuning hook: awq_b200_gemm_wtm with the activation-row tile forced (64, 128, 192; 0 = by M). */
+AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales,
+                           const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
+                           int group_size, void* workspace, size_t workspace_bytes,
+                           awq_b200_stream_t stream, int m_tile);
 
 /* ---- dispatch ------------------------------------------------------------ */
 

@@ -37,6 +37,9 @@ SIGNATURES = {
     "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I, _I, C.c_uint]),
     "awq_b200_gemm_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_gemm": (_I, _COMPUTE),
+    "awq_b200_gemm_smem": (_I, _COMPUTE),
+    "awq_b200_gemm_wtm": (_I, _COMPUTE),
+    "awq_b200_gemm_wtm_tile": (_I, _COMPUTE + [_I]),
     "awq_b200_gemv_max_rows": (_I, []),
     "awq_b200_linear_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_linear": (_I, _COMPUTE),

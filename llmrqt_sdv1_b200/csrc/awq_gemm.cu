@@ -14,10 +14,9 @@
 // Stages are handed over with mbarriers.  Every wait is bounded: on expiry the
 // kernel raises an abort flag, all roles fall through, tensor memory is freed
 // and a non-zero status word is left in the workspace.
-#include <cuda.h>
-
 #include "awq_common.cuh"
 #include "awq_ptx.cuh"
+#include "awq_tcgen05.cuh"
 
 namespace awq {
 
@@ -50,61 +49,6 @@ struct GemmParams {
   int group_size;
   int mtiles, ntiles;
 };
-
-// ---- PTX wrappers (mbarrier / bulk copy ones live in awq_ptx.cuh) -----------
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
-// 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address
-  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset: next 8-row group
-  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version (sm_100)
-  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
-  return d;
-}
 
 // Instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256.
 constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
@@ -346,13 +290,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 static EncodeTiledFn g_encode = nullptr;
 
-static int get_encode(EncodeTiledFn* out) {
+int get_encode(EncodeTiledFn* out) {
   EncodeTiledFn fn = __atomic_load_n(&g_encode, __ATOMIC_ACQUIRE);
   if (!fn) {
     void* sym = nullptr;
@@ -378,9 +318,15 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmP
   return AWQ_B200_OK;
 }
 
+// Weights-in-tensor-memory kernel (awq_wtm.cu).
+int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                 void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream, int m_tile);
+
+// variant: 0 = pick by the cost table, 1 = dequantised weights in shared memory (this file)
 int gemm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                   void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int variant) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1) return AWQ_B200_ERR_SHAPE;
@@ -395,14 +341,27 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
   EncodeTiledFn encode;
   if (int st = get_encode(&encode)) return st;
 
-  // Row halves per CTA tile.  A 256-row tile dequantises each weight once for twice the MMA work, so
-  // it keeps the tensor pipe fed where a 128-row tile is limited by the dequant warps; it is chosen
-  // unless the coarser tiles lose more to wave quantisation (tile time ratio measured ~1.7).
+  // Five tile shapes are available: the weights-in-tensor-memory kernel with 64 / 128 / 192 activation
+  // rows per tile, and this file's kernel (dequantised weights in shared memory) with 128 / 256 rows.
+  // Cost = waves of CTA tiles x measured time of one 64-k stage of that tile shape (microseconds on
+  // B200); all variants give identical bits, so the choice only affects speed.
   const int ntiles = (N + kBN - 1) / kBN;
-  const long long t1 = static_cast<long long>((M + 127) / 128) * ntiles;
-  const long long t2 = static_cast<long long>((M + 255) / 256) * ntiles;
-  const long long w1 = (t1 + di.sm_count - 1) / di.sm_count, w2 = (t2 + di.sm_count - 1) / di.sm_count;
-  const int MH = (M > 128 && 1.7 * static_cast<double>(w2) <= static_cast<double>(w1)) ? 2 : 1;
+  auto waves = [&](int rows) {
+    const long long t = static_cast<long long>((M + rows - 1) / rows) * ntiles;
+    return static_cast<double>((t + di.sm_count - 1) / di.sm_count);
+  };
+  const double c_wtm64 = waves(64) * 0.56, c_wtm128 = waves(128) * 0.66, c_wtm192 = waves(192) * 0.82;
+  const double c_smem1 = waves(128) * 0.80, c_smem2 = waves(256) * 1.08;
+  int MH = (M > 128 && c_smem2 <= c_smem1) ? 2 : 1;
+  if (variant == 0) {
+    const double c_smem = MH == 2 ? c_smem2 : c_smem1;
+    double c_w = c_wtm192;
+    int mt = 192;
+    if (c_wtm128 < c_w) { c_w = c_wtm128; mt = 128; }
+    if (c_wtm64 < c_w) { c_w = c_wtm64; mt = 64; }
+    if (c_w <= c_smem)
+      return wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes, stream, mt);
+  }
 
   CUtensorMap mx, mw;
   {
@@ -454,7 +413,15 @@ int awq_b200_gemm(const void* x, const void* packed, const void* scales, const i
                   void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                   awq_b200_stream_t stream) {
   return gemm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
-                       static_cast<cudaStream_t>(stream));
+                       static_cast<cudaStream_t>(stream), 0);
+}
+
+// Tuning hook: awq_b200_gemm restricted to the kernel that stages the dequantised weights in shared memory.
+int awq_b200_gemm_smem(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                       awq_b200_stream_t stream) {
+  return gemm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+                       static_cast<cudaStream_t>(stream), 1);
 }
 
 }  // extern "C"

@@ -1,0 +1,415 @@
+// W4A16 GEMM with the weights as the TMEM-resident A operand ("weights in tensor memory").
+//
+//   Y^T[n, m] = sum_k W^T[n, k] * X^T[k, m]
+//
+// The 16 dequant warps turn packed nibbles into the exact reference fp16 weight in registers and
+// write it straight into tensor memory (tcgen05.st): lane = output column n, two consecutive k per
+// 32-bit TMEM column.  tcgen05.mma then takes A = W^T from tensor memory and B = X (K-major rows
+// of the activations, staged by TMA with the 128-byte swizzle) from shared memory, with fp32
+// accumulators in tensor memory as well.  Compared with staging the dequantised weights in shared
+// memory this removes their shared-memory write and re-read, which is what bounds that variant.
+//
+// CTA tile: 256 output columns (two 128-lane halves) x MT activation rows, 64-k stages:
+//   warp 0      TMA producer: X tile [MT x 64] and the packed weights [2 x 256 columns x 16 bytes]
+//   warp 1      TMEM allocation, tcgen05.mma issue (M=128, N=MT, K=16), one thread
+//   warps 2-17  dequantise (4 words = 32 k of one column per thread and stage), then drain the
+//               accumulators: thread = column n, it reads MT values of its lane and stores Y[m, n]
+// TMEM columns: [0, MT) and [MT, 2MT) accumulators of the two halves, then the A ring
+// (32 columns per half and stage).  Every mbarrier wait is bounded (see awq_ptx.cuh).
+#include "awq_common.cuh"
+#include "awq_ptx.cuh"
+#include "awq_tcgen05.cuh"
+
+namespace awq {
+
+constexpr int kWtDequantThreads = 512;
+constexpr int kWtThreads = 64 + kWtDequantThreads;
+constexpr int kWtBN = 256;       // output columns per CTA tile
+constexpr int kWtBK = 64;
+constexpr int kWtRawBytes = kWtBN * (kWtBK / 2);   // 8 KiB: two boxes of [256 columns][16 bytes]
+
+template <int MT> struct WtCfg {
+  static_assert(MT % 16 == 0 && MT >= 16 && MT <= 192, "the MMA N extent");
+  static constexpr int kXBytes = MT * kWtBK * 2;                 // MT rows x 128 bytes
+  static constexpr int kXBytesPadded = (kXBytes + 1023) / 1024 * 1024;
+  static constexpr int kSzOff = kXBytesPadded + kWtRawBytes;         // 256 fp16 scales, then 32 qzeros words
+  static constexpr int kStageBytes = kXBytesPadded + kWtRawBytes + 1024;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) < 8 ? (200 * 1024 / kStageBytes) : 8;
+  static constexpr int kAStages = (512 - 2 * MT) / 64 < 4 ? (512 - 2 * MT) / 64 : 4;   // A ring depth (stages)
+  static constexpr int kABase = 2 * MT;                          // first TMEM column of the A ring
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(kAStages >= 2, "need a double-buffered A ring");
+  // The 16 dequant warps work in kGroups groups that take the k-stages in turn, so that a warp's
+  // latency chain (wait, unpack, tensor-memory store, arrive) overlaps the other groups' work.
+  static constexpr int kGroups = kAStages < 4 ? kAStages : 4;
+  static constexpr int kGroupWarps = 16 / kGroups;
+};
+
+struct WtParams {
+  const uint16_t* scales;
+  const uint32_t* qzeros;
+  const uint16_t* bias;
+  uint16_t* y;
+  unsigned* status;
+  int M, K, N;
+  int group_size;
+  int mtiles, ntiles;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(kWtThreads, 1)
+wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const WtParams p) {
+  using Cfg = WtCfg<MT>;
+  constexpr int NT = Cfg::kStages, NA = Cfg::kAStages;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ uint32_t s_tmem_base;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  auto x_addr = [&](int t) { return base + t * Cfg::kStageBytes; };
+  auto raw_addr = [&](int t) { return base + t * Cfg::kStageBytes + Cfg::kXBytesPadded; };
+  const uint32_t bar_base = base + NT * Cfg::kStageBytes;
+  auto bar_full_tma = [&](int t) { return bar_base + 8u * t; };
+  auto bar_empty_tma = [&](int t) { return bar_base + 8u * (NT + t); };    // MMA commit + 16 dequant warps
+  auto bar_a_full = [&](int a) { return bar_base + 8u * (2 * NT + a); };
+  auto bar_a_empty = [&](int a) { return bar_base + 8u * (2 * NT + NA + a); };
+  const uint32_t bar_acc_full = bar_base + 8u * (2 * NT + 2 * NA);
+  const uint32_t bar_acc_empty = bar_base + 8u * (2 * NT + 2 * NA + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int t = 0; t < NT; ++t) {
+      mbar_init(bar_full_tma(t), 1);
+      mbar_init(bar_empty_tma(t), 1 + Cfg::kGroupWarps);
+    }
+    for (int a = 0; a < NA; ++a) {
+      mbar_init(bar_a_full(a), Cfg::kGroupWarps);
+      mbar_init(bar_a_empty(a), 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, kWtDequantThreads / 32);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  const int nks = p.K / kWtBK;
+  const int num_tiles = p.mtiles * p.ntiles;
+  constexpr uint32_t kIdesc = make_f16_idesc(128, MT);
+  // Bulk copies need 16-byte aligned, 16-byte sized row segments of scales and qzeros: N % 32 == 0.
+  const bool sz_by_copy = (p.N & 31) == 0;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.mtiles) * MT;
+        const int n0 = (tile / p.mtiles) * kWtBN;
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int t = it % NT;
+          const uint32_t ph = (it / NT) & 1u;
+          if (!mbar_wait(bar_empty_tma(t), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+          const int ncols = min(kWtBN, p.N - n0);
+          const int grp = (ks * kWtBK) / p.group_size;
+          mbar_expect_tx(bar_full_tma(t), Cfg::kXBytes + kWtRawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0));
+          if (sz_by_copy) {
+            // scales and zero words of this stage's quantisation group ride in the same stage
+            bulk_load(x_addr(t) + Cfg::kSzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar_full_tma(t));
+            bulk_load(x_addr(t) + Cfg::kSzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3),
+                      ncols / 2, bar_full_tma(t));
+          }
+          tma_load_2d(x_addr(t), &map_x, ks * kWtBK, m0, bar_full_tma(t));
+          // packed weights of this 64-k stage: bytes [32*(ks&1), +32) of each column's 64 per 128-k block,
+          // as two boxes of 16 bytes so that a column's two halves land in separate, conflict-free planes
+          tma_load_3d(raw_addr(t), &map_w, (ks & 1) * 32, n0, ks >> 1, bar_full_tma(t));
+          tma_load_3d(raw_addr(t) + 4096, &map_w, (ks & 1) * 32 + 16, n0, ks >> 1, bar_full_tma(t));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+        if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int t = it % NT, a = it % NA;
+          const uint32_t ph = (it / NT) & 1u, pha = (it / NA) & 1u;
+          if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
+          if (!mbar_wait(bar_a_full(a), pha, abort_flag, 4)) { ok = false; break; }
+          tcgen05_fence_after();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int kk = 0; kk < kWtBK / 16; ++kk) {
+              const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kk * 8);
+              const uint64_t db = make_sw128_desc(x_addr(t) + kk * 32);
+              tcgen05_mma_f16_ts(tmem_base + h * MT, a_tmem, db, kIdesc, (ks | kk) != 0 ? 1u : 0u);
+            }
+          }
+          tcgen05_commit(bar_empty_tma(t));   // activations of this stage consumed
+          tcgen05_commit(bar_a_empty(a));     // A slots reusable
+        }
+        if (ok) tcgen05_commit(bar_acc_full);
+      }
+    }
+  } else {
+    // ---------------------- dequantise, then drain accumulators ---------------
+    constexpr int G = Cfg::kGroups, GW = Cfg::kGroupWarps;     // GW = 4 (G = 4) or 8 (G = 2)
+    const int id = tid - 64;                  // 0..511
+    const int dq_warp = id >> 5;              // 0..15
+    const int lane_q = warp & 3;              // TMEM lane quarter this warp may touch
+    const int grp_id = dq_warp / GW;          // which group of warps
+    const int sub = (dq_warp % GW) >> 2;      // GW == 8: the warp's 128-column half; GW == 4: 0 (it does both)
+    constexpr int NH = (GW == 4) ? 2 : 1;     // halves per warp
+    const int row = lane_q * 32 + lane;       // TMEM lane = column within a half
+    const uint32_t lane_addr = static_cast<uint32_t>(lane_q * 32) << 16;
+    // epilogue roles (all 16 warps): which half and which part of the m range
+    const int e_h = (dq_warp >> 2) & 1;
+    const int e_part = dq_warp >> 3;
+    const int zcols = p.N >> 3;
+    uint32_t it = 0, tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      const int m0 = (tile % p.mtiles) * MT;
+      const int n0 = (tile / p.mtiles) * kWtBN;
+      int ncol[NH];
+      bool nval[NH];
+      uint32_t zsh[NH];
+#pragma unroll
+      for (int hh = 0; hh < NH; ++hh) {
+        const int h = (NH == 2) ? hh : sub;
+        ncol[hh] = n0 + h * 128 + row;
+        nval[hh] = ncol[hh] < p.N;
+        zsh[hh] = awq_slot_shift(static_cast<uint32_t>(ncol[hh] & 7));
+      }
+      auto load_sz = [&](int ks, uint32_t (&s)[NH], uint32_t (&z)[NH]) {
+        const int grp = (ks * kWtBK) / p.group_size;
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) {
+          s[hh] = nval[hh] ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + ncol[hh]) : 0u;
+          z[hh] = nval[hh] ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (ncol[hh] >> 3)) : 0u;
+        }
+      };
+      uint32_t sc[NH], zw[NH];
+      int sz_group = -1;
+
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        if (static_cast<int>(it % G) != grp_id) continue;       // another group's stage
+        const int t = it % NT, a = it % NA;
+        const uint32_t ph = (it / NT) & 1u, pha = (it / NA) & 1u;
+        if (!sz_by_copy) {
+          const int qgrp = (ks * kWtBK) / p.group_size;
+          if (qgrp != sz_group) { load_sz(ks, sc, zw); sz_group = qgrp; }
+        }
+        if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) { ok = false; break; }
+        const unsigned char* raw = base_ptr + (raw_addr(t) - base);
+        if (sz_by_copy) {
+          const unsigned char* szp = base_ptr + (x_addr(t) - base) + Cfg::kSzOff;
+#pragma unroll
+          for (int hh = 0; hh < NH; ++hh) {
+            const int cl = ((NH == 2) ? hh : sub) * 128 + row;
+            sc[hh] = reinterpret_cast<const uint16_t*>(szp)[cl];
+            zw[hh] = reinterpret_cast<const uint32_t*>(szp + 512)[cl >> 3];
+          }
+        }
+        uint4 r[NH][2];
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) {
+          const int h = (NH == 2) ? hh : sub;
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh)
+            r[hh][kh] = *reinterpret_cast<const uint4*>(raw + kh * 4096 + (h * 128 + row) * 16);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
+        if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) {
+          const int h = (NH == 2) ? hh : sub;
+          const ZeroPair zp = make_zero_pair((zw[hh] >> zsh[hh]) & 0xFu);
+          const uint32_t s2 = sc[hh] * 0x00010001u;
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh) {
+            const uint32_t w[4] = {r[hh][kh].x, r[hh][kh].y, r[hh][kh].z, r[hh][kh].w};
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t q4[4];
+              dequant_word(w[i], zp, s2, q4);
+              o[4 * i + 0] = q4[0]; o[4 * i + 1] = q4[1]; o[4 * i + 2] = q4[2]; o[4 * i + 3] = q4[3];
+            }
+            tcgen05_st_32x32b_x16(tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kh * 16), o);
+          }
+        }
+        tcgen05_wait_st();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_a_full(a));
+      }
+      if (!ok) break;
+
+      // ------------------------------ epilogue --------------------------------
+      if (!mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int n = n0 + e_h * 128 + row;
+      const bool nvalid = n < p.N;
+      const uint16_t bias_n = (p.bias != nullptr && nvalid) ? p.bias[n] : static_cast<uint16_t>(0);
+      constexpr int kChunks = MT / 16;                 // 16 activation rows per chunk
+      constexpr int kHalfChunks = (kChunks + 1) / 2;   // the two warps of a (quarter, half) split the rows
+#pragma unroll 1
+      for (int ch = e_part * kHalfChunks; ch < min(kChunks, (e_part + 1) * kHalfChunks); ++ch) {
+        uint32_t v[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(tmem_base + lane_addr + static_cast<uint32_t>(e_h * MT + ch * 16))
+            : "memory");
+        tcgen05_wait_ld();
+        if (nvalid) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + ch * 16 + j;
+            if (m < p.M) {
+              __half hv = __float2half_rn(__uint_as_float(v[j]));
+              if (p.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
+              p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(hv);   // 32 lanes = 64 contiguous bytes
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, 0x100u | static_cast<unsigned>(s_abort));
+}
+
+}  // namespace awq
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+namespace awq {
+
+template <int MT>
+static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_count, EncodeTiledFn encode,
+                      cudaStream_t stream) {
+  using Cfg = WtCfg<MT>;
+  CUtensorMap mx, mw;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.K) * 2};
+    const cuuint32_t box[2] = {kWtBK, MT};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  }
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(p.N), static_cast<cuuint64_t>(p.K / kBlockK)};
+    const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(p.N) * 64};
+    const cuuint32_t box[3] = {16, kWtBN, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(packed), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  }
+  p.mtiles = (p.M + MT - 1) / MT;
+  p.ntiles = (p.N + kWtBN - 1) / kWtBN;
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(wtm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  const int tiles = p.mtiles * p.ntiles;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  wtm_kernel<MT><<<grid, kWtThreads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
+  AWQ_CUDA_TRY(cudaGetLastError());
+  return AWQ_B200_OK;
+}
+
+int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                 void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream, int m_tile) {
+  if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
+  if (int st = check_shape(K, N, group_size)) return st;
+  if (M < 1) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y) ||
+      (bias && !aligned16(bias)))
+    return AWQ_B200_ERR_ALIGN;
+  if (!workspace || workspace_bytes < 16) return AWQ_B200_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
+  EncodeTiledFn encode;
+  if (int st = get_encode(&encode)) return st;
+  WtParams p;
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
+  p.bias = static_cast<const uint16_t*>(bias);
+  p.y = static_cast<uint16_t*>(y);
+  p.status = static_cast<unsigned*>(workspace);
+  p.M = M; p.K = K; p.N = N;
+  p.group_size = group_size;
+  p.mtiles = p.ntiles = 0;
+  if (m_tile == 0) m_tile = M <= 64 ? 64 : (M <= 128 ? 128 : 192);
+  switch (m_tile) {
+    case 64: return launch_wtm<64>(x, packed, p, di.sm_count, encode, stream);
+    case 128: return launch_wtm<128>(x, packed, p, di.sm_count, encode, stream);
+    case 192: return launch_wtm<192>(x, packed, p, di.sm_count, encode, stream);
+    default: return AWQ_B200_ERR_SHAPE;
+  }
+}
+
+}  // namespace awq
+
+extern "C" {
+
+// Same contract as awq_b200_gemm (workspace = one zero-initialised status word); the weights take the
+// tensor-memory route.  Kept as a separate entry point so that the two GEMM kernels can be compared.
+int awq_b200_gemm_wtm(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                      void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                      awq_b200_stream_t stream) {
+  return awq::wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+                           static_cast<cudaStream_t>(stream), 0);
+}
+
+// Tuning hook: the same with the activation-row tile forced (64, 128 or 192; 0 = by M).
+int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                           const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                           size_t workspace_bytes, awq_b200_stream_t stream, int m_tile) {
+  return awq::wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+                           static_cast<cudaStream_t>(stream), m_tile);
+}
+
+}  // extern "C"

@@ -154,6 +154,18 @@ def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
                 lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out)
 
 
+def gemm_smem(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
+    """Prefill kernel, dequantised-weights-in-shared-memory variant only."""
+    return _run(lib.awq_b200_gemm_smem, "awq_b200_gemm", x, pw, bias,
+                lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out)
+
+
+def gemm_wtm(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch.Tensor:
+    """Prefill kernel, weights-in-tensor-memory variant, any M >= 1 (`m_tile` forces the row tile)."""
+    return _run(lib.awq_b200_gemm_wtm_tile, "awq_b200_gemm", x, pw, bias,
+                lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out, (m_tile,))
+
+
 def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
     """M <= 16 -> GEMV, else GEMM (dispatch inside the library).  `overlap` as in `gemv`."""
     return _run(lib.awq_b200_linear_ex, "awq_b200_linear", x, pw, bias,

@@ -192,6 +192,12 @@ def test_gemm_vs_oracle(K_, M, K, N):
     torch.cuda.synchronize()
     assert K_.gemm_status() == 0
     assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+    # both tensor-core kernels (weights staged in shared memory / in tensor memory, every row tile)
+    # multiply the same fp16 weights in the same k order: identical bits
+    assert torch.equal(K_.gemm_smem(dev(x), pw), y)
+    for mt in (64, 128, 192):
+        assert torch.equal(K_.gemm_wtm(dev(x), pw, m_tile=mt), y)
+    assert K_.gemm_status() == 0
 
 
 def test_gemm_bias_group_and_small_m(K_):
