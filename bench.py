@@ -516,7 +516,7 @@ def run_profile_case(args, torch):
             for pw in pws:
                 kernels.gemv(x, pw, out=y)
     else:
-        M, K, N = (8192, 4096, 28672) if args.profile_case == "gemm_large" else (2048, 4096, 6144)
+        M, K, N = {"gemm_large": (8192, 4096, 28672), "gemm_m64": (64, 4096, 28672)}.get(args.profile_case, (2048, 4096, 6144))
         qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
         pw = kernels.make_packed(qw, qz, sc, GROUP)
         x = torch.randn((M, K), device="cuda").half()
@@ -538,7 +538,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp", "qwen3_e2e"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "gemm", "gemm_large"],
+    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

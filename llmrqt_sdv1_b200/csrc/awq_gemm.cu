@@ -120,54 +120,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // Warp-uniform loop; lanes 0..MH-1 issue the activation boxes, lane MH the packed weights.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.mtiles) * (128 * MH);
-        const int n0 = (tile / p.mtiles) * kBN;
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int st = it % NT;
-          const uint32_t ph = (it / NT) & 1u;
-          if (!mbar_wait(bar_empty_tma(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
-          mbar_expect_tx(bar_full_tma(st), MH * kABytesHalf + kRawBytes);
-#pragma unroll
-          for (int h = 0; h < MH; ++h) tma_load_2d(a_addr(st, h), &map_x, ks * kBK, m0 + h * 128, bar_full_tma(st));
-          tma_load_3d(raw_addr(st), &map_w, (ks & 1) * 32, n0, ks >> 1, bar_full_tma(st));
-        }
+    }
+    uint32_t it = 0;
+    int st = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.mtiles) * (128 * MH);
+      const int n0 = (tile / p.mtiles) * kBN;
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        if (!mbar_wait(bar_empty_tma(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+        const uint32_t bar = bar_full_tma(st);
+        if (lane == 0) mbar_expect_tx(bar, MH * kABytesHalf + kRawBytes);
+        if (lane < MH) tma_load_2d(a_addr(st, lane), &map_x, ks * kBK, m0 + lane * 128, bar);
+        if (lane == MH) tma_load_3d(raw_addr(st), &map_w, (ks & 1) * 32, n0, ks >> 1, bar);
+        if (++st == NT) { st = 0; ph ^= 1u; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      uint32_t it = 0, tile_it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-        if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+    // Warp-uniform loop, one elected lane issues (see tcgen05_mma_f16_warp).
+    uint32_t it = 0, tile_it = 0;
+    int st = 0, sb = 0;
+    uint32_t ph = 0, phb = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+      tcgen05_fence_after();
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 3)) { ok = false; break; }
+        if (!mbar_wait(bar_full_b(sb), phb, abort_flag, 4)) { ok = false; break; }
         tcgen05_fence_after();
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int st = it % NT, sb = it % NB;
-          const uint32_t ph = (it / NT) & 1u, phb = (it / NB) & 1u;
-          if (!mbar_wait(bar_full_tma(st), ph, abort_flag, 3)) { ok = false; break; }
-          if (!mbar_wait(bar_full_b(sb), phb, abort_flag, 4)) { ok = false; break; }
-          tcgen05_fence_after();
 #pragma unroll
-          for (int h = 0; h < MH; ++h) {
+        for (int h = 0; h < MH; ++h) {
 #pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk) {
-              const uint64_t da = make_sw128_desc(a_addr(st, h) + kk * 32);
-              const uint64_t db = make_sw128_desc(b_addr(sb) + kk * 32);
-              tcgen05_mma_f16(tmem_base + h * 256, da, db, kInstrDesc, (ks | kk) != 0 ? 1u : 0u);
-            }
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t da = make_sw128_desc(a_addr(st, h) + kk * 32);
+            const uint64_t db = make_sw128_desc(b_addr(sb) + kk * 32);
+            tcgen05_mma_f16_warp(tmem_base + h * 256, da, db, kInstrDesc, (ks | kk) != 0 ? 1u : 0u);
           }
-          tcgen05_commit(bar_empty_tma(st));   // activations of this stage consumed
-          tcgen05_commit(bar_empty_b(sb));     // B buffer reusable
         }
-        if (ok) tcgen05_commit(bar_acc_full);
+        tcgen05_commit_warp(bar_empty_tma(st));   // activations of this stage consumed
+        tcgen05_commit_warp(bar_empty_b(sb));     // B buffer reusable
+        if (++st == NT) { st = 0; ph ^= 1u; }
+        if (++sb == NB) { sb = 0; phb ^= 1u; }
       }
+      if (ok) tcgen05_commit_warp(bar_acc_full);
     }
+    __syncwarp();
   } else {
     // ---------------------- dequantise, then drain accumulators ---------------
     const int id = tid - 64;                 // 0..511

@@ -10,7 +10,7 @@
 // memory this removes their shared-memory write and re-read, which is what bounds that variant.
 //
 // CTA tile: 256 output columns (two 128-lane halves) x MT activation rows, 64-k stages:
-//   warp 0      TMA producer: X tile [MT x 64] and the packed weights [2 x 256 columns x 16 bytes]
+//   warp 0      TMA producer: X tile [MT x 64] and the packed weights [256 columns x 32 bytes, 32-byte swizzle]
 //   warp 1      TMEM allocation, tcgen05.mma issue (M=128, N=MT, K=16), one thread
 //   warps 2-17  dequantise (4 words = 32 k of one column per thread and stage), then drain the
 //               accumulators: thread = column n, it reads MT values of its lane and stores Y[m, n]
@@ -20,13 +20,29 @@
 #include "awq_ptx.cuh"
 #include "awq_tcgen05.cuh"
 
+#ifdef AWQ_WTM_TRACE
+// Diagnostic build only: cycle stamps of CTA 0 (SM clock) for the first 48 k-stages.
+__device__ long long* g_wtm_trace = nullptr;
+#define WTM_TRACE(role, stage, slot)                                                          \
+  do {                                                                                        \
+    if ((AWQ_WTM_TRACE >> (role)) & 1) if (trace_buf && (stage) < 48) trace_buf[((role) * 48 + (stage)) * 8 + (slot)] = clock64(); \
+  } while (0)
+extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_wtm_trace(void* buf) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_wtm_trace, &buf, sizeof(buf)));
+}
+#else
+#define WTM_TRACE(role, stage, slot) do { } while (0)
+#endif
+
 namespace awq {
 
 constexpr int kWtDequantThreads = 512;
-constexpr int kWtThreads = 64 + kWtDequantThreads;
+// warp 0 and warp 18: copy producers (even and odd k-stages); warp 1: MMA issuer; warps 2..17: dequantise + epilogue
+constexpr int kWtProducer2Warp = 2 + kWtDequantThreads / 32;
+constexpr int kWtThreads = 64 + kWtDequantThreads + 32;
 constexpr int kWtBN = 256;       // output columns per CTA tile
 constexpr int kWtBK = 64;
-constexpr int kWtRawBytes = kWtBN * (kWtBK / 2);   // 8 KiB: two boxes of [256 columns][16 bytes]
+constexpr int kWtRawBytes = kWtBN * (kWtBK / 2);   // 8 KiB: [256 columns][32 bytes], 32-byte swizzle
 
 template <int MT> struct WtCfg {
   static_assert(MT % 16 == 0 && MT >= 16 && MT <= 192, "the MMA N extent");
@@ -105,6 +121,9 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   tcgen05_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+#ifdef AWQ_WTM_TRACE
+  long long* const trace_buf = blockIdx.x == 0 ? g_wtm_trace : nullptr;
+#endif
 
   const int nks = p.K / kWtBK;
   const int num_tiles = p.mtiles * p.ntiles;
@@ -112,66 +131,97 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   // Bulk copies need 16-byte aligned, 16-byte sized row segments of scales and qzeros: N % 32 == 0.
   const bool sz_by_copy = (p.N & 31) == 0;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp == 0 || warp == kWtProducer2Warp) {
+    // ------------------------------ TMA producers -----------------------------
+    // Two warps take the k-stages alternately: one warp's issue chain (wait, expect, three copy
+    // instructions) is longer than the time a small-MT stage takes to consume.
+    static_assert(NT % 2 == 0, "the two producers alternate over an even ring");
+    const uint32_t my_parity = warp == 0 ? 0u : 1u;
+    // Warp-uniform loop; lanes 0, 1, 3 and 4 each issue one of the stage's four copies, so that a stage costs
+    // three predicated instructions rather than a serial chain in one thread.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.mtiles) * MT;
-        const int n0 = (tile / p.mtiles) * kWtBN;
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int t = it % NT;
-          const uint32_t ph = (it / NT) & 1u;
+    }
+    const int stages_per_group = p.group_size / kWtBK;
+    uint32_t it = 0;
+    int t = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.mtiles) * MT;
+      const int n0 = (tile / p.mtiles) * kWtBN;
+      const int ncols = min(kWtBN, p.N - n0);
+      const uint32_t tx = Cfg::kXBytes + kWtRawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0);
+      int grp = 0, left = stages_per_group;
+      // lane 3 copies the scales row segment, lane 4 the zero words
+      const unsigned char* sz_src = (lane == 3) ? reinterpret_cast<const unsigned char*>(p.scales + n0)
+                                                : reinterpret_cast<const unsigned char*>(p.qzeros + (n0 >> 3));
+      const size_t sz_step = (lane == 3) ? static_cast<size_t>(p.N) * 2 : static_cast<size_t>(p.N >> 3) * 4;
+      const uint32_t sz_bytes = (lane == 3) ? ncols * 2 : ncols / 2;
+      const uint32_t sz_dst = Cfg::kSzOff + (lane == 3 ? 0 : 512);
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        if ((it & 1u) == my_parity) {
+          WTM_TRACE(0, it, 0);
           if (!mbar_wait(bar_empty_tma(t), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
-          const int ncols = min(kWtBN, p.N - n0);
-          const int grp = (ks * kWtBK) / p.group_size;
-          mbar_expect_tx(bar_full_tma(t), Cfg::kXBytes + kWtRawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0));
-          if (sz_by_copy) {
-            // scales and zero words of this stage's quantisation group ride in the same stage
-            bulk_load(x_addr(t) + Cfg::kSzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar_full_tma(t));
-            bulk_load(x_addr(t) + Cfg::kSzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3),
-                      ncols / 2, bar_full_tma(t));
+          WTM_TRACE(0, it, 1);
+          const uint32_t bar = bar_full_tma(t);
+          if (lane == 0) {
+            mbar_expect_tx(bar, tx);
+            tma_load_2d(x_addr(t), &map_x, ks * kWtBK, m0, bar);
           }
-          tma_load_2d(x_addr(t), &map_x, ks * kWtBK, m0, bar_full_tma(t));
-          // packed weights of this 64-k stage: bytes [32*(ks&1), +32) of each column's 64 per 128-k block,
-          // as two boxes of 16 bytes so that a column's two halves land in separate, conflict-free planes
-          tma_load_3d(raw_addr(t), &map_w, (ks & 1) * 32, n0, ks >> 1, bar_full_tma(t));
-          tma_load_3d(raw_addr(t) + 4096, &map_w, (ks & 1) * 32 + 16, n0, ks >> 1, bar_full_tma(t));
+          WTM_TRACE(0, it, 2);
+          // packed weights of this 64-k stage: bytes [32*(ks&1), +32) of each column's 64 per 128-k block, one
+          // 32-byte row per column; the 32-byte swizzle makes the per-column 16-byte reads conflict-free
+          if (lane == 1) tma_load_3d(raw_addr(t), &map_w, (ks & 1) * 32, n0, ks >> 1, bar);
+          WTM_TRACE(0, it, 3);
+          // scales and zero words of this stage's quantisation group ride in the same stage
+          if (sz_by_copy && (lane == 3 || lane == 4))
+            bulk_load(x_addr(t) + sz_dst, sz_src + static_cast<size_t>(grp) * sz_step, sz_bytes, bar);
+          WTM_TRACE(0, it, 4);
         }
+        if (--left == 0) { left = stages_per_group; ++grp; }
+        if (++t == NT) { t = 0; ph ^= 1u; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      uint32_t it = 0, tile_it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-        if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+    // The whole warp runs this loop with identical values and one elected lane issues: a loop that
+    // only lane 0 executes keeps descriptors in per-thread registers and costs ~70 cycles per MMA
+    // in operand moves, more than a 128 x 64 x 16 MMA takes to execute.
+    uint32_t it = 0, tile_it = 0;
+    int t = 0, a = 0;
+    uint32_t ph = 0, pha = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+      tcgen05_fence_after();
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        WTM_TRACE(1, it, 0);
+        if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
+        WTM_TRACE(1, it, 1);
+        if (!mbar_wait(bar_a_full(a), pha, abort_flag, 4)) { ok = false; break; }
+        WTM_TRACE(1, it, 2);
         tcgen05_fence_after();
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int t = it % NT, a = it % NA;
-          const uint32_t ph = (it / NT) & 1u, pha = (it / NA) & 1u;
-          if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
-          if (!mbar_wait(bar_a_full(a), pha, abort_flag, 4)) { ok = false; break; }
-          tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kWtBK / 16; ++kk) {
+          const uint64_t db = make_sw128_desc(x_addr(t) + kk * 32);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-#pragma unroll
-            for (int kk = 0; kk < kWtBK / 16; ++kk) {
-              const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kk * 8);
-              const uint64_t db = make_sw128_desc(x_addr(t) + kk * 32);
-              tcgen05_mma_f16_ts(tmem_base + h * MT, a_tmem, db, kIdesc, (ks | kk) != 0 ? 1u : 0u);
-            }
+            const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kk * 8);
+            tcgen05_mma_f16_ts_warp(tmem_base + h * MT, a_tmem, db, kIdesc, (ks | kk) != 0 ? 1u : 0u);
           }
-          tcgen05_commit(bar_empty_tma(t));   // activations of this stage consumed
-          tcgen05_commit(bar_a_empty(a));     // A slots reusable
         }
-        if (ok) tcgen05_commit(bar_acc_full);
+        tcgen05_commit_warp(bar_empty_tma(t));   // activations of this stage consumed
+        tcgen05_commit_warp(bar_a_empty(a));     // A slots reusable
+        WTM_TRACE(1, it, 3);
+        if (++t == NT) { t = 0; ph ^= 1u; }
+        if (++a == NA) { a = 0; pha ^= 1u; }
       }
+      if (ok) tcgen05_commit_warp(bar_acc_full);
     }
+    __syncwarp();
   } else {
     // ---------------------- dequantise, then drain accumulators ---------------
     constexpr int G = Cfg::kGroups, GW = Cfg::kGroupWarps;     // GW = 4 (G = 4) or 8 (G = 2)
@@ -221,7 +271,9 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           const int qgrp = (ks * kWtBK) / p.group_size;
           if (qgrp != sz_group) { load_sz(ks, sc, zw); sz_group = qgrp; }
         }
+        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 0);
         if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) { ok = false; break; }
+        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 1);
         const unsigned char* raw = base_ptr + (raw_addr(t) - base);
         if (sz_by_copy) {
           const unsigned char* szp = base_ptr + (x_addr(t) - base) + Cfg::kSzOff;
@@ -238,11 +290,12 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           const int h = (NH == 2) ? hh : sub;
 #pragma unroll
           for (int kh = 0; kh < 2; ++kh)
-            r[hh][kh] = *reinterpret_cast<const uint4*>(raw + kh * 4096 + (h * 128 + row) * 16);
+            r[hh][kh] = *reinterpret_cast<const uint4*>(raw + (h * 128 + row) * 32 + ((kh ^ ((row >> 2) & 1)) << 4));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; break; }
+        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 2);
         tcgen05_fence_after();
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) {
@@ -262,7 +315,9 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
             tcgen05_st_32x32b_x16(tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kh * 16), o);
           }
         }
+        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 3);
         tcgen05_wait_st();
+        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 4);
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_a_full(a));
@@ -340,10 +395,10 @@ static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_coun
   {
     const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(p.N), static_cast<cuuint64_t>(p.K / kBlockK)};
     const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(p.N) * 64};
-    const cuuint32_t box[3] = {16, kWtBN, 1};
+    const cuuint32_t box[3] = {32, kWtBN, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(packed), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
   }
