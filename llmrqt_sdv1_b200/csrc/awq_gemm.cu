@@ -130,8 +130,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.mtiles) * (128 * MH);
-      const int n0 = (tile / p.mtiles) * kBN;
+      int tile_m, tile_n;
+      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      const int m0 = tile_m * (128 * MH);
+      const int n0 = tile_n * kBN;
       for (int ks = 0; ks < nks; ++ks, ++it) {
         if (!mbar_wait(bar_empty_tma(st), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
         const uint32_t bar = bar_full_tma(st);
@@ -193,8 +195,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     uint32_t it = 0, tile_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-      const int m0 = (tile % p.mtiles) * (128 * MH);
-      const int n0 = (tile / p.mtiles) * kBN;
+      int tile_m, tile_n;
+      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      const int m0 = tile_m * (128 * MH);
+      const int n0 = tile_n * kBN;
       const int nA = n0 + col_local;
       const bool vA = nA < p.N;
       const uint32_t zshift = awq_slot_shift(static_cast<uint32_t>(nA & 7));
@@ -355,8 +359,8 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
     const long long t = static_cast<long long>((M + rows - 1) / rows) * ntiles;
     return static_cast<double>((t + di.sm_count - 1) / di.sm_count);
   };
-  const double c_wtm64 = waves(64) * 0.56, c_wtm128 = waves(128) * 0.66, c_wtm192 = waves(192) * 0.82;
-  const double c_smem1 = waves(128) * 0.80, c_smem2 = waves(256) * 1.08;
+  const double c_wtm64 = waves(64) * 0.43, c_wtm128 = waves(128) * 0.52, c_wtm192 = waves(192) * 0.64;
+  const double c_smem1 = waves(128) * 0.78, c_smem2 = waves(256) * 1.00;
   int MH = (M > 128 && c_smem2 <= c_smem1) ? 2 : 1;
   if (variant == 0) {
     const double c_smem = MH == 2 ? c_smem2 : c_smem1;

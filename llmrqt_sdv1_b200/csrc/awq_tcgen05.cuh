@@ -112,6 +112,21 @@ __device__ __forceinline__ void tcgen05_commit_warp(uint32_t bar) {
 }
 __device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Order in which a persistent grid walks the (row tile, column tile) grid: bands of kTileBandRows row
+// tiles, and inside a band row tiles fastest.  The ~148 tiles in flight then cover a compact block
+// (8 row tiles x ~18 column tiles) instead of every row tile of a few column tiles, so the working
+// set of one wave (activations + packed weights) stays small enough to be re-read from L2.
+constexpr int kTileBandRows = 8;
+__device__ __forceinline__ void tile_coords(int tile, int mtiles, int ntiles, int* mi, int* ni) {
+  const int band_tiles = kTileBandRows * ntiles;
+  const int band = tile / band_tiles;
+  const int first = band * kTileBandRows;
+  const int rows = min(kTileBandRows, mtiles - first);
+  const int r = tile - band * band_tiles;
+  *ni = r / rows;
+  *mi = first + (r - *ni * rows);
+}
+
 // Instruction descriptor for kind::f16: D fp32, A and B fp16, both K-major, given M and N.
 __host__ __device__ constexpr uint32_t make_f16_idesc(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);

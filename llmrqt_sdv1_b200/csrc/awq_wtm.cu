@@ -149,8 +149,10 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.mtiles) * MT;
-      const int n0 = (tile / p.mtiles) * kWtBN;
+      int tile_m, tile_n;
+      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      const int m0 = tile_m * MT;
+      const int n0 = tile_n * kWtBN;
       const int ncols = min(kWtBN, p.N - n0);
       const uint32_t tx = Cfg::kXBytes + kWtRawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0);
       int grp = 0, left = stages_per_group;
@@ -240,8 +242,10 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     uint32_t it = 0, tile_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-      const int m0 = (tile % p.mtiles) * MT;
-      const int n0 = (tile / p.mtiles) * kWtBN;
+      int tile_m, tile_n;
+      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      const int m0 = tile_m * MT;
+      const int n0 = tile_n * kWtBN;
       int ncol[NH];
       bool nval[NH];
       uint32_t zsh[NH];
