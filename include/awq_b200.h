@@ -129,7 +129,15 @@ enum awq_b200_flags {
   /* Decode kernel: add the split-k partial sums through the global workspace even where the
    * splits could form a thread-block cluster (2..8 splits) and add them over distributed shared
    * memory.  Both ways add in the same order and give identical bits; this flag exists for tests. */
-  AWQ_B200_NO_CLUSTER = 2
+  AWQ_B200_NO_CLUSTER = 2,
+  /* Decode kernel: which way the (column group, k range) work reaches the CTAs.  By default a
+   * shape that needs more than one wave of CTAs runs as a persistent stream (every resident CTA
+   * walks an equal share of the work through one copy pipeline) and smaller shapes as one CTA per
+   * (column group, k split).  These two flags force one or the other; they exist for tests and
+   * tuning.  The two decompositions add a column's k blocks in different (fixed) groupings, so
+   * their results agree to fp32 rounding, not bit for bit. */
+  AWQ_B200_GEMV_STREAM = 4,
+  AWQ_B200_GEMV_PER_SPLIT = 8
 };
 
 /* awq_b200_gemv with call flags.  No reference counterpart (the reference launches on the

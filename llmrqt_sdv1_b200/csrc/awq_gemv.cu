@@ -12,8 +12,7 @@
 // and the last CTA to arrive for a column range adds them in split order, so
 // results are deterministic and a row's value does not depend on how many rows
 // the call has.
-#include "awq_common.cuh"
-#include "awq_ptx.cuh"
+#include "awq_gemv_common.cuh"
 
 #ifdef AWQ_GEMV_TRACE
 // Diagnostic build only: per-CTA phase timestamps (ns) into a caller-provided buffer.
@@ -39,101 +38,6 @@ extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_gemv_tr
 #endif
 
 namespace awq {
-
-// A CTA has W compute warps (8 or 16) plus one warp that only issues bulk copies.
-constexpr int kGemvMaxBps = 32;   // per warp  // 128-k blocks per split (bounds the activation slice in smem)
-constexpr int kGemvMaxRows = 16;
-// 128-k blocks in flight per CTA (bulk copies): 5 x 17 KiB or 6 x 8.5 KiB of shared memory.
-__host__ __device__ constexpr int gemv_stages(int ntw, int w) { return w == 16 ? (ntw == 4 ? 3 : 4) : (ntw == 4 ? 5 : 6); }
-
-struct GemvParams {
-  const uint16_t* x;
-  const uint4* wp;
-  const uint16_t* scales;
-  const uint32_t* qzeros;
-  const uint16_t* bias;
-  uint16_t* y;
-  float* partial;
-  unsigned* counters;
-  unsigned* status;    // last counter slot: 0, or the code of a device-side wait that expired
-  int M, K, N;
-  int group_blocks;  // group_size / 128
-  int nblk;          // K / 128
-  int bps;           // blocks per split
-  int S;             // number of splits
-  int ntiles;        // N / 8
-  int cluster;       // 1: the S splits of a column range form one thread-block cluster and reduce over DSMEM
-};
-
-__device__ __forceinline__ void mma_16816(float acc[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// y = fp16(acc) then, with a bias, fp16(y + bias): the two roundings of the
-// reference's `out + bias` on an fp16 tensor.
-__device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, size_t row_off, int col,
-                                           float a, float b) {
-  uint32_t v = pack_half2(a, b);
-  if (bias != nullptr) {
-    const uint32_t bv = *reinterpret_cast<const uint32_t*>(bias + col);
-    asm("add.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(bv));
-  }
-  *reinterpret_cast<uint32_t*>(y + row_off + col) = v;
-}
-
-// One packed word (8 nibbles) -> four half2 for the tensor core, without scaling:
-// out[0], out[2] hold the exact codes q (nibbles 0/4 and 2/6: (q | 0x6400) - 1024);
-// out[1], out[3] hold 64 + q (nibbles 1/5 and 3/7 or-ed into the mantissa of 2^6),
-// whose constant 64 is removed afterwards through the per-block activation sums.
-__device__ __forceinline__ void unpack_codes(uint32_t w, uint32_t out[4]) {
-  constexpr uint32_t kLoMask = 0x000f000fu, kHiMask = 0x00f000f0u;
-  constexpr uint32_t k1024 = 0x64006400u, k64 = 0x54005400u;
-  const uint32_t w8 = w >> 8;
-  out[0] = h2_sub(lop3_and_or(w, kLoMask, k1024), k1024);
-  out[1] = lop3_and_or(w, kHiMask, k64);
-  out[2] = h2_sub(lop3_and_or(w8, kLoMask, k1024), k1024);
-  out[3] = lop3_and_or(w8, kHiMask, k64);
-}
-
-__device__ __forceinline__ float small_uint_to_float(uint32_t v) {   // exact for v < 2^23, no I2F
-  return __uint_as_float(0x4B000000u | v) - 8388608.0f;
-}
-
-__device__ __forceinline__ void store_out1(uint16_t* y, const uint16_t* bias, size_t row_off, int col, float a) {
-  __half h = __float2half_rn(a);
-  if (bias != nullptr) h = __hadd(h, __ushort_as_half(bias[col]));
-  y[row_off + col] = __half_as_ushort(h);
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float2 ld_dsmem_f2(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
-  return v;
-}
 
 // The W compute warps form a CW x KW grid (CW * KW = W): warp (cw, kw) owns NTW column tiles
 // (NTW/2 pairs of 16 columns) and every KW-th 128-k block of this CTA's k-range.  MT = 8 or 16 rows.
@@ -194,33 +98,36 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   // qzeros rows can be bulk-copied only if every row segment is 16-byte aligned and sized.
   const bool zeros_by_copy = ((p.N & 31) == 0) && ((valid_tiles & 3u) == 0u);
   const uint32_t sub_tx = valid_tiles * (512u + 16u + (zeros_by_copy ? 4u : 0u));
-  // One stage = the packed weights, scales and zero words of KW consecutive blocks.
+  // One stage = the packed weights, scales and zero words of KW consecutive blocks.  The whole
+  // producer warp calls this: lane j issues the copies of block j, so a stage costs three copy
+  // instructions however many blocks it has (a single thread issuing them one after another needs
+  // longer than the copies take).
   auto issue_stage = [&](int it) {
     const int st = it % ST;
     const int nblocks = min(KW, nb - it * KW);
-    mbar_expect_tx(bar_full(st), sub_tx * static_cast<uint32_t>(nblocks));
-    for (int j = 0; j < nblocks; ++j) {
-      const int bl = it * KW + j;
-      const uint32_t dst = smem_u32(ring + st * kStageBytes + j * kSubBytes);
-      const int grp = (b0 + bl) / p.group_blocks;
-      bulk_load(dst, wsrc + static_cast<size_t>(bl) * block_stride_u4, valid_tiles * 512u, bar_full(st));
+    const uint32_t bar = bar_full(st);
+    if (lane == 0) mbar_expect_tx(bar, sub_tx * static_cast<uint32_t>(nblocks));
+    if (lane < nblocks) {
+      const int bl = it * KW + lane;
+      const uint32_t dst = smem_u32(ring + st * kStageBytes + lane * kSubBytes);
+      const int grp = p.group_blocks == 1 ? (b0 + bl) : (b0 + bl) / p.group_blocks;
+      bulk_load(dst, wsrc + static_cast<size_t>(bl) * block_stride_u4, valid_tiles * 512u, bar);
       bulk_load(dst + kSubScaleOff, p.scales + static_cast<size_t>(grp) * p.N + static_cast<size_t>(cta_tile0) * 8,
-                valid_tiles * 16u, bar_full(st));
+                valid_tiles * 16u, bar);
       if (zeros_by_copy)
-        bulk_load(dst + kSubZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u,
-                  bar_full(st));
+        bulk_load(dst + kSubZeroOff, p.qzeros + static_cast<size_t>(grp) * zcols + cta_tile0, valid_tiles * 4u, bar);
     }
   };
 
-  int issued = 0;   // stages whose copies have been started (meaningful in the producer thread only)
-  if (is_producer && lane == 0) {
-    s_abort = 0;
-#pragma unroll
-    for (int st = 0; st < ST; ++st) {
-      mbar_init(bar_full(st), 1);
-      mbar_init(bar_empty(st), kGemvWarps);
+  int issued = 0;   // stages whose copies have been started (meaningful in the producer warp only)
+  if (is_producer) {
+    if (lane == 0) s_abort = 0;
+    if (lane < ST) {
+      mbar_init(bar_full(lane), 1);
+      mbar_init(bar_empty(lane), kGemvWarps);
+      mbar_fence_init();
     }
-    mbar_fence_init();
+    __syncwarp();
 #pragma unroll
     for (int st = 0; st < ST; ++st) {
       if (st < nit) {
@@ -269,12 +176,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
 
   if (is_producer) {
     // Producer warp: refill a stage as soon as all compute warps have released it.
-    if (lane == 0) {
-      for (int it = ST; it < nit; ++it) {
-        if (!mbar_wait(bar_empty(it % ST), static_cast<uint32_t>(it / ST - 1) & 1u, abort_flag, 2)) break;
-        issue_stage(it);
-        issued = it + 1;
-      }
+    for (int it = ST; it < nit; ++it) {
+      if (!mbar_wait(bar_empty(it % ST), static_cast<uint32_t>(it / ST - 1) & 1u, abort_flag, 2)) break;
+      issue_stage(it);
+      issued = it + 1;
     }
   } else {
     for (int it = 0; it < nit; ++it) {
@@ -318,16 +223,18 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
         load_x(bl, xv);
       }
       // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
-      // x[m,k]), rows 8..15 are 0 for the exact-code k and 64 for the k fed as 64 + q (-> H[m]).
+      // x[m,k]), rows 8..15 hold the constant carried by the code at that k, 1024 or 64 (-> H[m]).
       // Two short chains; nothing below waits for them until the very end of the block.
 #pragma unroll
       for (int mh = 0; mh < MH; ++mh) {
-        float SH0[4] = {0.f, 0.f, 0.f, 0.f}, SH1[4] = {0.f, 0.f, 0.f, 0.f};
-        constexpr uint32_t kOne = 0x3C003C00u, k64h = 0x54005400u;
+        float SH0[4], SH1[4];
+        constexpr uint32_t kOne = 0x3C003C00u;
+        mma_16816_first(SH0, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][0].x, xv[mh][0].y);
+        mma_16816_first(SH1, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][0].z, xv[mh][0].w);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          mma_16816(SH0, kOne, 0u, kOne, k64h, xv[mh][i].x, xv[mh][i].y);
-          mma_16816(SH1, kOne, 0u, kOne, k64h, xv[mh][i].z, xv[mh][i].w);
+        for (int i = 1; i < 4; ++i) {
+          mma_16816(SH0, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][i].x, xv[mh][i].y);
+          mma_16816(SH1, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][i].z, xv[mh][i].w);
         }
         T[mh] = make_float4(SH0[0] + SH1[0], SH0[1] + SH1[1], SH0[2] + SH1[2], SH0[3] + SH1[3]);
       }
@@ -340,24 +247,24 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
         // Two independent accumulation chains per block, both starting from zero.
         float blk[MH][2][4];
 #pragma unroll
-        for (int mh = 0; mh < MH; ++mh) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) blk[mh][0][e] = blk[mh][1][e] = 0.f;
-        }
-#pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint32_t qa[4], qb[4];
           unpack_codes(wa[i], qa);
           unpack_codes(wb[i], qb);
 #pragma unroll
           for (int mh = 0; mh < MH; ++mh) {
-            mma_16816(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
-            mma_16816(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
+            if (i == 0) {
+              mma_16816_first(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
+              mma_16816_first(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
+            } else {
+              mma_16816(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
+              mma_16816(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
+            }
           }
         }
 #pragma unroll
         for (int mh = 0; mh < MH; ++mh) {
-          // sum_k x*code = chain0 + chain1 - H   (H removes the "+64" of the odd nibbles)
+          // sum_k x*code = chain0 + chain1 - H   (H removes the constants 1024 / 64 carried by the codes)
           const float d0 = (blk[mh][0][0] + blk[mh][1][0]) - T[mh].z, d1 = (blk[mh][0][1] + blk[mh][1][1]) - T[mh].w;
           const float d2 = (blk[mh][0][2] + blk[mh][1][2]) - T[mh].z, d3 = (blk[mh][0][3] + blk[mh][1][3]) - T[mh].w;
           acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, d0), acc[mh][q][0]);
@@ -568,11 +475,22 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
   return best;
 }
 
+// Streaming (persistent, evenly balanced) variant, in awq_gemv_stream.cu.
+int gemv_stream_slots(int K, int N, int ntw, int w, int kw, int sm_count);
+int gemv_stream_launch(const GemvParams& base, int ntw, int w, int kw, int sm_count, int max_smem_optin,
+                       cudaStream_t stream, bool overlap_previous);
+
+// The streaming kernel pays off for very large matrices only (measured: level with the per-split grid
+// up to ~120 MB of packed weights, ahead of it at 16 rows beyond that): at least 32 units per resident CTA.
+static bool stream_by_default(const GemvPlan& plan, int nblk, int ntiles, int sm_count) {
+  const long long units = static_cast<long long>(plan_ncol(ntiles, 4, plan.w, plan.kw)) * ((nblk + plan.kw - 1) / plan.kw);
+  return units >= 32LL * (plan.w == 8 ? 2 : 1) * sm_count;
+}
+
 // The arrival counters sit in a fixed-size slot at the start of the workspace,
 // independent of the problem shape, so that one workspace can serve linears of
 // different sizes: partial sums of one call can then never land where another
 // call expects clean counters.
-constexpr int kGemvMaxCounters = 4096;
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
 template <int NTW, int MT, int KW, int W>
@@ -662,6 +580,24 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   p.bps = plan.bps;
   p.S = plan.S;
   p.ntiles = ntiles;
+  const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
+  bool use_stream = force_bps < 1 && stream_by_default(plan, nblk, ntiles, di.sm_count);
+  if (flags & AWQ_B200_GEMV_STREAM) use_stream = true;
+  if (flags & AWQ_B200_GEMV_PER_SPLIT) use_stream = false;
+  if (use_stream) {
+    p.bps = 0; p.S = 0; p.cluster = 0;
+    const int slots = gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, di.sm_count);
+    if (slots > 1) {
+      const size_t cb = counter_bytes(N);
+      const size_t need = cb + static_cast<size_t>(slots) * M * N * sizeof(float);
+      if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
+      if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
+      p.counters = static_cast<unsigned*>(workspace);
+      p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + cb);
+    }
+    return gemv_stream_launch(p, plan.ntw, plan.w, plan.kw, di.sm_count, di.max_smem_optin, stream, overlap);
+  }
+
   // A cluster needs its CTAs resident together; beyond one CTA per SM that costs more occupancy than the
   // shared-memory reduction saves.
   p.cluster = (plan.S >= 2 && plan.S <= 8 && static_cast<long long>(plan.ncol) * plan.S <= di.sm_count &&
@@ -676,7 +612,6 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   }
 
   const bool wide = M > 8;
-  const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
 #define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                             \
   if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                        \
     return wide ? launch_gemv<NTW_, 16, KW_, W_>(p, plan, di.max_smem_optin, stream, overlap)    \
@@ -709,8 +644,12 @@ size_t awq_b200_gemv_workspace_bytes(int M, int K, int N) {
   DeviceInfo di;
   int sm = 148;
   if (device_info(&di) == AWQ_B200_OK) sm = di.sm_count;
-  const GemvPlan plan = plan_gemv(K, N, sm);
-  return counter_bytes(N) + static_cast<size_t>(plan.S) * M * N * sizeof(float);
+  GemvPlan plan = plan_gemv(K, N, sm);
+  if (M > 8) plan.ntw = 2;
+  plan.ncol = plan_ncol(N / 8, plan.ntw, plan.w, plan.kw);
+  size_t slots = static_cast<size_t>(plan.S);
+  if (stream_by_default(plan, K / kBlockK, N / 8, sm)) slots = static_cast<size_t>(gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, sm));
+  return counter_bytes(N) + slots * M * N * sizeof(float);
 }
 
 int awq_b200_gemv(const void* x, const void* packed, const void* scales, const int32_t* qzeros,

@@ -131,21 +131,31 @@ def _run(fn, name, x, pw, bias, ws_bytes, out=None, extra=()):
     return y
 
 
-def gemv(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, no_cluster: bool = False) -> torch.Tensor:
+def _gemv_flags(overlap: bool, no_cluster: bool, mode) -> int:
+    if mode not in (None, "stream", "per_split"):
+        raise ValueError(f"mode must be None, 'stream' or 'per_split', got {mode!r}")
+    return ((_lib.OVERLAP_PREVIOUS if overlap else 0) | (_lib.NO_CLUSTER if no_cluster else 0) |
+            (_lib.GEMV_STREAM if mode == "stream" else 0) | (_lib.GEMV_PER_SPLIT if mode == "per_split" else 0))
+
+
+def gemv(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, no_cluster: bool = False,
+         mode=None) -> torch.Tensor:
     """Decode kernel, 1 <= M <= 16.  `overlap=True` lets the kernel prefetch its weights while the
     previous kernel of the stream drains; pass it only when the weights are not being written by
-    work still queued on that stream (i.e. not right after `repack`)."""
-    return _run(lib.awq_b200_gemv_ex, "awq_b200_gemv", x, pw, bias,
-                lib.awq_b200_gemv_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
-                ((_lib.OVERLAP_PREVIOUS if overlap else 0) | (_lib.NO_CLUSTER if no_cluster else 0),))
+    work still queued on that stream (i.e. not right after `repack`).  `mode` forces the persistent
+    stream ("stream") or the one-CTA-per-split grid ("per_split"); None lets the library choose."""
+    M = max(x.shape[0], 1)
+    ws = (lib.awq_b200_gemv_workspace_bytes(M, pw.K, pw.N) if mode is None
+          else lib.awq_b200_gemv_workspace_bytes_max(M, pw.K, pw.N))
+    return _run(lib.awq_b200_gemv_ex, "awq_b200_gemv", x, pw, bias, ws, out, (_gemv_flags(overlap, no_cluster, mode),))
 
 
 def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None, overlap: bool = False,
-              no_cluster: bool = False, kw: int = 0) -> torch.Tensor:
+              no_cluster: bool = False, kw: int = 0, mode=None) -> torch.Tensor:
     """Decode kernel with a forced decomposition (tuning and tests)."""
     return _run(lib.awq_b200_gemv_plan, "awq_b200_gemv_plan", x, pw, bias,
                 lib.awq_b200_gemv_workspace_bytes_max(max(x.shape[0], 1), pw.K, pw.N), out,
-                (ntw, kw, bps, (_lib.OVERLAP_PREVIOUS if overlap else 0) | (_lib.NO_CLUSTER if no_cluster else 0)))
+                (ntw, kw, bps, _gemv_flags(overlap, no_cluster, mode)))
 
 
 def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:

@@ -135,6 +135,43 @@ def test_gemv_every_decomposition(K_, ntw, kw, bps):
     assert K_.gemv_status() == 0
 
 
+@pytest.mark.parametrize("kw", [1, 2, 4, 8, 104, 108, 116])   # 1xx = 16 compute warps per CTA
+@pytest.mark.parametrize("K,N", [(2048, 1096), (1024, 264), (6144, 2048), (4096, 11008)])
+def test_gemv_stream_every_decomposition(K_, kw, K, N):
+    """The persistent stream variant: every in-CTA k split, ragged column counts, column groups that
+    straddle CTAs (partials + last-arriver reduction) and ones that do not; deterministic; a row's
+    bits independent of the row count (which switches the kernel to two passes per segment)."""
+    qw, qz, sc = tensors(K, N, 128, seed=K + N)
+    x = orc.make_activations(16, K, seed=5)
+    ref = orc.linear_forward(x, qw, qz, sc, 128)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    y16 = K_.gemv_plan(dev(x), pw, 0, 0, kw=kw, mode="stream")
+    assert orc.max_normalised_error(y16.cpu().numpy(), ref) <= TOL
+    assert torch.equal(y16, K_.gemv_plan(dev(x), pw, 0, 0, kw=kw, mode="stream", overlap=True))
+    for M in (1, 5, 8, 9):
+        yM = K_.gemv_plan(dev(x[:M]), pw, 0, 0, kw=kw, mode="stream")
+        assert torch.equal(yM, y16[:M]), f"rows differ between M={M} and M=16"
+    for ntw in (2, 4):     # column tiles per warp never change the order of additions
+        assert torch.equal(K_.gemv_plan(dev(x[:3]), pw, ntw, 0, kw=kw, mode="stream"), y16[:3])
+    assert K_.gemv_status() == 0
+
+
+def test_gemv_stream_and_per_split_agree(K_):
+    """The two ways of handing out the work group a column's k blocks differently, so they agree
+    to fp32 rounding; both stay within the tolerance of the oracle."""
+    K, N, M = 8192, 4096, 4
+    qw, qz, sc = tensors(K, N, 128, seed=21)
+    x = orc.make_activations(M, K, seed=22)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    a = K_.gemv(dev(x), pw, mode="stream").float()
+    b = K_.gemv(dev(x), pw, mode="per_split").float()
+    assert ((a - b).abs().max() / b.abs().max()).item() <= 1e-3
+    ref = orc.linear_forward(x, qw, qz, sc, 128)
+    assert orc.max_normalised_error(a.cpu().numpy(), ref) <= TOL
+    with pytest.raises(ValueError):
+        K_.gemv(dev(x), pw, mode="bogus")
+
+
 def test_gemv_row_result_independent_of_batch(K_):
     """A row's bits must not depend on M (decode q_len=1 and verify q_len=2 must agree,
     LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:161-166) nor on the run."""
