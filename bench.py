@@ -502,11 +502,12 @@ def run_profile_case(args, torch):
     """Small, self-terminating cases for `ncu` captures (a few launches, a few hundred MB)."""
     from llmrqt_sdv1_b200 import kernels, quantize
     torch.cuda.set_device(0)
-    if args.profile_case.startswith("gemv"):
+    if args.profile_case.startswith("gemv") or args.profile_case.startswith("skinny"):
         # gemv / gemv16: 24 distinct 2048x12288 weights (13 MB each, 314 MB > L2), two passes
-        # gemv70b: one 8192x57344 weight (235 MB > L2), three launches
-        M = 16 if args.profile_case == "gemv16" else 1
-        K, N, copies, passes = (8192, 57344, 1, 3) if args.profile_case == "gemv70b" else (2048, 12288, 24, 2)
+        # gemv70b / skinny70b / skinny70b_m16: one 8192x57344 weight (235 MB > L2), three launches
+        M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else 1
+        fn = kernels.skinny if args.profile_case.startswith("skinny") else kernels.gemv
+        K, N, copies, passes = (8192, 57344, 1, 3) if "70b" in args.profile_case else (2048, 12288, 24, 2)
         qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
         base = kernels.make_packed(qw, qz, sc, GROUP)
         pws = [base] + [kernels.PackedWeight(base.packed.clone(), qz, sc, K, N, GROUP) for _ in range(copies - 1)]
@@ -514,7 +515,7 @@ def run_profile_case(args, torch):
         y = torch.empty((M, N), dtype=torch.float16, device="cuda")
         for _ in range(passes):
             for pw in pws:
-                kernels.gemv(x, pw, out=y)
+                fn(x, pw, out=y)
     else:
         M, K, N = {"gemm_large": (8192, 4096, 28672), "gemm_m64": (64, 4096, 28672)}.get(args.profile_case, (2048, 4096, 6144))
         qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
@@ -538,7 +539,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp", "qwen3_e2e"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "gemm", "gemm_large", "gemm_m64"],
+    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

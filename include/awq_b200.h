@@ -207,6 +207,20 @@ AWQ_B200_API int awq_b200_gemm_wtm(const void* x, const void* packed, const void
                       const void* bias, void* y, int M, int K, int N, int group_size,
                       void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
 
+/* Few activation rows (1 <= M <= 64) on the tensor-memory path with split-K: the packed weights are
+ * cut into units of 256 columns x 128 k, every SM streams an equal share of the units through one
+ * copy pipeline, dequantises them into tensor memory as the tcgen05.mma A operand and accumulates in
+ * fp32; column tiles shared by several SMs are completed through fp32 partials added in k order.
+ * Same arguments and output contract as awq_b200_gemv_ex (bit-exact reference fp16 weights, fp32
+ * accumulation, one fp16 rounding, then the bias); a row's bits do not depend on M.  The workspace
+ * must hold awq_b200_skinny_workspace_bytes(M, K, N) bytes, start zero-initialised and is left
+ * clean.  Replaces the same reference calls as awq_b200_gemv
+ * (LLMQRT/runtime_refact/csrc/awq/gemv.cu:168-206 for one row, awq/gemm.cu:195-229 for several). */
+AWQ_B200_API size_t awq_b200_skinny_workspace_bytes(int M, int K, int N);
+AWQ_B200_API int awq_b200_skinny(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                    const void* bias, void* y, int M, int K, int N, int group_size,
+                    void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
+
 /* Tuning hook: awq_b200_gemm_wtm with the activation-row tile forced (64, 128, 192; 0 = by M). */
 AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales,
                            const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
@@ -220,15 +234,18 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
-/* M <= 16 -> awq_b200_gemv, else awq_b200_gemm.  Mirrors the row-count switch
- * in AWQLinearMMFunction.forward
+/* Picks the kernel from the row count and the shape: M <= 16 -> awq_b200_gemv, or awq_b200_skinny
+ * once the packed weights reach 48 MiB (a choice that depends on K and N only, so a row's bits do
+ * not change with the number of rows decoded together); 17 <= M <= 64 -> awq_b200_skinny where the
+ * GEMM would leave most SMs idle (N <= 18944 and K >= 4096); awq_b200_gemm otherwise.  Mirrors the
+ * row-count switch in AWQLinearMMFunction.forward
  * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), with
  * the threshold moved from 8 to 16 rows. */
 AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
 
-/* awq_b200_linear with call flags (the flags only affect the GEMV branch). */
+/* awq_b200_linear with call flags (the flags only affect the few-row kernels). */
 AWQ_B200_API int awq_b200_linear_ex(const void* x, const void* packed, const void* scales,
                        const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
                        int group_size, void* workspace, size_t workspace_bytes,

@@ -40,6 +40,8 @@ SIGNATURES = {
     "awq_b200_gemm_smem": (_I, _COMPUTE),
     "awq_b200_gemm_wtm": (_I, _COMPUTE),
     "awq_b200_gemm_wtm_tile": (_I, _COMPUTE + [_I]),
+    "awq_b200_skinny_workspace_bytes": (_Z, [_I, _I, _I]),
+    "awq_b200_skinny": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_gemv_max_rows": (_I, []),
     "awq_b200_linear_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_linear": (_I, _COMPUTE),

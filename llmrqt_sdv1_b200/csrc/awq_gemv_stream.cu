@@ -34,12 +34,6 @@ struct GemvStreamParams {
   long long units;     // ncol * ipc
 };
 
-// First unit of CTA b and the CTA that owns unit u, for G CTAs over U units.
-__host__ __device__ inline long long stream_first_unit(long long b, long long U, long long G) { return b * U / G; }
-__host__ __device__ inline int stream_cta_of(long long u, long long U, long long G) {
-  return static_cast<int>(((u + 1) * G + U - 1) / U - 1);
-}
-
 template <int W>
 __device__ __forceinline__ void compute_warps_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");

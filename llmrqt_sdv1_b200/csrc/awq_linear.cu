@@ -1,32 +1,58 @@
-// Row-count dispatch between the decode GEMV and the prefill GEMM.
+// Row-count and shape dispatch between the three linear kernels: the mma.sync decode GEMV, the
+// tensor-memory split-K kernel for few rows of a large matrix, and the prefill GEMM.
 #include "awq_common.cuh"
 
 namespace {
 constexpr size_t kGemmStatusBytes = 256;  // leading slot of the shared workspace: GEMM status word
+constexpr int kSkinnyMaxRows = 64;
+
+// Which kernel serves M rows of a K x N linear.  The choice for M <= 16 depends on (K, N) only, so a
+// row's bits do not change with the number of rows decoded together.
+//   rows <= 16: the split-K tensor-memory kernel once the packed weights reach 48 MiB (it is level with
+//               the GEMV at one row there and about twice as fast at 16 rows), the GEMV below that.
+//   17..64:     the same kernel where the GEMM would leave most SMs idle (at most 74 column tiles of
+//               256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
+enum class Route { kGemv, kSkinny, kGemm };
+Route route(int M, int K, int N) {
+  const long long packed_bytes = static_cast<long long>(K) * N / 2;
+  if (M <= awq_b200_gemv_max_rows()) return packed_bytes >= (48ll << 20) ? Route::kSkinny : Route::kGemv;
+  if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
+  return Route::kGemm;
 }
+}  // namespace
 
 extern "C" {
 
 size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
-  const int gemv_rows = M < awq_b200_gemv_max_rows() ? M : awq_b200_gemv_max_rows();
-  return kGemmStatusBytes + awq_b200_gemv_workspace_bytes(gemv_rows < 1 ? 1 : gemv_rows, K, N);
+  if (M < 1) M = 1;
+  size_t need = 0;
+  switch (route(M, K, N)) {
+    case Route::kGemv: need = awq_b200_gemv_workspace_bytes(M, K, N); break;
+    case Route::kSkinny: need = awq_b200_skinny_workspace_bytes(M, K, N); break;
+    case Route::kGemm: need = 0; break;
+  }
+  return kGemmStatusBytes + need;
 }
 
 // Workspace layout: [0, 256) GEMM status word (zero unless a device-side wait
-// expired), then the GEMV workspace (arrival counters first).  All of it must
+// expired), then the decode kernels' workspace (arrival counters first).  All of it must
 // be zero before the first call.
 int awq_b200_linear_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                        const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                        size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
   if (M < 1) return AWQ_B200_ERR_SHAPE;
   if (!workspace || workspace_bytes < kGemmStatusBytes) return AWQ_B200_ERR_WORKSPACE;
-  if (M <= awq_b200_gemv_max_rows()) {
-    return awq_b200_gemv_ex(x, packed, scales, qzeros, bias, y, M, K, N, group_size,
-                            static_cast<unsigned char*>(workspace) + kGemmStatusBytes,
-                            workspace_bytes - kGemmStatusBytes, stream, flags);
+  unsigned char* rest = static_cast<unsigned char*>(workspace) + kGemmStatusBytes;
+  const size_t rest_bytes = workspace_bytes - kGemmStatusBytes;
+  switch (route(M, K, N)) {
+    case Route::kGemv:
+      return awq_b200_gemv_ex(x, packed, scales, qzeros, bias, y, M, K, N, group_size, rest, rest_bytes, stream, flags);
+    case Route::kSkinny:
+      return awq_b200_skinny(x, packed, scales, qzeros, bias, y, M, K, N, group_size, rest, rest_bytes, stream, flags);
+    case Route::kGemm:
+      break;
   }
-  return awq_b200_gemm(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
-                       kGemmStatusBytes, stream);
+  return awq_b200_gemm(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, kGemmStatusBytes, stream);
 }
 
 int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,

@@ -32,6 +32,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the warp may sleep in hardware until the phase
+// completes or the hint runs out, instead of coming back to spin and take issue slots from the warps
+// that have work.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and raises *abort_flag) if the phase did not
 // complete in time or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
@@ -39,7 +53,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const unsigned long long t0 = clock64();
   unsigned spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_sleep(bar, parity, 2000u)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitLimitCycles) {

@@ -102,6 +102,45 @@ __device__ __forceinline__ void tcgen05_mma_f16_ts_warp(uint32_t d_tmem, uint32_
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Eight k-steps (128 k) of A-from-tensor-memory MMAs into one accumulator, then two commits, all
+// issued by one elected lane under a single election: A advances 8 tensor-memory columns per step;
+// the B descriptor advances `step_lo` (in 16-byte units) per step inside a 64-k half and `half_lo`
+// between the two halves.  `accumulate_first` = 0 starts a new accumulation.  Keeping the whole
+// group in one statement keeps the issuing warp's instruction count per unit small, which matters
+// because it shares its scheduler with busy dequant warps.
+__device__ __forceinline__ void tcgen05_mma_f16_ts_k8_commit2_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                                   uint32_t step_lo, uint32_t half_lo, uint32_t idesc,
+                                                                   uint32_t accumulate_first, uint32_t bar0,
+                                                                   uint32_t bar1) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi, lo0;\n\t.reg .b64 d;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "mov.b64 {lo0, hi}, %2;\n\t"
+      // first half: steps 0..3
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %5, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "add.u32 a, %1, 8;\n\t  add.u32 lo, lo0, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      // second half: steps 4..7
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo0, %4;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "add.u32 a, a, 8;\n\t  add.u32 lo, lo, %3;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %5, p;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(step_lo), "r"(half_lo), "r"(idesc), "r"(accumulate_first),
+        "r"(bar0), "r"(bar1)
+      : "memory");
+}
 __device__ __forceinline__ void tcgen05_commit_warp(uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred e;\n\t"

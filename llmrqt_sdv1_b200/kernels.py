@@ -158,6 +158,13 @@ def gemv_plan(x, pw: PackedWeight, ntw: int, bps: int, bias=None, out=None, over
                 (ntw, kw, bps, _gemv_flags(overlap, no_cluster, mode)))
 
 
+def skinny(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """Few rows (1 <= M <= 64) on the tensor-memory path with split-K over all SMs."""
+    return _run(lib.awq_b200_skinny, "awq_b200_skinny", x, pw, bias,
+                lib.awq_b200_skinny_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
+                (_lib.OVERLAP_PREVIOUS if overlap else 0,))
+
+
 def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
     """Prefill kernel (tcgen05), any M >= 1."""
     return _run(lib.awq_b200_gemm, "awq_b200_gemm", x, pw, bias,

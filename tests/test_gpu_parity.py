@@ -262,6 +262,57 @@ def test_gemm_matches_gemv_rows(K_):
 
 
 # --------------------------------------------------------------------------- full-size properties
+@pytest.mark.parametrize("K,N,G", [(128, 8, 128), (256, 264, 128), (1024, 1096, 128), (2048, 2048, 256),
+                                   (6144, 2048, 128), (4096, 4096, 128)])
+def test_skinny_vs_oracle(K_, K, N, G):
+    """The tensor-memory split-K kernel for 1..64 rows: ragged column counts (not a multiple of 32 or
+    of the 256-column tile), one k block, group 256, column tiles shared by several SMs and not."""
+    qw, qz, sc = tensors(K, N, G, seed=K + N)
+    x = orc.make_activations(64, K, seed=6)
+    ref = orc.linear_forward(x, qw, qz, sc, G)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    y64 = K_.skinny(dev(x), pw)
+    assert y64.shape == (64, N) and y64.dtype == torch.float16
+    assert orc.max_normalised_error(y64.cpu().numpy(), ref) <= TOL
+    for M in (1, 3, 16, 17, 33):
+        yM = K_.skinny(dev(x[:M]), pw, overlap=(M % 2 == 1))
+        assert torch.equal(yM, y64[:M]), f"rows differ between M={M} and M=64"
+    assert K_.gemv_status() == 0
+
+
+def test_skinny_bias_and_bounds(K_):
+    K, N = 1024, 520
+    qw, qz, sc = tensors(K, N, 128, seed=31)
+    x = orc.make_activations(5, K, seed=32)
+    bias = (np.random.default_rng(33).standard_normal(N) * 0.5).astype(np.float16)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
+    y = K_.skinny(dev(x), pw, bias=dev(bias))
+    ref = orc.linear_forward(x, qw, qz, sc, 128, bias=bias)
+    assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
+    # same weights as the GEMM path: identical dequantised operands, fp32 accumulation
+    yg = K_.gemm(dev(x), pw, bias=dev(bias))
+    assert ((y.float() - yg.float()).abs().max() / yg.float().abs().max()).item() <= 1e-3
+    with pytest.raises(ValueError):
+        K_.skinny(dev(orc.make_activations(65, K, seed=1)), pw)
+
+
+def test_linear_routes_large_shapes_to_skinny(K_):
+    """A shape above the 48 MiB switch: linear() must give the skinny kernel's bits for every M <= 16
+    (one kernel for all small row counts, so rows stay independent of the batch) and for 17..64 rows
+    when the GEMM would have few column tiles."""
+    K, N = 12288, 8192                      # 48 MiB packed, 32 column tiles, 96 k blocks
+    qw, qz, sc = _random_packed_inputs(K, N, 128, seed=40)
+    pw = K_.make_packed(qw, qz, sc, 128)
+    x = torch.randn((40, K), device="cuda", dtype=torch.float16)
+    y40 = K_.linear(x, pw)
+    assert torch.equal(y40, K_.skinny(x, pw))
+    for M in (1, 8, 9, 16, 17):
+        assert torch.equal(K_.linear(x[:M].contiguous(), pw), y40[:M])
+    W = K_.dequantize_packed(pw)
+    ref = x.float() @ W.float()
+    assert ((y40.float() - ref).abs().max() / ref.abs().max()).item() <= TOL
+
+
 def _random_packed_inputs(K, N, G, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     qw = torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
