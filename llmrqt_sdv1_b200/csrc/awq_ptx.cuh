@@ -5,6 +5,9 @@
 namespace awq {
 
 constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // ~2 s at 2 GHz
+#ifndef AWQ_WAIT_HINT_NS
+#define AWQ_WAIT_HINT_NS 2000u   // suspend-time hint of a blocked mbarrier wait
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -53,7 +56,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const unsigned long long t0 = clock64();
   unsigned spins = 0;
   while (true) {
-    if (mbar_try_wait_sleep(bar, parity, 2000u)) return true;
+    if (mbar_try_wait_sleep(bar, parity, AWQ_WAIT_HINT_NS)) return true;
+#ifdef AWQ_WAIT_NANOSLEEP
+    __nanosleep(AWQ_WAIT_NANOSLEEP);
+#endif
     if ((++spins & 63u) == 0u) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitLimitCycles) {

@@ -21,7 +21,8 @@
 //               depends on (K, N) only and the MMA N extent does not change how an element is summed.
 //
 // Warps: 0 and 18 copy producers (even / odd units), 1 and 19 MMA issuers (low / high 128 columns),
-// 2..17 dequantise and, at the end of a segment, drain the accumulators.
+// 2..17 dequantise (two groups of eight that take the units in turn) and, at the end of a segment,
+// drain the accumulators.
 // TMEM columns: [0, MT) and [MT, 2MT) accumulators of the two halves, then the A ring (128 columns
 // per unit: 64 per half).  Every mbarrier wait is bounded (see awq_ptx.cuh).
 #include "awq_gemv_common.cuh"
@@ -102,7 +103,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   auto stage_addr = [&](int t) { return base + t * Cfg::kStageBytes; };
   const uint32_t bar_base = base + NT * Cfg::kStageBytes;
   auto bar_full_tma = [&](int t) { return bar_base + 8u * t; };
-  auto bar_empty_tma = [&](int t) { return bar_base + 8u * (NT + t); };    // 16 dequant warps + 2 MMA commits
+  auto bar_empty_tma = [&](int t) { return bar_base + 8u * (NT + t); };    // 8 dequant warps + 2 MMA commits
   auto bar_a_full = [&](int a) { return bar_base + 8u * (2 * NT + a); };
   auto bar_a_empty = [&](int a) { return bar_base + 8u * (2 * NT + NA + a); };
   const uint32_t bar_acc_full = bar_base + 8u * (2 * NT + 2 * NA);
@@ -115,10 +116,10 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     s_abort = 0;
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_full_tma(t), 1);
-      mbar_init(bar_empty_tma(t), kSkDequantWarps + 2);
+      mbar_init(bar_empty_tma(t), kSkDequantWarps / 2 + 2);
     }
     for (int a = 0; a < NA; ++a) {
-      mbar_init(bar_a_full(a), kSkDequantWarps);
+      mbar_init(bar_a_full(a), kSkDequantWarps / 2);
       mbar_init(bar_a_empty(a), 2);
     }
     mbar_init(bar_acc_full, 2);
@@ -250,21 +251,23 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     __syncwarp();
   } else {
     // ---------------------- dequantise, then drain accumulators ---------------
-    // Warp (quarter q, half h, k half kh): thread = column h*128 + 32q + lane, words [8kh, 8kh+8) of
-    // the column's 16 words of the unit -> 32 tensor-memory columns (two stores of 16).
+    // Warp (quarter q, half h, group g): thread = column h*128 + 32q + lane.  The two groups take the
+    // units in turn, so that one group's latency chain (wait, unpack, tensor-memory store, arrive)
+    // overlaps the other's; a thread unpacks all 16 words of its column per unit it handles: 64
+    // tensor-memory columns, four stores of 16.
     asm volatile("griddepcontrol.wait;" ::: "memory");   // y and the workspace belong to the previous kernel until here
     const int id = tid - 64;                  // 0..511
     const int dq_warp = id >> 5;              // 0..15
     const int lane_q = warp & 3;              // TMEM lane quarter this warp may touch
     const int idx = dq_warp >> 2;             // 0..3, each (quarter, idx) pair exactly once
-    const int h = idx & 1, kh = idx >> 1;
+    const int h = idx & 1, grp = idx >> 1;
     const int cl = h * 128 + lane_q * 32 + lane;            // column within the tile
     const uint32_t lane_addr = static_cast<uint32_t>(lane_q * 32) << 16;
     const uint32_t raw_off = static_cast<uint32_t>(Cfg::kRawOff + cl * 64);
     const uint32_t swz = static_cast<uint32_t>((cl >> 1) & 3);
     const int zcols = p.N >> 3;
     // epilogue role: half e_h, rows [e_part * MT/2, +MT/2)
-    const int e_h = h, e_part = kh;
+    const int e_h = h, e_part = grp;
     bool ok = true;
     int gs = 0, seg = 0;
     while (gs < my_units) {
@@ -280,6 +283,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       int sz_group = -1;
 
       for (int j = 0; j < seg_units; ++j, ++gs) {
+        if ((gs & 1) != grp) continue;                           // the other group's unit
         const int t = gs % NT, a = gs % NA;
         const uint32_t ph = static_cast<uint32_t>(gs / NT) & 1u, pha = static_cast<uint32_t>(gs / NA) & 1u;
         if (!sz_by_copy) {
@@ -290,28 +294,30 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             sz_group = qgrp;
           }
         }
-        if (dq_warp == 0) SK_TRACE(2, gs, 0);
+        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 0);
         if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
         if (!ok) continue;
-        if (dq_warp == 0) SK_TRACE(2, gs, 1);
+        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 1);
         const unsigned char* stage = base_ptr + t * Cfg::kStageBytes;
         if (sz_by_copy) {
-          sc = nvalid ? reinterpret_cast<const uint16_t*>(stage + Cfg::kSzOff)[cl] : 0u;
-          zw = nvalid ? reinterpret_cast<const uint32_t*>(stage + Cfg::kSzOff + 512)[cl >> 3] : 0u;
+          // Columns beyond N read stale shared memory here; their lanes of the product are never stored.
+          sc = reinterpret_cast<const uint16_t*>(stage + Cfg::kSzOff)[cl];
+          zw = reinterpret_cast<const uint32_t*>(stage + Cfg::kSzOff + 512)[cl >> 3];
         }
-        uint4 r[2];
+        uint4 r[4];
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-          r[c] = *reinterpret_cast<const uint4*>(stage + raw_off + (((2 * kh + c) ^ swz) << 4));
+        for (int c = 0; c < 4; ++c)
+          r[c] = *reinterpret_cast<const uint4*>(stage + raw_off + ((static_cast<uint32_t>(c) ^ swz) << 4));
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; continue; }
-        if (dq_warp == 0) SK_TRACE(2, gs, 2);
+        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 2);
         tcgen05_fence_after();
         const ZeroPair zp = make_zero_pair((zw >> zsh) & 0xFu);
         const uint32_t s2 = sc * 0x00010001u;
+        const uint32_t a_addr = tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + a * 128 + h * 64);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           const uint32_t w[4] = {r[c].x, r[c].y, r[c].z, r[c].w};
           uint32_t o[16];
 #pragma unroll
@@ -326,11 +332,11 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 #endif
             o[4 * i + 0] = q4[0]; o[4 * i + 1] = q4[1]; o[4 * i + 2] = q4[2]; o[4 * i + 3] = q4[3];
           }
-          tcgen05_st_32x32b_x16(tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + a * 128 + h * 64 + kh * 32 + c * 16), o);
+          tcgen05_st_32x32b_x16(a_addr + static_cast<uint32_t>(c * 16), o);
         }
-        if (dq_warp == 0) SK_TRACE(2, gs, 3);
+        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 3);
         tcgen05_wait_st();
-        if (dq_warp == 0) SK_TRACE(2, gs, 4);
+        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 4);
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_a_full(a));
