@@ -193,7 +193,7 @@ def decode_detail(torch, kernels, quantize, peaks):
 
             def fn():
                 for pw, y in zip(pws, ys):
-                    kernels.gemv(x, pw, out=y, overlap=True)
+                    kernels.linear(x, pw, out=y, overlap=True)
             ms = time_graph(torch, fn, iters=5) / copies
             gbs = gemv_bytes(M, K, N) / (ms * 1e-3) / 1e9
             rows.append({"linear": name, "K": K, "N": N, "M": M, "us": round(ms * 1e3, 3), "gbs": round(gbs, 1),
@@ -241,7 +241,7 @@ def run_qwen3_decode(args, torch, peaks):
 
     def step():
         for pw, y in zip(pws, ys):
-            kernels.gemv(xs[pw.K], pw, out=y, overlap=True)
+            kernels.linear(xs[pw.K], pw, out=y, overlap=True)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -360,8 +360,8 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
 
     def step():
         for i in range(FFN70B_LAYERS):
-            kernels.gemv(x_g, pw_g[i], out=y_g[i], overlap=True)
-            kernels.gemv(x_d, pw_d[i], out=y_d[i], overlap=True)
+            kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
+            kernels.linear(x_d, pw_d[i], out=y_d[i], overlap=True)
             if world > 1:
                 dist.all_reduce(y_d[i])
 
@@ -427,6 +427,49 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     e2e_ms = float(t2.item())
+    # The other row counts of the sharded configuration: M = 16 (decode batch) and M = 4096 (prefill),
+    # same layers, same all-reduce, device time, max over ranks.
+    tp_detail = []
+    for Md in (16, 4096):
+        xg = torch.randn((Md, Kg), device=dev).half()
+        xd = torch.randn((Md, kd_local), device=dev).half()
+        yg = torch.empty((Md, ng_local), dtype=torch.float16, device=dev)
+        yd = torch.empty((Md, Nd), dtype=torch.float16, device=dev)
+
+        def step_m():
+            for i in range(FFN70B_LAYERS):
+                kernels.linear(xg, pw_g[i], out=yg)
+                kernels.linear(xd, pw_d[i], out=yd)
+                if world > 1:
+                    dist.all_reduce(yd)
+        for _ in range(3):
+            step_m()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5 if Md == 16 else 2
+        e0.record()
+        for _ in range(reps):
+            step_m()
+        e1.record()
+        torch.cuda.synchronize()
+        tm = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms_m = float(tm.item())
+        flops = 2.0 * Md * (Kg * Ng + Kd * Nd) * FFN70B_LAYERS
+        row = {"M": Md, "ms_per_step": round(ms_m, 4)}
+        if Md <= 64:
+            gb = FFN70B_LAYERS * (gemv_bytes(Md, Kg, Ng) + gemv_bytes(Md, Kd, Nd)) / (ms_m * 1e-3) / 1e9
+            row.update({"gbs_all_ranks": round(gb, 1), "frac_measured_per_gpu": round(gb / world / peaks["hbm_gbs"], 4)})
+        else:
+            tf = flops / (ms_m * 1e-3) / 1e12
+            row.update({"tflops_all_ranks": round(tf, 1),
+                        "frac_measured_per_gpu": round(tf / world / peaks["tflops"], 4),
+                        "frac_nominal_per_gpu": round(tf / world / 2250.0, 4)})
+        tp_detail.append(row)
+        del xg, xd, yg, yd
     if rank != 0:
         return
     value = step_bytes_total / (ms * 1e-3) / 1e9
@@ -441,11 +484,11 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                    "l2": "inputs larger than L2 (8 distinct layers per step)", "cuda_graph": graphed},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "awq::gemv_kernel (+ncclAllReduce in the step)", "per_gpu": True},
+                     "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+ncclAllReduce in the step)", "per_gpu": True},
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
                 "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
-        "gpu_launches": 2 * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(),
+        "gpu_launches": 2 * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
     }
     print(json.dumps(line), flush=True)
 
