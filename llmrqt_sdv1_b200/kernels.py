@@ -191,12 +191,12 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
 
 
 def gemv_status(dev: torch.device | None = None) -> int:
-    """Status word of the decode kernel in this stream's workspaces (0 = no device-side wait expired).
+    """Status word of the decode kernels (GEMV and split-K tensor-memory kernel) in this stream's workspaces (0 = no device-side wait expired).
     Synchronises."""
     dev = dev or torch.device("cuda", torch.cuda.current_device())
     stream = torch.cuda.current_stream(dev).cuda_stream
     status = 0
-    for kind, off in (("awq_b200_gemv", 0), ("awq_b200_gemv_plan", 0), ("awq_b200_linear", 256)):
+    for kind, off in (("awq_b200_gemv", 0), ("awq_b200_gemv_plan", 0), ("awq_b200_skinny", 0), ("awq_b200_linear", 256)):
         ws = _workspaces.get((dev.index, stream, kind))
         if ws is not None:
             status |= int(ws[off + 4095 * 4: off + 4096 * 4].view(torch.int32).item())
