@@ -427,6 +427,17 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     e2e_ms = float(t2.item())
+    # The same M = 1 step without the all-reduce (what the collective costs): device time, max over ranks.
+    def step_local():
+        for i in range(FFN70B_LAYERS):
+            kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
+            kernels.linear(x_d, pw_d[i], out=y_d[i], overlap=True)
+    ms_local = time_graph(torch, step_local, iters=max(args.steps, 5))
+    t3 = torch.tensor([ms_local], device=dev)
+    if world > 1:
+        dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+    ms_local = float(t3.item())
+
     # The other row counts of the sharded configuration: M = 16 (decode batch) and M = 4096 (prefill),
     # same layers, same all-reduce, device time, max over ranks.
     tp_detail = []
@@ -489,6 +500,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
                 "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
         "gpu_launches": 2 * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
+        "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
     }
     print(json.dumps(line), flush=True)
 
