@@ -181,6 +181,11 @@ AWQ_B200_API int awq_b200_gemv_plan(const void* x, const void* packed, const voi
 
 /* ---- prefill: TMA + tcgen05/TMEM GEMM, any M >= 1 ----------------------- */
 
+/* Workspace of the GEMM entry points.  Its first 256 bytes (status word) must be zero before the first
+ * call; 256 bytes are enough for a correct result.  With the full size returned here the tensor-memory
+ * kernel may cut the tiles of a partial last wave along k, share them between all SMs and finish them
+ * through fp32 partial tiles that a small second kernel adds in k order (deterministic; equal to the
+ * one-CTA-per-tile result to fp32 rounding). */
 AWQ_B200_API size_t awq_b200_gemm_workspace_bytes(int M, int K, int N);
 
 /* Y[M, N] = X[M, K] . W (+ bias) with fp32 accumulation in tensor memory.
@@ -196,7 +201,7 @@ AWQ_B200_API int awq_b200_gemm(const void* x, const void* packed, const void* sc
 
 /* Tuning hook: awq_b200_gemm restricted to the kernel that stages the dequantised weights in
  * shared memory (awq_b200_gemm itself picks per shape between that kernel and awq_b200_gemm_wtm;
- * both produce identical bits). */
+ * both produce identical bits as long as every tile is finished by one CTA). */
 AWQ_B200_API int awq_b200_gemm_smem(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                        const void* bias, void* y, int M, int K, int N, int group_size,
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);

@@ -108,6 +108,13 @@ __device__ __forceinline__ void dequant_word(uint32_t w, ZeroPair zp, uint32_t s
   out[3] = h2_mul(h2_fma(a3, kSixteenth, zp.hi), s2);
 }
 
+// Even split of U work units over G persistent CTAs (G <= U): CTA b owns units
+// [stream_first_unit(b), stream_first_unit(b + 1)), and stream_cta_of(u) is the CTA that owns unit u.
+__host__ __device__ inline long long stream_first_unit(long long b, long long U, long long G) { return b * U / G; }
+__host__ __device__ inline int stream_cta_of(long long u, long long U, long long G) {
+  return static_cast<int>(((u + 1) * G + U - 1) / U - 1);
+}
+
 __device__ __forceinline__ uint32_t half_bits_x2(uint16_t h) { return static_cast<uint32_t>(h) * 0x00010001u; }
 
 #endif  // __CUDACC__

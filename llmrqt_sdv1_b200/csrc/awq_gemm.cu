@@ -328,6 +328,7 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmP
 }
 
 // Weights-in-tensor-memory kernel (awq_wtm.cu).
+size_t wtm_workspace_bytes(int sm_count);
 int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream, int m_tile);
@@ -359,7 +360,15 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
     const long long t = static_cast<long long>((M + rows - 1) / rows) * ntiles;
     return static_cast<double>((t + di.sm_count - 1) / di.sm_count);
   };
-  const double c_wtm64 = waves(64) * 0.43, c_wtm128 = waves(128) * 0.52, c_wtm192 = waves(192) * 0.64;
+  // The tensor-memory variant shares a partial last wave between all SMs when the workspace allows
+  // (see awq_wtm.cu): its cost then grows with the exact tile count, plus a little for the fix-up.
+  const bool can_split = workspace_bytes >= wtm_workspace_bytes(di.sm_count);
+  auto waves_wtm = [&](int rows) {
+    const long long t = static_cast<long long>((M + rows - 1) / rows) * ntiles;
+    if (!can_split || t <= di.sm_count) return waves(rows);
+    return static_cast<double>(t) / di.sm_count + 0.05;
+  };
+  const double c_wtm64 = waves_wtm(64) * 0.43, c_wtm128 = waves_wtm(128) * 0.52, c_wtm192 = waves_wtm(192) * 0.64;
   const double c_smem1 = waves(128) * 0.78, c_smem2 = waves(256) * 1.00;
   int MH = (M > 128 && c_smem2 <= c_smem1) ? 2 : 1;
   if (variant == 0) {
@@ -413,9 +422,14 @@ using namespace awq;
 
 extern "C" {
 
+// 256 bytes (the status word) are enough for a correct result; with the full size the tensor-memory
+// variant may cut the tiles of a partial last wave along k and share them between all SMs.
 size_t awq_b200_gemm_workspace_bytes(int M, int K, int N) {
   (void)M; (void)K; (void)N;
-  return 256;  // one status word, padded
+  DeviceInfo di;
+  int sm = 148;
+  if (device_info(&di) == AWQ_B200_OK) sm = di.sm_count;
+  return wtm_workspace_bytes(sm);
 }
 
 int awq_b200_gemm(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,

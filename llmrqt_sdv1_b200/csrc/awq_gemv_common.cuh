@@ -116,11 +116,4 @@ __device__ __forceinline__ float2 ld_dsmem_f2(uint32_t local_addr, uint32_t rank
   return v;
 }
 
-// Even split of U work units over G persistent CTAs (G <= U): CTA b owns units
-// [stream_first_unit(b), stream_first_unit(b + 1)), and stream_cta_of(u) is the CTA that owns unit u.
-__host__ __device__ inline long long stream_first_unit(long long b, long long U, long long G) { return b * U / G; }
-__host__ __device__ inline int stream_cta_of(long long u, long long U, long long G) {
-  return static_cast<int>(((u + 1) * G + U - 1) / U - 1);
-}
-
 }  // namespace awq

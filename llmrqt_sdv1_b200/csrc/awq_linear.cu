@@ -29,14 +29,14 @@ size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
   switch (route(M, K, N)) {
     case Route::kGemv: need = awq_b200_gemv_workspace_bytes(M, K, N); break;
     case Route::kSkinny: need = awq_b200_skinny_workspace_bytes(M, K, N); break;
-    case Route::kGemm: need = 0; break;
+    case Route::kGemm: return awq_b200_gemm_workspace_bytes(M, K, N);   // status word first there too
   }
   return kGemmStatusBytes + need;
 }
 
 // Workspace layout: [0, 256) GEMM status word (zero unless a device-side wait
-// expired), then the decode kernels' workspace (arrival counters first).  All of it must
-// be zero before the first call.
+// expired), then 16 KiB of arrival counters shared by all kernels (each leaves them zero), then
+// scratch for partial sums.  The first 256 + 16 KiB bytes must be zero before the first call.
 int awq_b200_linear_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                        const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                        size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
@@ -52,7 +52,8 @@ int awq_b200_linear_ex(const void* x, const void* packed, const void* scales, co
     case Route::kGemm:
       break;
   }
-  return awq_b200_gemm(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, kGemmStatusBytes, stream);
+  // Same buffer: the GEMM's counters sit where the decode kernels keep theirs (both leave them zero).
+  return awq_b200_gemm(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes, stream);
 }
 
 int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,

@@ -67,10 +67,55 @@ struct WtParams {
   const uint16_t* bias;
   uint16_t* y;
   unsigned* status;
+  float* partial;        // tail split only: two fp32 tiles [MT][256] per CTA
   int M, K, N;
   int group_size;
   int mtiles, ntiles;
+  int tail_split;        // 1: the tiles of the last, partial wave are cut along k and shared by all CTAs
 };
+
+// What a CTA works on, in order: its tile of every full wave, then its share of the last wave.  With
+// the tail split the tiles left over after the full waves (fewer than there are CTAs) are flattened
+// into (tile, 64-k stage) units and every CTA takes an equal, contiguous share; a share touches at
+// most two tiles.  A tile finished by several CTAs goes through fp32 partial tiles in the workspace
+// (slot 2*b + 0/1 for CTA b's first / second tail item); a small second kernel adds them in CTA (= k)
+// order and writes y, so no CTA ever waits for another.
+struct WtItem {
+  int tile;        // global tile index
+  int ks0, ks1;    // 64-k stages [ks0, ks1)
+  int tail;        // index among the tail tiles, or -1 for a tile of a full wave
+};
+struct WtCursor {
+  int b, G, nks, full_rounds, tail_tiles, r;
+  long long u, u_end, Ut;
+  __device__ void init(int b_, int G_, int nks_, int num_tiles, int tail_split) {
+    b = b_; G = G_; nks = nks_; r = 0;
+    full_rounds = tail_split ? num_tiles / G : (num_tiles + G - 1) / G;
+    tail_tiles = tail_split ? num_tiles - full_rounds * G : 0;
+    total_tiles = num_tiles;
+    Ut = static_cast<long long>(tail_tiles) * nks;
+    u = b * Ut / G;
+    u_end = (b + 1) * Ut / G;
+  }
+  int total_tiles;
+  __device__ bool next(WtItem* w) {
+    while (r < full_rounds) {
+      const int tile = r * G + b;
+      ++r;
+      if (tile < total_tiles) { *w = WtItem{tile, 0, nks, -1}; return true; }
+    }
+    if (u < u_end) {
+      const int tt = static_cast<int>(u / nks);
+      const int k0 = static_cast<int>(u - static_cast<long long>(tt) * nks);
+      const int len = static_cast<int>(min(static_cast<long long>(nks - k0), u_end - u));
+      *w = WtItem{full_rounds * G + tt, k0, k0 + len, tt};
+      u += len;
+      return true;
+    }
+    return false;
+  }
+};
+
 
 template <int MT>
 __global__ void __launch_bounds__(kWtThreads, 1)
@@ -148,21 +193,24 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     int t = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    WtCursor cur;
+    cur.init(blockIdx.x, gridDim.x, nks, num_tiles, p.tail_split);
+    WtItem w;
+    while (ok && cur.next(&w)) {
       int tile_m, tile_n;
-      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      tile_coords(w.tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
       const int m0 = tile_m * MT;
       const int n0 = tile_n * kWtBN;
       const int ncols = min(kWtBN, p.N - n0);
       const uint32_t tx = Cfg::kXBytes + kWtRawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0);
-      int grp = 0, left = stages_per_group;
+      int grp = w.ks0 / stages_per_group, left = stages_per_group - (w.ks0 - grp * stages_per_group);
       // lane 3 copies the scales row segment, lane 4 the zero words
       const unsigned char* sz_src = (lane == 3) ? reinterpret_cast<const unsigned char*>(p.scales + n0)
                                                 : reinterpret_cast<const unsigned char*>(p.qzeros + (n0 >> 3));
       const size_t sz_step = (lane == 3) ? static_cast<size_t>(p.N) * 2 : static_cast<size_t>(p.N >> 3) * 4;
       const uint32_t sz_bytes = (lane == 3) ? ncols * 2 : ncols / 2;
       const uint32_t sz_dst = Cfg::kSzOff + (lane == 3 ? 0 : 512);
-      for (int ks = 0; ks < nks; ++ks, ++it) {
+      for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
         if ((it & 1u) == my_parity) {
           WTM_TRACE(0, it, 0);
           if (!mbar_wait(bar_empty_tma(t), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
@@ -196,10 +244,13 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     int t = 0, a = 0;
     uint32_t ph = 0, pha = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+    WtCursor cur;
+    cur.init(blockIdx.x, gridDim.x, nks, num_tiles, p.tail_split);
+    WtItem w;
+    for (; ok && cur.next(&w); ++tile_it) {
       if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
       tcgen05_fence_after();
-      for (int ks = 0; ks < nks; ++ks, ++it) {
+      for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
         WTM_TRACE(1, it, 0);
         if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
         WTM_TRACE(1, it, 1);
@@ -212,7 +263,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t a_tmem = tmem_base + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kk * 8);
-            tcgen05_mma_f16_ts_warp(tmem_base + h * MT, a_tmem, db, kIdesc, (ks | kk) != 0 ? 1u : 0u);
+            tcgen05_mma_f16_ts_warp(tmem_base + h * MT, a_tmem, db, kIdesc, (ks != w.ks0 || kk != 0) ? 1u : 0u);
           }
         }
         tcgen05_commit_warp(bar_empty_tma(t));   // activations of this stage consumed
@@ -240,10 +291,15 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     const int e_part = dq_warp >> 3;
     const int zcols = p.N >> 3;
     uint32_t it = 0, tile_it = 0;
+    // After a failed wait a warp stops computing and only walks through its remaining items.
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+    int tail_seen = 0;                        // tail items this CTA has finished (it has at most two)
+    WtCursor cur;
+    cur.init(blockIdx.x, gridDim.x, nks, num_tiles, p.tail_split);
+    WtItem w;
+    for (; cur.next(&w); ++tile_it) {
       int tile_m, tile_n;
-      tile_coords(tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
+      tile_coords(w.tile, p.mtiles, p.ntiles, &tile_m, &tile_n);
       const int m0 = tile_m * MT;
       const int n0 = tile_n * kWtBN;
       int ncol[NH];
@@ -267,7 +323,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       uint32_t sc[NH], zw[NH];
       int sz_group = -1;
 
-      for (int ks = 0; ks < nks; ++ks, ++it) {
+      for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
         if (static_cast<int>(it % G) != grp_id) continue;       // another group's stage
         const int t = it % NT, a = it % NA;
         const uint32_t ph = (it / NT) & 1u, pha = (it / NA) & 1u;
@@ -276,7 +332,8 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           if (qgrp != sz_group) { load_sz(ks, sc, zw); sz_group = qgrp; }
         }
         if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 0);
-        if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) { ok = false; break; }
+        if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
+        if (!ok) continue;
         if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 1);
         const unsigned char* raw = base_ptr + (raw_addr(t) - base);
         if (sz_by_copy) {
@@ -298,7 +355,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
-        if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; break; }
+        if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; continue; }
         if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 2);
         tcgen05_fence_after();
 #pragma unroll
@@ -326,42 +383,61 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_a_full(a));
       }
-      if (!ok) break;
 
       // ------------------------------ epilogue --------------------------------
-      if (!mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) { ok = false; break; }
-      tcgen05_fence_after();
+      // A tile of the tail that several CTAs share: contributors are the CTAs that own its first and
+      // last unit and all between; this CTA's partial tile goes to its slot 2*b + (items finished).
+      int nc = 1, c_first = 0;
+      if (w.tail >= 0) {
+        const long long t0u = static_cast<long long>(w.tail) * nks;
+        c_first = stream_cta_of(t0u, cur.Ut, cur.G);
+        nc = stream_cta_of(t0u + nks - 1, cur.Ut, cur.G) - c_first + 1;
+      }
+      const bool direct = (nc == 1);
+      float* my_partial = direct ? nullptr
+                                 : p.partial + static_cast<size_t>(2 * blockIdx.x + tail_seen) * (MT * kWtBN);
+      if (ok && !mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) ok = false;
       const int n = n0 + e_h * 128 + row;
       const bool nvalid = n < p.N;
       const uint16_t bias_n = (p.bias != nullptr && nvalid) ? p.bias[n] : static_cast<uint16_t>(0);
-      constexpr int kChunks = MT / 16;                 // 16 activation rows per chunk
-      constexpr int kHalfChunks = (kChunks + 1) / 2;   // the two warps of a (quarter, half) split the rows
+      if (ok) {
+        tcgen05_fence_after();
+        constexpr int kChunks = MT / 16;                 // 16 activation rows per chunk
+        constexpr int kHalfChunks = (kChunks + 1) / 2;   // the two warps of a (quarter, half) split the rows
 #pragma unroll 1
-      for (int ch = e_part * kHalfChunks; ch < min(kChunks, (e_part + 1) * kHalfChunks); ++ch) {
-        uint32_t v[16];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-            : "r"(tmem_base + lane_addr + static_cast<uint32_t>(e_h * MT + ch * 16))
-            : "memory");
-        tcgen05_wait_ld();
-        if (nvalid) {
+        for (int ch = e_part * kHalfChunks; ch < min(kChunks, (e_part + 1) * kHalfChunks); ++ch) {
+          uint32_t v[16];
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+              : "r"(tmem_base + lane_addr + static_cast<uint32_t>(e_h * MT + ch * 16))
+              : "memory");
+          tcgen05_wait_ld();
+          if (direct) {
+            if (nvalid) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + ch * 16 + j;
-            if (m < p.M) {
-              __half hv = __float2half_rn(__uint_as_float(v[j]));
-              if (p.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
-              p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(hv);   // 32 lanes = 64 contiguous bytes
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + ch * 16 + j;
+                if (m < p.M) {
+                  __half hv = __float2half_rn(__uint_as_float(v[j]));
+                  if (p.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
+                  p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(hv);   // 32 lanes = 64 contiguous bytes
+                }
+              }
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)      // [row of the tile][column of the tile] fp32, 32 lanes = 128 contiguous bytes
+              __stcg(my_partial + (ch * 16 + j) * kWtBN + e_h * 128 + row, __uint_as_float(v[j]));
           }
         }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty);
+      if (w.tail >= 0) ++tail_seen;
     }
   }
 
@@ -376,14 +452,75 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
 
 }  // namespace awq
 
+namespace awq {
+
+// Second kernel of the tail split: block (tt, chunk) adds the partial tiles of tail tile tt for 16
+// of its rows, in contributor order, and writes y.  256 threads = 4 rows x 64 float4 columns at a time.
+template <int MT>
+__global__ void __launch_bounds__(256) wtm_fixup_kernel(const WtParams p, int G, int nks, int full_rounds,
+                                                         int tail_tiles) {
+  const int tt = blockIdx.x;
+  const long long Ut = static_cast<long long>(tail_tiles) * nks;
+  const long long t0u = static_cast<long long>(tt) * nks;
+  const int c_first = stream_cta_of(t0u, Ut, G);
+  const int nc = stream_cta_of(t0u + nks - 1, Ut, G) - c_first + 1;
+  if (nc == 1) return;                       // finished by one CTA, which wrote y itself
+  int tile_m, tile_n;
+  tile_coords(full_rounds * G + tt, p.mtiles, p.ntiles, &tile_m, &tile_n);
+  const int m0 = tile_m * MT, n0 = tile_n * kWtBN;
+  const int col = (threadIdx.x & 63) * 4;
+  const int n = n0 + col;
+  const int r0 = blockIdx.y * 16 + (threadIdx.x >> 6);
+  float4 sum[4];
+  for (int c = 0; c < nc; ++c) {
+    const int cc = c_first + c;
+    const int first_tail = static_cast<int>((cc * Ut / G) / nks);
+    const float* src = p.partial + static_cast<size_t>(2 * cc + (first_tail == tt ? 0 : 1)) * (MT * kWtBN) + col;
+    float4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __ldcg(reinterpret_cast<const float4*>(src + (r0 + 4 * i) * kWtBN));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (c == 0) sum[i] = v[i];
+      else { sum[i].x += v[i].x; sum[i].y += v[i].y; sum[i].z += v[i].z; sum[i].w += v[i].w; }
+    }
+  }
+  if (n >= p.N) return;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + r0 + 4 * i;
+    if (m >= p.M) continue;
+    __half2 lo = __floats2half2_rn(sum[i].x, sum[i].y), hi = __floats2half2_rn(sum[i].z, sum[i].w);
+    if (p.bias != nullptr) {
+      lo = __hadd2(lo, *reinterpret_cast<const __half2*>(p.bias + n));
+      hi = __hadd2(hi, *reinterpret_cast<const __half2*>(p.bias + n + 2));
+    }
+    uint2 out;
+    out.x = *reinterpret_cast<uint32_t*>(&lo);
+    out.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.y + static_cast<size_t>(m) * p.N + n) = out;
+  }
+}
+
+}  // namespace awq
+
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
 namespace awq {
 
+// Workspace layout of the GEMM entry points: [0, 256) status word; [256, 256 + 16 KiB) left alone (the
+// decode kernels keep their arrival counters there when awq_b200_linear shares the buffer); then the
+// fp32 partial tiles of the tail split, which need no initialisation.
+constexpr size_t kWtPartialOff = 256 + 16384;
+
+size_t wtm_workspace_bytes(int sm_count) {
+  return kWtPartialOff + static_cast<size_t>(sm_count) * 2 * 192 * kWtBN * sizeof(float);
+}
+
 template <int MT>
 static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_count, EncodeTiledFn encode,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, size_t workspace_bytes) {
   using Cfg = WtCfg<MT>;
   CUtensorMap mx, mw;
   {
@@ -411,8 +548,20 @@ static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_coun
   AWQ_CUDA_TRY(cudaFuncSetAttribute(wtm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   const int tiles = p.mtiles * p.ntiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
+  // Tail split: worth it when the last wave is partial and the idle time it would leave (a fraction of
+  // one tile's k loop) clearly exceeds the cost of the partial tiles (~10 us), and the caller's
+  // workspace has room for two fp32 tiles per CTA.
+  const int tail = tiles % grid;
+  const double idle_us = tail ? (1.0 - static_cast<double>(tail) / grid) * (p.K / kWtBK) * 0.6 : 0.0;
+  const size_t need = kWtPartialOff + static_cast<size_t>(grid) * 2 * MT * kWtBN * sizeof(float);
+  p.tail_split = (tiles > grid && idle_us > 20.0 && p.partial != nullptr && workspace_bytes >= need) ? 1 : 0;
   wtm_kernel<MT><<<grid, kWtThreads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
   AWQ_CUDA_TRY(cudaGetLastError());
+  if (p.tail_split) {
+    const int full_rounds = tiles / grid;
+    wtm_fixup_kernel<MT><<<dim3(tail, MT / 16), 256, 0, stream>>>(p, grid, p.K / kWtBK, full_rounds, tail);
+    AWQ_CUDA_TRY(cudaGetLastError());
+  }
   return AWQ_B200_OK;
 }
 
@@ -438,14 +587,17 @@ int wtm_dispatch(const void* x, const void* packed, const void* scales, const in
   p.bias = static_cast<const uint16_t*>(bias);
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
+  const bool roomy = workspace_bytes > kWtPartialOff;
+  p.partial = roomy ? reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWtPartialOff) : nullptr;
   p.M = M; p.K = K; p.N = N;
   p.group_size = group_size;
   p.mtiles = p.ntiles = 0;
+  p.tail_split = 0;
   if (m_tile == 0) m_tile = M <= 64 ? 64 : (M <= 128 ? 128 : 192);
   switch (m_tile) {
-    case 64: return launch_wtm<64>(x, packed, p, di.sm_count, encode, stream);
-    case 128: return launch_wtm<128>(x, packed, p, di.sm_count, encode, stream);
-    case 192: return launch_wtm<192>(x, packed, p, di.sm_count, encode, stream);
+    case 64: return launch_wtm<64>(x, packed, p, di.sm_count, encode, stream, workspace_bytes);
+    case 128: return launch_wtm<128>(x, packed, p, di.sm_count, encode, stream, workspace_bytes);
+    case 192: return launch_wtm<192>(x, packed, p, di.sm_count, encode, stream, workspace_bytes);
     default: return AWQ_B200_ERR_SHAPE;
   }
 }

@@ -177,6 +177,12 @@ def gemm_smem(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
                 lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out)
 
 
+def gemm_wtm_unsplit(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch.Tensor:
+    """`gemm_wtm` with a workspace too small for partial tiles: every tile is finished by one CTA
+    (the bits of the shared-memory variant).  For tests."""
+    return _run(lib.awq_b200_gemm_wtm_tile, "awq_b200_gemm_unsplit", x, pw, bias, 256, out, (m_tile,))
+
+
 def gemm_wtm(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch.Tensor:
     """Prefill kernel, weights-in-tensor-memory variant, any M >= 1 (`m_tile` forces the row tile)."""
     return _run(lib.awq_b200_gemm_wtm_tile, "awq_b200_gemm", x, pw, bias,

@@ -313,6 +313,35 @@ def test_linear_routes_large_shapes_to_skinny(K_):
     assert ((y40.float() - ref).abs().max() / ref.abs().max()).item() <= TOL
 
 
+def test_gemm_tail_split(K_):
+    """176 tiles of 192 x 256 on 148 SMs: the 28 tiles of the last wave are cut along k, shared by all
+    SMs and finished through fp32 partial tiles.  Same result to fp32 rounding as one CTA per tile,
+    deterministic, counters left clean (second call identical)."""
+    M, K, N = 2048, 4096, 4096
+    qw, qz, sc = _random_packed_inputs(K, N, 128, seed=77)
+    pw = K_.make_packed(qw, qz, sc, 128)
+    x = torch.randn((M, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(3)).half()
+    bias = (torch.randn(N, device="cuda") * 0.1).half()
+    y = K_.gemm_wtm(x, pw, bias=bias, m_tile=192)
+    y_again = K_.gemm_wtm(x, pw, bias=bias, m_tile=192)
+    y_unsplit = K_.gemm_wtm_unsplit(x, pw, bias=bias, m_tile=192)
+    assert K_.gemm_status() == 0
+    assert torch.equal(y, y_again)
+    ref = torch.matmul(x, K_.dequantize(qw, qz, sc, 128)).float() + bias.float()
+    scale = ref.abs().max()
+    assert (y.float() - ref).abs().max() / scale <= TOL
+    assert (y.float() - y_unsplit.float()).abs().max() / scale <= 1e-3
+    assert torch.equal(y_unsplit, K_.gemm_smem(x, pw, bias=bias))
+    # ragged rows and columns through the shared tiles as well
+    M2, N2 = 2000, 4040
+    qw, qz, sc = _random_packed_inputs(K, N2, 128, seed=78)
+    pw2 = K_.make_packed(qw, qz, sc, 128)
+    y2 = K_.gemm_wtm(x[:M2].contiguous(), pw2, m_tile=192)
+    ref2 = torch.matmul(x[:M2], K_.dequantize(qw, qz, sc, 128)).float()
+    assert (y2.float() - ref2).abs().max() / ref2.abs().max() <= TOL
+    assert K_.gemm_status() == 0
+
+
 def _random_packed_inputs(K, N, G, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     qw = torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
