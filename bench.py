@@ -11,7 +11,8 @@ One JSON line on stdout (rank 0).  Workloads:
                 larger than the 126 MB L2, so no flush is needed between steps).
   ffn70b_tp     (default at N>1)  the 70B-class FFN linears, M=1, tensor-parallel over
                 the N ranks: gate_up 8192->57344 column-sharded, down 28672->8192
-                row-sharded + one NCCL all-reduce; one step = 8 layers.
+                row-sharded + one all-reduce (the library's one-shot peer all-reduce for small outputs,
+                NCCL timed beside it); one step = 8 layers.
 
 `value` times the kernels alone (inputs resident in HBM, one CUDA graph per step);
 `e2e` times the module API (`AWQLinear_GEMM.forward`) with the activations starting in
@@ -358,7 +359,25 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     pw_d = [m.packed() for m in down]
     step_bytes_total = FFN70B_LAYERS * (gemv_bytes(M, Kg, Ng) + gemv_bytes(M, Kd, Nd))
 
+    # Row-parallel partial outputs are summed by the library's one-shot peer all-reduce (every rank reads
+    # all partials over NVLink); the NCCL all-reduce is timed beside it.
+    peer = None
+    if world > 1:
+        from llmrqt_sdv1_b200.sharded import PeerSum
+        peer = PeerSum(64 * Nd, dev)
+        for m in down:
+            m.use_peer_sum(peer)
+
     def step():
+        for i in range(FFN70B_LAYERS):
+            kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
+            if world > 1:
+                kernels.linear(x_d, pw_d[i], out=peer.partial(M, Nd), overlap=True)
+                peer.reduce(M, Nd, out=y_d[i])
+            else:
+                kernels.linear(x_d, pw_d[i], out=y_d[i], overlap=True)
+
+    def step_nccl():
         for i in range(FFN70B_LAYERS):
             kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
             kernels.linear(x_d, pw_d[i], out=y_d[i], overlap=True)
@@ -438,6 +457,13 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         dist.all_reduce(t3, op=dist.ReduceOp.MAX)
     ms_local = float(t3.item())
 
+    ms_nccl = None
+    if world > 1:
+        ms_nccl = time_graph(torch, step_nccl, iters=max(args.steps, 5))
+        t4 = torch.tensor([ms_nccl], device=dev)
+        dist.all_reduce(t4, op=dist.ReduceOp.MAX)
+        ms_nccl = float(t4.item())
+
     # The other row counts of the sharded configuration: M = 16 (decode batch) and M = 4096 (prefill),
     # same layers, same all-reduce, device time, max over ranks.
     tp_detail = []
@@ -450,9 +476,13 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         def step_m():
             for i in range(FFN70B_LAYERS):
                 kernels.linear(xg, pw_g[i], out=yg)
-                kernels.linear(xd, pw_d[i], out=yd)
-                if world > 1:
-                    dist.all_reduce(yd)
+                if world > 1 and peer.fits(Md, Nd):
+                    kernels.linear(xd, pw_d[i], out=peer.partial(Md, Nd))
+                    peer.reduce(Md, Nd, out=yd)
+                else:
+                    kernels.linear(xd, pw_d[i], out=yd)
+                    if world > 1:
+                        dist.all_reduce(yd)
         for _ in range(3):
             step_m()
         torch.cuda.synchronize()
@@ -490,17 +520,20 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "ffn70b_tp: 70B-class FFN linears, gate_up 8192->57344 column-sharded, down "
-                               "28672->8192 row-sharded + NCCL all-reduce, M=1, W4A16 g128, 8 layers per step",
+                               "28672->8192 row-sharded + one-shot all-reduce over peer memory (NVLink), M=1, W4A16 g128, 8 layers per step",
                    "M": M, "tp": world, "group_size": GROUP, "bytes_per_step_all_ranks": step_bytes_total,
                    "l2": "inputs larger than L2 (8 distinct layers per step)", "cuda_graph": graphed},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+ncclAllReduce in the step)", "per_gpu": True},
+                     "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+awq::peer_allreduce_kernel in the step)", "per_gpu": True},
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
                 "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
-        "gpu_launches": 2 * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
+        "gpu_launches": (3 if world > 1 else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
+        "with_nccl_allreduce": (None if ms_nccl is None else
+                                {"ms_per_step": ms_nccl, "value": step_bytes_total / (ms_nccl * 1e-3) / 1e9, "unit": "GB/s"}),
+        "peer_allreduce_status": (peer.status() if peer is not None else None),
     }
     print(json.dumps(line), flush=True)
 

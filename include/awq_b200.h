@@ -232,6 +232,25 @@ AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const
                            int group_size, void* workspace, size_t workspace_bytes,
                            awq_b200_stream_t stream, int m_tile);
 
+/* ---- row-parallel shards: one-shot sum over peer memory ------------------- */
+
+/* Bytes of the per-rank flag array of awq_b200_peer_allreduce (zero before the first call). */
+AWQ_B200_API size_t awq_b200_peer_allreduce_flag_bytes(void);
+
+/* out[i] = fp16( sum over ranks r of bufs[r][i] ) (+ bias[i % ncols]), i < count, on every rank of one node.
+ * bufs / flags are DEVICE arrays of `world` pointers into memory every rank can load and store (peer-mapped
+ * or symmetric allocations, exchanged by the caller): bufs[r] is rank r's fp16 partial, written by earlier
+ * work on this stream; flags[r] is rank r's flag array.  Every rank reads all partials with plain peer loads
+ * and adds them in rank order in fp32, so all ranks get identical bits; the call returns (stream-wise) only
+ * after every peer has read this rank's partial, so the partial may be rewritten by the next kernel.
+ * All ranks must make matching calls in the same order.  count % 8 == 0, buffers 16-byte aligned,
+ * world <= 16.  Waits on peers are bounded (~2 s): on expiry word 34 of the flag array becomes non-zero
+ * and the output is invalid.  The reference has no counterpart (it is single-GPU,
+ * LLMQRT/runtime_refact/core/base.py:44); this replaces the all-reduce of a row-parallel linear
+ * (spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:186-199) at decode sizes. */
+AWQ_B200_API int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* out, const void* bias,
+                            size_t count, int ncols, int rank, int world, awq_b200_stream_t stream);
+
 /* ---- dispatch ------------------------------------------------------------ */
 
 /* Largest M routed to the GEMV kernel by awq_b200_linear (16). */

@@ -1,0 +1,161 @@
+// One-shot sum of the row-parallel partial outputs over peer memory (NVLink / NVSwitch).
+//
+// A row-sharded linear (down / o projections split along K) leaves one [M, N] fp16 partial per GPU;
+// the result is their sum.  At decode sizes (16 KB for one row of N = 8192) a ring or tree collective
+// is pure latency: the library all-reduce costs ~65 us on 8 GPUs.  Here every rank reads all peers'
+// partials directly with plain peer loads and adds them itself:
+//
+//   1. ready:  rank r stores the call's epoch into slot [r] of every peer's flag array (system scope,
+//              release) - "my partial for this call is written" (the kernel that wrote it precedes
+//              this one on the stream);
+//   2. wait:   every block polls its OWN flag array until all slots show the epoch (acquire);
+//   3. sum:    16-byte peer loads that bypass L1, fp32 adds in rank order (every rank gets identical
+//              bits), one fp16 rounding, store to the local output;
+//   4. done:   the last block to finish stores the epoch into the peers' done slots and waits for
+//              theirs, so that no rank overwrites its partial (next call) while a peer still reads it.
+//
+// Buffers and flag arrays live in symmetric memory that the caller allocated and exchanged (one
+// pointer per rank, as a device array).  The epoch is kept in device memory and advanced by the kernel,
+// so the call can be captured in a CUDA graph and replayed.  No multicast / multimem loads are used.
+// Every wait is bounded (~2 s); on expiry the kernel sets a status word and returns, and the output of
+// that call is invalid.
+#include "awq_common.cuh"
+
+namespace awq {
+
+constexpr int kArMaxWorld = 16;
+constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // ~2 s at 2 GHz
+
+// Flag array layout (uint32 words) in each rank's symmetric flag buffer:
+//   [0, 16)   ready[r]   written by rank r
+//   [16, 32)  done[r]    written by rank r
+//   [32]      epoch of the last completed call (local)
+//   [33]      blocks of the current call that finished summing (local)
+//   [34]      status: 0, or 1 / 2 when the ready / done wait expired (local, sticky)
+constexpr int kArReadyOff = 0, kArDoneOff = 16, kArEpochOff = 32, kArBlocksOff = 33, kArStatusOff = 34;
+constexpr int kArFlagWords = 64;
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {   // no L1 allocation: the same addresses carry new data every call
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Waits until flags[off + r] == epoch for every r < world.  Returns false on expiry.
+__device__ __forceinline__ bool wait_all(const unsigned* flags, int off, int world, unsigned epoch) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const unsigned long long t0 = clock64();
+    while (ld_acquire_sys(flags + off + threadIdx.x) != epoch) {
+      if (clock64() - t0 > kArWaitLimitCycles) { s_ok = 0; break; }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(512)
+peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint16_t* out, const uint16_t* bias,
+                      size_t count, int ncols, int rank, int world) {
+  unsigned* my_flags = flags[rank];
+  const unsigned epoch = my_flags[kArEpochOff] + 1u;   // written only by this kernel's last block, a launch ago
+  if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(flags[threadIdx.x] + kArReadyOff + rank, epoch);
+  const bool ready = wait_all(my_flags, kArReadyOff, world, epoch);
+  if (!ready && threadIdx.x == 0) atomicCAS(my_flags + kArStatusOff, 0u, 1u);
+
+  if (ready) {
+    const size_t vecs = count / 8;                       // 8 halves per 16-byte load
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      uint4 v[kArMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kArMaxWorld; ++r)
+        if (r < world) v[r] = ld_peer_16(bufs[r] + i * 8);
+#pragma unroll
+      for (int r = 0; r < kArMaxWorld; ++r) {
+        if (r < world) {
+          const __half2* h = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+      }
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+      if (bias != nullptr) {
+        const size_t col = (i * 8) % static_cast<size_t>(ncols);
+        const uint4 b = *reinterpret_cast<const uint4*>(bias + col);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], bh[e]);
+      }
+      *reinterpret_cast<uint4*>(out + i * 8) = o;
+    }
+  }
+
+  // The last block to get here tells the peers that this rank has read their partials, waits for the
+  // same from them, and closes the call.
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(my_flags + kArBlocksOff, 1u);
+    s_last = (prev == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x < world) st_release_sys(flags[threadIdx.x] + kArDoneOff + rank, epoch);
+  const bool done = wait_all(my_flags, kArDoneOff, world, epoch);
+  if (threadIdx.x == 0) {
+    if (!done) atomicCAS(my_flags + kArStatusOff, 0u, 2u);
+    my_flags[kArBlocksOff] = 0u;
+    my_flags[kArEpochOff] = epoch;
+  }
+}
+
+}  // namespace awq
+
+extern "C" {
+
+size_t awq_b200_peer_allreduce_flag_bytes(void) { return awq::kArFlagWords * sizeof(unsigned); }
+
+// bufs / flags: device arrays of `world` pointers (this rank's own at index `rank`).  `count` fp16 elements,
+// a multiple of 8; every buffer 16-byte aligned.  `bias` (optional, [ncols]) is added after the sum.
+int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* out, const void* bias, size_t count,
+                            int ncols, int rank, int world, awq_b200_stream_t stream) {
+  using namespace awq;
+  if (!bufs || !flags || !out) return AWQ_B200_ERR_NULL;
+  if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return AWQ_B200_ERR_SHAPE;
+  if (count == 0 || (count % 8) != 0 || (bias && (ncols < 8 || (ncols % 8) != 0))) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(out) || (bias && !aligned16(bias))) return AWQ_B200_ERR_ALIGN;
+  const size_t vecs = count / 8;
+  int blocks = static_cast<int>((vecs + 511) / 512);
+  if (blocks > 64) blocks = 64;        // all blocks must be resident together: they wait on one another's peers
+  peer_allreduce_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint16_t* const*>(bufs), reinterpret_cast<unsigned* const*>(flags),
+      static_cast<uint16_t*>(out), static_cast<const uint16_t*>(bias), count, ncols, rank, world);
+  AWQ_CUDA_TRY(cudaGetLastError());
+  return AWQ_B200_OK;
+}
+
+}  // extern "C"

@@ -196,6 +196,18 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
 
+def peer_allreduce(bufs_dev: int, flags_dev: int, local_buf: torch.Tensor, M: int, N: int, rank: int, world: int,
+                   out: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Sum of the ranks' [M, N] fp16 partials held in symmetric memory (see `sharded.PeerSum`).
+    `bufs_dev` / `flags_dev` are device arrays of per-rank pointers."""
+    dev = local_buf.device
+    _lib.set_device(dev.index)
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=dev)
+    check(lib.awq_b200_peer_allreduce(bufs_dev, flags_dev, y.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                      M * N, N, rank, world, _stream(local_buf)), "awq_b200_peer_allreduce")
+    return y
+
+
 def gemv_status(dev: torch.device | None = None) -> int:
     """Status word of the decode kernels (GEMV and split-K tensor-memory kernel) in this stream's workspaces (0 = no device-side wait expired).
     Synchronises."""

@@ -127,6 +127,46 @@ class ColumnParallelAWQLinear(nn.Module):
         return y
 
 
+class PeerSum:
+    """One-shot sum of small row-parallel partial outputs over peer memory (NVLink), for CUDA ranks of
+    one node.  Each rank writes its fp16 partial into `partial(M, N)` (symmetric memory); `reduce`
+    launches the library's peer all-reduce kernel, in which every rank reads all partials with plain
+    peer loads, adds them in rank order in fp32 and writes the fp16 result locally (identical bits on
+    every rank).  Replaces an NCCL all-reduce whose cost at these sizes (16 KB ... 1 MB) is all latency.
+    One instance serves any number of layers on a stream: a call finishes only after every peer has
+    read this rank's partial."""
+
+    def __init__(self, max_elems: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.max_elems = (int(max_elems) + 7) // 8 * 8
+        self.buf = symm_mem.empty(self.max_elems, dtype=torch.float16, device=device)
+        self.flags = symm_mem.empty(_lib.lib.awq_b200_peer_allreduce_flag_bytes() // 4, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self._h_buf = symm_mem.rendezvous(self.buf, group)
+        self._h_flags = symm_mem.rendezvous(self.flags, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)            # every rank's flags are zero before anyone signals
+
+    def fits(self, M: int, N: int) -> bool:
+        return M * N <= self.max_elems and (M * N) % 8 == 0
+
+    def partial(self, M: int, N: int) -> torch.Tensor:
+        return self.buf[:M * N].view(M, N)
+
+    def reduce(self, M: int, N: int, out: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> torch.Tensor:
+        from . import kernels
+        return kernels.peer_allreduce(self._h_buf.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev, self.buf,
+                                      M, N, self.rank, self.world, out=out, bias=bias)
+
+    def status(self) -> int:
+        """0, or which wait expired in some call (1: peers' partials, 2: peers' reads).  Synchronises."""
+        return int(self.flags[34].item())
+
+
 class RowParallelAWQLinear(nn.Module):
     """y = all_reduce_sum( x[..., shard] . W[shard, :] ) (+ bias on rank 0)."""
 
@@ -159,9 +199,22 @@ class RowParallelAWQLinear(nn.Module):
     def packed(self):
         return _packed(self.linear)
 
+    def use_peer_sum(self, peer_sum: PeerSum | None) -> None:
+        """Sum small outputs with `peer_sum` (shared between layers) instead of an NCCL all-reduce."""
+        self.peer_sum = peer_sum
+
     def forward(self, x):
         if not self.input_is_parallel:
             x = x[..., self.rank * self.k_local:(self.rank + 1) * self.k_local]
+        ps = getattr(self, "peer_sum", None)
+        if ps is not None and self.world > 1 and x.is_cuda and x.dtype == torch.float16:
+            rows = x.numel() // x.shape[-1]
+            N = self.linear.out_features
+            if ps.fits(rows, N):
+                from . import kernels
+                kernels.linear(x.reshape(rows, -1), self.packed(), bias=self.linear.bias, out=ps.partial(rows, N))
+                y = ps.reduce(rows, N)
+                return y.view(*x.shape[:-1], N) if x.dim() > 2 else y.view(1, rows, N)
         y = self.linear(x)
         if self.world > 1:
             y = y.contiguous()
