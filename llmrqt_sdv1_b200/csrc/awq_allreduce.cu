@@ -43,9 +43,13 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ uint4 ld_peer_16(const void* p) {   // no L1 allocation: the same addresses carry new data every call
+// Peer partials are read with L1 bypassed (the same addresses carry new data every call) but as ordinary
+// coalescable loads: a warp's 32 x 16 bytes travel as four 128-byte requests.  Volatile loads are issued
+// one 16-byte request per thread, and thousands of those per call over NVLink cost hundreds of
+// microseconds on 8 GPUs.
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
   uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p)
                : "memory");
@@ -67,7 +71,9 @@ __device__ __forceinline__ bool wait_all(const unsigned* flags, int off, int wor
   return s_ok != 0;
 }
 
-__global__ void __launch_bounds__(512)
+constexpr int kArThreads = 256;
+
+__global__ void __launch_bounds__(kArThreads)
 peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint16_t* out, const uint16_t* bias,
                       size_t count, int ncols, int rank, int world) {
   unsigned* my_flags = flags[rank];
@@ -149,9 +155,9 @@ int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* o
   if (count == 0 || (count % 8) != 0 || (bias && (ncols < 8 || (ncols % 8) != 0))) return AWQ_B200_ERR_SHAPE;
   if (!aligned16(out) || (bias && !aligned16(bias))) return AWQ_B200_ERR_ALIGN;
   const size_t vecs = count / 8;
-  int blocks = static_cast<int>((vecs + 511) / 512);
+  int blocks = static_cast<int>((vecs + kArThreads - 1) / kArThreads);
   if (blocks > 64) blocks = 64;        // all blocks must be resident together: they wait on one another's peers
-  peer_allreduce_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+  peer_allreduce_kernel<<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint16_t* const*>(bufs), reinterpret_cast<unsigned* const*>(flags),
       static_cast<uint16_t*>(out), static_cast<const uint16_t*>(bias), count, ncols, rank, world);
   AWQ_CUDA_TRY(cudaGetLastError());

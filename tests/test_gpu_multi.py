@@ -1,0 +1,87 @@
+"""Two-GPU tests of the row-parallel path: the one-shot all-reduce over peer memory against an fp32 sum
+of the gathered partials, and RowParallelAWQLinear with it against the NCCL all-reduce.  Skipped on
+boxes with fewer than two GPUs.  NVLS is switched off in the child processes (plain peer loads only)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, results):
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from llmrqt_sdv1_b200 import quantize
+        from llmrqt_sdv1_b200.sharded import PeerSum, RowParallelAWQLinear
+        ps = PeerSum(16 * 4096, dev)
+        ok = True
+        for (M, N) in [(1, 4096), (5, 2048), (16, 4096)]:
+            for it in range(4):            # the same buffers carry new data every call
+                g = torch.Generator(device=dev).manual_seed(10 * it + rank)
+                part = torch.randn((M, N), device=dev, generator=g).half()
+                ps.partial(M, N).copy_(part)
+                y = ps.reduce(M, N)
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                ref = torch.stack([p.float() for p in parts]).sum(0).half()
+                ys = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(ys, y)
+                ok = ok and torch.equal(y, ref) and all(torch.equal(ys[0], t) for t in ys)
+        # bias is added after the sum
+        bias = torch.randn(4096, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).half()
+        ps.partial(2, 4096).fill_(0.5)
+        yb = ps.reduce(2, 4096, bias=bias)
+        ok = ok and torch.equal(yb, (torch.full((2, 4096), 0.5 * world, device=dev).half() + bias))
+        # the module: peer sum and NCCL all-reduce agree (fp32 sum of fp16 partials vs fp16 ring adds)
+        K, N = 1024, 2048
+        qw, qz, sc = quantize.random_awq_tensors(K // world, N, 128, seed=3 + rank, device=dev)
+        mod = RowParallelAWQLinear.from_local(qw, qz, sc, None, 128)
+        x = torch.randn((3, K // world), device=dev, generator=torch.Generator(device=dev).manual_seed(rank)).half()
+        y_nccl = mod(x)
+        mod.use_peer_sum(ps)
+        y_peer = mod(x)
+        rel = ((y_peer.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max()).item()
+        ok = ok and y_peer.shape == y_nccl.shape and rel <= 2e-3
+        # a graph with several calls replays correctly (the epoch lives in device memory)
+        outs = [torch.empty((1, 4096), dtype=torch.float16, device=dev) for _ in range(3)]
+        ps.partial(1, 4096).fill_(float(rank + 1))
+        for o in outs:
+            ps.reduce(1, 4096, out=o)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for o in outs:
+                ps.reduce(1, 4096, out=o)
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        expect = float(sum(range(1, world + 1)))
+        ok = ok and all(bool((o == expect).all()) for o in outs)
+        results[rank] = (ok, ps.status())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_allreduce_two_gpus():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        ok, status = results[rank]
+        assert ok, f"rank {rank} saw a wrong sum"
+        assert status == 0, f"rank {rank}: a wait on a peer expired (status {status})"
