@@ -384,17 +384,28 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
             if world > 1:
                 dist.all_reduce(y_d[i])
 
+    # Which exchange the timed step uses: both are timed briefly first (device time, max over ranks, so
+    # every rank makes the same choice) and the faster one is the configuration that is measured.
+    allreduce, calib = "none", {}
+    if world > 1:
+        for name, fn in (("peer", step), ("nccl", step_nccl)):
+            dist.barrier()
+            tc = torch.tensor([time_graph(torch, fn, iters=5)], device=dev)
+            dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+            calib[name] = float(tc.item())
+        allreduce = "peer" if calib["peer"] <= calib["nccl"] else "nccl"
+    step_timed = step_nccl if allreduce == "nccl" else step
     for _ in range(max(args.warmup, 3)):
-        step()
+        step_timed()
     torch.cuda.synchronize()
     graphed = True
     try:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            step()
+            step_timed()
         run = graph.replay
     except Exception:
-        graphed, run = False, step
+        graphed, run = False, step_timed
     for _ in range(max(args.warmup, 3)):
         run()
     torch.cuda.synchronize()
@@ -457,13 +468,6 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         dist.all_reduce(t3, op=dist.ReduceOp.MAX)
     ms_local = float(t3.item())
 
-    ms_nccl = None
-    if world > 1:
-        ms_nccl = time_graph(torch, step_nccl, iters=max(args.steps, 5))
-        t4 = torch.tensor([ms_nccl], device=dev)
-        dist.all_reduce(t4, op=dist.ReduceOp.MAX)
-        ms_nccl = float(t4.item())
-
     # The other row counts of the sharded configuration: M = 16 (decode batch) and M = 4096 (prefill),
     # same layers, same all-reduce, device time, max over ranks.
     tp_detail = []
@@ -525,15 +529,14 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                    "l2": "inputs larger than L2 (8 distinct layers per step)", "cuda_graph": graphed},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+awq::peer_allreduce_kernel in the step)", "per_gpu": True},
+                     "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+ the all-reduce named in allreduce.used)", "per_gpu": True},
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
                 "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
-        "gpu_launches": (3 if world > 1 else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
+        "gpu_launches": (3 if allreduce == "peer" else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
-        "with_nccl_allreduce": (None if ms_nccl is None else
-                                {"ms_per_step": ms_nccl, "value": step_bytes_total / (ms_nccl * 1e-3) / 1e9, "unit": "GB/s"}),
-        "peer_allreduce_status": (peer.status() if peer is not None else None),
+        "allreduce": {"used": allreduce, "calibration_ms_per_step": calib,
+                      "peer_status": (peer.status() if peer is not None else None)},
     }
     print(json.dumps(line), flush=True)
 
