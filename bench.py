@@ -409,10 +409,13 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         run()
     torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)      # set up before the barrier: its start-up time differs between ranks
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
+    # One more untimed step right before the timed ones: the step's own exchange lines the ranks up, so
+    # that the timed region does not begin with one rank waiting for another to leave the barrier.
+    run()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(args.steps):
