@@ -352,7 +352,7 @@ def _random_packed_inputs(K, N, G, seed):
 
 @pytest.mark.parametrize("K,N,M", [(8192, 57344, 1), (28672, 8192, 16), (2048, 12288, 4)])
 def test_gemv_full_size_vs_device_dequant_matmul(K_, K, N, M):
-    """BASELINE-size decode linears: the kernel against dequant (proved bit-exact above)
+    """Full-size decode linears (70B-class and Qwen3 shapes): the kernel against dequant (proved bit-exact above)
     followed by a library fp16 matmul on the same device, plus the unpack round trip."""
     qw, qz, sc = _random_packed_inputs(K, N, 128, seed=K + N)
     pw = K_.make_packed(qw, qz, sc, 128)
