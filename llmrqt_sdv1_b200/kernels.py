@@ -35,11 +35,15 @@ def _kn(qweight: torch.Tensor) -> tuple[int, int]:
 class PackedWeight:
     """Kernel-layout weight of one linear: packed nibbles plus the on-disk
     scales / qzeros it is used with."""
-    __slots__ = ("packed", "qzeros", "scales", "K", "N", "group_size", "fresh")
+    __slots__ = ("packed", "qzeros", "scales", "K", "N", "group_size", "fresh", "_ptrs", "_ws_need")
 
     def __init__(self, packed, qzeros, scales, K, N, group_size, fresh=False):
         self.packed, self.qzeros, self.scales = packed, qzeros, scales
         self.K, self.N, self.group_size = K, N, group_size
+        # per-call constants of the hot wrapper: raw pointers (the tensors above keep them alive) and
+        # the workspace size per row count
+        self._ptrs = (packed.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), packed.device)
+        self._ws_need = {}
         # True while the repack kernel that produced `packed` may still be queued: the first
         # compute call must then not prefetch the weights ahead of the previous kernel.
         self.fresh = fresh
@@ -190,10 +194,37 @@ def gemm_wtm(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch
 
 
 def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
-    """M <= 16 -> GEMV, else GEMM (dispatch inside the library).  `overlap` as in `gemv`."""
-    return _run(lib.awq_b200_linear_ex, "awq_b200_linear", x, pw, bias,
-                lib.awq_b200_linear_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
-                (_lib.OVERLAP_PREVIOUS if overlap else 0,))
+    """The library's dispatcher (decode GEMV, split-K tensor-memory kernel or GEMM by rows and shape).
+    `overlap` as in `gemv`.  This is the per-token call of the module, so the wrapper keeps its own
+    work to a minimum: cached pointers and workspace sizes, one ctypes call."""
+    wp, sp, zp, dev = pw._ptrs
+    if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != pw.K:
+        raise ValueError(f"x must be fp16 [M, {pw.K}], got {x.dtype} {tuple(x.shape)}")
+    if x.device != dev:
+        if x.device.type != "cuda":
+            raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
+        raise RuntimeError("all tensors of one call must be on the same device")
+    if bias is not None and bias.device != dev:
+        raise RuntimeError("all tensors of one call must be on the same device")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.shape[0]
+    _lib.set_device(dev.index)
+    need = pw._ws_need.get(M)
+    if need is None:
+        need = pw._ws_need[M] = lib.awq_b200_linear_workspace_bytes(max(M, 1), pw.K, pw.N)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    key = (dev.index, stream, "awq_b200_linear")
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _workspace(dev, stream, need, "awq_b200_linear")
+    y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
+    st = lib.awq_b200_linear_ex(x.data_ptr(), wp, sp, zp, bias.data_ptr() if bias is not None else None,
+                                y.data_ptr(), M, pw.K, pw.N, pw.group_size, ws.data_ptr(), ws.numel(), stream,
+                                _lib.OVERLAP_PREVIOUS if overlap else 0)
+    if st != 0:
+        check(st, "awq_b200_linear")
+    return y
 
 
 def peer_allreduce(bufs_dev: int, flags_dev: int, local_buf: torch.Tensor, M: int, N: int, rank: int, world: int,

@@ -52,7 +52,10 @@ class AWQLinearMMFunction(Function):
         else:
             pw = ext.packed_for(qweight, qzeros, scales, group_size)
             overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
-            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw, overlap=overlap).reshape(out_shape)
+            # the bias is added inside the kernel: fp16(acc), then fp16(y + bias) - the two roundings of the
+            # reference's `out + bias` on fp16 tensors (linear_awq.py:205)
+            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw, bias=bias, overlap=overlap).reshape(out_shape)
+            bias = None
         out = out + bias if bias is not None else out
         if out.dim() == 2:          # the reference always hands back a 3-D tensor
             out = out.unsqueeze(0)
@@ -123,8 +126,10 @@ class AWQLinear_GEMM(nn.Module):
         if input_dtype != torch.float16:
             x = x.to(torch.float16)
         with torch.no_grad():
-            out = AWQLinearMMFunction.apply(x, self.qweight, self.qzeros, self.scales, self.w_bit,
-                                            self.group_size, self.bias, self.out_features, self.impl_mode)
+            # The reference goes through AWQLinearMMFunction.apply (linear_awq.py:385-395); under
+            # no_grad that is the same computation plus ~10 us of autograd bookkeeping per call.
+            out = AWQLinearMMFunction.forward(None, x, self.qweight, self.qzeros, self.scales, self.w_bit,
+                                              self.group_size, self.bias, self.out_features, self.impl_mode)
         if input_dtype != torch.float16:
             out = out.to(dtype=input_dtype)
         return out
