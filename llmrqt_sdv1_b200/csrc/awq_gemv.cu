@@ -444,7 +444,11 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
   double best_t = 1e30;
   const int ws[2] = {8, 16};
   for (int w : ws) {
-    if (w == 16 && nblk > 16) continue;   // 16 warps only paid off for short k in the sweep
+    // 16-warp CTAs win some shapes when a kernel is timed alone (2048 -> 2048: 2.7 vs 3.0 us) but lose
+    // inside a sequence of linears: one such CTA fills an SM, so the next launch cannot start its weight
+    // prefetch beside it (28-layer decode step: 562 -> 547 us without them).  The planner leaves them out;
+    // forced plans can still select them.
+    if (w == 16) continue;
     const double slots = (w == 8 ? 2.0 : 1.0) * sm_count;   // resident CTAs
     for (int kw = w; kw >= (w == 8 ? 1 : 4); kw >>= 1) {
       const int ncol = plan_ncol(ntiles, ntw, w, kw);
@@ -471,6 +475,10 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
       }
     }
   }
+  // Narrow outputs with a medium k (e.g. 6144 -> 2048): inside a sequence of decode linears four cluster
+  // splits of four k-splitting warps beat every plan the fitted model ranks first (28-layer step 545 -> 522 us).
+  if (ntiles <= 256 && nblk > 32 && nblk <= 64)
+    best = GemvPlan{ntw, 8, 4, (nblk + 3) / 4, 4, plan_ncol(ntiles, ntw, 8, 4)};
   best.S = (nblk + best.bps - 1) / best.bps;
   return best;
 }
