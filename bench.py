@@ -361,21 +361,31 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
 
     # Row-parallel partial outputs are summed by the library's one-shot peer all-reduce (every rank reads
     # all partials over NVLink); the NCCL all-reduce is timed beside it.
-    peer = None
+    peer, peer_error = None, None
     if world > 1:
         from llmrqt_sdv1_b200.sharded import PeerSum
-        peer = PeerSum(64 * Nd, dev)
-        for m in down:
-            m.use_peer_sum(peer)
+        try:
+            peer = PeerSum(64 * Nd, dev)
+        except Exception as e:          # no symmetric memory on this box: every rank falls back to NCCL
+            peer_error = f"{type(e).__name__}: {e}"[:200]
+        flag = torch.tensor([0 if peer is not None else 1], device=dev)
+        dist.all_reduce(flag)           # all ranks must agree, or the exchanges would not match
+        if int(flag.item()) != 0:
+            peer = None
+        if peer is not None:
+            for m in down:
+                m.use_peer_sum(peer)
 
     def step():
         for i in range(FFN70B_LAYERS):
             kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
-            if world > 1:
+            if peer is not None:
                 kernels.linear(x_d, pw_d[i], out=peer.partial(M, Nd), overlap=True)
                 peer.reduce(M, Nd, out=y_d[i])
             else:
                 kernels.linear(x_d, pw_d[i], out=y_d[i], overlap=True)
+                if world > 1:
+                    dist.all_reduce(y_d[i])
 
     def step_nccl():
         for i in range(FFN70B_LAYERS):
@@ -388,12 +398,12 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     # every rank makes the same choice) and the faster one is the configuration that is measured.
     allreduce, calib = "none", {}
     if world > 1:
-        for name, fn in (("peer", step), ("nccl", step_nccl)):
+        for name, fn in ((("peer", step),) if peer is not None else ()) + (("nccl", step_nccl),):
             dist.barrier()
             tc = torch.tensor([time_graph(torch, fn, iters=5)], device=dev)
             dist.all_reduce(tc, op=dist.ReduceOp.MAX)
             calib[name] = float(tc.item())
-        allreduce = "peer" if calib["peer"] <= calib["nccl"] else "nccl"
+        allreduce = "peer" if "peer" in calib and calib["peer"] <= calib["nccl"] else "nccl"
     step_timed = step_nccl if allreduce == "nccl" else step
     for _ in range(max(args.warmup, 3)):
         step_timed()
@@ -483,7 +493,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         def step_m():
             for i in range(FFN70B_LAYERS):
                 kernels.linear(xg, pw_g[i], out=yg)
-                if world > 1 and peer.fits(Md, Nd):
+                if peer is not None and peer.fits(Md, Nd):
                     kernels.linear(xd, pw_d[i], out=peer.partial(Md, Nd))
                     peer.reduce(Md, Nd, out=yd)
                 else:
@@ -544,7 +554,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         "gpu_launches": (3 if allreduce == "peer" else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
         "allreduce": {"used": allreduce, "calibration_ms_per_step": calib,
-                      "peer_status": (peer.status() if peer is not None else None)},
+                      "peer_status": (peer.status() if peer is not None else None), "peer_unavailable": peer_error},
     }
     print(json.dumps(line), flush=True)
 
