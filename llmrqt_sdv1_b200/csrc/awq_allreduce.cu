@@ -76,6 +76,11 @@ constexpr int kArThreads = 256;
 __global__ void __launch_bounds__(kArThreads)
 peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint16_t* out, const uint16_t* bias,
                       size_t count, int ncols, int rank, int world) {
+  // Launched with programmatic stream serialization: this grid may start while the kernel that writes the
+  // partial is still finishing, and the next kernel of the stream may start (and prefetch its weights) while
+  // this one waits for the peers.  Nothing below touches memory before the previous kernel has completed.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned* my_flags = flags[rank];
   const unsigned epoch = my_flags[kArEpochOff] + 1u;   // written only by this kernel's last block, a launch ago
   if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(flags[threadIdx.x] + kArReadyOff + rank, epoch);
@@ -157,10 +162,18 @@ int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* o
   const size_t vecs = count / 8;
   int blocks = static_cast<int>((vecs + kArThreads - 1) / kArThreads);
   if (blocks > 64) blocks = 64;        // all blocks must be resident together: they wait on one another's peers
-  peer_allreduce_kernel<<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint16_t* const*>(bufs), reinterpret_cast<unsigned* const*>(flags),
-      static_cast<uint16_t*>(out), static_cast<const uint16_t*>(bias), count, ncols, rank, world);
-  AWQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kArThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, reinterpret_cast<const uint16_t* const*>(bufs),
+                                  reinterpret_cast<unsigned* const*>(flags), static_cast<uint16_t*>(out),
+                                  static_cast<const uint16_t*>(bias), count, ncols, rank, world));
   return AWQ_B200_OK;
 }
 
