@@ -222,57 +222,9 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       } else {
         load_x(bl, xv);
       }
-      // Per-block activation sums from the tensor core: A rows 0..7 are all ones (-> S[m] = sum_k
-      // x[m,k]), rows 8..15 hold the constant carried by the code at that k, 1024 or 64 (-> H[m]).
-      // Two short chains; nothing below waits for them until the very end of the block.
-#pragma unroll
-      for (int mh = 0; mh < MH; ++mh) {
-        float SH0[4], SH1[4];
-        constexpr uint32_t kOne = 0x3C003C00u;
-        mma_16816_first(SH0, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][0].x, xv[mh][0].y);
-        mma_16816_first(SH1, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][0].z, xv[mh][0].w);
-#pragma unroll
-        for (int i = 1; i < 4; ++i) {
-          mma_16816(SH0, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][i].x, xv[mh][i].y);
-          mma_16816(SH1, kOne, kCodeOffsetLo, kOne, kCodeOffsetHi, xv[mh][i].z, xv[mh][i].w);
-        }
-        T[mh] = make_float4(SH0[0] + SH1[0], SH0[1] + SH1[1], SH0[2] + SH1[2], SH0[3] + SH1[3]);
-      }
+      gemv_block_sums<MH>(xv, T);
       GEMV_TRACE_IT(9);
-#pragma unroll
-      for (int q = 0; q < NP; ++q) {
-        const uint32_t wa[4] = {wv[2 * q].x, wv[2 * q].y, wv[2 * q].z, wv[2 * q].w};
-        const uint32_t wb[4] = {wv[2 * q + 1].x, wv[2 * q + 1].y, wv[2 * q + 1].z, wv[2 * q + 1].w};
-        const float sa = sc[2 * q], za = zp[2 * q], sb = sc[2 * q + 1], zb = zp[2 * q + 1];
-        // Two independent accumulation chains per block, both starting from zero.
-        float blk[MH][2][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t qa[4], qb[4];
-          unpack_codes(wa[i], qa);
-          unpack_codes(wb[i], qb);
-#pragma unroll
-          for (int mh = 0; mh < MH; ++mh) {
-            if (i == 0) {
-              mma_16816_first(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
-              mma_16816_first(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
-            } else {
-              mma_16816(blk[mh][0], qa[0], qb[0], qa[1], qb[1], xv[mh][i].x, xv[mh][i].y);
-              mma_16816(blk[mh][1], qa[2], qb[2], qa[3], qb[3], xv[mh][i].z, xv[mh][i].w);
-            }
-          }
-        }
-#pragma unroll
-        for (int mh = 0; mh < MH; ++mh) {
-          // sum_k x*code = chain0 + chain1 - H   (H removes the constants 1024 / 64 carried by the codes)
-          const float d0 = (blk[mh][0][0] + blk[mh][1][0]) - T[mh].z, d1 = (blk[mh][0][1] + blk[mh][1][1]) - T[mh].w;
-          const float d2 = (blk[mh][0][2] + blk[mh][1][2]) - T[mh].z, d3 = (blk[mh][0][3] + blk[mh][1][3]) - T[mh].w;
-          acc[mh][q][0] = fmaf(sa, fmaf(-za, T[mh].x, d0), acc[mh][q][0]);
-          acc[mh][q][1] = fmaf(sa, fmaf(-za, T[mh].y, d1), acc[mh][q][1]);
-          acc[mh][q][2] = fmaf(sb, fmaf(-zb, T[mh].x, d2), acc[mh][q][2]);
-          acc[mh][q][3] = fmaf(sb, fmaf(-zb, T[mh].y, d3), acc[mh][q][3]);
-        }
-      }
+      gemv_block_pairs<NTW, MH>(wv, sc, zp, xv, T, acc);
       GEMV_TRACE_IT(10);
     }
   }
