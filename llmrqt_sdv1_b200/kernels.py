@@ -15,6 +15,10 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+# The raw handle of the current stream without building a torch.cuda.Stream object (2 us cheaper per call).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _prep(*tensors: torch.Tensor) -> torch.device:
     dev = tensors[0].device
     if dev.type != "cuda":
@@ -193,13 +197,14 @@ def gemm_wtm(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch
                 lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out, (m_tile,))
 
 
-def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_shape=None) -> torch.Tensor:
     """The library's dispatcher (decode GEMV, split-K tensor-memory kernel or GEMM by rows and shape).
-    `overlap` as in `gemv`.  This is the per-token call of the module, so the wrapper keeps its own
-    work to a minimum: cached pointers and workspace sizes, one ctypes call."""
+    `overlap` as in `gemv`.  `x` is fp16 [..., K]; its leading dimensions are the rows.  The result is
+    `out`, or a new tensor of `out_shape` (default [M, N]).  This is the per-token call of the module, so
+    the wrapper keeps its own work to a minimum: cached pointers and workspace sizes, one ctypes call."""
     wp, sp, zp, dev = pw._ptrs
-    if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != pw.K:
-        raise ValueError(f"x must be fp16 [M, {pw.K}], got {x.dtype} {tuple(x.shape)}")
+    if x.dtype != torch.float16 or x.dim() < 2 or x.shape[-1] != pw.K:
+        raise ValueError(f"x must be fp16 [..., {pw.K}], got {x.dtype} {tuple(x.shape)}")
     if x.device != dev:
         if x.device.type != "cuda":
             raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
@@ -208,17 +213,20 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
         raise RuntimeError("all tensors of one call must be on the same device")
     if not x.is_contiguous():
         x = x.contiguous()
-    M = x.shape[0]
-    _lib.set_device(dev.index)
+    M = x.numel() // pw.K
+    index = dev.index
+    _lib.set_device(index)
     need = pw._ws_need.get(M)
     if need is None:
         need = pw._ws_need[M] = lib.awq_b200_linear_workspace_bytes(max(M, 1), pw.K, pw.N)
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    key = (dev.index, stream, "awq_b200_linear")
-    ws = _workspaces.get(key)
+    stream = _raw_stream(index) if _raw_stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspaces.get((index, stream, "awq_b200_linear"))
     if ws is None or ws.numel() < need:
         ws = _workspace(dev, stream, need, "awq_b200_linear")
-    y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
+    if out is not None:
+        y = out
+    else:
+        y = torch.empty(out_shape if out_shape is not None else (M, pw.N), dtype=torch.float16, device=dev)
     st = lib.awq_b200_linear_ex(x.data_ptr(), wp, sp, zp, bias.data_ptr() if bias is not None else None,
                                 y.data_ptr(), M, pw.K, pw.N, pw.group_size, ws.data_ptr(), ws.numel(), stream,
                                 _lib.OVERLAP_PREVIOUS if overlap else 0)

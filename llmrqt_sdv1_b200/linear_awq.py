@@ -15,12 +15,18 @@ from torch.autograd import Function
 AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
 
 
+_KERNELS = None
+
+
 def _kernels():
     # Imported on first use so that host-only helpers (packing, sharding plans)
     # stay importable for inspection; any compute call still fails loudly
     # without the CUDA library.
-    from . import kernels, sq_fp8_kernels
-    return kernels, sq_fp8_kernels
+    global _KERNELS
+    if _KERNELS is None:
+        from . import kernels, sq_fp8_kernels
+        _KERNELS = (kernels, sq_fp8_kernels)
+    return _KERNELS
 
 
 def pack_awq_int4(values: torch.Tensor) -> torch.Tensor:
@@ -54,8 +60,10 @@ class AWQLinearMMFunction(Function):
             overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
             # the bias is added inside the kernel: fp16(acc), then fp16(y + bias) - the two roundings of the
             # reference's `out + bias` on fp16 tensors (linear_awq.py:205)
-            out = kernels.linear(x.reshape(-1, x.shape[-1]), pw, bias=bias, overlap=overlap).reshape(out_shape)
-            bias = None
+            # 2-D input comes back 3-D, as from the reference (linear_awq.py:209-210)
+            shape3 = (1,) + tuple(out_shape) if len(out_shape) == 2 else out_shape
+            return kernels.linear(x if x.dim() >= 2 else x.unsqueeze(0), pw, bias=bias, overlap=overlap,
+                                  out_shape=shape3)
         out = out + bias if bias is not None else out
         if out.dim() == 2:          # the reference always hands back a 3-D tensor
             out = out.unsqueeze(0)
@@ -116,9 +124,21 @@ class AWQLinear_GEMM(nn.Module):
         return self
 
     def forward(self, x):
-        assert x.device == self.qweight.device, "when awq linear fwd, input and qweight must be same device!"
-        assert self.qzeros.device == self.qweight.device, "when awq linear fwd, qzeros and qweight must be same device!"
-        assert self.scales.device == self.qweight.device, "when awq linear fwd, scales and qweight must be same device!"
+        buffers = self._buffers
+        qweight, qzeros, scales = buffers["qweight"], buffers["qzeros"], buffers["scales"]
+        dev = qweight.device
+        assert x.device == dev, "when awq linear fwd, input and qweight must be same device!"
+        assert qzeros.device == dev, "when awq linear fwd, qzeros and qweight must be same device!"
+        assert scales.device == dev, "when awq linear fwd, scales and qweight must be same device!"
+        if x.dtype == torch.float16 and self.impl_mode == "auto" and x.dim() >= 2 and x.numel() != 0:
+            # The per-token path: straight to the library's dispatcher.  Nothing here records autograd
+            # state (the result is a fresh tensor written by the kernel), so no no_grad block is needed.
+            kernels, ext = _kernels()
+            pw = ext.packed_for(qweight, qzeros, scales, self.group_size)
+            overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
+            shape = x.shape[:-1] + (self.out_features,)
+            return kernels.linear(x, pw, bias=self.bias, overlap=overlap,
+                                  out_shape=(1,) + tuple(shape) if len(shape) == 2 else shape)
         out_shape = x.shape[:-1] + (self.out_features,)
         if x.shape[0] == 0:
             return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
@@ -128,7 +148,7 @@ class AWQLinear_GEMM(nn.Module):
         with torch.no_grad():
             # The reference goes through AWQLinearMMFunction.apply (linear_awq.py:385-395); under
             # no_grad that is the same computation plus ~10 us of autograd bookkeeping per call.
-            out = AWQLinearMMFunction.forward(None, x, self.qweight, self.qzeros, self.scales, self.w_bit,
+            out = AWQLinearMMFunction.forward(None, x, qweight, qzeros, scales, self.w_bit,
                                               self.group_size, self.bias, self.out_features, self.impl_mode)
         if input_dtype != torch.float16:
             out = out.to(dtype=input_dtype)
