@@ -155,8 +155,10 @@ def run_reference(args, rank):
 
 
 # ----------------------------------------------------------------------------- GPU arm helpers
-def time_graph(torch, fn, iters, warmup=3, reps=3):
-    """Median ms per call of `fn` (a sequence of launches on the current stream), graph-replayed."""
+def time_graph(torch, fn, iters, warmup=3, reps=3, min_ms=4.0):
+    """Median ms per call of `fn` (a sequence of launches on the current stream), graph-replayed.
+    `iters` is raised until one repetition lasts at least `min_ms` (short repetitions are measured while
+    the clocks are still ramping)."""
     for _ in range(warmup):
         fn()
     g = torch.cuda.CUDAGraph()
@@ -164,6 +166,14 @@ def time_graph(torch, fn, iters, warmup=3, reps=3):
         fn()
     g.replay()
     torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(3):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    est = max(a.elapsed_time(b) / 3, 1e-3)
+    iters = max(iters, min(2000, int(min_ms / est) + 1))
     out = []
     for _ in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -365,8 +365,10 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
   const bool can_split = workspace_bytes >= wtm_workspace_bytes(di.sm_count);
   auto waves_wtm = [&](int rows) {
     const long long t = static_cast<long long>((M + rows - 1) / rows) * ntiles;
-    if (!can_split || t <= di.sm_count) return waves(rows);
-    return static_cast<double>(t) / di.sm_count + 0.05;
+    // the split is taken when the idle share of the last (or only) wave is worth more than ~35 us
+    const double idle_us = (t % di.sm_count) ? (1.0 - static_cast<double>(t % di.sm_count) / di.sm_count) * (K / 64) * 0.6 : 0.0;
+    if (!can_split || idle_us <= 35.0) return waves(rows);
+    return static_cast<double>(t) / di.sm_count + 0.08;
   };
   const double c_wtm64 = waves_wtm(64) * 0.43, c_wtm128 = waves_wtm(128) * 0.52, c_wtm192 = waves_wtm(192) * 0.64;
   const double c_smem1 = waves(128) * 0.78, c_smem2 = waves(256) * 1.00;

@@ -547,18 +547,23 @@ static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_coun
   p.ntiles = (p.N + kWtBN - 1) / kWtBN;
   AWQ_CUDA_TRY(cudaFuncSetAttribute(wtm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   const int tiles = p.mtiles * p.ntiles;
-  const int grid = tiles < sm_count ? tiles : sm_count;
-  // Tail split: worth it when the last wave is partial and the idle time it would leave (a fraction of
-  // one tile's k loop) clearly exceeds the cost of the partial tiles (~10 us), and the caller's
-  // workspace has room for two fp32 tiles per CTA.
-  const int tail = tiles % grid;
-  const double idle_us = tail ? (1.0 - static_cast<double>(tail) / grid) * (p.K / kWtBK) * 0.6 : 0.0;
-  const size_t need = kWtPartialOff + static_cast<size_t>(grid) * 2 * MT * kWtBN * sizeof(float);
-  p.tail_split = (tiles > grid && idle_us > 20.0 && p.partial != nullptr && workspace_bytes >= need) ? 1 : 0;
+  // Tail split: worth it when the last wave is partial - or the only wave leaves SMs idle - and the idle
+  // time it would leave (a fraction of one tile's k loop) clearly exceeds the cost of the partial tiles
+  // (~10 us), and the caller's workspace has room for two fp32 tiles per CTA.  With fewer tiles than SMs
+  // every tile is then cut along k and all SMs work (full_rounds = 0).
+  const int tail = tiles % sm_count;   // with fewer tiles than SMs: all of them
+  const double idle_us = tail ? (1.0 - static_cast<double>(tail) / sm_count) * (p.K / kWtBK) * 0.6 : 0.0;
+  const size_t need = kWtPartialOff + static_cast<size_t>(sm_count) * 2 * MT * kWtBN * sizeof(float);
+  p.tail_split = (idle_us > 35.0 && p.partial != nullptr && workspace_bytes >= need) ? 1 : 0;
+  // Every CTA of a split grid must own at least one unit (the fix-up adds the slots of all CTAs between a
+  // tile's first and last contributor): no more CTAs than units.
+  const long long units = static_cast<long long>(tiles) * (p.K / kWtBK);
+  const int grid = p.tail_split ? static_cast<int>(units < sm_count ? units : sm_count)
+                                : (tiles < sm_count ? tiles : sm_count);
   wtm_kernel<MT><<<grid, kWtThreads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
   AWQ_CUDA_TRY(cudaGetLastError());
   if (p.tail_split) {
-    const int full_rounds = tiles / grid;
+    const int full_rounds = tiles / grid;   // 0 when every tile is split
     wtm_fixup_kernel<MT><<<dim3(tail, MT / 16), 256, 0, stream>>>(p, grid, p.K / kWtBK, full_rounds, tail);
     AWQ_CUDA_TRY(cudaGetLastError());
   }

@@ -230,10 +230,17 @@ def test_gemm_vs_oracle(K_, M, K, N):
     assert K_.gemm_status() == 0
     assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
     # both tensor-core kernels (weights staged in shared memory / in tensor memory, every row tile)
-    # multiply the same fp16 weights in the same k order: identical bits
-    assert torch.equal(K_.gemm_smem(dev(x), pw), y)
+    # multiply the same fp16 weights in the same k order: identical bits as long as one CTA finishes a tile;
+    # where the tensor-memory kernel cuts tiles along k (long k, SMs otherwise idle) the fp32 partial sums
+    # are added in k order instead: equal to fp32 rounding, and the same bits on every call
+    ys = K_.gemm_smem(dev(x), pw)
+    scale = float(ys.float().abs().max())
+    assert float((y.float() - ys.float()).abs().max()) <= 1e-3 * scale
     for mt in (64, 128, 192):
-        assert torch.equal(K_.gemm_wtm(dev(x), pw, m_tile=mt), y)
+        assert torch.equal(K_.gemm_wtm_unsplit(dev(x), pw, m_tile=mt), ys)
+        ym = K_.gemm_wtm(dev(x), pw, m_tile=mt)
+        assert float((ym.float() - ys.float()).abs().max()) <= 1e-3 * scale
+        assert torch.equal(ym, K_.gemm_wtm(dev(x), pw, m_tile=mt))
     assert K_.gemm_status() == 0
 
 
@@ -332,6 +339,17 @@ def test_gemm_tail_split(K_):
     assert (y.float() - ref).abs().max() / scale <= TOL
     assert (y.float() - y_unsplit.float()).abs().max() / scale <= 1e-3
     assert torch.equal(y_unsplit, K_.gemm_smem(x, pw, bias=bias))
+    # fewer tiles than SMs: every tile is cut along k and all SMs work
+    M3, N3 = 300, 1024
+    qw, qz, sc = _random_packed_inputs(K, N3, 128, seed=79)
+    pw3 = K_.make_packed(qw, qz, sc, 128)
+    for mt in (64, 128, 192):
+        y3 = K_.gemm_wtm(x[:M3].contiguous(), pw3, m_tile=mt)
+        y3u = K_.gemm_wtm_unsplit(x[:M3].contiguous(), pw3, m_tile=mt)
+        ref3 = torch.matmul(x[:M3], K_.dequantize(qw, qz, sc, 128)).float()
+        assert (y3.float() - ref3).abs().max() / ref3.abs().max() <= TOL
+        assert (y3.float() - y3u.float()).abs().max() / ref3.abs().max() <= 1e-3
+        assert torch.equal(y3, K_.gemm_wtm(x[:M3].contiguous(), pw3, m_tile=mt))
     # ragged rows and columns through the shared tiles as well
     M2, N2 = 2000, 4040
     qw, qz, sc = _random_packed_inputs(K, N2, 128, seed=78)
