@@ -213,6 +213,30 @@ def decode_detail(torch, kernels, quantize, peaks):
     return rows
 
 
+def ffn70b_single_gpu(torch, kernels, quantize, peaks):
+    """The N > 1 workload (8 layers of the 70B-class gate_up and down linears, M = 1) unsharded on this one
+    GPU: the 1-GPU point of the 1/2/4/8 series that `--gpus N` reports for N > 1."""
+    Kg, Ng = FFN70B["gate_up"]
+    Kd, Nd = FFN70B["down"]
+    pws = []
+    for layer in range(FFN70B_LAYERS):
+        for (K, N, seed) in ((Kg, Ng, 1000 * layer), (Kd, Nd, 1000 * layer + 500)):
+            qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=seed, device="cuda")
+            pws.append(kernels.make_packed(qw, qz, sc, GROUP))
+            del qw
+    xs = {K: torch.randn((1, K), device="cuda").half() for K in (Kg, Kd)}
+    ys = {N: torch.empty((1, N), dtype=torch.float16, device="cuda") for N in (Ng, Nd)}
+
+    def step():
+        for pw in pws:
+            kernels.linear(xs[pw.K], pw, out=ys[pw.N], overlap=True)
+    ms = time_graph(torch, step, iters=10)
+    nbytes = FFN70B_LAYERS * (gemv_bytes(1, Kg, Ng) + gemv_bytes(1, Kd, Nd))
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": "ffn70b_tp at tp=1", "ms_per_step": round(ms, 4), "value": round(gbs, 1), "unit": "GB/s",
+            "frac_measured": round(gbs / peaks["hbm_gbs"], 4), "frac_nominal_8tbs": round(gbs / 8000.0, 4)}
+
+
 def prefill_detail(torch, kernels, quantize, peaks):
     rows = []
     for K, N in PREFILL_SHAPES:
@@ -325,6 +349,7 @@ def run_qwen3_decode(args, torch, peaks):
     if not args.no_detail:
         line["decode_detail"] = decode_detail(torch, kernels, quantize, peaks)
         line["prefill_detail"] = prefill_detail(torch, kernels, quantize, peaks)
+        line["ffn70b_tp_n1"] = ffn70b_single_gpu(torch, kernels, quantize, peaks)
         best = max(line["prefill_detail"], key=lambda r: r["tflops"])
         # Each shape is timed in repetitions of >= 4 ms of back-to-back launches, i.e. under the power cap:
         # the sustained library figure is the matching denominator; the burst figure is given beside it.
