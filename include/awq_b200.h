@@ -137,7 +137,10 @@ enum awq_b200_flags {
    * tuning.  The two decompositions add a column's k blocks in different (fixed) groupings, so
    * their results agree to fp32 rounding, not bit for bit. */
   AWQ_B200_GEMV_STREAM = 4,
-  AWQ_B200_GEMV_PER_SPLIT = 8
+  AWQ_B200_GEMV_PER_SPLIT = 8,
+  /* awq_b200_linear_fused only: where the call takes the GEMM route, use the kernel that stages the
+   * dequantised weights in shared memory (as awq_b200_gemm_smem does).  For tests. */
+  AWQ_B200_GEMM_SMEM = 16
 };
 
 /* awq_b200_gemv with call flags.  No reference counterpart (the reference launches on the
@@ -274,6 +277,38 @@ AWQ_B200_API int awq_b200_linear_ex(const void* x, const void* packed, const voi
                        const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
                        int group_size, void* workspace, size_t workspace_bytes,
                        awq_b200_stream_t stream, unsigned flags);
+
+/* Elementwise work that follows the linear in a decoder layer, done in the kernel's epilogue.  Every
+ * step rounds to fp16 where the unfused sequence of fp16 tensor operations does (the reference's
+ * modules run exactly that sequence: `out + bias`, linear_awq.py:205; Hugging Face's gated MLP
+ * `down_proj(act_fn(gate_proj(x)) * up_proj(x))` and the decoder layer's `residual + hidden_states`
+ * around the reference's quantized linears, nn_models/modules/nonlinear/transformer_layer.py:139-151):
+ *   h = fp16(acc);  h = fp16(h + bias[n])                                (bias != NULL)
+ *   gated = 1: the columns are (gate, up) pairs (2j, 2j+1) - build such a weight with
+ *              awq_b200_interleave_columns - and y has N / 2 columns:
+ *              h = fp16(fp16(silu(h_gate)) * h_up), silu(v) = v / (1 + exp(-v)) in fp32
+ *   h = fp16(h + residual[m][column of y])                                (residual != NULL)
+ * y is [M, N] fp16, or [M, N / 2] with gated = 1 (which needs N % 16 == 0); bias is in the column order
+ * of the packed weight; residual has the shape of y and may be y itself. */
+typedef struct awq_b200_epilogue {
+  const void* bias;
+  const void* residual;
+  int gated;
+} awq_b200_epilogue;
+
+/* awq_b200_linear_ex with an epilogue (NULL = none).  Same routing, workspace and flags. */
+AWQ_B200_API int awq_b200_linear_fused(const void* x, const void* packed, const void* scales,
+                          const int32_t* qzeros, const awq_b200_epilogue* epilogue, void* y, int M, int K,
+                          int N, int group_size, void* workspace, size_t workspace_bytes,
+                          awq_b200_stream_t stream, unsigned flags);
+
+/* Column-interleaves two AWQ int4 tensors of equal shape (qweight [K, n/8] or qzeros [K/G, n/8], int32
+ * words in the on-disk nibble order): column 2j of `out` [rows, 2 * words_per_row] is column j of `a`,
+ * column 2j+1 is column j of `b`.  With the scales interleaved the same way this turns the separate gate
+ * and up projections of a gated MLP (which the reference keeps as two AWQ linears) into the one weight
+ * a gated epilogue expects.  Load-time utility. */
+AWQ_B200_API int awq_b200_interleave_columns(const int32_t* a, const int32_t* b, int32_t* out, int rows,
+                                int words_per_row, awq_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -47,7 +47,14 @@ SIGNATURES = {
     "awq_b200_gemv_max_rows": (_I, []),
     "awq_b200_linear_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_linear": (_I, _COMPUTE),
+    "awq_b200_linear_fused": (_I, _COMPUTE + [C.c_uint]),   # 5th argument: const awq_b200_epilogue*
+    "awq_b200_interleave_columns": (_I, [_P, _P, _P, _I, _I, _P]),
 }
+
+
+class Epilogue(C.Structure):
+    """awq_b200_epilogue."""
+    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("gated", C.c_int)]
 
 
 class AWQKernelError(RuntimeError):
@@ -73,6 +80,7 @@ OVERLAP_PREVIOUS = 1
 NO_CLUSTER = 2
 GEMV_STREAM = 4
 GEMV_PER_SPLIT = 8
+GEMM_SMEM = 16
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(1, 9)
 _VALUE_ERRORS = {ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_TOO_LARGE}
 

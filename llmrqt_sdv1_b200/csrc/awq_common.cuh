@@ -38,6 +38,41 @@ inline int check_shape(int K, int N, int group_size) {
   return AWQ_B200_OK;
 }
 
+// What happens to a finished fp32 sum on its way to Y (the launches a decoder layer would otherwise
+// spend on elementwise kernels after the linear).  Every step rounds to fp16 exactly where the unfused
+// sequence of fp16 tensor operations does, so fused and unfused results agree bit for bit except for
+// the last place of the exponential inside SiLU:
+//   h = fp16(acc);  h = fp16(h + bias[col])                                   (bias optional)
+//   gated: columns come in (gate, up) pairs (2j, 2j+1) and Y has N/2 columns:
+//          h = fp16(fp16(silu(h_gate)) * h_up)      - `act_fn(gate_proj(x)) * up_proj(x)` of a gated MLP
+//   h = fp16(h + residual[m][out col])                                         (residual optional)
+struct Epilogue {
+  const uint16_t* bias;       // [N] in the column order of the packed weight, or null
+  const uint16_t* residual;   // [M, out_cols] fp16, or null
+  int gated;                  // 0 / 1
+};
+inline int epilogue_out_cols(const Epilogue& e, int N) { return e.gated ? N / 2 : N; }
+inline int check_epilogue(const Epilogue& e, int N) {
+  if ((e.bias && !aligned16(e.bias)) || (e.residual && !aligned16(e.residual))) return AWQ_B200_ERR_ALIGN;
+  if (e.gated && N % 16 != 0) return AWQ_B200_ERR_SHAPE;
+  return AWQ_B200_OK;
+}
+
+// The kernels behind the C entry points, with the full epilogue (same argument rules as the entry points).
+int gemv_run(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+             void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+             cudaStream_t stream, unsigned flags);
+int skinny_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                    void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream, unsigned flags);
+int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                 void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream, int m_tile);
+// variant: 0 = pick by the cost table, 1 = dequantised weights in shared memory
+int gemm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                  cudaStream_t stream, int variant);
+
 struct DeviceInfo {
   int sm_count;
   int cc_major;
@@ -116,6 +151,124 @@ __host__ __device__ inline int stream_cta_of(long long u, long long U, long long
 }
 
 __device__ __forceinline__ uint32_t half_bits_x2(uint16_t h) { return static_cast<uint32_t>(h) * 0x00010001u; }
+
+// ---------------------------------------------------------------------------
+// device side: the epilogue (see struct Epilogue)
+// ---------------------------------------------------------------------------
+// SiLU of an fp16 value as an fp16 tensor operation computes it: in fp32, x / (1 + exp(-x)), one rounding.
+__device__ __forceinline__ __half silu_half(__half g) {
+  const float x = __half2float(g);
+  return __float2half_rn(x / (1.0f + expf(-x)));
+}
+
+// Finishes the adjacent columns (col, col + 1), col even, of row m: one fp16 pair of Y, or with a gated
+// epilogue the single element (m, col / 2).
+__device__ __forceinline__ void epilogue_store_pair(uint16_t* y, const Epilogue& e, int m, int N, int col, float a,
+                                                    float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  if (e.bias != nullptr) h = __hadd2(h, *reinterpret_cast<const __half2*>(e.bias + col));
+  if (e.gated) {
+    __half o = __hmul(silu_half(__low2half(h)), __high2half(h));
+    const size_t at = static_cast<size_t>(m) * (N >> 1) + (col >> 1);
+    if (e.residual != nullptr) o = __hadd(o, __ushort_as_half(e.residual[at]));
+    y[at] = __half_as_ushort(o);
+  } else {
+    const size_t at = static_cast<size_t>(m) * N + col;
+    if (e.residual != nullptr) h = __hadd2(h, *reinterpret_cast<const __half2*>(e.residual + at));
+    *reinterpret_cast<__half2*>(y + at) = h;
+  }
+}
+
+// One column of row m.  Not for gated epilogues (their callers go through epilogue_store_pair).
+__device__ __forceinline__ void epilogue_store_one(uint16_t* y, const Epilogue& e, int m, int N, int col, float a) {
+  __half h = __float2half_rn(a);
+  if (e.bias != nullptr) h = __hadd(h, __ushort_as_half(e.bias[col]));
+  const size_t at = static_cast<size_t>(m) * N + col;
+  if (e.residual != nullptr) h = __hadd(h, __ushort_as_half(e.residual[at]));
+  y[at] = __half_as_ushort(h);
+}
+
+// One column per lane, lane l of the warp holding column col0 + l with col0 even; every lane of the warp
+// must call (lanes whose column or row lies outside the matrix pass valid = false).  `h` is the rounded sum
+// with the bias already added.  A gated epilogue pairs neighbouring lanes through a shuffle and the even
+// lane stores.
+__device__ __forceinline__ void epilogue_finish_lane(uint16_t* y, const Epilogue& e, int m, int N, int col, __half h,
+                                                     bool valid) {
+  if (!e.gated) {
+    if (valid) {
+      const size_t at = static_cast<size_t>(m) * N + col;
+      if (e.residual != nullptr) h = __hadd(h, __ushort_as_half(e.residual[at]));
+      y[at] = __half_as_ushort(h);
+    }
+    return;
+  }
+  const unsigned up = __shfl_xor_sync(0xffffffffu, static_cast<unsigned>(__half_as_ushort(h)), 1);
+  if (valid && (col & 1) == 0) {
+    __half o = __hmul(silu_half(h), __ushort_as_half(static_cast<unsigned short>(up)));
+    const size_t at = static_cast<size_t>(m) * (N >> 1) + (col >> 1);
+    if (e.residual != nullptr) o = __hadd(o, __ushort_as_half(e.residual[at]));
+    y[at] = __half_as_ushort(o);
+  }
+}
+__device__ __forceinline__ void epilogue_store_lane(uint16_t* y, const Epilogue& e, int m, int N, int col, float a,
+                                                    bool valid) {
+  __half h = __float2half_rn(a);
+  if (e.bias != nullptr && valid) h = __hadd(h, __ushort_as_half(e.bias[col]));
+  epilogue_finish_lane(y, e, m, N, col, h, valid);
+}
+
+// 2 * W adjacent columns of row m starting at `col` (a multiple of 2 * W), as W half2 words holding the
+// rounded sums with the bias already added.  W = 2 or 4.
+template <int W>
+__device__ __forceinline__ void epilogue_finish_words(uint16_t* y, const Epilogue& e, int m, int N, int col,
+                                                      const uint32_t (&h)[W]) {
+  static_assert(W == 2 || W == 4, "2 or 4 words");
+  if (e.gated) {
+    uint32_t o[W / 2];
+#pragma unroll
+    for (int j = 0; j < W / 2; ++j) {
+      const __half2 p0 = *reinterpret_cast<const __half2*>(&h[2 * j]);
+      const __half2 p1 = *reinterpret_cast<const __half2*>(&h[2 * j + 1]);
+      const __half2 r = __halves2half2(__hmul(silu_half(__low2half(p0)), __high2half(p0)),
+                                       __hmul(silu_half(__low2half(p1)), __high2half(p1)));
+      o[j] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    const size_t at = static_cast<size_t>(m) * (N >> 1) + (col >> 1);
+    if (W == 4) {
+      if (e.residual != nullptr) {
+        const uint2 r = *reinterpret_cast<const uint2*>(e.residual + at);
+        asm("add.f16x2 %0, %1, %2;" : "=r"(o[0]) : "r"(o[0]), "r"(r.x));
+        asm("add.f16x2 %0, %1, %2;" : "=r"(o[W / 2 - 1]) : "r"(o[W / 2 - 1]), "r"(r.y));
+      }
+      *reinterpret_cast<uint2*>(y + at) = make_uint2(o[0], o[W / 2 - 1]);
+    } else {
+      if (e.residual != nullptr) {
+        const uint32_t r = *reinterpret_cast<const uint32_t*>(e.residual + at);
+        asm("add.f16x2 %0, %1, %2;" : "=r"(o[0]) : "r"(o[0]), "r"(r));
+      }
+      *reinterpret_cast<uint32_t*>(y + at) = o[0];
+    }
+    return;
+  }
+  const size_t at = static_cast<size_t>(m) * N + col;
+  uint32_t o[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) o[j] = h[j];
+  if (e.residual != nullptr) {
+    uint32_t r[W];
+    if (W == 4) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(e.residual + at);
+      r[0] = rv.x; r[1] = rv.y; r[W - 2] = rv.z; r[W - 1] = rv.w;
+    } else {
+      const uint2 rv = *reinterpret_cast<const uint2*>(e.residual + at);
+      r[0] = rv.x; r[1] = rv.y;
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) asm("add.f16x2 %0, %1, %2;" : "=r"(o[j]) : "r"(o[j]), "r"(r[j]));
+  }
+  if (W == 4) *reinterpret_cast<uint4*>(y + at) = make_uint4(o[0], o[1], o[W - 2], o[W - 1]);
+  else *reinterpret_cast<uint2*>(y + at) = make_uint2(o[0], o[1]);
+}
 
 #endif  // __CUDACC__
 

@@ -42,7 +42,7 @@ template <int MH> struct GemmCfg {
 struct GemmParams {
   const uint16_t* scales;
   const uint32_t* qzeros;
-  const uint16_t* bias;
+  Epilogue epi;
   uint16_t* y;
   unsigned* status;  // workspace word: 0 = ok, else which wait expired
   int M, K, N;
@@ -245,7 +245,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       // ------------------------------ epilogue --------------------------------
       if (!mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) { ok = false; break; }
       tcgen05_fence_after();
-      const bool has_bias = p.bias != nullptr;
+      const bool has_bias = p.epi.bias != nullptr;
+      const bool plain = !p.epi.gated && p.epi.residual == nullptr;
 #pragma unroll 1
       for (int h = 0; h < MH; ++h) {
         const int row = m0 + h * 128 + lane_q * 32 + lane;
@@ -265,7 +266,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
               if (col < p.N) {
                 uint32_t b2[4] = {0u, 0u, 0u, 0u};
                 if (has_bias) {
-                  const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                  const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.epi.bias + col));
                   b2[0] = bv.x; b2[1] = bv.y; b2[2] = bv.z; b2[3] = bv.w;
                 }
                 uint4 out;
@@ -273,7 +274,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 out.y = cvt_pack_bias(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]), b2[1], has_bias);
                 out.z = cvt_pack_bias(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]), b2[2], has_bias);
                 out.w = cvt_pack_bias(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]), b2[3], has_bias);
-                *reinterpret_cast<uint4*>(yrow + col) = out;
+                if (plain) {
+                  *reinterpret_cast<uint4*>(yrow + col) = out;
+                } else {
+                  const uint32_t words[4] = {out.x, out.y, out.z, out.w};
+                  epilogue_finish_words<4>(p.y, p.epi, row, p.N, col, words);
+                }
               }
             }
           }
@@ -329,20 +335,17 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmP
 
 // Weights-in-tensor-memory kernel (awq_wtm.cu).
 size_t wtm_workspace_bytes(int sm_count);
-int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
-                 void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
-                 cudaStream_t stream, int m_tile);
 
 // variant: 0 = pick by the cost table, 1 = dequantised weights in shared memory (this file)
-int gemm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+int gemm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                   void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                   cudaStream_t stream, int variant) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1) return AWQ_B200_ERR_SHAPE;
-  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y) ||
-      (bias && !aligned16(bias)))
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;
+  if (int st = check_epilogue(epi, N)) return st;
   if (!workspace || workspace_bytes < 16) return AWQ_B200_ERR_WORKSPACE;
   if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
   DeviceInfo di;
@@ -380,7 +383,7 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
     if (c_wtm128 < c_w) { c_w = c_wtm128; mt = 128; }
     if (c_wtm64 < c_w) { c_w = c_wtm64; mt = 64; }
     if (c_w <= c_smem)
-      return wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes, stream, mt);
+      return wtm_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, workspace, workspace_bytes, stream, mt);
   }
 
   CUtensorMap mx, mw;
@@ -408,7 +411,7 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
   GemmParams p;
   p.scales = static_cast<const uint16_t*>(scales);
   p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
-  p.bias = static_cast<const uint16_t*>(bias);
+  p.epi = epi;
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   p.M = M; p.K = K; p.N = N;
@@ -437,7 +440,7 @@ size_t awq_b200_gemm_workspace_bytes(int M, int K, int N) {
 int awq_b200_gemm(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                   void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                   awq_b200_stream_t stream) {
-  return gemm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+  return gemm_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace, workspace_bytes,
                        static_cast<cudaStream_t>(stream), 0);
 }
 
@@ -445,7 +448,7 @@ int awq_b200_gemm(const void* x, const void* packed, const void* scales, const i
 int awq_b200_gemm_smem(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                        void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                        awq_b200_stream_t stream) {
-  return gemm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+  return gemm_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace, workspace_bytes,
                        static_cast<cudaStream_t>(stream), 1);
 }
 

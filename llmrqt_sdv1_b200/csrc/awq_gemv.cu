@@ -49,8 +49,12 @@ namespace awq {
 // per block and row come from the tensor core as well.  Sums are added in a fixed order: a warp's
 // blocks in k order, then the KW warps of a column group in kw order (shared memory), then the
 // grid-level splits in split order (cluster shared memory or the global workspace).
-template <int NTW, int MT, int KW, int W>
-__global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(const GemvParams p) {
+// FUSED = false compiles the residual / gated parts of the epilogue out (bias only).
+template <int NTW, int MT, int KW, int W, bool FUSED>
+__global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(const typename GemvParamsOf<FUSED>::type p) {
+  const GemvFusion* fusion = nullptr;   // compile-time null in the unfused variants
+  if constexpr (FUSED) fusion = &p.fusion;
+  const bool gated = fusion != nullptr && fusion->gated != 0;
   constexpr int kGemvWarps = W;
   constexpr int kGemvThreads = (W + 1) * 32;
   static_assert(NTW == 2 || NTW == 4, "column tiles are processed in pairs");
@@ -243,7 +247,8 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
 
   // ---- epilogue -------------------------------------------------------------------------------
   // A compute thread holds rows m = 8*mh + 2c, +1 of columns n and n + 8 of each of its pairs.
-  const bool direct = (p.S == 1);
+  // A gated epilogue needs both columns of a pair in one thread: it always finishes through the partials.
+  const bool direct = (p.S == 1) && !gated;
   const bool via_cluster = (p.cluster != 0);
   float* red_k = reinterpret_cast<float*>(ring);                 // [KW][M][kCtaCols]  (KW > 1 only)
   float* red = red_k + (KW > 1 ? KW * p.M * kCtaCols : 0);       // [M][kCtaCols]      (cluster only)
@@ -251,7 +256,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   auto emit = [&](int m, int nl, float v) {
     const int n = cta_tile0 * 8 + nl;
     if (n >= p.N) return;
-    if (direct) store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, n, v);
+    if (direct) variant_store_one(p, fusion, m, n, v);
     else if (via_cluster) red[m * kCtaCols + nl] = v;
     else __stcg(p.partial + (static_cast<size_t>(split) * p.M + m) * p.N + n, v);
   };
@@ -313,7 +318,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       for (int r = 1; r < 8; ++r) {
         if (r < p.S) { sum.x += v[r].x; sum.y += v[r].y; }
       }
-      store_out2(p.y, p.bias, static_cast<size_t>(m) * p.N, cta_tile0 * 8 + nl, sum.x, sum.y);
+      variant_store_pair(p, fusion, m, cta_tile0 * 8 + nl, sum.x, sum.y);
     }
     cluster_sync_all();   // nobody leaves while its shared memory may still be read
     GEMV_TRACE(6);
@@ -359,7 +364,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
         }
       }
     }
-    store_out2(p.y, p.bias, static_cast<size_t>(row) * p.N, col, sum.x, sum.y);
+    variant_store_pair(p, fusion, row, col, sum.x, sum.y);
   }
   GEMV_TRACE(6);
 }
@@ -437,7 +442,7 @@ static GemvPlan plan_gemv(int K, int N, int sm_count) {
 
 // Streaming (persistent, evenly balanced) variant, in awq_gemv_stream.cu.
 int gemv_stream_slots(int K, int N, int ntw, int w, int kw, int sm_count);
-int gemv_stream_launch(const GemvParams& base, int ntw, int w, int kw, int sm_count, int max_smem_optin,
+int gemv_stream_launch(const GemvParams& base, const GemvFusion& fusion, int ntw, int w, int kw, int sm_count, int max_smem_optin,
                        cudaStream_t stream, bool overlap_previous);
 
 // The streaming kernel pays off for very large matrices only (measured: level with the per-split grid
@@ -453,13 +458,16 @@ static bool stream_by_default(const GemvPlan& plan, int nblk, int ntiles, int sm
 // call expects clean counters.
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
-template <int NTW, int MT, int KW, int W>
-static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_optin, cudaStream_t stream,
-                       bool overlap_previous) {
+template <int NTW, int MT, int KW, int W, bool FUSED>
+static int launch_gemv(const GemvParams& p_plain, const GemvFusion& fusion, const GemvPlan& plan, int max_smem_optin,
+                       cudaStream_t stream, bool overlap_previous) {
+  typename GemvParamsOf<FUSED>::type p;
+  static_cast<GemvParams&>(p) = p_plain;
+  if constexpr (FUSED) p.fusion = fusion;
   const size_t smem = static_cast<size_t>(gemv_stages(NTW, W)) * W * NTW * (512 + 32) + 2 * gemv_stages(NTW, W) * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW, W, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
@@ -483,20 +491,21 @@ static int launch_gemv(const GemvParams& p, const GemvPlan& plan, int max_smem_o
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW, W>, p));
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW, W, FUSED>, p));
   return AWQ_B200_OK;
 }
 
 int gemv_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
-                  const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                  const Epilogue& epi, void* y, int M, int K, int N, int group_size, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream, int force_ntw, int force_kw, int force_bps,
                   unsigned flags, int force_w = 0) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) ||
-      !aligned16(y) || (bias && !aligned16(bias)))
+      !aligned16(y))
     return AWQ_B200_ERR_ALIGN;
+  if (int st = check_epilogue(epi, N)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
@@ -529,7 +538,9 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   p.wp = static_cast<const uint4*>(packed);
   p.scales = static_cast<const uint16_t*>(scales);
   p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
-  p.bias = static_cast<const uint16_t*>(bias);
+  p.bias = epi.bias;
+  const GemvFusion fusion{epi.residual, epi.gated};
+  const bool fused = epi.gated || epi.residual != nullptr;
   p.y = static_cast<uint16_t*>(y);
   p.partial = nullptr;
   p.counters = nullptr;
@@ -547,7 +558,7 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   if (use_stream) {
     p.bps = 0; p.S = 0; p.cluster = 0;
     const int slots = gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, di.sm_count);
-    if (slots > 1) {
+    if (slots > 1 || epi.gated) {
       const size_t cb = counter_bytes(N);
       const size_t need = cb + static_cast<size_t>(slots) * M * N * sizeof(float);
       if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
@@ -555,14 +566,14 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
       p.counters = static_cast<unsigned*>(workspace);
       p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + cb);
     }
-    return gemv_stream_launch(p, plan.ntw, plan.w, plan.kw, di.sm_count, di.max_smem_optin, stream, overlap);
+    return gemv_stream_launch(p, fusion, plan.ntw, plan.w, plan.kw, di.sm_count, di.max_smem_optin, stream, overlap);
   }
 
   // A cluster needs its CTAs resident together; beyond one CTA per SM that costs more occupancy than the
   // shared-memory reduction saves.
   p.cluster = (plan.S >= 2 && plan.S <= 8 && static_cast<long long>(plan.ncol) * plan.S <= di.sm_count &&
                !(flags & AWQ_B200_NO_CLUSTER)) ? 1 : 0;
-  if (plan.S > 1 && !p.cluster) {
+  if ((plan.S > 1 || epi.gated) && !p.cluster) {
     const size_t cb = counter_bytes(N);
     const size_t need = cb + static_cast<size_t>(plan.S) * M * N * sizeof(float);
     if (!workspace || workspace_bytes < need) return AWQ_B200_ERR_WORKSPACE;
@@ -574,14 +585,23 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   const bool wide = M > 8;
 #define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                             \
   if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                        \
-    return wide ? launch_gemv<NTW_, 16, KW_, W_>(p, plan, di.max_smem_optin, stream, overlap)    \
-                : launch_gemv<NTW_, 8, KW_, W_>(p, plan, di.max_smem_optin, stream, overlap);
+    return fused ? (wide ? launch_gemv<NTW_, 16, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap)    \
+                         : launch_gemv<NTW_, 8, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap))    \
+                 : (wide ? launch_gemv<NTW_, 16, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap)   \
+                         : launch_gemv<NTW_, 8, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap));
   AWQ_GEMV_CASE(2, 1, 8) AWQ_GEMV_CASE(2, 2, 8) AWQ_GEMV_CASE(2, 4, 8) AWQ_GEMV_CASE(2, 8, 8)
   AWQ_GEMV_CASE(4, 1, 8) AWQ_GEMV_CASE(4, 2, 8) AWQ_GEMV_CASE(4, 4, 8) AWQ_GEMV_CASE(4, 8, 8)
   AWQ_GEMV_CASE(2, 4, 16) AWQ_GEMV_CASE(2, 8, 16) AWQ_GEMV_CASE(2, 16, 16)
   AWQ_GEMV_CASE(4, 4, 16) AWQ_GEMV_CASE(4, 8, 16) AWQ_GEMV_CASE(4, 16, 16)
   return AWQ_B200_ERR_SHAPE;
 #undef AWQ_GEMV_CASE
+}
+
+int gemv_run(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+             void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+             cudaStream_t stream, unsigned flags) {
+  return gemv_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, workspace, workspace_bytes, stream,
+                       0, 0, 0, flags);
 }
 
 size_t gemv_workspace_bytes(int M, int K, int N) {
@@ -615,14 +635,14 @@ size_t awq_b200_gemv_workspace_bytes(int M, int K, int N) {
 int awq_b200_gemv(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                   const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                   size_t workspace_bytes, awq_b200_stream_t stream) {
-  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+  return gemv_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace,
                        workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0, 0u);
 }
 
 int awq_b200_gemv_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                      const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                      size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
-  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+  return gemv_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace,
                        workspace_bytes, static_cast<cudaStream_t>(stream), 0, 0, 0, flags);
 }
 
@@ -636,7 +656,7 @@ int awq_b200_gemv_plan(const void* x, const void* packed, const void* scales, co
                        const void* bias, void* y, int M, int K, int N, int group_size,
                        void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, int ntw,
                        int kw, int bps, unsigned flags) {
-  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace,
+  return gemv_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace,
                        workspace_bytes, static_cast<cudaStream_t>(stream), ntw, kw % 100, bps, flags,
                        kw >= 100 ? 16 : (kw > 0 ? 8 : 0));
 }
@@ -690,7 +710,7 @@ int awq_b200_gemv_static(const void* x, const void* packed, const void* scales, 
   if (awq_b200_gemv_workspace_bytes(M, K, N) > kGemvStaticScratchBytes) return AWQ_B200_ERR_TOO_LARGE;
   void* scratch = nullptr;
   if (int st = static_scratch_for_current_device(static_cast<cudaStream_t>(stream), &scratch)) return st;
-  return gemv_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, scratch, kGemvStaticScratchBytes,
+  return gemv_dispatch(x, packed, scales, qzeros, Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, scratch, kGemvStaticScratchBytes,
                        static_cast<cudaStream_t>(stream), 0, 0, 0, 0u);
 }
 

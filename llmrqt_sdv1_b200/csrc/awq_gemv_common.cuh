@@ -32,6 +32,17 @@ struct GemvParams {
   int ntiles;        // N / 8
   int cluster;       // 1: the S splits of a column range form one thread-block cluster and reduce over DSMEM
 };
+// What a FUSED kernel variant carries besides the bias (see struct Epilogue).  The unfused variants keep
+// the plain parameter block, so their code does not change with what the fused ones can do.
+struct GemvFusion {
+  const uint16_t* residual;
+  int gated;
+};
+struct GemvParamsFused : GemvParams {
+  GemvFusion fusion;
+};
+template <bool FUSED> struct GemvParamsOf { using type = GemvParams; };
+template <> struct GemvParamsOf<true> { using type = GemvParamsFused; };
 
 __device__ __forceinline__ void mma_16816(float acc[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -53,18 +64,6 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// y = fp16(acc) then, with a bias, fp16(y + bias): the two roundings of the
-// reference's `out + bias` on an fp16 tensor.
-__device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, size_t row_off, int col,
-                                           float a, float b) {
-  uint32_t v = pack_half2(a, b);
-  if (bias != nullptr) {
-    const uint32_t bv = *reinterpret_cast<const uint32_t*>(bias + col);
-    asm("add.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(bv));
-  }
-  *reinterpret_cast<uint32_t*>(y + row_off + col) = v;
 }
 
 // One packed word (8 nibbles) -> four half2 for the tensor core, without scaling and without
@@ -165,10 +164,33 @@ __device__ __forceinline__ float small_uint_to_float(uint32_t v) {   // exact fo
   return __uint_as_float(0x4B000000u | v) - 8388608.0f;
 }
 
+// The stores of a kernel variant: FUSED = false is the bias-only epilogue, FUSED = true the full one.
+// y = fp16(acc) then, with a bias, fp16(y + bias): the two roundings of the reference's `out + bias` on an
+// fp16 tensor.
+__device__ __forceinline__ void store_out2(uint16_t* y, const uint16_t* bias, size_t row_off, int col,
+                                           float a, float b) {
+  uint32_t v = pack_half2(a, b);
+  if (bias != nullptr) {
+    const uint32_t bv = *reinterpret_cast<const uint32_t*>(bias + col);
+    asm("add.f16x2 %0, %1, %2;" : "=r"(v) : "r"(v), "r"(bv));
+  }
+  *reinterpret_cast<uint32_t*>(y + row_off + col) = v;
+}
 __device__ __forceinline__ void store_out1(uint16_t* y, const uint16_t* bias, size_t row_off, int col, float a) {
   __half h = __float2half_rn(a);
   if (bias != nullptr) h = __hadd(h, __ushort_as_half(bias[col]));
   y[row_off + col] = __half_as_ushort(h);
+}
+// The stores of a kernel variant: P = GemvParams is the bias-only epilogue, P = GemvParamsFused the full one
+// (`f` is its fusion block; ignored otherwise).
+__device__ __forceinline__ void variant_store_one(const GemvParams& p, const GemvFusion* f, int m, int col, float a) {
+  if (f != nullptr) epilogue_store_one(p.y, Epilogue{p.bias, f->residual, f->gated}, m, p.N, col, a);
+  else store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, col, a);
+}
+__device__ __forceinline__ void variant_store_pair(const GemvParams& p, const GemvFusion* f, int m, int col, float a,
+                                                   float b) {
+  if (f != nullptr) epilogue_store_pair(p.y, Epilogue{p.bias, f->residual, f->gated}, m, p.N, col, a, b);
+  else store_out2(p.y, p.bias, static_cast<size_t>(m) * p.N, col, a, b);
 }
 
 __device__ __forceinline__ void cluster_sync_all() {

@@ -33,15 +33,24 @@ struct GemvStreamParams {
   int ipc;             // units per column group
   long long units;     // ncol * ipc
 };
+struct GemvStreamParamsFused : GemvStreamParams {
+  GemvFusion fusion;
+};
+template <bool FUSED> struct GemvStreamParamsOf { using type = GemvStreamParams; };
+template <> struct GemvStreamParamsOf<true> { using type = GemvStreamParamsFused; };
 
 template <int W>
 __device__ __forceinline__ void compute_warps_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
 }
 
-template <int NTW, int MT, int KW, int W>
-__global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kernel(const GemvStreamParams sp) {
+// FUSED = false compiles the residual / gated parts of the epilogue out (bias only).
+template <int NTW, int MT, int KW, int W, bool FUSED>
+__global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kernel(const typename GemvStreamParamsOf<FUSED>::type sp) {
   const GemvParams& p = sp.g;
+  const GemvFusion* fusion = nullptr;   // compile-time null in the unfused variants
+  if constexpr (FUSED) fusion = &sp.fusion;
+  const bool gated = fusion != nullptr && fusion->gated != 0;
   constexpr int kComputeThreads = W * 32;
   static_assert(NTW == 2 || NTW == 4, "column tiles are processed in pairs");
   static_assert(W == 8 || W == 16, "8 or 16 compute warps");
@@ -182,7 +191,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kern
       const int c_last = stream_cta_of(cg_u0 + ipc - 1, U, G);
       const int nc = c_last - c_first + 1;
       const int slot = static_cast<int>(blockIdx.x) - c_first;
-      const bool direct = (nc == 1);
+      const bool direct = (nc == 1) && !gated;   // a gated epilogue pairs columns in the reduction below
       for (int pass = 0; pass < kPasses; ++pass) {
         const int cta_tile0 = cg * kGroupTiles + pass * kCtaTiles;
         const int tile0 = cta_tile0 + cw * NTW;
@@ -271,7 +280,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kern
         auto emit = [&](int m, int nl, float v) {
           const int n = cta_tile0 * 8 + nl;
           if (n >= p.N) return;
-          if (direct) store_out1(p.y, p.bias, static_cast<size_t>(m) * p.N, n, v);
+          if (direct) variant_store_one(p, fusion, m, n, v);
           else __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + n, v);
         };
         // A compute thread holds rows m = 8*mh + 2c, +1 of columns n and n + 8 of each of its pairs.
@@ -331,7 +340,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kern
                 sum.x += v.x;
                 sum.y += v.y;
               }
-              store_out2(p.y, p.bias, static_cast<size_t>(row) * p.N, col, sum.x, sum.y);
+              variant_store_pair(p, fusion, row, col, sum.x, sum.y);
             }
           }
         }
@@ -380,15 +389,18 @@ int gemv_stream_slots(int K, int N, int ntw, int w, int kw, int sm_count) {
   return worst;
 }
 
-template <int NTW, int MT, int KW, int W>
-static int launch_stream(const GemvStreamParams& sp, int grid, int max_smem_optin, cudaStream_t stream,
-                         bool overlap_previous) {
+template <int NTW, int MT, int KW, int W, bool FUSED>
+static int launch_stream(const GemvStreamParams& sp_plain, const GemvFusion& fusion, int grid, int max_smem_optin,
+                         cudaStream_t stream, bool overlap_previous) {
+  typename GemvStreamParamsOf<FUSED>::type sp;
+  static_cast<GemvStreamParams&>(sp) = sp_plain;
+  if constexpr (FUSED) sp.fusion = fusion;
   constexpr int ST = gemv_stages(NTW, W);
   constexpr int kCtaCols = (W / KW) * NTW * 8;
   const size_t smem = static_cast<size_t>(ST) * W * NTW * (512 + 32) + (KW > 1 ? KW : 0) * MT * kCtaCols * 4 + 2 * ST * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<NTW, MT, KW, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_stream_kernel<NTW, MT, KW, W, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
@@ -405,14 +417,14 @@ static int launch_stream(const GemvStreamParams& sp, int grid, int max_smem_opti
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NTW, MT, KW, W>, sp));
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NTW, MT, KW, W, FUSED>, sp));
   return AWQ_B200_OK;
 }
 
 // Launches the streaming kernel for a decomposition (ntw, w, kw) the caller has validated.  `base`
 // carries pointers and sizes; partial / counters must be set when gemv_stream_slots(...) > 1.
-int gemv_stream_launch(const GemvParams& base, int ntw, int w, int kw, int sm_count, int max_smem_optin,
-                       cudaStream_t stream, bool overlap_previous) {
+int gemv_stream_launch(const GemvParams& base, const GemvFusion& fusion, int ntw, int w, int kw, int sm_count,
+                       int max_smem_optin, cudaStream_t stream, bool overlap_previous) {
   GemvStreamParams sp;
   sp.g = base;
   const int group_tiles = (w / kw) * 4;
@@ -422,10 +434,13 @@ int gemv_stream_launch(const GemvParams& base, int ntw, int w, int kw, int sm_co
   sp.units = static_cast<long long>(sp.ncol) * sp.ipc;
   const int grid = stream_grid(w, sm_count, sp.units);
   const bool wide = base.M > 8;
+  const bool fused = fusion.gated || fusion.residual != nullptr;
 #define AWQ_STREAM_CASE(NTW_, KW_, W_)                                                                \
   if (ntw == NTW_ && kw == KW_ && w == W_)                                                            \
-    return wide ? launch_stream<NTW_, 16, KW_, W_>(sp, grid, max_smem_optin, stream, overlap_previous) \
-                : launch_stream<NTW_, 8, KW_, W_>(sp, grid, max_smem_optin, stream, overlap_previous);
+    return fused ? (wide ? launch_stream<NTW_, 16, KW_, W_, true>(sp, fusion, grid, max_smem_optin, stream, overlap_previous)   \
+                         : launch_stream<NTW_, 8, KW_, W_, true>(sp, fusion, grid, max_smem_optin, stream, overlap_previous))   \
+                 : (wide ? launch_stream<NTW_, 16, KW_, W_, false>(sp, fusion, grid, max_smem_optin, stream, overlap_previous)  \
+                         : launch_stream<NTW_, 8, KW_, W_, false>(sp, fusion, grid, max_smem_optin, stream, overlap_previous));
   AWQ_STREAM_CASE(2, 1, 8) AWQ_STREAM_CASE(2, 2, 8) AWQ_STREAM_CASE(2, 4, 8) AWQ_STREAM_CASE(2, 8, 8)
   AWQ_STREAM_CASE(4, 1, 8) AWQ_STREAM_CASE(4, 2, 8) AWQ_STREAM_CASE(4, 4, 8) AWQ_STREAM_CASE(4, 8, 8)
   AWQ_STREAM_CASE(2, 4, 16) AWQ_STREAM_CASE(2, 8, 16) AWQ_STREAM_CASE(2, 16, 16)

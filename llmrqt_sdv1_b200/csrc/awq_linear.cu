@@ -37,23 +37,47 @@ size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
 // Workspace layout: [0, 256) GEMM status word (zero unless a device-side wait
 // expired), then 16 KiB of arrival counters shared by all kernels (each leaves them zero), then
 // scratch for partial sums.  The first 256 + 16 KiB bytes must be zero before the first call.
-int awq_b200_linear_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
-                       const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
-                       size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
+static int linear_run(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                      const awq::Epilogue& epi, void* y, int M, int K, int N, int group_size, void* workspace,
+                      size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
   if (M < 1) return AWQ_B200_ERR_SHAPE;
   if (!workspace || workspace_bytes < kGemmStatusBytes) return AWQ_B200_ERR_WORKSPACE;
   unsigned char* rest = static_cast<unsigned char*>(workspace) + kGemmStatusBytes;
   const size_t rest_bytes = workspace_bytes - kGemmStatusBytes;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (route(M, K, N)) {
     case Route::kGemv:
-      return awq_b200_gemv_ex(x, packed, scales, qzeros, bias, y, M, K, N, group_size, rest, rest_bytes, stream, flags);
+      return awq::gemv_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kSkinny:
-      return awq_b200_skinny(x, packed, scales, qzeros, bias, y, M, K, N, group_size, rest, rest_bytes, stream, flags);
+      return awq::skinny_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kGemm:
       break;
   }
   // Same buffer: the GEMM's counters sit where the decode kernels keep theirs (both leave them zero).
-  return awq_b200_gemm(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes, stream);
+  return awq::gemm_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, workspace, workspace_bytes, s,
+                            (flags & AWQ_B200_GEMM_SMEM) ? 1 : 0);
+}
+
+int awq_b200_linear_ex(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                       const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                       size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
+  return linear_run(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K,
+                    N, group_size, workspace, workspace_bytes, stream, flags);
+}
+
+// The linear with the elementwise work that follows it in a decoder layer done in its epilogue: see
+// awq_b200_epilogue in the header.  Same routing, workspace and flags as awq_b200_linear_ex.
+int awq_b200_linear_fused(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                          const awq_b200_epilogue* epilogue, void* y, int M, int K, int N, int group_size,
+                          void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags) {
+  awq::Epilogue epi{nullptr, nullptr, 0};
+  if (epilogue != nullptr) {
+    if (epilogue->gated != 0 && epilogue->gated != 1) return AWQ_B200_ERR_SHAPE;
+    epi.bias = static_cast<const uint16_t*>(epilogue->bias);
+    epi.residual = static_cast<const uint16_t*>(epilogue->residual);
+    epi.gated = epilogue->gated;
+  }
+  return linear_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, workspace, workspace_bytes, stream, flags);
 }
 
 int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,

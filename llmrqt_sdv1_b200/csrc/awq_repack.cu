@@ -87,6 +87,29 @@ __global__ void unpack_kernel(const uint32_t* __restrict__ packed, uint32_t* __r
   }
 }
 
+// Column interleave of two on-disk int4 tensors: output word c of a row holds columns 8c .. 8c+7 of the
+// interleaved tensor = columns 4c .. 4c+3 of `a` (even positions) and of `b` (odd positions), i.e. channels
+// 4 * (c & 1) + t, t = 0..3, of word c / 2 of each input.
+__global__ void interleave_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b,
+                                  uint32_t* __restrict__ out, long long rows, int words) {
+  const long long total = rows * 2 * words;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / (2 * words);
+    const int c = static_cast<int>(idx - r * 2 * words);
+    const uint32_t wa = a[r * words + (c >> 1)], wb = b[r * words + (c >> 1)];
+    const uint32_t first = static_cast<uint32_t>(c & 1) * 4u;
+    uint32_t w = 0;
+#pragma unroll
+    for (uint32_t t = 0; t < 4; ++t) {
+      const uint32_t sh = awq_slot_shift(first + t);
+      w |= ((wa >> sh) & 0xFu) << awq_slot_shift(2 * t);
+      w |= ((wb >> sh) & 0xFu) << awq_slot_shift(2 * t + 1);
+    }
+    out[idx] = w;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // dequant from the on-disk layout: one thread per qweight word (8 channels at
 // one k).  The slot order pairs nibble i with nibble i+4 = channels (2i, 2i+1),
@@ -202,6 +225,18 @@ int awq_b200_repack(const int32_t* qweight, void* packed, int K, int N, awq_b200
   const long long chunks = static_cast<long long>(K / 8) * (N / 8);
   repack_kernel<<<grid_for(chunks, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint32_t*>(qweight), static_cast<uint32_t*>(packed), K, N);
+  AWQ_CUDA_TRY(cudaGetLastError());
+  return AWQ_B200_OK;
+}
+
+int awq_b200_interleave_columns(const int32_t* a, const int32_t* b, int32_t* out, int rows, int words_per_row,
+                                awq_b200_stream_t stream) {
+  if (!a || !b || !out) return AWQ_B200_ERR_NULL;
+  if (rows <= 0 || words_per_row <= 0) return AWQ_B200_ERR_SHAPE;
+  const long long total = static_cast<long long>(rows) * 2 * words_per_row;
+  interleave_kernel<<<grid_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(a), reinterpret_cast<const uint32_t*>(b), reinterpret_cast<uint32_t*>(out), rows,
+      words_per_row);
   AWQ_CUDA_TRY(cudaGetLastError());
   return AWQ_B200_OK;
 }

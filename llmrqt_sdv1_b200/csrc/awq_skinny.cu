@@ -72,7 +72,7 @@ template <int MT> struct SkCfg {
 struct SkParams {
   const uint16_t* scales;
   const uint32_t* qzeros;
-  const uint16_t* bias;
+  Epilogue epi;
   uint16_t* y;
   float* partial;        // [slot][M][N] fp32, used by column tiles that straddle CTAs
   unsigned* counters;    // one arrival counter per column tile
@@ -353,7 +353,6 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       if (ok && !mbar_wait(bar_acc_full, static_cast<uint32_t>(seg) & 1u, abort_flag, 6)) ok = false;
       if (ok) {
         tcgen05_fence_after();
-        const uint16_t bias_n = (p.bias != nullptr && nvalid) ? p.bias[n] : static_cast<uint16_t>(0);
         constexpr int kChunksPerPart = MT / 16;          // chunks of 8 activation rows per warp
 #pragma unroll 1
         for (int ch = e_part * kChunksPerPart; ch < (e_part + 1) * kChunksPerPart; ++ch) {
@@ -364,20 +363,14 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                        : "r"(tmem_base + lane_addr + static_cast<uint32_t>(e_h * MT + ch * 8))
                        : "memory");
           tcgen05_wait_ld();
-          if (nvalid) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int m = ch * 8 + i;
-              if (m < p.M) {
-                const float val = __uint_as_float(v[i]);
-                if (direct) {
-                  __half hv = __float2half_rn(val);
-                  if (p.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
-                  p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(hv);   // 32 lanes = 64 contiguous bytes
-                } else {
-                  __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + n, val);
-                }
-              }
+          for (int i = 0; i < 8; ++i) {
+            const int m = ch * 8 + i;
+            if (m < p.M) {                               // warp-uniform
+              const float val = __uint_as_float(v[i]);
+              // 32 lanes = 32 consecutive columns starting at a multiple of 32: 64 contiguous bytes of a row
+              if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, n, val, nvalid);
+              else if (nvalid) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + n, val);
             }
           }
         }
@@ -411,7 +404,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
               sum.x += v.x;
               sum.y += v.y;
             }
-            store_out2(p.y, p.bias, static_cast<size_t>(row) * p.N, col, sum.x, sum.y);
+            epilogue_store_pair(p.y, p.epi, row, p.N, col, sum.x, sum.y);
           }
         }
         dequant_warps_sync();   // s_last is rewritten by the next straddling segment
@@ -503,15 +496,15 @@ static int launch_skinny(const void* x, const void* packed, SkParams p, int grid
   return AWQ_B200_OK;
 }
 
-int skinny_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+int skinny_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                     void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream, unsigned flags) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > 64) return AWQ_B200_ERR_SHAPE;
-  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y) ||
-      (bias && !aligned16(bias)))
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;
+  if (int st = check_epilogue(epi, N)) return st;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
@@ -524,7 +517,7 @@ int skinny_dispatch(const void* x, const void* packed, const void* scales, const
   SkParams p;
   p.scales = static_cast<const uint16_t*>(scales);
   p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
-  p.bias = static_cast<const uint16_t*>(bias);
+  p.epi = epi;
   p.y = static_cast<uint16_t*>(y);
   p.counters = static_cast<unsigned*>(workspace);
   p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + skinny_counter_bytes());
@@ -555,7 +548,7 @@ size_t awq_b200_skinny_workspace_bytes(int M, int K, int N) {
 int awq_b200_skinny(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                     void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                     awq_b200_stream_t stream, unsigned flags) {
-  return awq::skinny_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+  return awq::skinny_dispatch(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace, workspace_bytes,
                               static_cast<cudaStream_t>(stream), flags);
 }
 

@@ -64,7 +64,7 @@ template <int MT> struct WtCfg {
 struct WtParams {
   const uint16_t* scales;
   const uint32_t* qzeros;
-  const uint16_t* bias;
+  Epilogue epi;
   uint16_t* y;
   unsigned* status;
   float* partial;        // tail split only: two fp32 tiles [MT][256] per CTA
@@ -399,7 +399,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       if (ok && !mbar_wait(bar_acc_full, tile_it & 1u, abort_flag, 6)) ok = false;
       const int n = n0 + e_h * 128 + row;
       const bool nvalid = n < p.N;
-      const uint16_t bias_n = (p.bias != nullptr && nvalid) ? p.bias[n] : static_cast<uint16_t>(0);
+      const uint16_t bias_n = (p.epi.bias != nullptr && nvalid) ? p.epi.bias[n] : static_cast<uint16_t>(0);
       if (ok) {
         tcgen05_fence_after();
         constexpr int kChunks = MT / 16;                 // 16 activation rows per chunk
@@ -416,15 +416,14 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
               : "memory");
           tcgen05_wait_ld();
           if (direct) {
-            if (nvalid) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int m = m0 + ch * 16 + j;
-                if (m < p.M) {
-                  __half hv = __float2half_rn(__uint_as_float(v[j]));
-                  if (p.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
-                  p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(hv);   // 32 lanes = 64 contiguous bytes
-                }
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + ch * 16 + j;
+              if (m < p.M) {                            // warp-uniform
+                __half hv = __float2half_rn(__uint_as_float(v[j]));
+                if (p.epi.bias != nullptr) hv = __hadd(hv, __ushort_as_half(bias_n));
+                // 32 lanes = 32 consecutive columns starting at a multiple of 32: 64 contiguous bytes of a row
+                epilogue_finish_lane(p.y, p.epi, m, p.N, n, hv, nvalid);
               }
             }
           } else {
@@ -491,14 +490,12 @@ __global__ void __launch_bounds__(256) wtm_fixup_kernel(const WtParams p, int G,
     const int m = m0 + r0 + 4 * i;
     if (m >= p.M) continue;
     __half2 lo = __floats2half2_rn(sum[i].x, sum[i].y), hi = __floats2half2_rn(sum[i].z, sum[i].w);
-    if (p.bias != nullptr) {
-      lo = __hadd2(lo, *reinterpret_cast<const __half2*>(p.bias + n));
-      hi = __hadd2(hi, *reinterpret_cast<const __half2*>(p.bias + n + 2));
+    if (p.epi.bias != nullptr) {
+      lo = __hadd2(lo, *reinterpret_cast<const __half2*>(p.epi.bias + n));
+      hi = __hadd2(hi, *reinterpret_cast<const __half2*>(p.epi.bias + n + 2));
     }
-    uint2 out;
-    out.x = *reinterpret_cast<uint32_t*>(&lo);
-    out.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p.y + static_cast<size_t>(m) * p.N + n) = out;
+    const uint32_t words[2] = {*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi)};
+    epilogue_finish_words<2>(p.y, p.epi, m, p.N, n, words);
   }
 }
 
@@ -570,15 +567,15 @@ static int launch_wtm(const void* x, const void* packed, WtParams p, int sm_coun
   return AWQ_B200_OK;
 }
 
-int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream, int m_tile) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1) return AWQ_B200_ERR_SHAPE;
-  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y) ||
-      (bias && !aligned16(bias)))
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;
+  if (int st = check_epilogue(epi, N)) return st;
   if (!workspace || workspace_bytes < 16) return AWQ_B200_ERR_WORKSPACE;
   if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
   DeviceInfo di;
@@ -589,7 +586,7 @@ int wtm_dispatch(const void* x, const void* packed, const void* scales, const in
   WtParams p;
   p.scales = static_cast<const uint16_t*>(scales);
   p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
-  p.bias = static_cast<const uint16_t*>(bias);
+  p.epi = epi;
   p.y = static_cast<uint16_t*>(y);
   p.status = static_cast<unsigned*>(workspace);
   const bool roomy = workspace_bytes > kWtPartialOff;
@@ -616,7 +613,7 @@ extern "C" {
 int awq_b200_gemm_wtm(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                       awq_b200_stream_t stream) {
-  return awq::wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+  return awq::wtm_dispatch(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace, workspace_bytes,
                            static_cast<cudaStream_t>(stream), 0);
 }
 
@@ -624,7 +621,7 @@ int awq_b200_gemm_wtm(const void* x, const void* packed, const void* scales, con
 int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                            const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
                            size_t workspace_bytes, awq_b200_stream_t stream, int m_tile) {
-  return awq::wtm_dispatch(x, packed, scales, qzeros, bias, y, M, K, N, group_size, workspace, workspace_bytes,
+  return awq::wtm_dispatch(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M, K, N, group_size, workspace, workspace_bytes,
                            static_cast<cudaStream_t>(stream), m_tile);
 }
 

@@ -3,6 +3,8 @@ with torch, pass raw device pointers plus the current stream, and turn status
 codes into exceptions.  No arithmetic happens here."""
 from __future__ import annotations
 
+from ctypes import addressof as _addressof
+
 import torch
 
 from . import _lib
@@ -232,6 +234,80 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_
                                 _lib.OVERLAP_PREVIOUS if overlap else 0)
     if st != 0:
         check(st, "awq_b200_linear")
+    return y
+
+
+def interleave_columns(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Two AWQ int4 tensors of equal shape (qweight [K, n/8] or qzeros [K/G, n/8], int32) -> [rows, 2n/8]
+    with column 2j from `a` and column 2j+1 from `b`."""
+    if a.dtype != torch.int32 or b.dtype != torch.int32 or a.dim() != 2 or a.shape != b.shape:
+        raise ValueError("interleave_columns needs two int32 [rows, words] tensors of equal shape")
+    a, b = a.contiguous(), b.contiguous()
+    _prep(a, b)
+    out = torch.empty((a.shape[0], 2 * a.shape[1]), dtype=torch.int32, device=a.device)
+    check(lib.awq_b200_interleave_columns(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.shape[0], a.shape[1],
+                                          _stream(a)), "awq_b200_interleave_columns")
+    return out
+
+
+def make_gated_packed(gate, up, group_size) -> PackedWeight:
+    """One kernel-layout weight [K, 2n] from the (qweight, qzeros, scales) of a gate and an up projection
+    [K, n] each, columns interleaved (gate j, up j) as the gated epilogue of `linear_fused` expects."""
+    (gq, gz, gs), (uq, uz, us) = gate, up
+    if gs.shape != us.shape or gs.dtype != torch.float16 or us.dtype != torch.float16:
+        raise ValueError("gate and up scales must be fp16 tensors of equal shape")
+    scales = torch.stack((gs, us), dim=-1).reshape(gs.shape[0], 2 * gs.shape[1])
+    return make_packed(interleave_columns(gq, uq), interleave_columns(gz, uz), scales, group_size)
+
+
+def interleave_bias(gate_bias: torch.Tensor, up_bias: torch.Tensor) -> torch.Tensor:
+    """The bias of a `make_gated_packed` weight: [2n] in the packed column order."""
+    return torch.stack((gate_bias, up_bias), dim=-1).reshape(-1).contiguous()
+
+
+def linear_fused(x, pw: PackedWeight, bias=None, residual=None, gated: bool = False, out=None,
+                 overlap: bool = False, out_shape=None, flags: int = 0) -> torch.Tensor:
+    """`linear` with the elementwise work that follows it done in the kernel's epilogue: bias, then with
+    `gated` SiLU(gate) * up over the (gate, up) column pairs of a `make_gated_packed` weight (the result
+    has N / 2 columns), then `+ residual` (fp16, the shape of the result).  Every step rounds to fp16 as
+    the separate fp16 tensor operations would."""
+    wp, sp, zp, dev = pw._ptrs
+    if x.dtype != torch.float16 or x.dim() < 2 or x.shape[-1] != pw.K:
+        raise ValueError(f"x must be fp16 [..., {pw.K}], got {x.dtype} {tuple(x.shape)}")
+    for t in (x, bias, residual, out):
+        if t is not None and t.device != dev:
+            if t.device.type != "cuda":
+                raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
+            raise RuntimeError("all tensors of one call must be on the same device")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.numel() // pw.K
+    ncols = pw.N // 2 if gated else pw.N
+    if residual is not None:
+        if residual.dtype != torch.float16 or residual.numel() != M * ncols:
+            raise ValueError(f"residual must be fp16 with {M} x {ncols} elements")
+        if not residual.is_contiguous():
+            residual = residual.contiguous()
+    index = dev.index
+    _lib.set_device(index)
+    need = pw._ws_need.get(M)
+    if need is None:
+        need = pw._ws_need[M] = lib.awq_b200_linear_workspace_bytes(max(M, 1), pw.K, pw.N)
+    stream = _raw_stream(index) if _raw_stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspaces.get((index, stream, "awq_b200_linear"))
+    if ws is None or ws.numel() < need:
+        ws = _workspace(dev, stream, need, "awq_b200_linear")
+    if out is not None:
+        y = out
+    else:
+        y = torch.empty(out_shape if out_shape is not None else (M, ncols), dtype=torch.float16, device=dev)
+    epi = _lib.Epilogue(bias.data_ptr() if bias is not None else None,
+                        residual.data_ptr() if residual is not None else None, 1 if gated else 0)
+    st = lib.awq_b200_linear_fused(x.data_ptr(), wp, sp, zp, _addressof(epi), y.data_ptr(), M, pw.K, pw.N,
+                                   pw.group_size, ws.data_ptr(), ws.numel(), stream,
+                                   (_lib.OVERLAP_PREVIOUS if overlap else 0) | flags)
+    if st != 0:
+        check(st, "awq_b200_linear_fused")
     return y
 
 

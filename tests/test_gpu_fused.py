@@ -1,0 +1,149 @@
+"""The fused epilogues (bias, SiLU(gate) * up over interleaved column pairs, residual add) of every
+kernel behind `awq_b200_linear_fused`, against the unfused kernel followed by the separate fp16 tensor
+operations, and against the CPU oracle.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import awq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def K_():
+    from llmrqt_sdv1_b200 import kernels
+    assert torch.cuda.is_available()
+    return kernels
+
+
+def _random_awq(K, N, G, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    qw = torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
+    qz = torch.randint(-2**31, 2**31 - 1, (K // G, N // 8), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
+    sc = (torch.rand((K // G, N), device="cuda", generator=g) * 0.004 + 0.001).half()
+    return qw, qz, sc
+
+
+def _places(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance in fp16 representable values."""
+    def line(t):
+        u = t.contiguous().view(torch.int16).to(torch.int32)
+        mag = u & 0x7FFF
+        return torch.where(u < 0, -mag, mag)
+    return (line(a) - line(b)).abs()
+
+
+def test_interleave_matches_oracle_and_dequant(K_):
+    K, n, G = 256, 72, 128
+    gq, gz, gs = orc.make_awq_tensors(K, n, G, seed=1)
+    uq, uz, us = orc.make_awq_tensors(K, n, G, seed=2)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    out = K_.interleave_columns(dev(gq), dev(uq))
+    assert np.array_equal(out.cpu().numpy(), orc.interleave_columns(gq, uq))
+    assert np.array_equal(K_.interleave_columns(dev(gz), dev(uz)).cpu().numpy(), orc.interleave_columns(gz, uz))
+    pw = K_.make_gated_packed((dev(gq), dev(gz), dev(gs)), (dev(uq), dev(uz), dev(us)), G)
+    W = K_.dequantize_packed(pw).cpu().numpy()
+    assert np.array_equal(W[:, 0::2].view(np.uint16), orc.dequantize(gq, gz, gs, G).view(np.uint16))
+    assert np.array_equal(W[:, 1::2].view(np.uint16), orc.dequantize(uq, uz, us, G).view(np.uint16))
+
+
+def test_gated_vs_oracle_small(K_):
+    """One small gated MLP front half end to end against the numpy oracle (separate gate and up linears,
+    SiLU * up, residual)."""
+    K, n, G = 512, 192, 128
+    gq, gz, gs = orc.make_awq_tensors(K, n, G, seed=3)
+    uq, uz, us = orc.make_awq_tensors(K, n, G, seed=4)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    pw = K_.make_gated_packed((dev(gq), dev(gz), dev(gs)), (dev(uq), dev(uz), dev(us)), G)
+    for M in (1, 7, 16, 40, 200):
+        x = orc.make_activations(M, K, seed=M)
+        res = orc.make_activations(M, n, seed=100 + M)
+        ref = orc.add_residual(orc.silu_mul(orc.linear_forward(x, gq, gz, gs, G), orc.linear_forward(x, uq, uz, us, G)), res)
+        y = K_.linear_fused(dev(x), pw, residual=dev(res), gated=True).cpu().numpy()
+        assert y.shape == (M, n)
+        assert orc.max_normalised_error(y, ref) <= TOL, M
+    assert K_.gemv_status() == 0 and K_.gemm_status() == 0
+
+
+def _check_against_unfused(K_, M, K, n, flags, seed, with_bias=True):
+    """Fused result against the same kernel without epilogue (same decomposition, hence the same fp32 sums)
+    followed by the separate fp16 tensor operations."""
+    G = 128
+    gate, up = _random_awq(K, n, G, seed), _random_awq(K, n, G, seed + 1)
+    pw = K_.make_gated_packed(gate, up, G)
+    gen = torch.Generator(device="cuda").manual_seed(seed + 2)
+    x = torch.randn((M, K), device="cuda", generator=gen).half()
+    bias = (torch.randn(2 * n, device="cuda", generator=gen) * 0.5).half() if with_bias else None
+    res_half = torch.randn((M, n), device="cuda", generator=gen).half()
+    res_full = torch.randn((M, 2 * n), device="cuda", generator=gen).half()
+    y_plain = K_.linear_fused(x, pw, bias=bias, flags=flags)                      # [M, 2n], bias only
+    # residual only: exact
+    y_res = K_.linear_fused(x, pw, bias=bias, residual=res_full, flags=flags)
+    assert torch.equal(y_res, y_plain + res_full)
+    # gated (+ residual): SiLU may differ in its last place on a few elements
+    ref = F.silu(y_plain[:, 0::2]) * y_plain[:, 1::2]
+    y_gated = K_.linear_fused(x, pw, bias=bias, gated=True, flags=flags)
+    assert y_gated.shape == (M, n)
+    d = _places(y_gated, ref)
+    assert int(d.max()) <= 2 and float((d != 0).float().mean()) < 2e-3
+    y_both = K_.linear_fused(x, pw, bias=bias, residual=res_half, gated=True, flags=flags)
+    exact = d == 0
+    assert torch.equal(y_both[exact], (ref + res_half)[exact])
+    # in place on the residual buffer (the decoder layer's `h = h + ...`)
+    h = res_half.clone()
+    K_.linear_fused(x, pw, bias=bias, residual=h, gated=True, out=h, flags=flags)
+    assert torch.equal(h, y_both)
+    # and the unfused result itself is right
+    W = K_.dequantize_packed(pw)
+    full = torch.matmul(x, W).float() + (bias.float() if bias is not None else 0.0)
+    assert (y_plain.float() - full).abs().max() / full.abs().max() <= TOL
+    assert K_.gemv_status() == 0 and K_.gemm_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 16])
+@pytest.mark.parametrize("K,n,mode", [
+    (128, 64, "per_split"),                 # one split: finished through a single partial
+    (2048, 1024, "per_split"),              # a few splits (cluster reduction where it applies)
+    (2048, 1024, "per_split_no_cluster"),   # the same through the global partials
+    (6144, 1024, "per_split"),
+    (2048, 2048, "stream"),                 # persistent stream, segments with one and with several contributors
+    (2048, 6144, None),                     # the library's own choice for the gate_up shape of the decode config
+    (4096, 72, None),                       # ragged: N = 144 is not a multiple of the column tile
+])
+def test_decode_kernels_fused(K_, M, K, n, mode):
+    from llmrqt_sdv1_b200 import _lib
+    flags = {"per_split": _lib.GEMV_PER_SPLIT, "per_split_no_cluster": _lib.GEMV_PER_SPLIT | _lib.NO_CLUSTER,
+             "stream": _lib.GEMV_STREAM, None: 0}[mode]
+    _check_against_unfused(K_, M, K, n, flags, seed=K + n + M)
+
+
+@pytest.mark.parametrize("M,K,n", [(24, 4096, 1024), (64, 4096, 520), (3, 8192, 6144), (16, 8192, 6144)])
+def test_split_k_tensor_memory_kernel_fused(K_, M, K, n):
+    """17..64 rows of a narrow matrix, and few rows of a 48 MiB weight: the split-K tensor-memory kernel."""
+    _check_against_unfused(K_, M, K, n, 0, seed=K + n + M)
+
+
+@pytest.mark.parametrize("M,K,n,smem", [(300, 4096, 512, False),     # fewer tiles than SMs: tiles cut along k, fix-up kernel
+                                         (2048, 1024, 1024, False),  # whole tiles, weights in tensor memory
+                                         (2048, 1024, 1024, True),   # weights in shared memory
+                                         (1000, 512, 1016, False),   # ragged rows and columns
+                                         (1000, 512, 1016, True)])
+def test_gemm_kernels_fused(K_, M, K, n, smem):
+    from llmrqt_sdv1_b200 import _lib
+    _check_against_unfused(K_, M, K, n, _lib.GEMM_SMEM if smem else 0, seed=K + n + M, with_bias=(M != 300))
+
+
+def test_fused_argument_checks(K_):
+    qw, qz, sc = _random_awq(256, 72, 128, seed=9)       # N = 72: not a multiple of 16
+    pw = K_.make_packed(qw, qz, sc, 128)
+    x = torch.randn((2, 256), device="cuda").half()
+    with pytest.raises(ValueError):
+        K_.linear_fused(x, pw, gated=True)
+    with pytest.raises(ValueError):
+        K_.linear_fused(x, pw, residual=torch.zeros((2, 8), device="cuda").half())
+    y = K_.linear_fused(x, pw)                            # no epilogue at all = the plain linear
+    assert torch.equal(y, K_.linear(x, pw))

@@ -111,3 +111,37 @@ def test_c_oracle_matches_goldens(golden_dir):
     y3 = c_oracle.linear_forward(g["x3"], g["qweight"], g["qzeros"], g["scales"], int(g["group_size"]), g["bias"])
     assert orc.max_normalised_error(y3, g["y3"]) <= 1e-3
     assert c_oracle.threads() >= 1
+
+
+def _ulp_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Distance in fp16 representable values (sign-magnitude bits mapped onto a line)."""
+    def line(v):
+        u = v.view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
+    return np.abs(line(a) - line(b))
+
+
+def test_gated_epilogue_restatement_matches_torch():
+    """The epilogue restatements against the tensor operations the reference's layers run on fp16 tensors
+    (torch's own CPU kernels): SiLU(gate) * up and the residual add."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(11)
+    gate = (rng.standard_normal((64, 512)) * 3).astype(np.float16)
+    up = (rng.standard_normal((64, 512)) * 2).astype(np.float16)
+    ref = (F.silu(torch.from_numpy(gate)) * torch.from_numpy(up)).numpy()
+    got = orc.silu_mul(gate, up)
+    d = _ulp_distance(got, ref)
+    # the last place of exp() is not part of the contract: SiLU may differ by one fp16 place on a few
+    # elements, which the product can turn into two
+    assert d.max() <= 2 and (d != 0).mean() < 1e-3
+    res = (rng.standard_normal((64, 512))).astype(np.float16)
+    assert np.array_equal(orc.add_residual(got, res).view(np.uint16),
+                          (torch.from_numpy(got) + torch.from_numpy(res)).numpy().view(np.uint16))
+
+
+def test_interleave_columns_restatement():
+    rng = np.random.default_rng(12)
+    a, b = rng.integers(0, 16, size=(5, 64)), rng.integers(0, 16, size=(5, 64))
+    out = orc.unpack_logical(orc.interleave_columns(orc.pack_logical(a), orc.pack_logical(b)))
+    assert np.array_equal(out[:, 0::2], a) and np.array_equal(out[:, 1::2], b)
