@@ -14,6 +14,7 @@ import torch
 import torch.nn as nn
 
 from .linear_awq import AWQLinear_GEMM
+from .mlp_awq import AWQGatedMLP
 from .quantize import quantize_weight
 
 
@@ -42,8 +43,29 @@ def quantize_model_(model, group_size: int = 128, skip=("lm_head",)) -> int:
     return replaced
 
 
+@torch.no_grad()
+def fuse_mlp_(model) -> int:
+    """Replace, in place, every decoder layer's gated MLP whose three projections are `AWQLinear_GEMM`
+    modules and whose activation is SiLU by an `AWQGatedMLP` (gate and up in one launch with the
+    SiLU(gate) * up epilogue).  Call it after the checkpoint tensors are in place.  Returns how many
+    were replaced.  The reference's fusers stop at q/k/v (utils/fused_utils.py:43-105) and leave the MLP
+    as Hugging Face built it."""
+    replaced = 0
+    for layer in decoder_layers(model):
+        mlp = getattr(layer, "mlp", None)
+        projs = [getattr(mlp, n, None) for n in ("gate_proj", "up_proj", "down_proj")]
+        act = getattr(mlp, "act_fn", None)
+        is_silu = isinstance(act, nn.SiLU) or getattr(act, "__name__", "") == "silu" or \
+            type(act).__name__ in ("SiLUActivation", "SiLU")
+        if mlp is None or not all(isinstance(p, AWQLinear_GEMM) for p in projs) or not is_silu:
+            continue
+        layer.mlp = AWQGatedMLP(*projs)
+        replaced += 1
+    return replaced
+
+
 def set_impl_mode(model, mode: str) -> None:
     """"auto" = the sm_100a kernels, "dequant_matmul" = materialise the fp16 weight + library matmul."""
     for m in model.modules():
-        if isinstance(m, AWQLinear_GEMM):
+        if isinstance(m, (AWQLinear_GEMM, AWQGatedMLP)):
             m.impl_mode = mode

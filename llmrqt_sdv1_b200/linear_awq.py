@@ -123,7 +123,9 @@ class AWQLinear_GEMM(nn.Module):
         ext.packed_for(self.qweight, self.qzeros, self.scales, self.group_size)
         return self
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """`residual` (optional, not in the reference's signature): a tensor of the result's shape that the
+        kernel's epilogue adds after the bias, as `residual + forward(x)` on fp16 tensors would."""
         buffers = self._buffers
         qweight, qzeros, scales = buffers["qweight"], buffers["qzeros"], buffers["scales"]
         dev = qweight.device
@@ -137,8 +139,10 @@ class AWQLinear_GEMM(nn.Module):
             pw = ext.packed_for(qweight, qzeros, scales, self.group_size)
             overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
             shape = x.shape[:-1] + (self.out_features,)
-            return kernels.linear(x, pw, bias=self.bias, overlap=overlap,
-                                  out_shape=(1,) + tuple(shape) if len(shape) == 2 else shape)
+            shape = (1,) + tuple(shape) if len(shape) == 2 else shape
+            if residual is None:
+                return kernels.linear(x, pw, bias=self.bias, overlap=overlap, out_shape=shape)
+            return kernels.linear_fused(x, pw, bias=self.bias, residual=residual, overlap=overlap, out_shape=shape)
         out_shape = x.shape[:-1] + (self.out_features,)
         if x.shape[0] == 0:
             return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
@@ -150,6 +154,8 @@ class AWQLinear_GEMM(nn.Module):
             # no_grad that is the same computation plus ~10 us of autograd bookkeeping per call.
             out = AWQLinearMMFunction.forward(None, x, qweight, qzeros, scales, self.w_bit,
                                               self.group_size, self.bias, self.out_features, self.impl_mode)
+        if residual is not None:
+            out = residual.to(torch.float16).reshape(out.shape) + out
         if input_dtype != torch.float16:
             out = out.to(dtype=input_dtype)
         return out

@@ -147,3 +147,57 @@ def test_fused_argument_checks(K_):
         K_.linear_fused(x, pw, residual=torch.zeros((2, 8), device="cuda").half())
     y = K_.linear_fused(x, pw)                            # no epilogue at all = the plain linear
     assert torch.equal(y, K_.linear(x, pw))
+
+
+def _module(K, N, seed, bias=False):
+    from llmrqt_sdv1_b200 import AWQLinear_GEMM
+    qw, qz, sc = _random_awq(K, N, 128, seed)
+    m = AWQLinear_GEMM(4, 128, K, N, bias, "cuda")
+    m.qweight, m.qzeros, m.scales = qw, qz, sc
+    if bias:
+        m.bias = (torch.randn(N, device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed)) * 0.2).half()
+    return m
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 2048), (1, 7, 2048), (2, 100, 2048), (300, 2048)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gated_mlp_module(K_, shape, bias):
+    """`AWQGatedMLP` against the three-module form it replaces (different column counts may pick different
+    k-splits, so the comparison is the layer-output bound, not bit equality), with and without residual,
+    and against its own `dequant_matmul` mode."""
+    from llmrqt_sdv1_b200 import AWQGatedMLP
+    hidden, inter = 2048, 1536
+    gate, up, down = _module(hidden, inter, 1, bias), _module(hidden, inter, 2, bias), _module(inter, hidden, 3, bias)
+    mlp = AWQGatedMLP(gate, up, down)
+    x = torch.randn(shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).half() * 4
+    res = torch.randn(shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(6)).half()
+    ref = down(F.silu(gate(x)) * up(x)).reshape(shape)          # AWQLinear_GEMM hands 2-D input back 3-D
+    y = mlp(x)
+    assert y.shape == tuple(shape) and y.dtype == torch.float16
+    scale = ref.float().abs().max()
+    assert (y.float() - ref.float()).abs().max() / scale <= TOL
+    y_res = mlp(x, residual=res)
+    assert torch.equal(y_res, y + res)
+    mlp.impl_mode = "dequant_matmul"
+    y_dm = mlp(x, residual=res)
+    assert (y_dm.float() - y_res.float()).abs().max() / (ref.float() + res.float()).abs().max() <= TOL
+    # the plain module's residual argument
+    o = down(torch.randn(shape[:-1] + (inter,), device="cuda").half())
+    x_d = torch.randn(shape[:-1] + (inter,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(8)).half()
+    assert torch.equal(down(x_d, residual=res).reshape(shape), down(x_d).reshape(shape) + res)
+    assert o.shape[-1] == hidden
+    assert K_.gemv_status() == 0 and K_.gemm_status() == 0
+
+
+def test_gated_mlp_state_dict_and_dtype(K_):
+    from llmrqt_sdv1_b200 import AWQGatedMLP
+    mlp = AWQGatedMLP(_module(256, 128, 1), _module(256, 128, 2), _module(128, 256, 3))
+    names = set(mlp.state_dict().keys())
+    assert {"gate_up_qweight", "gate_up_qzeros", "gate_up_scales", "down_proj.qweight"} <= names
+    assert mlp.gate_up_qweight.shape == (256, 32) and mlp.gate_up_scales.shape == (2, 256)
+    x = torch.randn((3, 256), device="cuda").bfloat16()
+    y = mlp(x)
+    assert y.dtype == torch.bfloat16 and y.shape == (3, 256)
+    assert mlp(torch.zeros((0, 256), device="cuda").half()).shape == (0, 256)
+    with pytest.raises(ValueError):
+        AWQGatedMLP(_module(256, 128, 1), _module(256, 64, 2), _module(128, 256, 3))

@@ -53,3 +53,28 @@ def test_qwen3_shaped_model_prefill_and_decode_parity():
     confident = (top2[:, 0] - top2[:, 1]) > 2 * err_prefill * logits_ref.abs().max()
     agree = logits_new[0, 127:-1].argmax(-1) == logits_ref[0, 127:-1].argmax(-1)
     assert bool(agree[confident].all())
+
+
+@torch.no_grad()
+def test_fused_mlp_in_model():
+    """`fuse_mlp_` swaps every layer's MLP for the two-launch form; prefill and decode logits stay within
+    the compounded layer bound of the unfused model's."""
+    from llmrqt_sdv1_b200 import AWQGatedMLP, kernels
+    from llmrqt_sdv1_b200.hf_adapter import fuse_mlp_, set_impl_mode
+    torch.backends.cuda.enable_cudnn_sdp(False)
+    model = _build(layers=2)
+    set_impl_mode(model, "auto")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    ids = torch.randint(0, 151936, (1, 96), device="cuda", generator=g)
+    ref_prefill = model(ids).logits.float()
+    step = model(ids[:, :95], use_cache=True)
+    ref_decode = model(ids[:, 95:96], past_key_values=step.past_key_values, use_cache=True).logits.float()
+    assert fuse_mlp_(model) == 2
+    assert all(isinstance(layer.mlp, AWQGatedMLP) for layer in model.model.layers)
+    new_prefill = model(ids).logits.float()
+    step = model(ids[:, :95], use_cache=True)
+    new_decode = model(ids[:, 95:96], past_key_values=step.past_key_values, use_cache=True).logits.float()
+    torch.cuda.synchronize()
+    assert kernels.gemm_status() == 0 and kernels.gemv_status() == 0
+    assert float((new_prefill - ref_prefill).abs().max() / ref_prefill.abs().max()) <= 1e-2
+    assert float((new_decode - ref_decode).abs().max() / ref_decode.abs().max()) <= 1e-2
