@@ -213,6 +213,46 @@ def decode_detail(torch, kernels, quantize, peaks):
     return rows
 
 
+def mlp_fusion_detail(torch, kernels, quantize):
+    """The MLP of the decode configuration (hidden 2048, intermediate 6144) over 28 layers of distinct weights
+    (0.5 GB > L2), `h = h + down(silu(gate(h)) * up(h))`, as the three linears plus separate elementwise
+    kernels the reference's layer runs, and as two launches with fused epilogues.  us per layer, CUDA graph."""
+    import torch.nn.functional as F
+    hidden, inter, layers = 2048, 6144, 28
+    sep, fused = [], []
+    for layer in range(layers):
+        gate = quantize.random_awq_tensors(hidden, inter, GROUP, seed=10 * layer, device="cuda")
+        up = quantize.random_awq_tensors(hidden, inter, GROUP, seed=10 * layer + 1, device="cuda")
+        down = quantize.random_awq_tensors(inter, hidden, GROUP, seed=10 * layer + 2, device="cuda")
+        pw_d = kernels.make_packed(*down, GROUP)
+        sep.append((kernels.make_packed(*gate, GROUP), kernels.make_packed(*up, GROUP), pw_d))
+        fused.append((kernels.make_gated_packed(gate, up, GROUP), pw_d))
+    out = {}
+    for M in (1, 16):
+        h = torch.randn((M, hidden), device="cuda").half()
+        g, u, a = (torch.empty((M, inter), dtype=torch.float16, device="cuda") for _ in range(3))
+        d = torch.empty((M, hidden), dtype=torch.float16, device="cuda")
+
+        def step_separate():
+            for pw_g, pw_u, pw_d in sep:
+                kernels.linear(h, pw_g, out=g, overlap=True)
+                kernels.linear(h, pw_u, out=u, overlap=True)
+                torch.mul(F.silu(g), u, out=a)
+                kernels.linear(a, pw_d, out=d, overlap=True)
+                h.add_(d)
+
+        def step_fused():
+            for pw_gu, pw_d in fused:
+                kernels.linear_fused(h, pw_gu, gated=True, out=a, overlap=True)
+                kernels.linear_fused(a, pw_d, residual=h, out=h, overlap=True)
+        t_sep = time_graph(torch, step_separate, iters=10) / layers
+        h.normal_()
+        t_fused = time_graph(torch, step_fused, iters=10) / layers
+        out["M%d" % M] = {"separate_us_per_layer": round(t_sep * 1e3, 2), "fused_us_per_layer": round(t_fused * 1e3, 2),
+                          "launches_per_layer": {"separate": 6, "fused": 2}}
+    return out
+
+
 def ffn70b_single_gpu(torch, kernels, quantize, peaks):
     """The N > 1 workload (8 layers of the 70B-class gate_up and down linears, M = 1) unsharded on this one
     GPU: the 1-GPU point of the 1/2/4/8 series that `--gpus N` reports for N > 1."""
@@ -350,6 +390,7 @@ def run_qwen3_decode(args, torch, peaks):
         line["decode_detail"] = decode_detail(torch, kernels, quantize, peaks)
         line["prefill_detail"] = prefill_detail(torch, kernels, quantize, peaks)
         line["ffn70b_tp_n1"] = ffn70b_single_gpu(torch, kernels, quantize, peaks)
+        line["mlp_fusion"] = mlp_fusion_detail(torch, kernels, quantize)
         best = max(line["prefill_detail"], key=lambda r: r["tflops"])
         # Each shape is timed in repetitions of >= 4 ms of back-to-back launches, i.e. under the power cap:
         # the sustained library figure is the matching denominator; the burst figure is given beside it.

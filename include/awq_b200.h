@@ -261,13 +261,14 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
-/* Picks the kernel from the row count and the shape: M <= 16 -> awq_b200_gemv, or awq_b200_skinny
+/* Picks the kernel from the row count and the shape: M <= 8 -> awq_b200_gemv, or awq_b200_skinny
  * once the packed weights reach 48 MiB (a choice that depends on K and N only, so a row's bits do
- * not change with the number of rows decoded together); 17 <= M <= 64 -> awq_b200_skinny where the
- * GEMM would leave most SMs idle (N <= 18944 and K >= 4096); awq_b200_gemm otherwise.  Mirrors the
- * row-count switch in AWQLinearMMFunction.forward
- * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), with
- * the threshold moved from 8 to 16 rows. */
+ * not change with the number of rows decoded together, up to 8 rows); 9 <= M <= 16 -> the same with
+ * the switch at 16 MiB (the GEMV's 16-row variant is the slower one); 17 <= M <= 64 ->
+ * awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
+ * awq_b200_gemm otherwise.  Mirrors the row-count switch in AWQLinearMMFunction.forward
+ * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), which also changes kernel
+ * (and with it the order of additions) above 8 rows. */
 AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);

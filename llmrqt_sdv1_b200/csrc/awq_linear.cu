@@ -6,16 +6,23 @@ namespace {
 constexpr size_t kGemmStatusBytes = 256;  // leading slot of the shared workspace: GEMM status word
 constexpr int kSkinnyMaxRows = 64;
 
-// Which kernel serves M rows of a K x N linear.  The choice for M <= 16 depends on (K, N) only, so a
-// row's bits do not change with the number of rows decoded together.
-//   rows <= 16: the split-K tensor-memory kernel once the packed weights reach 48 MiB (it is level with
-//               the GEMV at one row there and about twice as fast at 16 rows), the GEMV below that.
-//   17..64:     the same kernel where the GEMM would leave most SMs idle (at most 74 column tiles of
-//               256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
+// Which kernel serves M rows of a K x N linear.
+//   rows <= 8:  the GEMV, or the split-K tensor-memory kernel once the packed weights reach 48 MiB (level
+//               with the GEMV at one row there).  The choice depends on (K, N) only, so a row's bits do not
+//               change with the number of rows decoded together, up to 8 rows.
+//   9..16:      the GEMV's 16-row variant re-reads the activations once per warp and runs at about half the
+//               speed of its 8-row variant, so the tensor-memory kernel takes over from 16 MiB of packed
+//               weights (20 - 35 % faster there).  Like the reference's switch from its GEMV to its GEMM
+//               at 8 rows, this changes the order of additions between 8 and 9 rows.
+//   17..64:     the tensor-memory kernel where the GEMM would leave most SMs idle (at most 74 column tiles
+//               of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
 enum class Route { kGemv, kSkinny, kGemm };
 Route route(int M, int K, int N) {
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
-  if (M <= awq_b200_gemv_max_rows()) return packed_bytes >= (48ll << 20) ? Route::kSkinny : Route::kGemv;
+  if (M <= awq_b200_gemv_max_rows()) {
+    const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
+    return packed_bytes >= from_bytes ? Route::kSkinny : Route::kGemv;
+  }
   if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
   return Route::kGemm;
 }

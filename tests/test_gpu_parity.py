@@ -318,6 +318,20 @@ def test_linear_routes_large_shapes_to_skinny(K_):
     W = K_.dequantize_packed(pw)
     ref = x.float() @ W.float()
     assert ((y40.float() - ref).abs().max() / ref.abs().max()).item() <= TOL
+    # a 16 MiB weight: the GEMV up to 8 rows, the tensor-memory kernel for 9..16
+    K2, N2 = 4096, 8192
+    qw, qz, sc = _random_packed_inputs(K2, N2, 128, seed=41)
+    pw2 = K_.make_packed(qw, qz, sc, 128)
+    x2 = torch.randn((16, K2), device="cuda", dtype=torch.float16)
+    y16 = K_.linear(x2, pw2)
+    assert torch.equal(y16, K_.skinny(x2, pw2))
+    assert torch.equal(K_.linear(x2[:9].contiguous(), pw2), y16[:9])
+    y8 = K_.linear(x2[:8].contiguous(), pw2)
+    assert torch.equal(y8, K_.gemv(x2[:8].contiguous(), pw2))
+    assert torch.equal(K_.linear(x2[:1].contiguous(), pw2), y8[:1])
+    ref2 = x2.float() @ K_.dequantize_packed(pw2).float()
+    assert ((y16.float() - ref2).abs().max() / ref2.abs().max()).item() <= TOL
+    assert K_.gemv_status() == 0
 
 
 def test_gemm_tail_split(K_):
