@@ -201,3 +201,33 @@ def test_gated_mlp_state_dict_and_dtype(K_):
     assert mlp(torch.zeros((0, 256), device="cuda").half()).shape == (0, 256)
     with pytest.raises(ValueError):
         AWQGatedMLP(_module(256, 128, 1), _module(256, 64, 2), _module(128, 256, 3))
+
+
+def test_graphed_step_matches_eager(K_):
+    """A chain of modules (plain, gated MLP with residual) captured once and replayed: same bits as the eager
+    calls, also for new inputs given from pinned host memory."""
+    from llmrqt_sdv1_b200 import AWQGatedMLP, GraphedStep
+    qkv, o = _module(512, 1024, 11, bias=True), _module(1024, 512, 12)
+    mlp = AWQGatedMLP(_module(512, 768, 13), _module(512, 768, 14), _module(768, 512, 15))
+
+    def chain(x):
+        a = qkv(x)
+        h = o(a, residual=x)
+        return mlp(h, residual=h), a
+
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    x0 = torch.randn((1, 3, 512), device="cuda", generator=gen).half()
+    step = GraphedStep(chain, (x0,))
+    y_g, a_g = step(x0)
+    y_e, a_e = chain(x0)
+    assert torch.equal(y_g, y_e) and torch.equal(a_g, a_e)
+    x1 = torch.randn((1, 3, 512), generator=torch.Generator().manual_seed(22)).half().pin_memory()
+    y_g, _ = step(x1)
+    y_e, _ = chain(x1.cuda())
+    assert torch.equal(y_g, y_e)
+    assert len(step.static_outputs) == 2
+    assert step.status() == 0
+    with pytest.raises(ValueError):
+        step(torch.zeros((1, 4, 512), dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        step(x0, x0)
