@@ -264,7 +264,7 @@ AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 /* Picks the kernel from the row count and the shape: M <= 8 -> awq_b200_gemv, or awq_b200_skinny
  * once the packed weights reach 48 MiB (a choice that depends on K and N only, so a row's bits do
  * not change with the number of rows decoded together, up to 8 rows); 9 <= M <= 16 -> the same with
- * the switch at 16 MiB (the GEMV's 16-row variant is the slower one); 17 <= M <= 64 ->
+ * the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice); 17 <= M <= 64 ->
  * awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
  * awq_b200_gemm otherwise.  Mirrors the row-count switch in AWQLinearMMFunction.forward
  * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), which also changes kernel

@@ -79,6 +79,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = blockIdx.y;
+  // More than MT rows: gridDim.z CTAs per (column group, split), each with its own MT rows.  The halves run
+  // side by side and read the same weights at about the same time, so the second read is an L2 hit.
+  const int row0 = blockIdx.z * MT;
+  const int rows = min(p.M - row0, MT);      // rows of this CTA
   GEMV_TRACE(0);
   const bool is_producer = (warp == kGemvWarps);
   const int cw = warp % CW, kw = (warp / CW) % KW;
@@ -155,8 +159,8 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
 #pragma unroll
   for (int mh = 0; mh < MH; ++mh) {
     const int m = mh * 8 + g;
-    xvalid[mh] = m < p.M;
-    xlane[mh] = p.x + static_cast<size_t>(xvalid[mh] ? m : 0) * p.K + static_cast<size_t>(b0) * kBlockK + c * 32;
+    xvalid[mh] = m < rows;
+    xlane[mh] = p.x + static_cast<size_t>(xvalid[mh] ? row0 + m : 0) * p.K + static_cast<size_t>(b0) * kBlockK + c * 32;
   }
   auto load_x = [&](int bl, uint4 (&xv)[MH][4]) {
 #pragma unroll
@@ -251,14 +255,14 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   const bool direct = (p.S == 1) && !gated;
   const bool via_cluster = (p.cluster != 0);
   float* red_k = reinterpret_cast<float*>(ring);                 // [KW][M][kCtaCols]  (KW > 1 only)
-  float* red = red_k + (KW > 1 ? KW * p.M * kCtaCols : 0);       // [M][kCtaCols]      (cluster only)
+  float* red = red_k + (KW > 1 ? KW * rows * kCtaCols : 0);       // [M][kCtaCols]      (cluster only)
   // Where one finished element of this CTA goes: y, the cluster buffer, or the global partials.
   auto emit = [&](int m, int nl, float v) {
     const int n = cta_tile0 * 8 + nl;
     if (n >= p.N) return;
-    if (direct) variant_store_one(p, fusion, m, n, v);
+    if (direct) variant_store_one(p, fusion, row0 + m, n, v);
     else if (via_cluster) red[m * kCtaCols + nl] = v;
-    else __stcg(p.partial + (static_cast<size_t>(split) * p.M + m) * p.N + n, v);
+    else __stcg(p.partial + (static_cast<size_t>(split) * p.M + row0 + m) * p.N + n, v);
   };
   if (!is_producer) {
 #pragma unroll
@@ -271,10 +275,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int m = mh * 8 + 2 * c + e;
-            if (m >= p.M) continue;
+            if (m >= rows) continue;
             const float v = acc[mh][q][half * 2 + e];
             if (KW == 1) emit(m, nl, v);
-            else red_k[(kw * p.M + m) * kCtaCols + nl] = v;
+            else red_k[(kw * rows + m) * kCtaCols + nl] = v;
           }
         }
       }
@@ -283,10 +287,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   if (KW > 1) {
     // The KW warps of a column group add their sums in kw order.
     __syncthreads();
-    for (int e = tid; e < p.M * kCtaCols; e += kGemvThreads) {
+    for (int e = tid; e < rows * kCtaCols; e += kGemvThreads) {
       float v = red_k[e];
 #pragma unroll
-      for (int j = 1; j < KW; ++j) v += red_k[j * p.M * kCtaCols + e];
+      for (int j = 1; j < KW; ++j) v += red_k[j * rows * kCtaCols + e];
       emit(e / kCtaCols, e % kCtaCols, v);
     }
   }
@@ -301,7 +305,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
     // the other CTAs' shared memory, and writes that slice of y.
     cluster_sync_all();
     const int ncols = min(kCtaCols, p.N - cta_tile0 * 8);
-    const int total_pairs = (p.M * kCtaCols) >> 1;
+    const int total_pairs = (rows * kCtaCols) >> 1;
     const int per_rank = (total_pairs + p.S - 1) / p.S;
     const int first = split * per_rank;
     const int last_pair = min(first + per_rank, total_pairs);
@@ -318,7 +322,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       for (int r = 1; r < 8; ++r) {
         if (r < p.S) { sum.x += v[r].x; sum.y += v[r].y; }
       }
-      variant_store_pair(p, fusion, m, cta_tile0 * 8 + nl, sum.x, sum.y);
+      variant_store_pair(p, fusion, row0 + m, cta_tile0 * 8 + nl, sum.x, sum.y);
     }
     cluster_sync_all();   // nobody leaves while its shared memory may still be read
     GEMV_TRACE(6);
@@ -329,9 +333,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   GEMV_TRACE(4);
   __syncthreads();
   if (tid == 0) {
-    const unsigned prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+    const unsigned counter = blockIdx.z * gridDim.x + blockIdx.x;
+    const unsigned prev = atomicAdd(&p.counters[counter], 1u);
     const int last = (prev == static_cast<unsigned>(p.S - 1));
-    if (last) p.counters[blockIdx.x] = 0u;  // every split has arrived: leave the counter clean
+    if (last) p.counters[counter] = 0u;  // every split has arrived: leave the counter clean
     s_last = last;
   }
   __syncthreads();
@@ -343,9 +348,9 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   const int col0 = cta_tile0 * 8;
   const int ncols = min(kCtaCols, p.N - col0);
   const int pairs = ncols >> 1;
-  for (int i = tid; i < p.M * pairs; i += kGemvThreads) {
-    const int row = i / pairs;
-    const int col = col0 + 2 * (i - row * pairs);
+  for (int i = tid; i < rows * pairs; i += kGemvThreads) {
+    const int row = row0 + i / pairs;
+    const int col = col0 + 2 * (i - (row - row0) * pairs);
     const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
     const size_t split_stride = static_cast<size_t>(p.M) * p.N;
     // Loads are issued eight at a time (independent), the additions stay in split order.
@@ -471,7 +476,7 @@ static int launch_gemv(const GemvParams& p_plain, const GemvFusion& fusion, cons
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(plan.ncol, plan.S);
+  cfg.gridDim = dim3(plan.ncol, plan.S, (p.M + MT - 1) / MT);
   cfg.blockDim = dim3((W + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -519,17 +524,23 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   if (plan.w == 16 && plan.kw < 4) plan.kw = 4;
   if (force_bps >= 1) plan.bps = force_bps < nblk ? force_bps : nblk;
   if (plan.bps > kGemvMaxBps * plan.kw) plan.bps = kGemvMaxBps * plan.kw;
-  // The 16-row variant keeps twice the accumulators: run it with two tiles per warp.  Only the
-  // k-splits (kw, bps) decide the order of additions, so this cannot change a row's result.
-  if (M > 8 && force_ntw == 0) plan.ntw = 2;
+  // More than 8 rows.  The per-split grid runs two CTAs of 8 rows per (column group, split) with the plan
+  // of 8 rows; the stream keeps its 16-row variant, which holds twice the accumulators and therefore runs
+  // with two tiles per warp.  Only the k-splits (kw, bps) decide the order of additions, so neither changes
+  // a row's result.
+  bool use_stream = force_bps < 1 && stream_by_default(plan, nblk, ntiles, di.sm_count);
+  if (flags & AWQ_B200_GEMV_STREAM) use_stream = true;
+  if (flags & AWQ_B200_GEMV_PER_SPLIT) use_stream = false;
+  if (M > 8 && force_ntw == 0 && use_stream) plan.ntw = 2;
+  const int row_halves = (!use_stream && M > 8) ? 2 : 1;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
   plan.ncol = plan_ncol(ntiles, plan.ntw, plan.w, plan.kw);
   unsigned* p_status = nullptr;
-  while (plan.ncol > kGemvMaxCounters - 1 && plan.ntw < 4) {
+  while (plan.ncol * row_halves > kGemvMaxCounters - 1 && plan.ntw < 4) {
     plan.ntw *= 2;
     plan.ncol = plan_ncol(ntiles, plan.ntw, plan.w, plan.kw);
   }
-  if (plan.S > 65535 || plan.ncol > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
+  if (plan.S > 65535 || plan.ncol * row_halves > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
   if (workspace && workspace_bytes >= counter_bytes(N) && aligned16(workspace))
     p_status = static_cast<unsigned*>(workspace) + (kGemvMaxCounters - 1);
 
@@ -552,9 +563,6 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   p.S = plan.S;
   p.ntiles = ntiles;
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
-  bool use_stream = force_bps < 1 && stream_by_default(plan, nblk, ntiles, di.sm_count);
-  if (flags & AWQ_B200_GEMV_STREAM) use_stream = true;
-  if (flags & AWQ_B200_GEMV_PER_SPLIT) use_stream = false;
   if (use_stream) {
     p.bps = 0; p.S = 0; p.cluster = 0;
     const int slots = gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, di.sm_count);
@@ -571,7 +579,7 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
 
   // A cluster needs its CTAs resident together; beyond one CTA per SM that costs more occupancy than the
   // shared-memory reduction saves.
-  p.cluster = (plan.S >= 2 && plan.S <= 8 && static_cast<long long>(plan.ncol) * plan.S <= di.sm_count &&
+  p.cluster = (plan.S >= 2 && plan.S <= 8 && static_cast<long long>(plan.ncol) * plan.S * row_halves <= di.sm_count &&
                !(flags & AWQ_B200_NO_CLUSTER)) ? 1 : 0;
   if ((plan.S > 1 || epi.gated) && !p.cluster) {
     const size_t cb = counter_bytes(N);
@@ -582,13 +590,10 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
     p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + cb);
   }
 
-  const bool wide = M > 8;
-#define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                             \
-  if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                        \
-    return fused ? (wide ? launch_gemv<NTW_, 16, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap)    \
-                         : launch_gemv<NTW_, 8, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap))    \
-                 : (wide ? launch_gemv<NTW_, 16, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap)   \
-                         : launch_gemv<NTW_, 8, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap));
+#define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                                        \
+  if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                                   \
+    return fused ? launch_gemv<NTW_, 8, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap) \
+                 : launch_gemv<NTW_, 8, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap);
   AWQ_GEMV_CASE(2, 1, 8) AWQ_GEMV_CASE(2, 2, 8) AWQ_GEMV_CASE(2, 4, 8) AWQ_GEMV_CASE(2, 8, 8)
   AWQ_GEMV_CASE(4, 1, 8) AWQ_GEMV_CASE(4, 2, 8) AWQ_GEMV_CASE(4, 4, 8) AWQ_GEMV_CASE(4, 8, 8)
   AWQ_GEMV_CASE(2, 4, 16) AWQ_GEMV_CASE(2, 8, 16) AWQ_GEMV_CASE(2, 16, 16)

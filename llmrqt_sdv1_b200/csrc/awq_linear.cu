@@ -10,10 +10,10 @@ constexpr int kSkinnyMaxRows = 64;
 //   rows <= 8:  the GEMV, or the split-K tensor-memory kernel once the packed weights reach 48 MiB (level
 //               with the GEMV at one row there).  The choice depends on (K, N) only, so a row's bits do not
 //               change with the number of rows decoded together, up to 8 rows.
-//   9..16:      the GEMV's 16-row variant re-reads the activations once per warp and runs at about half the
-//               speed of its 8-row variant, so the tensor-memory kernel takes over from 16 MiB of packed
-//               weights (20 - 35 % faster there).  Like the reference's switch from its GEMV to its GEMM
-//               at 8 rows, this changes the order of additions between 8 and 9 rows.
+//   9..16:      the GEMV serves more than 8 rows as two CTAs of 8 rows per column group, which doubles its
+//               unpacking work (1.3 - 1.9 times the 8-row time), so the tensor-memory kernel takes over from
+//               16 MiB of packed weights (20 - 35 % faster there).  Like the reference's switch from its GEMV
+//               to its GEMM at 8 rows, this changes the order of additions between 8 and 9 rows.
 //   17..64:     the tensor-memory kernel where the GEMM would leave most SMs idle (at most 74 column tiles
 //               of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
 enum class Route { kGemv, kSkinny, kGemm };
