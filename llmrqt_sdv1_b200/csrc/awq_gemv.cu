@@ -50,7 +50,8 @@ namespace awq {
 // blocks in k order, then the KW warps of a column group in kw order (shared memory), then the
 // grid-level splits in split order (cluster shared memory or the global workspace).
 // FUSED = false compiles the residual / gated parts of the epilogue out (bias only).
-template <int NTW, int MT, int KW, int W, bool FUSED>
+// ROW_HALVES = true serves more than MT rows with gridDim.z CTAs per (column group, split).
+template <int NTW, int MT, int KW, int W, bool FUSED, bool ROW_HALVES>
 __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(const typename GemvParamsOf<FUSED>::type p) {
   const GemvFusion* fusion = nullptr;   // compile-time null in the unfused variants
   if constexpr (FUSED) fusion = &p.fusion;
@@ -81,8 +82,8 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   const int split = blockIdx.y;
   // More than MT rows: gridDim.z CTAs per (column group, split), each with its own MT rows.  The halves run
   // side by side and read the same weights at about the same time, so the second read is an L2 hit.
-  const int row0 = blockIdx.z * MT;
-  const int rows = min(p.M - row0, MT);      // rows of this CTA
+  const int row0 = ROW_HALVES ? blockIdx.z * MT : 0;
+  const int rows = ROW_HALVES ? min(p.M - row0, MT) : p.M;      // rows of this CTA
   GEMV_TRACE(0);
   const bool is_producer = (warp == kGemvWarps);
   const int cw = warp % CW, kw = (warp / CW) % KW;
@@ -333,7 +334,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   GEMV_TRACE(4);
   __syncthreads();
   if (tid == 0) {
-    const unsigned counter = blockIdx.z * gridDim.x + blockIdx.x;
+    const unsigned counter = (ROW_HALVES ? blockIdx.z * gridDim.x : 0u) + blockIdx.x;
     const unsigned prev = atomicAdd(&p.counters[counter], 1u);
     const int last = (prev == static_cast<unsigned>(p.S - 1));
     if (last) p.counters[counter] = 0u;  // every split has arrived: leave the counter clean
@@ -463,7 +464,7 @@ static bool stream_by_default(const GemvPlan& plan, int nblk, int ntiles, int sm
 // call expects clean counters.
 static size_t counter_bytes(int /*N*/) { return kGemvMaxCounters * sizeof(unsigned); }
 
-template <int NTW, int MT, int KW, int W, bool FUSED>
+template <int NTW, int MT, int KW, int W, bool FUSED, bool ROW_HALVES>
 static int launch_gemv(const GemvParams& p_plain, const GemvFusion& fusion, const GemvPlan& plan, int max_smem_optin,
                        cudaStream_t stream, bool overlap_previous) {
   typename GemvParamsOf<FUSED>::type p;
@@ -472,11 +473,11 @@ static int launch_gemv(const GemvParams& p_plain, const GemvFusion& fusion, cons
   const size_t smem = static_cast<size_t>(gemv_stages(NTW, W)) * W * NTW * (512 + 32) + 2 * gemv_stages(NTW, W) * 8;
   if (smem > static_cast<size_t>(max_smem_optin)) return AWQ_B200_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW, W, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(gemv_kernel<NTW, MT, KW, W, FUSED, ROW_HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(plan.ncol, plan.S, (p.M + MT - 1) / MT);
+  cfg.gridDim = dim3(plan.ncol, plan.S, ROW_HALVES ? (p.M + MT - 1) / MT : 1);
   cfg.blockDim = dim3((W + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -496,7 +497,7 @@ static int launch_gemv(const GemvParams& p_plain, const GemvFusion& fusion, cons
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW, W, FUSED>, p));
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<NTW, MT, KW, W, FUSED, ROW_HALVES>, p));
   return AWQ_B200_OK;
 }
 
@@ -590,16 +591,21 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
     p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + cb);
   }
 
-#define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                                        \
-  if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                                   \
-    return fused ? launch_gemv<NTW_, 8, KW_, W_, true>(p, fusion, plan, di.max_smem_optin, stream, overlap) \
-                 : launch_gemv<NTW_, 8, KW_, W_, false>(p, fusion, plan, di.max_smem_optin, stream, overlap);
+#define AWQ_GEMV_LAUNCH(NTW_, KW_, W_, F_, R_) \
+  launch_gemv<NTW_, 8, KW_, W_, F_, R_>(p, fusion, plan, di.max_smem_optin, stream, overlap)
+#define AWQ_GEMV_CASE(NTW_, KW_, W_)                                                                      \
+  if (plan.ntw == NTW_ && plan.kw == KW_ && plan.w == W_)                                                 \
+    return fused ? (row_halves > 1 ? AWQ_GEMV_LAUNCH(NTW_, KW_, W_, true, true)                           \
+                                   : AWQ_GEMV_LAUNCH(NTW_, KW_, W_, true, false))                         \
+                 : (row_halves > 1 ? AWQ_GEMV_LAUNCH(NTW_, KW_, W_, false, true)                          \
+                                   : AWQ_GEMV_LAUNCH(NTW_, KW_, W_, false, false));
   AWQ_GEMV_CASE(2, 1, 8) AWQ_GEMV_CASE(2, 2, 8) AWQ_GEMV_CASE(2, 4, 8) AWQ_GEMV_CASE(2, 8, 8)
   AWQ_GEMV_CASE(4, 1, 8) AWQ_GEMV_CASE(4, 2, 8) AWQ_GEMV_CASE(4, 4, 8) AWQ_GEMV_CASE(4, 8, 8)
   AWQ_GEMV_CASE(2, 4, 16) AWQ_GEMV_CASE(2, 8, 16) AWQ_GEMV_CASE(2, 16, 16)
   AWQ_GEMV_CASE(4, 4, 16) AWQ_GEMV_CASE(4, 8, 16) AWQ_GEMV_CASE(4, 16, 16)
   return AWQ_B200_ERR_SHAPE;
 #undef AWQ_GEMV_CASE
+#undef AWQ_GEMV_LAUNCH
 }
 
 int gemv_run(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
