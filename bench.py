@@ -479,20 +479,17 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
 
     # Row-parallel partial outputs are summed by the library's one-shot peer all-reduce (every rank reads
     # all partials over NVLink); the NCCL all-reduce is timed beside it.
-    peer, peer_error = None, None
+    peers, peer, peer_error = {}, None, None
     if world > 1:
         from llmrqt_sdv1_b200.sharded import PeerSum
         try:
-            peer = PeerSum(64 * Nd, dev)
+            peers = {"peer_push": PeerSum(64 * Nd, dev, mode="push"), "peer_pull": PeerSum(64 * Nd, dev, mode="pull")}
         except Exception as e:          # no symmetric memory on this box: every rank falls back to NCCL
             peer_error = f"{type(e).__name__}: {e}"[:200]
-        flag = torch.tensor([0 if peer is not None else 1], device=dev)
+        flag = torch.tensor([0 if peers else 1], device=dev)
         dist.all_reduce(flag)           # all ranks must agree, or the exchanges would not match
         if int(flag.item()) != 0:
-            peer = None
-        if peer is not None:
-            for m in down:
-                m.use_peer_sum(peer)
+            peers = {}
 
     def step():
         for i in range(FFN70B_LAYERS):
@@ -516,12 +513,17 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     # every rank makes the same choice) and the faster one is the configuration that is measured.
     allreduce, calib = "none", {}
     if world > 1:
-        for name, fn in ((("peer", step),) if peer is not None else ()) + (("nccl", step_nccl),):
+        for name in list(peers) + ["nccl"]:
+            peer = peers.get(name)
             dist.barrier()
-            tc = torch.tensor([time_graph(torch, fn, iters=5)], device=dev)
+            tc = torch.tensor([time_graph(torch, step_nccl if name == "nccl" else step, iters=5)], device=dev)
             dist.all_reduce(tc, op=dist.ReduceOp.MAX)
             calib[name] = float(tc.item())
-        allreduce = "peer" if "peer" in calib and calib["peer"] <= calib["nccl"] else "nccl"
+        allreduce = min(calib, key=calib.get)
+        peer = peers.get(allreduce)
+        if peer is not None:
+            for m in down:
+                m.use_peer_sum(peer)
     step_timed = step_nccl if allreduce == "nccl" else step
     for _ in range(max(args.warmup, 3)):
         step_timed()
@@ -669,7 +671,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
                 "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
-        "gpu_launches": (3 if allreduce == "peer" else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
+        "gpu_launches": (3 if allreduce.startswith("peer") else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
         "allreduce": {"used": allreduce, "calibration_ms_per_step": calib,
                       "peer_status": (peer.status() if peer is not None else None), "peer_unavailable": peer_error},

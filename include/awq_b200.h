@@ -254,6 +254,19 @@ AWQ_B200_API size_t awq_b200_peer_allreduce_flag_bytes(void);
 AWQ_B200_API int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* out, const void* bias,
                             size_t count, int ncols, int rank, int world, awq_b200_stream_t stream);
 
+/* The same sum with the data pushed instead of pulled: every rank stores its partial into a receive slot on
+ * each peer in a self-validating wire format (8-byte words of 4 payload bytes + the call's counter), so a
+ * rank waits for one one-way trip over NVLink, polling its own memory, and needs neither fences nor flags.
+ * `partial` is this rank's [count] fp16 partial (any memory of this GPU); recv[r] points to rank r's receive
+ * area of 2 * world * slot_elems * 4 bytes (peer-mapped like the flag arrays, zero before the first call;
+ * slot_elems >= count, a multiple of 8); its two halves alternate on the parity of the call counter kept in
+ * the flag array, which makes a closing hand-shake unnecessary.  Same flag arrays, ordering rules,
+ * bit-identical results on all ranks, bounded waits (status word 34 becomes 3) and graph-capture behaviour
+ * as awq_b200_peer_allreduce. */
+AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* recv, void* const* flags, void* out,
+                                 const void* bias, size_t count, int ncols, size_t slot_elems, int rank,
+                                 int world, awq_b200_stream_t stream);
+
 /* ---- dispatch ------------------------------------------------------------ */
 
 /* Largest M routed to the GEMV kernel by awq_b200_linear (16). */

@@ -31,8 +31,11 @@ constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // ~2 s at 2 
 //   [16, 32)  done[r]    written by rank r
 //   [32]      epoch of the last completed call (local)
 //   [33]      blocks of the current call that finished summing (local)
-//   [34]      status: 0, or 1 / 2 when the ready / done wait expired (local, sticky)
+//   [34]      status: 0, or 1 / 2 when the ready / done wait expired, 3 for the push variant's wait (local, sticky)
+//   [35], [36] epoch and finished-block counter of the push variant (local)
 constexpr int kArReadyOff = 0, kArDoneOff = 16, kArEpochOff = 32, kArBlocksOff = 33, kArStatusOff = 34;
+constexpr int kArPushEpochOff = 35, kArPushBlocksOff = 36;
+constexpr int kArMaxBlocks = 64;
 constexpr int kArFlagWords = 64;
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
@@ -144,6 +147,126 @@ peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint1
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Push variant.  Instead of publishing a flag and letting the peers pull the partial (a flag's one-way trip
+// followed by a load's round trip over NVLink), every rank stores its partial into a receive slot on each
+// peer, and the data carries its own flag: each 8-byte word on the wire is {4 bytes of payload, the call's
+// epoch}, written with 16-byte stores of two such words.  An 8-byte word arrives whole, so a receiver polls
+// its own memory until both words of a 16-byte line show the current epoch and then owns the payload: no
+// fence, no separate flag, one one-way trip.  The wire format doubles the bytes, which at these sizes
+// (16 KB ... 1 MB per rank) costs less than a second trip.
+//
+// There is no "done" phase.  The receive slots are double-buffered on the parity of the call's epoch (kept
+// in device memory, so captured graphs replay correctly): a rank overwrites slot [e & 1] in call e + 2, which
+// it can reach only after finishing call e + 1, which it finished only after receiving every peer's words of
+// call e + 1, which a peer sends only after its own call e has completed (calls on a stream do not overlap:
+// each kernel of the chain waits for its predecessor before touching anything).
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_wire_16(void* p, uint32_t d0, uint32_t d1, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_wire_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// recv[r]: rank r's receive area, 2 parities x world slots x (4 * slot_elems) bytes (wire format).
+__global__ void __launch_bounds__(kArThreads)
+peer_allreduce_push_kernel(const uint16_t* partial, unsigned char* const* recv, unsigned* const* flags, uint16_t* out,
+                           const uint16_t* bias, size_t count, int ncols, size_t slot_elems, int rank, int world) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ int s_ok;
+  unsigned* my_flags = flags[rank];
+  const unsigned epoch = my_flags[kArPushEpochOff] + 1u;   // written only by this kernel's last block, a launch ago
+  const size_t slot_bytes = slot_elems * 4;
+  const size_t par_off = static_cast<size_t>(epoch & 1u) * world;
+  const size_t vecs = count / 8;
+  const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+
+  // 1. this thread's vectors of the partial go to every peer's slot [parity][rank], two wire lines each
+  for (size_t i = first; i < vecs; i += stride) {
+    const uint4 v = *reinterpret_cast<const uint4*>(partial + i * 8);
+#pragma unroll
+    for (int r = 0; r < kArMaxWorld; ++r) {
+      if (r < world && r != rank) {
+        unsigned char* dst = recv[r] + (par_off + rank) * slot_bytes + i * 32;
+        st_wire_16(dst, v.x, v.y, epoch);
+        st_wire_16(dst + 16, v.z, v.w, epoch);
+      }
+    }
+  }
+
+  // 2. the same vectors of every peer, polled out of this rank's own memory, summed in rank order
+  const unsigned char* slots = recv[rank] + par_off * slot_bytes;
+  for (size_t i = first; i < vecs; i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    bool ok = true;
+#pragma unroll
+    for (int r = 0; r < kArMaxWorld; ++r) {
+      if (r < world) {
+        uint4 v;
+        if (r == rank) {
+          v = *reinterpret_cast<const uint4*>(partial + i * 8);
+        } else {
+          const unsigned char* src = slots + static_cast<size_t>(r) * slot_bytes + i * 32;
+          uint4 a = ld_wire_16(src), b = ld_wire_16(src + 16);
+          if (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch) {
+            const unsigned long long t0 = clock64();
+            do {
+              a = ld_wire_16(src);
+              b = ld_wire_16(src + 16);
+              if (clock64() - t0 > kArWaitLimitCycles) { ok = false; break; }
+            } while (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch);
+          }
+          v = make_uint4(a.x, a.z, b.x, b.z);
+        }
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+    }
+    if (!ok) { s_ok = 0; break; }
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+    if (bias != nullptr) {
+      const size_t col = (i * 8) % static_cast<size_t>(ncols);
+      const uint4 bv = *reinterpret_cast<const uint4*>(bias + col);
+      const __half2* bh = reinterpret_cast<const __half2*>(&bv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], bh[e]);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+
+  // 3. the last block closes the call
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_ok == 0) atomicCAS(my_flags + kArStatusOff, 0u, 3u);
+    const unsigned prev = atomicAdd(my_flags + kArPushBlocksOff, 1u);
+    if (prev == gridDim.x - 1) {
+      my_flags[kArPushBlocksOff] = 0u;
+      my_flags[kArPushEpochOff] = epoch;
+    }
+  }
+}
+
 }  // namespace awq
 
 extern "C" {
@@ -174,6 +297,38 @@ int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* o
   AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, reinterpret_cast<const uint16_t* const*>(bufs),
                                   reinterpret_cast<unsigned* const*>(flags), static_cast<uint16_t*>(out),
                                   static_cast<const uint16_t*>(bias), count, ncols, rank, world));
+  return AWQ_B200_OK;
+}
+
+// Push variant: `partial` is this rank's [count] fp16 partial (any device memory of this GPU); `recv` is a device
+// array of `world` pointers to the ranks' receive areas of 2 * world * slot_elems * 4 bytes each (peer-mapped
+// memory, zero before the first call; slot_elems >= count, a multiple of 8); `flags` as above.
+int awq_b200_peer_allreduce_push(const void* partial, void* const* recv, void* const* flags, void* out, const void* bias,
+                                 size_t count, int ncols, size_t slot_elems, int rank, int world,
+                                 awq_b200_stream_t stream) {
+  using namespace awq;
+  if (!partial || !recv || !flags || !out) return AWQ_B200_ERR_NULL;
+  if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) return AWQ_B200_ERR_SHAPE;
+  if (count == 0 || (count % 8) != 0 || slot_elems < count || (slot_elems % 8) != 0 ||
+      (bias && (ncols < 8 || (ncols % 8) != 0)))
+    return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(partial) || !aligned16(out) || (bias && !aligned16(bias))) return AWQ_B200_ERR_ALIGN;
+  const size_t vecs = count / 8;
+  int blocks = static_cast<int>((vecs + kArThreads - 1) / kArThreads);
+  if (blocks > kArMaxBlocks) blocks = kArMaxBlocks;   // one flag per block and peer; all blocks resident together
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kArThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_allreduce_push_kernel, static_cast<const uint16_t*>(partial),
+                                  reinterpret_cast<unsigned char* const*>(recv), reinterpret_cast<unsigned* const*>(flags),
+                                  static_cast<uint16_t*>(out), static_cast<const uint16_t*>(bias), count, ncols,
+                                  slot_elems, rank, world));
   return AWQ_B200_OK;
 }
 

@@ -323,6 +323,19 @@ def peer_allreduce(bufs_dev: int, flags_dev: int, local_buf: torch.Tensor, M: in
     return y
 
 
+def peer_allreduce_push(partial: torch.Tensor, recv_dev: int, flags_dev: int, slot_elems: int, M: int, N: int,
+                        rank: int, world: int, out: torch.Tensor | None = None,
+                        bias: torch.Tensor | None = None) -> torch.Tensor:
+    """`peer_allreduce` with the partials pushed into the peers' receive slots (see `sharded.PeerSum`)."""
+    dev = partial.device
+    _lib.set_device(dev.index)
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=dev)
+    check(lib.awq_b200_peer_allreduce_push(partial.data_ptr(), recv_dev, flags_dev, y.data_ptr(),
+                                           bias.data_ptr() if bias is not None else None, M * N, N, slot_elems,
+                                           rank, world, _stream(partial)), "awq_b200_peer_allreduce_push")
+    return y
+
+
 def gemv_status(dev: torch.device | None = None) -> int:
     """Status word of the decode kernels (GEMV and split-K tensor-memory kernel) in this stream's workspaces (0 = no device-side wait expired).
     Synchronises."""

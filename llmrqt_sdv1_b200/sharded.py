@@ -129,18 +129,22 @@ class ColumnParallelAWQLinear(nn.Module):
 
 class PeerSum:
     """One-shot sum of small row-parallel partial outputs over peer memory (NVLink), for CUDA ranks of
-    one node.  Each rank writes its fp16 partial into `partial(M, N)` (symmetric memory); `reduce`
-    launches the library's peer all-reduce kernel, in which every rank reads all partials with plain
-    peer loads, adds them in rank order in fp32 and writes the fp16 result locally (identical bits on
-    every rank).  Replaces an NCCL all-reduce whose cost at these sizes (16 KB ... 1 MB) is all latency.
-    One instance serves any number of layers on a stream: a call finishes only after every peer has
-    read this rank's partial."""
+    one node.  Each rank writes its fp16 partial into `partial(M, N)`; `reduce` launches the library's peer
+    all-reduce kernel, which adds the ranks' partials in rank order in fp32 and writes the fp16 result
+    locally (identical bits on every rank).  Replaces an NCCL all-reduce whose cost at these sizes
+    (16 KB ... 1 MB) is all latency.  One instance serves any number of layers on a stream.
 
-    def __init__(self, max_elems: int, device, group=None):
+    mode "push" (default): every rank stores its partial into a receive slot on each peer in a wire format
+    that carries its own flag; a rank waits for one one-way trip, polling its own memory.  mode "pull": every rank publishes a flag
+    and reads the peers' partials with peer loads, then waits until all peers have read its own."""
+
+    def __init__(self, max_elems: int, device, group=None, mode: str = "push"):
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib
+        if mode not in ("push", "pull"):
+            raise ValueError(f"mode must be 'push' or 'pull', got {mode!r}")
         group = group if group is not None else dist.group.WORLD
-        self.group = group
+        self.group, self.mode = group, mode
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.max_elems = (int(max_elems) + 7) // 8 * 8
         self.buf = symm_mem.empty(self.max_elems, dtype=torch.float16, device=device)
@@ -148,6 +152,11 @@ class PeerSum:
         self.flags.zero_()
         self._h_buf = symm_mem.rendezvous(self.buf, group)
         self._h_flags = symm_mem.rendezvous(self.flags, group)
+        if mode == "push":
+            # wire format: 4 bytes per fp16 element, two parities, one slot per rank
+            self.recv = symm_mem.empty(4 * self.world * self.max_elems, dtype=torch.float16, device=device)
+            self.recv.zero_()
+            self._h_recv = symm_mem.rendezvous(self.recv, group)
         torch.cuda.synchronize(device)
         dist.barrier(group)            # every rank's flags are zero before anyone signals
 
@@ -159,11 +168,15 @@ class PeerSum:
 
     def reduce(self, M: int, N: int, out: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> torch.Tensor:
         from . import kernels
+        if self.mode == "push":
+            return kernels.peer_allreduce_push(self.buf, self._h_recv.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev,
+                                               self.max_elems, M, N, self.rank, self.world, out=out, bias=bias)
         return kernels.peer_allreduce(self._h_buf.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev, self.buf,
                                       M, N, self.rank, self.world, out=out, bias=bias)
 
     def status(self) -> int:
-        """0, or which wait expired in some call (1: peers' partials, 2: peers' reads).  Synchronises."""
+        """0, or which wait expired in some call (1: peers' partials, 2: peers' reads, 3: peers' pushes).
+        Synchronises."""
         return int(self.flags[34].item())
 
 

@@ -25,7 +25,18 @@ def _worker(rank: int, world: int, port: int, results):
     try:
         from llmrqt_sdv1_b200 import quantize
         from llmrqt_sdv1_b200.sharded import PeerSum, RowParallelAWQLinear
-        ps = PeerSum(16 * 4096, dev)
+        ok, status = True, 0
+        for mode in ("push", "pull"):
+            ok_mode, st = _check_mode(mode, rank, world, dev, dist, quantize, PeerSum, RowParallelAWQLinear)
+            ok, status = ok and ok_mode, status | st
+        results[rank] = (ok, status)
+    finally:
+        dist.destroy_process_group()
+
+
+def _check_mode(mode, rank, world, dev, dist, quantize, PeerSum, RowParallelAWQLinear):
+    if True:
+        ps = PeerSum(16 * 4096, dev, mode=mode)
         ok = True
         for (M, N) in [(1, 4096), (5, 2048), (16, 4096)]:
             for it in range(4):            # the same buffers carry new data every call
@@ -54,7 +65,8 @@ def _worker(rank: int, world: int, port: int, results):
         y_peer = mod(x)
         rel = ((y_peer.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max()).item()
         ok = ok and y_peer.shape == y_nccl.shape and rel <= 2e-3
-        # a graph with several calls replays correctly (the epoch lives in device memory)
+        # a graph with an odd number of calls replays correctly (the epoch, and with it the receive slot in
+        # use, lives in device memory)
         outs = [torch.empty((1, 4096), dtype=torch.float16, device=dev) for _ in range(3)]
         ps.partial(1, 4096).fill_(float(rank + 1))
         for o in outs:
@@ -68,9 +80,7 @@ def _worker(rank: int, world: int, port: int, results):
         torch.cuda.synchronize()
         expect = float(sum(range(1, world + 1)))
         ok = ok and all(bool((o == expect).all()) for o in outs)
-        results[rank] = (ok, ps.status())
-    finally:
-        dist.destroy_process_group()
+        return ok, ps.status()
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
