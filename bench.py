@@ -525,6 +525,17 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
             for m in down:
                 m.use_peer_sum(peer)
     step_timed = step_nccl if allreduce == "nccl" else step
+    # the exchange that is timed against the library collective on the same partials (fp32 sum of fp16
+    # partials vs NCCL's fp16 additions: equal to a few fp16 places)
+    agrees = None
+    if world > 1 and peer is not None:
+        step()
+        y_peer = y_d[-1].float().clone()
+        step_nccl()
+        scale = y_d[-1].float().abs().max().clamp_min(1e-6)
+        bad = torch.tensor([float(((y_peer - y_d[-1].float()).abs().max() / scale) > 2e-3)], device=dev)
+        dist.all_reduce(bad)
+        agrees = bool(bad.item() == 0)
     for _ in range(max(args.warmup, 3)):
         step_timed()
     torch.cuda.synchronize()
@@ -674,7 +685,8 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         "gpu_launches": (3 if allreduce.startswith("peer") else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
         "allreduce": {"used": allreduce, "calibration_ms_per_step": calib,
-                      "peer_status": (peer.status() if peer is not None else None), "peer_unavailable": peer_error},
+                      "peer_status": (peer.status() if peer is not None else None), "peer_unavailable": peer_error,
+                      "agrees_with_nccl": agrees},
     }
     print(json.dumps(line), flush=True)
 
