@@ -59,3 +59,18 @@ def test_torch_quantizer_matches_reference(golden_dir):
     qw, qz, sc = quantize_weight(w, G)
     assert np.array_equal(qw.numpy(), g["qweight"]) and np.array_equal(qz.numpy(), g["qzeros"])
     assert np.array_equal(sc.numpy().view(np.uint16), g["scales"].view(np.uint16))
+
+
+def test_fused_modules_have_no_cpu_path():
+    """The two-launch MLP and the graphed step need the CUDA library's device code: on CPU tensors they
+    raise instead of computing something else."""
+    from llmrqt_sdv1_b200 import AWQGatedMLP, GraphedStep
+    gate, up = AWQLinear_GEMM(4, 128, 128, 128, False, "cpu"), AWQLinear_GEMM(4, 128, 128, 128, False, "cpu")
+    down = AWQLinear_GEMM(4, 128, 128, 128, False, "cpu")
+    with pytest.raises(RuntimeError):
+        AWQGatedMLP(gate, up, down)           # interleaving the columns is a device kernel
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            GraphedStep(lambda x: x, (torch.zeros(4),))
+    with pytest.raises(ValueError):
+        AWQGatedMLP(gate, AWQLinear_GEMM(4, 128, 128, 64, False, "cpu"), down)
