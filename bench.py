@@ -587,20 +587,51 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         hy.copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
-    for _ in range(3):
-        e2e_step()
-    if world > 1:
-        dist.barrier()
-    a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a2.record()
-    for _ in range(args.steps):
-        e2e_step()
-    b2.record()
-    torch.cuda.synchronize()
-    t2 = torch.tensor([a2.elapsed_time(b2) / args.steps], device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item())
+    def time_e2e(fn):
+        for _ in range(3):
+            fn()
+        if world > 1:
+            dist.barrier()
+        a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a2.record()
+        for _ in range(args.steps):
+            fn()
+        b2.record()
+        torch.cuda.synchronize()
+        t2 = torch.tensor([a2.elapsed_time(b2) / args.steps], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        return float(t2.item())
+
+    e2e_eager_ms = time_e2e(e2e_step)
+    e2e_ms, e2e_api = e2e_eager_ms, "ColumnParallelAWQLinear / RowParallelAWQLinear forward"
+    # The same module calls captured once (GraphedStep) where the exchange is the library's own kernel: per step
+    # the host inputs are copied in, the graph is replayed, the result is copied out.  Every rank must take the
+    # same route, so a rank that cannot capture sends all of them back to the eager calls.
+    if world == 1 or allreduce.startswith("peer"):
+        graphed_step = None
+        try:
+            from llmrqt_sdv1_b200 import GraphedStep
+
+            def module_chain(xg, xd):
+                y = None
+                for i in range(FFN70B_LAYERS):
+                    gate_up[i](xg)
+                    y = down[i](xd)
+                return y
+            graphed_step = GraphedStep(module_chain, (dxg, dxd))
+        except Exception:
+            graphed_step = None
+        ok_flag = torch.tensor([0 if graphed_step is not None else 1], device=dev)
+        if world > 1:
+            dist.all_reduce(ok_flag)
+        if int(ok_flag.item()) == 0:
+            def e2e_graphed():
+                y = graphed_step(hxg, hxd)
+                hy.copy_(y, non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_ms = time_e2e(e2e_graphed)
+            e2e_api = "GraphedStep over ColumnParallelAWQLinear / RowParallelAWQLinear forward"
     # The same M = 1 step without the all-reduce (what the collective costs): device time, max over ranks.
     def step_local():
         for i in range(FFN70B_LAYERS):
@@ -681,7 +712,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                      "kernel": "awq::skinny_kernel / awq::gemv_kernel by shard size (+ the all-reduce named in allreduce.used)", "per_gpu": True},
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
-                "api": "ColumnParallelAWQLinear / RowParallelAWQLinear forward"},
+                "api": e2e_api, "eager_ms_per_step": e2e_eager_ms},
         "gpu_launches": (3 if allreduce.startswith("peer") else 2) * FFN70B_LAYERS * args.steps, "clocks": sampler.summary(), "tp_detail": tp_detail,
         "without_allreduce": {"ms_per_step": ms_local, "value": step_bytes_total / (ms_local * 1e-3) / 1e9, "unit": "GB/s"},
         "allreduce": {"used": allreduce, "calibration_ms_per_step": calib,

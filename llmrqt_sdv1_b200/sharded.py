@@ -225,7 +225,10 @@ class RowParallelAWQLinear(nn.Module):
             N = self.linear.out_features
             if ps.fits(rows, N):
                 from . import kernels
-                kernels.linear(x.reshape(rows, -1), self.packed(), bias=self.linear.bias, out=ps.partial(rows, N))
+                pw = self.packed()
+                overlap, pw.fresh = not pw.fresh, False     # first call after a repack: no weight prefetch
+                kernels.linear(x.reshape(rows, -1), pw, bias=self.linear.bias, out=ps.partial(rows, N),
+                               overlap=overlap)
                 y = ps.reduce(rows, N)
                 return y.view(*x.shape[:-1], N) if x.dim() > 2 else y.view(1, rows, N)
         y = self.linear(x)
