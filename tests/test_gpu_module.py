@@ -85,3 +85,34 @@ def test_extension_function_api():
         assert orc.max_normalised_error(y.cpu().numpy(), orc.linear_forward(x, qw, qz, sc, 128)) <= TOL
     with pytest.raises(NotImplementedError):
         ext.cutlass_f8f8bf16_rowwise_sm89()
+
+
+def test_load_checkpoint_fills_and_repacks(tmp_path):
+    """`checkpoint.load_checkpoint` into CUDA modules: buffers equal the file's tensors, the kernel layout is
+    ready before the first forward, and the forward equals that of the module the file was saved from."""
+    import os
+    from llmrqt_sdv1_b200 import AWQLinear_GEMM, checkpoint, kernels, quantize
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = AWQLinear_GEMM(4, 128, 256, 512, True, "cuda")
+            self.b = AWQLinear_GEMM(4, 128, 512, 256, False, "cuda")
+
+        def forward(self, x):
+            return self.b(self.a(x))
+
+    src = Block()
+    for i, m in enumerate((src.a, src.b)):
+        m.qweight, m.qzeros, m.scales = quantize.random_awq_tensors(m.in_features, m.out_features, 128, seed=i, device="cuda")
+    src.a.bias = (torch.randn(512, device="cuda") * 0.1).half()
+    path = os.path.join(tmp_path, "block.safetensors")
+    checkpoint.save_checkpoint(src.state_dict(), path)
+    dst = Block()
+    report = checkpoint.load_checkpoint(dst, path)
+    assert sorted(report["loaded"]) == sorted(src.state_dict()) and not report["missing"]
+    for k, v in src.state_dict().items():
+        assert torch.equal(dst.state_dict()[k], v), k
+    x = torch.randn((1, 5, 256), device="cuda").half()
+    assert torch.equal(dst(x), src(x))
+    assert kernels.gemv_status() == 0
