@@ -164,8 +164,12 @@ AWQ_B200_API int awq_b200_gemv_ex(const void* x, const void* packed, const void*
  *   - All calls share the one array and it keeps the previous call's partial sums: calls that can
  *     overlap on the GPU (different streams) race.  Serialise them, or use awq_b200_gemv with one
  *     workspace per stream.
- * Results are bit-identical to awq_b200_gemv. */
+ * Results are bit-identical to awq_b200_gemv.
+ * awq_b200_gemv_static_status copies the array's status word (0, or the code of a device-side wait that
+ * expired in some earlier call on the current device) to *status_out on the host; it synchronises with
+ * `stream` and allocates nothing either. */
 AWQ_B200_API size_t awq_b200_gemv_static_scratch_bytes(void);
+AWQ_B200_API int awq_b200_gemv_static_status(unsigned* status_out, awq_b200_stream_t stream);
 AWQ_B200_API int awq_b200_gemv_static(const void* x, const void* packed, const void* scales,
                          const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
                          int group_size, awq_b200_stream_t stream);
@@ -237,7 +241,17 @@ AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const
 
 /* ---- row-parallel shards: one-shot sum over peer memory ------------------- */
 
-/* Bytes of the per-rank flag array of awq_b200_peer_allreduce (zero before the first call). */
+/* Bytes of the per-rank flag array of awq_b200_peer_allreduce (zero before the first call).  Two of its
+ * 32-bit words are the caller's to read and write (with no call in flight):
+ *   AWQ_B200_PEER_STATUS_WORD      0, or 1 / 2 / 3 after a wait on a peer expired (pull form: the peers'
+ *                                  partials / the peers' reads; push form: the peers' pushes).  Sticky.
+ *   AWQ_B200_PEER_WAIT_LIMIT_WORD  how long one call may wait for its peers, in units of 1024 SM clock
+ *                                  cycles; 0 selects the default of about 2 s.
+ * After an expiry the ranks' call counters no longer agree and later calls expire as well.  Recover with
+ * a collective reset: with no call in flight on any rank, every rank zeroes its flag array (the limit word
+ * may be kept) and its receive area, and all ranks meet at a barrier before the next call. */
+#define AWQ_B200_PEER_STATUS_WORD 34
+#define AWQ_B200_PEER_WAIT_LIMIT_WORD 37
 AWQ_B200_API size_t awq_b200_peer_allreduce_flag_bytes(void);
 
 /* out[i] = fp16( sum over ranks r of bufs[r][i] ) (+ bias[i % ncols]), i < count, on every rank of one node.
@@ -247,8 +261,8 @@ AWQ_B200_API size_t awq_b200_peer_allreduce_flag_bytes(void);
  * and adds them in rank order in fp32, so all ranks get identical bits; the call returns (stream-wise) only
  * after every peer has read this rank's partial, so the partial may be rewritten by the next kernel.
  * All ranks must make matching calls in the same order.  count % 8 == 0, buffers 16-byte aligned,
- * world <= 16.  Waits on peers are bounded (~2 s): on expiry word 34 of the flag array becomes non-zero
- * and the output is invalid.  The reference has no counterpart (it is single-GPU,
+ * world <= 16.  Waits on peers are bounded (see AWQ_B200_PEER_WAIT_LIMIT_WORD): on expiry the status word
+ * of the flag array becomes non-zero and the output is invalid.  The reference has no counterpart (it is single-GPU,
  * LLMQRT/runtime_refact/core/base.py:44); this replaces the all-reduce of a row-parallel linear
  * (spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:186-199) at decode sizes. */
 AWQ_B200_API int awq_b200_peer_allreduce(const void* const* bufs, void* const* flags, void* out, const void* bias,
@@ -261,8 +275,8 @@ AWQ_B200_API int awq_b200_peer_allreduce(const void* const* bufs, void* const* f
  * area of 2 * world * slot_elems * 4 bytes (peer-mapped like the flag arrays, zero before the first call;
  * slot_elems >= count, a multiple of 8); its two halves alternate on the parity of the call counter kept in
  * the flag array, which makes a closing hand-shake unnecessary.  Same flag arrays, ordering rules,
- * bit-identical results on all ranks, bounded waits (status word 34 becomes 3) and graph-capture behaviour
- * as awq_b200_peer_allreduce. */
+ * bit-identical results on all ranks, bounded waits (the status word becomes 3; one limit covers the
+ * whole call) and graph-capture behaviour as awq_b200_peer_allreduce. */
 AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* recv, void* const* flags, void* out,
                                  const void* bias, size_t count, int ncols, size_t slot_elems, int rank,
                                  int world, awq_b200_stream_t stream);

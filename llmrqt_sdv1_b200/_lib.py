@@ -33,6 +33,7 @@ SIGNATURES = {
     "awq_b200_linear_ex": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_gemv_static_scratch_bytes": (_Z, []),
     "awq_b200_gemv_static": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "awq_b200_gemv_static_status": (_I, [_P, _P]),
     "awq_b200_gemv_workspace_bytes_max": (_Z, [_I, _I, _I]),
     "awq_b200_gemv_plan": (_I, _COMPUTE + [_I, _I, _I, C.c_uint]),
     "awq_b200_gemm_workspace_bytes": (_Z, [_I, _I, _I]),

@@ -18,13 +18,16 @@
 // pointer per rank, as a device array).  The epoch is kept in device memory and advanced by the kernel,
 // so the call can be captured in a CUDA graph and replayed.  No multicast / multimem loads are used.
 // Every wait is bounded (~2 s); on expiry the kernel sets a status word and returns, and the output of
-// that call is invalid.
+// that call is invalid.  The ranks must make matching calls: after an expired wait (or any other mismatch
+// in the number of calls) the ranks' call counters disagree and every later call expires too, until the flag
+// arrays and receive areas have been zeroed again on every rank with no call in flight (a collective reset;
+// the wait-limit word may be kept).
 #include "awq_common.cuh"
 
 namespace awq {
 
 constexpr int kArMaxWorld = 16;
-constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // ~2 s at 2 GHz
+constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // default limit of a wait on a peer: ~2 s at 2 GHz
 
 // Flag array layout (uint32 words) in each rank's symmetric flag buffer:
 //   [0, 16)   ready[r]   written by rank r
@@ -33,8 +36,11 @@ constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // ~2 s at 2 
 //   [33]      blocks of the current call that finished summing (local)
 //   [34]      status: 0, or 1 / 2 when the ready / done wait expired, 3 for the push variant's wait (local, sticky)
 //   [35], [36] epoch and finished-block counter of the push variant (local)
+//   [37]      limit of a wait on a peer in units of 1024 SM cycles; 0 = the default of ~2 s (local, set by the host)
 constexpr int kArReadyOff = 0, kArDoneOff = 16, kArEpochOff = 32, kArBlocksOff = 33, kArStatusOff = 34;
-constexpr int kArPushEpochOff = 35, kArPushBlocksOff = 36;
+constexpr int kArPushEpochOff = 35, kArPushBlocksOff = 36, kArLimitOff = 37;
+static_assert(kArStatusOff == AWQ_B200_PEER_STATUS_WORD && kArLimitOff == AWQ_B200_PEER_WAIT_LIMIT_WORD,
+              "the header documents these two words");
 constexpr int kArMaxBlocks = 64;
 constexpr int kArFlagWords = 64;
 
@@ -59,15 +65,21 @@ __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ unsigned long long wait_limit_cycles(const unsigned* my_flags) {
+  const unsigned kcycles = my_flags[kArLimitOff];
+  return kcycles != 0u ? static_cast<unsigned long long>(kcycles) << 10 : kArWaitLimitCycles;
+}
+
 // Waits until flags[off + r] == epoch for every r < world.  Returns false on expiry.
-__device__ __forceinline__ bool wait_all(const unsigned* flags, int off, int world, unsigned epoch) {
+__device__ __forceinline__ bool wait_all(const unsigned* flags, int off, int world, unsigned epoch,
+                                         unsigned long long limit) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if (threadIdx.x < world) {
     const unsigned long long t0 = clock64();
     while (ld_acquire_sys(flags + off + threadIdx.x) != epoch) {
-      if (clock64() - t0 > kArWaitLimitCycles) { s_ok = 0; break; }
+      if (clock64() - t0 > limit) { s_ok = 0; break; }
     }
   }
   __syncthreads();
@@ -86,8 +98,9 @@ peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint1
   asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned* my_flags = flags[rank];
   const unsigned epoch = my_flags[kArEpochOff] + 1u;   // written only by this kernel's last block, a launch ago
+  const unsigned long long limit = wait_limit_cycles(my_flags);
   if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(flags[threadIdx.x] + kArReadyOff + rank, epoch);
-  const bool ready = wait_all(my_flags, kArReadyOff, world, epoch);
+  const bool ready = wait_all(my_flags, kArReadyOff, world, epoch, limit);
   if (!ready && threadIdx.x == 0) atomicCAS(my_flags + kArStatusOff, 0u, 1u);
 
   if (ready) {
@@ -139,7 +152,7 @@ peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint1
   __syncthreads();
   if (!s_last) return;
   if (threadIdx.x < world) st_release_sys(flags[threadIdx.x] + kArDoneOff + rank, epoch);
-  const bool done = wait_all(my_flags, kArDoneOff, world, epoch);
+  const bool done = wait_all(my_flags, kArDoneOff, world, epoch, limit);
   if (threadIdx.x == 0) {
     if (!done) atomicCAS(my_flags + kArStatusOff, 0u, 2u);
     my_flags[kArBlocksOff] = 0u;
@@ -184,6 +197,7 @@ peer_allreduce_push_kernel(const uint16_t* partial, unsigned char* const* recv, 
   __shared__ int s_ok;
   unsigned* my_flags = flags[rank];
   const unsigned epoch = my_flags[kArPushEpochOff] + 1u;   // written only by this kernel's last block, a launch ago
+  const unsigned long long limit = wait_limit_cycles(my_flags);
   const size_t slot_bytes = slot_elems * 4;
   const size_t par_off = static_cast<size_t>(epoch & 1u) * world;
   const size_t vecs = count / 8;
@@ -206,7 +220,11 @@ peer_allreduce_push_kernel(const uint16_t* partial, unsigned char* const* recv, 
   }
 
   // 2. the same vectors of every peer, polled out of this rank's own memory, summed in rank order
+  // One limit for the whole call: once a wait has run out (in this thread or, seen through s_ok, in another
+  // thread of the block) no further word is polled, so a call returns about one limit after it started.
   const unsigned char* slots = recv[rank] + par_off * slot_bytes;
+  volatile int* block_ok = &s_ok;
+  const unsigned long long t_call = clock64();
   for (size_t i = first; i < vecs; i += stride) {
     float acc[8];
 #pragma unroll
@@ -214,20 +232,18 @@ peer_allreduce_push_kernel(const uint16_t* partial, unsigned char* const* recv, 
     bool ok = true;
 #pragma unroll
     for (int r = 0; r < kArMaxWorld; ++r) {
-      if (r < world) {
+      if (r < world && ok) {
         uint4 v;
         if (r == rank) {
           v = *reinterpret_cast<const uint4*>(partial + i * 8);
         } else {
           const unsigned char* src = slots + static_cast<size_t>(r) * slot_bytes + i * 32;
           uint4 a = ld_wire_16(src), b = ld_wire_16(src + 16);
-          if (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch) {
-            const unsigned long long t0 = clock64();
-            do {
-              a = ld_wire_16(src);
-              b = ld_wire_16(src + 16);
-              if (clock64() - t0 > kArWaitLimitCycles) { ok = false; break; }
-            } while (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch);
+          unsigned spins = 0;
+          while (a.y != epoch || a.w != epoch || b.y != epoch || b.w != epoch) {
+            if ((++spins & 15u) == 0u && (*block_ok == 0 || clock64() - t_call > limit)) { ok = false; break; }
+            a = ld_wire_16(src);
+            b = ld_wire_16(src + 16);
           }
           v = make_uint4(a.x, a.z, b.x, b.z);
         }

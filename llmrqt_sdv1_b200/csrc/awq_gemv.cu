@@ -14,29 +14,6 @@
 // the call has.
 #include "awq_gemv_common.cuh"
 
-#ifdef AWQ_GEMV_TRACE
-// Diagnostic build only: per-CTA phase timestamps (ns) into a caller-provided buffer.
-__device__ unsigned long long* g_gemv_trace = nullptr;
-__device__ __forceinline__ unsigned long long gemv_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Slot base depends on N so that two different linears launched back to back land in separate regions.
-#define GEMV_TRACE(i)                                                                              \
-  do {                                                                                             \
-    if ((threadIdx.x & 31) == 0 && threadIdx.x < 64 && g_gemv_trace)                               \
-      g_gemv_trace[(((p.N >> 10) & 3) * 8192 + (blockIdx.y * gridDim.x + blockIdx.x) * 2 + (threadIdx.x >> 5)) * 16 + (i)] = gemv_now(); \
-  } while (0)
-#define GEMV_TRACE_IT(i) do { if (it == 0) GEMV_TRACE(i); else if (it == 1) GEMV_TRACE((i) + 4); } while (0)
-extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_gemv_trace(void* buf) {
-  return static_cast<int>(cudaMemcpyToSymbol(g_gemv_trace, &buf, sizeof(buf)));
-}
-#else
-#define GEMV_TRACE(i) do { } while (0)
-#define GEMV_TRACE_IT(i) do { } while (0)
-#endif
-
 namespace awq {
 
 // The W compute warps form a CW x KW grid (CW * KW = W): warp (cw, kw) owns NTW column tiles
@@ -84,7 +61,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   // side by side and read the same weights at about the same time, so the second read is an L2 hit.
   const int row0 = ROW_HALVES ? blockIdx.z * MT : 0;
   const int rows = ROW_HALVES ? min(p.M - row0, MT) : p.M;      // rows of this CTA
-  GEMV_TRACE(0);
   const bool is_producer = (warp == kGemvWarps);
   const int cw = warp % CW, kw = (warp / CW) % KW;
   const int b0 = split * p.bps;
@@ -150,7 +126,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
   // (both are no-ops unless the launch asked for programmatic dependent launch).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  GEMV_TRACE(1);
   __syncthreads();   // mbarrier initialisation visible to every warp
 
   // Activations go straight from global memory (L1/L2 resident) to the mma B fragments: lane
@@ -196,8 +171,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       const uint32_t ph = static_cast<uint32_t>(it / ST) & 1u;
       const int bl = it * KW + kw;               // this warp's block in this iteration
       if (!mbar_wait(bar_full(st), ph, abort_flag, 1)) break;
-      if (it == 0) GEMV_TRACE(2);
-      GEMV_TRACE_IT(7);
       uint4 wv[NTW];
       float sc[NTW], zp[NTW];
       if (bl < nb) {
@@ -220,7 +193,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty(st));
       if (bl >= nb) continue;
-      GEMV_TRACE_IT(8);
 
       uint4 xv[MH][4];
       float4 T[MH];
@@ -232,12 +204,9 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
         load_x(bl, xv);
       }
       gemv_block_sums<MH>(xv, T);
-      GEMV_TRACE_IT(9);
       gemv_block_pairs<NTW, MH>(wv, sc, zp, xv, T, acc);
-      GEMV_TRACE_IT(10);
     }
   }
-  GEMV_TRACE(3);
   __syncthreads();
   if (s_abort != 0) {
     // A wait expired.  Let this CTA's outstanding copies land (bounded) before shared memory is
@@ -295,10 +264,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       emit(e / kCtaCols, e % kCtaCols, v);
     }
   }
-  if (direct) {
-    GEMV_TRACE(6);
-    return;
-  }
+  if (direct) return;
 
   if (via_cluster) {
     // The S splits of this column range are the CTAs of one cluster (rank = split).  Each rank
@@ -326,12 +292,10 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
       variant_store_pair(p, fusion, row0 + m, cta_tile0 * 8 + nl, sum.x, sum.y);
     }
     cluster_sync_all();   // nobody leaves while its shared memory may still be read
-    GEMV_TRACE(6);
     return;
   }
 
   __threadfence();
-  GEMV_TRACE(4);
   __syncthreads();
   if (tid == 0) {
     const unsigned counter = (ROW_HALVES ? blockIdx.z * gridDim.x : 0u) + blockIdx.x;
@@ -341,7 +305,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
     s_last = last;
   }
   __syncthreads();
-  GEMV_TRACE(5);
   if (!s_last) return;
   __threadfence();
 
@@ -372,7 +335,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_kernel(cons
     }
     variant_store_pair(p, fusion, row, col, sum.x, sum.y);
   }
-  GEMV_TRACE(6);
 }
 
 
@@ -711,6 +673,16 @@ static int static_scratch_for_current_device(cudaStream_t stream, void** out) {
 extern "C" {
 
 size_t awq_b200_gemv_static_scratch_bytes(void) { return kGemvStaticScratchBytes; }
+
+int awq_b200_gemv_static_status(unsigned* status_out, awq_b200_stream_t stream) {
+  if (!status_out) return AWQ_B200_ERR_NULL;
+  void* scratch = nullptr;
+  if (int st = static_scratch_for_current_device(static_cast<cudaStream_t>(stream), &scratch)) return st;
+  AWQ_CUDA_TRY(cudaMemcpyAsync(status_out, static_cast<unsigned*>(scratch) + (kGemvMaxCounters - 1), sizeof(unsigned),
+                               cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  AWQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return AWQ_B200_OK;
+}
 
 int awq_b200_gemv_static(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                          const void* bias, void* y, int M, int K, int N, int group_size,

@@ -256,11 +256,6 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kern
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_empty(st));
           if (bl >= p.nblk || valid_tiles == 0u) continue;
-#ifdef AWQ_GEMV_COPY_ONLY
-          // Diagnostic build only: consume the stage without the arithmetic (measures the copy pipeline).
-          acc[0][0][0] += __uint_as_float(wv[0].x & 1u) + sc[0] + zp[0];
-          continue;
-#endif
 
           uint4 xv[MH][4];
           float4 T[MH];

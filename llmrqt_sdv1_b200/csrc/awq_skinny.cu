@@ -28,21 +28,6 @@
 #include "awq_gemv_common.cuh"
 #include "awq_tcgen05.cuh"
 
-#ifdef AWQ_SKINNY_TRACE
-// Diagnostic build only: cycle stamps of CTA 0 (SM clock) for its first 48 units.
-__device__ long long* g_skinny_trace = nullptr;
-#define SK_TRACE(role, unit, slot)                                                                        \
-  do {                                                                                                    \
-    if (((AWQ_SKINNY_TRACE >> (role)) & 1) && trace_buf && (unit) < 48)                                   \
-      trace_buf[((role) * 48 + (unit)) * 8 + (slot)] = clock64();                                         \
-  } while (0)
-extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_skinny_trace(void* buf) {
-  return static_cast<int>(cudaMemcpyToSymbol(g_skinny_trace, &buf, sizeof(buf)));
-}
-#else
-#define SK_TRACE(role, unit, slot) do { } while (0)
-#endif
-
 namespace awq {
 
 constexpr int kSkDequantWarps = 16;
@@ -137,9 +122,6 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   tcgen05_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
-#ifdef AWQ_SKINNY_TRACE
-  long long* const trace_buf = blockIdx.x == 0 ? g_skinny_trace : nullptr;
-#endif
 
   const long long U = p.units, G = gridDim.x;
   const long long u0 = stream_first_unit(blockIdx.x, U, G), u1 = stream_first_unit(blockIdx.x + 1, U, G);
@@ -201,12 +183,9 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     }
     int next = NT + my_parity;
     for (; next < my_units; next += 2) {
-      if (warp == 0) SK_TRACE(0, next, 0);
       if (!mbar_wait(bar_empty_tma(next % NT), static_cast<uint32_t>(next / NT - 1) & 1u, abort_flag, 1)) break;
-      if (warp == 0) SK_TRACE(0, next, 1);
       issue(next, tile, kb, true, true);
       advance();
-      if (warp == 0) SK_TRACE(0, next, 2);
     }
     // Do not leave while a copy of this warp may still be writing shared memory: wait (bounded) for
     // the last ring's worth of its units to land.
@@ -230,18 +209,14 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       if (!mbar_wait(bar_acc_empty, (static_cast<uint32_t>(seg) & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
       tcgen05_fence_after();
       for (int j = 0; j < seg_units; ++j, ++gs) {
-        if (warp == 1) SK_TRACE(1, gs, 0);
         if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
-        if (warp == 1) SK_TRACE(1, gs, 1);
         if (!mbar_wait(bar_a_full(a), pha, abort_flag, 4)) { ok = false; break; }
-        if (warp == 1) SK_TRACE(1, gs, 2);
         tcgen05_fence_after();
         // eight k-steps into this half's accumulator, then: activations of this unit consumed, A slot reusable
         tcgen05_mma_f16_ts_k8_commit2_warp(tmem_base + h * MT,
                                            tmem_base + static_cast<uint32_t>(Cfg::kABase + a * 128 + h * 64),
                                            make_sw128_desc(stage_addr(t)), 32u >> 4, Cfg::kXHalfBytes >> 4, kIdesc,
                                            j != 0 ? 1u : 0u, bar_empty_tma(t), bar_a_empty(a));
-        if (warp == 1) SK_TRACE(1, gs, 3);
         if (++t == NT) { t = 0; ph ^= 1u; }
         if (++a == NA) { a = 0; pha ^= 1u; }
       }
@@ -294,10 +269,8 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             sz_group = qgrp;
           }
         }
-        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 0);
         if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
         if (!ok) continue;
-        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 1);
         const unsigned char* stage = base_ptr + t * Cfg::kStageBytes;
         if (sz_by_copy) {
           // Columns beyond N read stale shared memory here; their lanes of the product are never stored.
@@ -311,7 +284,6 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; continue; }
-        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 2);
         tcgen05_fence_after();
         const ZeroPair zp = make_zero_pair((zw >> zsh) & 0xFu);
         const uint32_t s2 = sc * 0x00010001u;
@@ -323,20 +295,12 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint32_t q4[4];
-#if defined(AWQ_SKINNY_DIAG) && AWQ_SKINNY_DIAG == 1
-            unpack_codes(w[i], q4);            // diagnostic build only: 5 operations per word, wrong values
-#elif defined(AWQ_SKINNY_DIAG) && AWQ_SKINNY_DIAG == 2
-            q4[0] = w[i]; q4[1] = w[i] ^ s2; q4[2] = w[i] + zp.lo; q4[3] = ~w[i];   // diagnostic: ~no arithmetic
-#else
             dequant_word(w[i], zp, s2, q4);
-#endif
             o[4 * i + 0] = q4[0]; o[4 * i + 1] = q4[1]; o[4 * i + 2] = q4[2]; o[4 * i + 3] = q4[3];
           }
           tcgen05_st_32x32b_x16(a_addr + static_cast<uint32_t>(c * 16), o);
         }
-        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 3);
         tcgen05_wait_st();
-        if (dq_warp == 0 || dq_warp == 8) SK_TRACE(2, gs, 4);
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_a_full(a));

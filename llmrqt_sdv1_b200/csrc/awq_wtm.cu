@@ -20,20 +20,6 @@
 #include "awq_ptx.cuh"
 #include "awq_tcgen05.cuh"
 
-#ifdef AWQ_WTM_TRACE
-// Diagnostic build only: cycle stamps of CTA 0 (SM clock) for the first 48 k-stages.
-__device__ long long* g_wtm_trace = nullptr;
-#define WTM_TRACE(role, stage, slot)                                                          \
-  do {                                                                                        \
-    if ((AWQ_WTM_TRACE >> (role)) & 1) if (trace_buf && (stage) < 48) trace_buf[((role) * 48 + (stage)) * 8 + (slot)] = clock64(); \
-  } while (0)
-extern "C" __attribute__((visibility("default"))) int awq_b200_debug_set_wtm_trace(void* buf) {
-  return static_cast<int>(cudaMemcpyToSymbol(g_wtm_trace, &buf, sizeof(buf)));
-}
-#else
-#define WTM_TRACE(role, stage, slot) do { } while (0)
-#endif
-
 namespace awq {
 
 constexpr int kWtDequantThreads = 512;
@@ -166,10 +152,6 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   tcgen05_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
-#ifdef AWQ_WTM_TRACE
-  long long* const trace_buf = blockIdx.x == 0 ? g_wtm_trace : nullptr;
-#endif
-
   const int nks = p.K / kWtBK;
   const int num_tiles = p.mtiles * p.ntiles;
   constexpr uint32_t kIdesc = make_f16_idesc(128, MT);
@@ -212,23 +194,18 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       const uint32_t sz_dst = Cfg::kSzOff + (lane == 3 ? 0 : 512);
       for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
         if ((it & 1u) == my_parity) {
-          WTM_TRACE(0, it, 0);
           if (!mbar_wait(bar_empty_tma(t), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
-          WTM_TRACE(0, it, 1);
           const uint32_t bar = bar_full_tma(t);
           if (lane == 0) {
             mbar_expect_tx(bar, tx);
             tma_load_2d(x_addr(t), &map_x, ks * kWtBK, m0, bar);
           }
-          WTM_TRACE(0, it, 2);
           // packed weights of this 64-k stage: bytes [32*(ks&1), +32) of each column's 64 per 128-k block, one
           // 32-byte row per column; the 32-byte swizzle makes the per-column 16-byte reads conflict-free
           if (lane == 1) tma_load_3d(raw_addr(t), &map_w, (ks & 1) * 32, n0, ks >> 1, bar);
-          WTM_TRACE(0, it, 3);
           // scales and zero words of this stage's quantisation group ride in the same stage
           if (sz_by_copy && (lane == 3 || lane == 4))
             bulk_load(x_addr(t) + sz_dst, sz_src + static_cast<size_t>(grp) * sz_step, sz_bytes, bar);
-          WTM_TRACE(0, it, 4);
         }
         if (--left == 0) { left = stages_per_group; ++grp; }
         if (++t == NT) { t = 0; ph ^= 1u; }
@@ -251,11 +228,8 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       if (!mbar_wait(bar_acc_empty, (tile_it & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
       tcgen05_fence_after();
       for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
-        WTM_TRACE(1, it, 0);
         if (!mbar_wait(bar_full_tma(t), ph, abort_flag, 3)) { ok = false; break; }
-        WTM_TRACE(1, it, 1);
         if (!mbar_wait(bar_a_full(a), pha, abort_flag, 4)) { ok = false; break; }
-        WTM_TRACE(1, it, 2);
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kWtBK / 16; ++kk) {
@@ -268,7 +242,6 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         }
         tcgen05_commit_warp(bar_empty_tma(t));   // activations of this stage consumed
         tcgen05_commit_warp(bar_a_empty(a));     // A slots reusable
-        WTM_TRACE(1, it, 3);
         if (++t == NT) { t = 0; ph ^= 1u; }
         if (++a == NA) { a = 0; pha ^= 1u; }
       }
@@ -331,10 +304,8 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           const int qgrp = (ks * kWtBK) / p.group_size;
           if (qgrp != sz_group) { load_sz(ks, sc, zw); sz_group = qgrp; }
         }
-        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 0);
         if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
         if (!ok) continue;
-        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 1);
         const unsigned char* raw = base_ptr + (raw_addr(t) - base);
         if (sz_by_copy) {
           const unsigned char* szp = base_ptr + (x_addr(t) - base) + Cfg::kSzOff;
@@ -356,7 +327,6 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; continue; }
-        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 2);
         tcgen05_fence_after();
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) {
@@ -376,9 +346,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
             tcgen05_st_32x32b_x16(tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + (a * 2 + h) * 32 + kh * 16), o);
           }
         }
-        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 3);
         tcgen05_wait_st();
-        if (lane == 0 && (dq_warp % GW) == 0) WTM_TRACE(2, it, 4);
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_a_full(a));

@@ -122,6 +122,24 @@ def _workspace(dev: torch.device, stream: int, nbytes: int, kind: str) -> torch.
     return ws
 
 
+def _check_out(out, out_shape, M: int, ncols: int, dev: torch.device) -> None:
+    """The kernels write M * ncols contiguous fp16 elements at `out`: anything else (a strided view, a
+    shorter tensor, another dtype) would be an out-of-bounds or misplaced write on the device, so it is
+    refused here, before the call."""
+    if out is not None:
+        if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() != M * ncols:
+            raise ValueError(f"out must be a contiguous fp16 tensor of {M} x {ncols} elements, got {out.dtype} "
+                             f"{tuple(out.shape)} (contiguous: {out.is_contiguous()})")
+        if out.device != dev:
+            raise RuntimeError("all tensors of one call must be on the same device")
+    elif out_shape is not None:
+        n = 1
+        for d in out_shape:
+            n *= int(d)
+        if n != M * ncols:
+            raise ValueError(f"out_shape {tuple(out_shape)} does not hold {M} x {ncols} elements")
+
+
 def _check_x(x: torch.Tensor, pw: PackedWeight) -> torch.Tensor:
     if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != pw.K:
         raise ValueError(f"x must be fp16 [M, {pw.K}], got {x.dtype} {tuple(x.shape)}")
@@ -130,8 +148,9 @@ def _check_x(x: torch.Tensor, pw: PackedWeight) -> torch.Tensor:
 
 def _run(fn, name, x, pw, bias, ws_bytes, out=None, extra=()):
     x = _check_x(x, pw)
-    dev = _prep(x, pw.packed, pw.qzeros, pw.scales, bias)
     M = x.shape[0]
+    _check_out(out, None, M, pw.N, x.device)
+    dev = _prep(x, pw.packed, pw.qzeros, pw.scales, bias)
     y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
     stream = _stream(x)
     ws = _workspace(dev, stream, ws_bytes, name)
@@ -216,6 +235,10 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_
     if not x.is_contiguous():
         x = x.contiguous()
     M = x.numel() // pw.K
+    if out is not None or out_shape is not None:
+        _check_out(out, out_shape, M, pw.N, dev)
+    if dev.type != "cuda":
+        raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
     index = dev.index
     _lib.set_device(index)
     need = pw._ws_need.get(M)
@@ -288,6 +311,10 @@ def linear_fused(x, pw: PackedWeight, bias=None, residual=None, gated: bool = Fa
             raise ValueError(f"residual must be fp16 with {M} x {ncols} elements")
         if not residual.is_contiguous():
             residual = residual.contiguous()
+    if out is not None or out_shape is not None:
+        _check_out(out, out_shape, M, ncols, dev)
+    if dev.type != "cuda":
+        raise RuntimeError("llmrqt_sdv1_b200 kernels need CUDA tensors; there is no CPU fallback")
     index = dev.index
     _lib.set_device(index)
     need = pw._ws_need.get(M)
@@ -316,6 +343,7 @@ def peer_allreduce(bufs_dev: int, flags_dev: int, local_buf: torch.Tensor, M: in
     """Sum of the ranks' [M, N] fp16 partials held in symmetric memory (see `sharded.PeerSum`).
     `bufs_dev` / `flags_dev` are device arrays of per-rank pointers."""
     dev = local_buf.device
+    _check_out(out, None, M, N, dev)
     _lib.set_device(dev.index)
     y = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=dev)
     check(lib.awq_b200_peer_allreduce(bufs_dev, flags_dev, y.data_ptr(), bias.data_ptr() if bias is not None else None,
@@ -328,6 +356,7 @@ def peer_allreduce_push(partial: torch.Tensor, recv_dev: int, flags_dev: int, sl
                         bias: torch.Tensor | None = None) -> torch.Tensor:
     """`peer_allreduce` with the partials pushed into the peers' receive slots (see `sharded.PeerSum`)."""
     dev = partial.device
+    _check_out(out, None, M, N, dev)
     _lib.set_device(dev.index)
     y = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=dev)
     check(lib.awq_b200_peer_allreduce_push(partial.data_ptr(), recv_dev, flags_dev, y.data_ptr(),

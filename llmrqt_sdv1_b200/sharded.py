@@ -174,10 +174,39 @@ class PeerSum:
         return kernels.peer_allreduce(self._h_buf.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev, self.buf,
                                       M, N, self.rank, self.world, out=out, bias=bias)
 
+    STATUS_WORD, WAIT_LIMIT_WORD = 34, 37      # AWQ_B200_PEER_STATUS_WORD / AWQ_B200_PEER_WAIT_LIMIT_WORD
+
     def status(self) -> int:
         """0, or which wait expired in some call (1: peers' partials, 2: peers' reads, 3: peers' pushes).
-        Synchronises."""
-        return int(self.flags[34].item())
+        Sticky until `reset`.  Synchronises."""
+        return int(self.flags[self.STATUS_WORD].item())
+
+    def check(self) -> None:
+        """Raise if a wait on a peer has expired since the last reset (the outputs of that call and of
+        every later call are invalid: the ranks' call counters no longer agree)."""
+        st = self.status()
+        if st != 0:
+            raise RuntimeError(f"peer all-reduce: a wait on a peer expired (status {st}); call reset() on every rank")
+
+    def set_wait_limit(self, seconds: float | None, sm_clock_hz: float = 1.9e9) -> None:
+        """How long one call may wait for its peers before it gives up and sets the status word
+        (None = the library's default of about 2 s).  Takes effect with the next launch."""
+        kcycles = 0 if seconds is None else max(1, min(0xFFFFFFFF, int(seconds * sm_clock_hz / 1024)))
+        self.flags[self.WAIT_LIMIT_WORD] = kcycles if kcycles < 2 ** 31 else kcycles - 2 ** 32
+
+    def reset(self) -> None:
+        """Collective: bring every rank's call counters, flags, status word and receive slots back to their
+        initial state after an expired wait or a mismatched number of calls.  All ranks must call it, with
+        no exchange in flight; the wait limit is kept."""
+        torch.cuda.synchronize(self.flags.device)
+        dist.barrier(self.group)           # nobody is still pushing into a slot that is about to be cleared
+        limit = self.flags[self.WAIT_LIMIT_WORD].clone()
+        self.flags.zero_()
+        self.flags[self.WAIT_LIMIT_WORD] = limit
+        if self.mode == "push":
+            self.recv.zero_()
+        torch.cuda.synchronize(self.flags.device)
+        dist.barrier(self.group)
 
 
 class RowParallelAWQLinear(nn.Module):

@@ -24,6 +24,8 @@ def load(rebuild: bool = False):
     lib = C.CDLL(_LIB)
     P, I = C.c_void_p, C.c_int
     lib.awq_oracle_threads.restype = I
+    lib.awq_oracle_set_threads.argtypes = [I]
+    lib.awq_oracle_set_threads.restype = I
     lib.awq_oracle_dequant.argtypes = [P, P, P, P, I, I, I]
     lib.awq_oracle_matmul.argtypes = [P, P, P, P, I, I, I]
     lib.awq_oracle_linear.argtypes = [P, P, P, P, P, P, I, I, I, I]
@@ -38,6 +40,16 @@ def _p(a):
 
 def threads() -> int:
     return load().awq_oracle_threads()
+
+
+def use_all_cores() -> int:
+    """Run the OpenMP loops on every core this process may use, whatever OMP_NUM_THREADS says (launchers
+    of multi-process jobs set it to 1).  Returns the thread count now in effect."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return load().awq_oracle_set_threads(max(n, 1))
 
 
 def dequantize(qweight, qzeros, scales, group_size) -> np.ndarray:

@@ -74,3 +74,31 @@ def test_fused_modules_have_no_cpu_path():
             GraphedStep(lambda x: x, (torch.zeros(4),))
     with pytest.raises(ValueError):
         AWQGatedMLP(gate, AWQLinear_GEMM(4, 128, 128, 64, False, "cpu"), down)
+
+
+def test_out_tensor_is_validated_before_the_call():
+    """`out` is written by the kernel as M x N contiguous fp16 elements: anything else must be refused on the
+    host (it would be a stray write on the device).  The checks run before any CUDA call, so CPU tensors show
+    them; a well-formed call with CPU tensors then still refuses to compute."""
+    from llmrqt_sdv1_b200 import kernels
+    K, N = 128, 64
+    pw = kernels.PackedWeight(torch.zeros((1, N, 16), dtype=torch.int32), torch.zeros((1, N // 8), dtype=torch.int32),
+                              torch.zeros((1, N), dtype=torch.float16), K, N, 128)
+    x = torch.zeros((2, K), dtype=torch.float16)
+    bad_outs = [torch.zeros((2, N), dtype=torch.float32),                 # wrong dtype
+                torch.zeros((2, 2 * N), dtype=torch.float16)[:, ::2],     # strided view
+                torch.zeros((1, N), dtype=torch.float16),                 # too short
+                torch.zeros((3, N), dtype=torch.float16)]                 # too long
+    for out in bad_outs:
+        with pytest.raises(ValueError):
+            kernels.linear(x, pw, out=out)
+        with pytest.raises(ValueError):
+            kernels.linear_fused(x, pw, out=out)
+        with pytest.raises(ValueError):
+            kernels.gemv(x, pw, out=out)
+    with pytest.raises(ValueError):
+        kernels.linear_fused(x, pw, gated=True, out=torch.zeros((2, N), dtype=torch.float16))   # gated: N / 2 columns
+    with pytest.raises(ValueError):
+        kernels.linear(x, pw, out_shape=(1, 2, N + 8))
+    with pytest.raises(RuntimeError):
+        kernels.linear(x, pw, out=torch.zeros((2, N), dtype=torch.float16))

@@ -36,13 +36,17 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     torch.cuda.set_device(0)
     _lib.set_device(0)
     assert lib.awq_b200_gemv_static_scratch_bytes() == 8 << 20
-    # K = 6144, N = 2048 is planned with several grid-level k-splits, i.e. it really uses the scratch.
+    # K = 6144, N = 2048 is planned with four grid-level k-splits.  Up to 8 rows those four CTAs form a
+    # cluster and add their sums over shared memory; with more than 8 rows the grid outgrows one CTA per SM
+    # and the partial sums go through the scratch array.  So the 16-row calls are the ones that use the
+    # array, and two of them in a row (different activations) check that the second call is not disturbed
+    # by what the first one left behind.
     K, N, G = 6144, 2048, 128
     qw, qz, sc = orc.make_awq_tensors(K, N, G, seed=11)
     pw = kernels.make_packed(*(torch.from_numpy(t).cuda() for t in (qw, qz, sc)), G)
     bias = torch.from_numpy(np.random.default_rng(5).standard_normal(N).astype(np.float16)).cuda()
     assert lib.awq_b200_gemv_workspace_bytes(4, K, N) > lib.awq_b200_gemv_counter_bytes(N)   # partial sums needed
-    for call, M in enumerate((4, 4, 16, 1)):          # back-to-back calls share the array
+    for call, M in enumerate((16, 16, 4, 16, 1)):     # back-to-back calls share the array
         x = torch.from_numpy(orc.make_activations(M, K, seed=call)).cuda()
         ref = kernels.gemv(x, pw, bias=bias)
         st, y = _static_gemv(lib, x, pw, bias)
@@ -52,6 +56,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         want = orc.linear_forward(x.cpu().numpy(), qw, qz, sc, G, bias.cpu().numpy())
         assert orc.max_normalised_error(y.cpu().numpy(), want) <= 2e-3
     assert kernels.gemv_status() == 0
+    import ctypes
+    word = ctypes.c_uint(0xFFFFFFFF)
+    assert lib.awq_b200_gemv_static_status(ctypes.addressof(word), torch.cuda.current_stream().cuda_stream) == 0
+    assert word.value == 0, f"a device-side wait expired in the static-scratch entry point (code {word.value})"
 
 
 def test_static_scratch_entry_point_rejects_what_does_not_fit():
