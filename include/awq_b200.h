@@ -233,6 +233,20 @@ AWQ_B200_API int awq_b200_skinny(const void* x, const void* packed, const void* 
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
 
+/* Decode rows (1 <= M <= 16) of a large matrix on the tensor-memory path with the cheapest possible unpack:
+ * same split-K stream of 256-column x 128-k units as awq_b200_skinny, but the nibbles go to tensor memory as
+ * unscaled codes (1024 + q or 64 + q: five logic operations per packed word) and the kernel applies
+ * s * (sum x*code - H - z * sum x) in fp32 once per unit when it reads the unit's accumulator back, H and
+ * sum x coming from a warp that adds up the activation tile.  The weights are therefore multiplied
+ * un-rounded, as in the reference's GEMV (LLMQRT/runtime_refact/csrc/awq/gemv.cu:138): results are within
+ * the 2e-3 layer bound of the fp16-weight path, not bit-equal to awq_b200_skinny.  Deterministic; a row's bits
+ * do not depend on M.  Same arguments, workspace rules and flags as awq_b200_skinny; replaces the same
+ * reference calls as awq_b200_gemv. */
+AWQ_B200_API size_t awq_b200_decode_workspace_bytes(int M, int K, int N);
+AWQ_B200_API int awq_b200_decode(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                    const void* bias, void* y, int M, int K, int N, int group_size,
+                    void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
+
 /* Tuning hook: awq_b200_gemm_wtm with the activation-row tile forced (64, 128, 192; 0 = by M). */
 AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales,
                            const int32_t* qzeros, const void* bias, void* y, int M, int K, int N,
@@ -288,14 +302,12 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
-/* Picks the kernel from the row count and the shape: M <= 8 -> awq_b200_gemv, or awq_b200_skinny
- * once the packed weights reach 48 MiB (a choice that depends on K and N only, so a row's bits do
- * not change with the number of rows decoded together, up to 8 rows); 9 <= M <= 16 -> the same with
- * the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice); 17 <= M <= 64 ->
- * awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
- * awq_b200_gemm otherwise.  Mirrors the row-count switch in AWQLinearMMFunction.forward
- * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), which also changes kernel
- * (and with it the order of additions) above 8 rows. */
+/* Picks the kernel from the row count and the shape: M <= 16 -> awq_b200_gemv, or awq_b200_decode
+ * once the packed weights reach 16 MiB (a choice that depends on K and N only, so a row's bits do
+ * not change with the number of rows decoded together); 17 <= M <= 64 -> awq_b200_skinny where the
+ * GEMM would leave most SMs idle (N <= 18944 and K >= 4096); awq_b200_gemm otherwise.  Mirrors the
+ * row-count switch in AWQLinearMMFunction.forward
+ * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185). */
 AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);

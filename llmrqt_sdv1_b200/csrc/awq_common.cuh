@@ -65,6 +65,9 @@ int gemv_run(const void* x, const void* packed, const void* scales, const int32_
 int skinny_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                     void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream, unsigned flags);
+int decode_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                    void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream, unsigned flags);
 int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream, int m_tile);

@@ -1,5 +1,6 @@
-// Row-count and shape dispatch between the three linear kernels: the mma.sync decode GEMV, the
-// tensor-memory split-K kernel for few rows of a large matrix, and the prefill GEMM.
+// Row-count and shape dispatch between the linear kernels: the mma.sync decode GEMV, the two tensor-memory
+// split-K kernels for few rows of a large matrix (unscaled codes up to 16 rows, exact fp16 weights up to 64),
+// and the prefill GEMM.
 #include "awq_common.cuh"
 
 namespace {
@@ -7,22 +8,16 @@ constexpr size_t kGemmStatusBytes = 256;  // leading slot of the shared workspac
 constexpr int kSkinnyMaxRows = 64;
 
 // Which kernel serves M rows of a K x N linear.
-//   rows <= 8:  the GEMV, or the split-K tensor-memory kernel once the packed weights reach 48 MiB (level
-//               with the GEMV at one row there).  The choice depends on (K, N) only, so a row's bits do not
-//               change with the number of rows decoded together, up to 8 rows.
-//   9..16:      the GEMV serves more than 8 rows as two CTAs of 8 rows per column group, which doubles its
-//               unpacking work (1.3 - 1.9 times the 8-row time), so the tensor-memory kernel takes over from
-//               16 MiB of packed weights (20 - 35 % faster there).  Like the reference's switch from its GEMV
-//               to its GEMM at 8 rows, this changes the order of additions between 8 and 9 rows.
-//   17..64:     the tensor-memory kernel where the GEMM would leave most SMs idle (at most 74 column tiles
-//               of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
-enum class Route { kGemv, kSkinny, kGemm };
+//   rows <= 16: the GEMV, or the tensor-memory decode kernel (unscaled codes, awq_decode.cu) once the packed
+//               weights reach 16 MiB.  The choice depends on (K, N) only, so a row's bits do not change with
+//               the number of rows decoded together.
+//   17..64:     the exact-weight tensor-memory kernel where the GEMM would leave most SMs idle (at most 74
+//               column tiles of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
+enum class Route { kGemv, kDecode, kSkinny, kGemm };
+constexpr long long kDecodeFromBytes = 16ll << 20;
 Route route(int M, int K, int N) {
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
-  if (M <= awq_b200_gemv_max_rows()) {
-    const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
-    return packed_bytes >= from_bytes ? Route::kSkinny : Route::kGemv;
-  }
+  if (M <= awq_b200_gemv_max_rows()) return packed_bytes >= kDecodeFromBytes ? Route::kDecode : Route::kGemv;
   if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
   return Route::kGemm;
 }
@@ -35,6 +30,7 @@ size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
   size_t need = 0;
   switch (route(M, K, N)) {
     case Route::kGemv: need = awq_b200_gemv_workspace_bytes(M, K, N); break;
+    case Route::kDecode: need = awq_b200_decode_workspace_bytes(M, K, N); break;
     case Route::kSkinny: need = awq_b200_skinny_workspace_bytes(M, K, N); break;
     case Route::kGemm: return awq_b200_gemm_workspace_bytes(M, K, N);   // status word first there too
   }
@@ -55,6 +51,8 @@ static int linear_run(const void* x, const void* packed, const void* scales, con
   switch (route(M, K, N)) {
     case Route::kGemv:
       return awq::gemv_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
+    case Route::kDecode:
+      return awq::decode_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kSkinny:
       return awq::skinny_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kGemm:

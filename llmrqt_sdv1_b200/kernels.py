@@ -194,6 +194,13 @@ def skinny(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
 
+def decode(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """Decode rows (1 <= M <= 16) on the tensor-memory path with unscaled codes (split-K over all SMs)."""
+    return _run(lib.awq_b200_decode, "awq_b200_decode", x, pw, bias,
+                lib.awq_b200_decode_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
+                (_lib.OVERLAP_PREVIOUS if overlap else 0,))
+
+
 def gemm(x, pw: PackedWeight, bias=None, out=None) -> torch.Tensor:
     """Prefill kernel (tcgen05), any M >= 1."""
     return _run(lib.awq_b200_gemm, "awq_b200_gemm", x, pw, bias,
@@ -371,7 +378,8 @@ def gemv_status(dev: torch.device | None = None) -> int:
     dev = dev or torch.device("cuda", torch.cuda.current_device())
     stream = torch.cuda.current_stream(dev).cuda_stream
     status = 0
-    for kind, off in (("awq_b200_gemv", 0), ("awq_b200_gemv_plan", 0), ("awq_b200_skinny", 0), ("awq_b200_linear", 256)):
+    for kind, off in (("awq_b200_gemv", 0), ("awq_b200_gemv_plan", 0), ("awq_b200_skinny", 0), ("awq_b200_decode", 0),
+                      ("awq_b200_linear", 256)):
         ws = _workspaces.get((dev.index, stream, kind))
         if ws is not None:
             status |= int(ws[off + 4095 * 4: off + 4096 * 4].view(torch.int32).item())

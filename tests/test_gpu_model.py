@@ -78,3 +78,72 @@ def test_fused_mlp_in_model():
     assert kernels.gemm_status() == 0 and kernels.gemv_status() == 0
     assert float((new_prefill - ref_prefill).abs().max() / ref_prefill.abs().max()) <= 1e-2
     assert float((new_decode - ref_decode).abs().max() / ref_decode.abs().max()) <= 1e-2
+
+
+@torch.no_grad()
+def test_fused_qkv_attention_in_model():
+    """`fuse_qkv_` replaces q/k/v by one linear of 4096 columns (the shape the reference's fuser builds):
+    same logits as the three separate linears up to the kernels' summation order."""
+    from llmrqt_sdv1_b200 import kernels
+    from llmrqt_sdv1_b200.hf_adapter import FusedQKVAttention, fuse_qkv_, set_impl_mode
+    torch.backends.cuda.enable_cudnn_sdp(False)
+    model = _build(layers=2)
+    set_impl_mode(model, "auto")
+    g = torch.Generator(device="cuda").manual_seed(2)
+    ids = torch.randint(0, 151936, (1, 64), device="cuda", generator=g)
+    ref_prefill = model(ids).logits.float()
+    step = model(ids[:, :63], use_cache=True)
+    ref_decode = model(ids[:, 63:64], past_key_values=step.past_key_values, use_cache=True).logits.float()
+    assert fuse_qkv_(model) == 2
+    attn = model.model.layers[0].self_attn
+    assert isinstance(attn, FusedQKVAttention) and attn.qkv_proj.out_features == 4096
+    new_prefill = model(ids).logits.float()
+    step = model(ids[:, :63], use_cache=True)
+    new_decode = model(ids[:, 63:64], past_key_values=step.past_key_values, use_cache=True).logits.float()
+    torch.cuda.synchronize()
+    assert kernels.gemm_status() == 0 and kernels.gemv_status() == 0
+    assert float((new_prefill - ref_prefill).abs().max() / ref_prefill.abs().max()) <= 1e-2
+    assert float((new_decode - ref_decode).abs().max() / ref_decode.abs().max()) <= 1e-2
+
+
+@torch.no_grad()
+def test_graphed_decoder_all_28_layers():
+    """Config 5 in full depth: the whole decode step captured in one CUDA graph gives the tokens of the same
+    step run eagerly, its logits stay within the compounded layer bound of the `dequant_matmul` model's, and
+    its greedy tokens agree with Hugging Face's `generate` wherever the reference's top-2 margin is clear."""
+    from llmrqt_sdv1_b200 import kernels
+    from llmrqt_sdv1_b200.decoder import GraphedDecoder
+    from llmrqt_sdv1_b200.hf_adapter import fuse_mlp_, fuse_qkv_, set_impl_mode
+    torch.backends.cuda.enable_cudnn_sdp(False)
+    model = _build(layers=28)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    prompt = torch.randint(0, 151936, (1, 128), device="cuda", generator=g)
+    set_impl_mode(model, "dequant_matmul")
+    seq_ref = model.generate(prompt, max_new_tokens=24, min_new_tokens=24, do_sample=False)
+    logits_ref = model(seq_ref).logits.float()
+    set_impl_mode(model, "auto")
+    assert fuse_qkv_(model) == 28 and fuse_mlp_(model) == 28
+
+    eager = GraphedDecoder(model, max_len=192, capture=False)
+    seq_eager = eager.generate(prompt, 24)
+    graphed = GraphedDecoder(model, max_len=192)
+    seq_graph = graphed.generate(prompt, 24)
+    seq_again = graphed.generate(prompt, 24)
+    torch.cuda.synchronize()
+    assert graphed.graph is not None
+    assert torch.equal(seq_graph, seq_eager), "graph replay and eager steps disagree"
+    assert torch.equal(seq_graph, seq_again), "two generations from the same prompt disagree"
+    assert kernels.gemm_status() == 0 and kernels.gemv_status() == 0
+
+    # 28 layers x 4 fused linears compound the per-layer 2e-3 bound
+    err = graphed.teacher_forced_error(seq_ref, logits_ref)
+    assert err <= 2e-2, err
+    # greedy tokens: equal to the reference's wherever its own top-2 margin exceeds twice the logit error,
+    # up to the first position where the sequences part (after that the inputs differ)
+    ref_new, got_new = seq_ref[0, 128:].tolist(), seq_graph[0, 128:].tolist()
+    top2 = logits_ref[0, 127:-1].topk(2, dim=-1).values
+    margin = (top2[:, 0] - top2[:, 1]) / logits_ref.abs().max()
+    for i, (a, b) in enumerate(zip(ref_new, got_new)):
+        if a != b:
+            assert float(margin[i]) <= 2 * err, f"token {i} differs although the reference margin is clear"
+            break
