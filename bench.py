@@ -972,11 +972,12 @@ def run_profile_case(args, torch):
     """Small, self-terminating cases for `ncu` captures (a few launches, a few hundred MB)."""
     from llmrqt_sdv1_b200 import kernels, quantize
     torch.cuda.set_device(0)
-    if args.profile_case.startswith("gemv") or args.profile_case.startswith("skinny"):
+    if args.profile_case.startswith(("gemv", "skinny", "decode")):
         # gemv / gemv16: 24 distinct 2048x12288 weights (13 MB each, 314 MB > L2), two passes
-        # gemv70b / skinny70b / skinny70b_m16: one 8192x57344 weight (235 MB > L2), three launches
-        M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else 1
-        fn = kernels.skinny if args.profile_case.startswith("skinny") else kernels.gemv
+        # gemv70b / skinny70b[_m16] / decode70b[_m4]: one 8192x57344 weight (235 MB > L2), three launches
+        M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else (4 if args.profile_case == "decode70b_m4" else 1)
+        fn = (kernels.skinny if args.profile_case.startswith("skinny") else
+              kernels.decode_i8 if args.profile_case.startswith("decode") else kernels.gemv)
         K, N, copies, passes = (8192, 57344, 1, 3) if "70b" in args.profile_case else (2048, 12288, 24, 2)
         qw, qz, sc = quantize.random_awq_tensors(K, N, GROUP, seed=1, device="cuda")
         base = kernels.make_packed(qw, qz, sc, GROUP)
@@ -1009,7 +1010,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp", "qwen3_e2e"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "gemm", "gemm_large", "gemm_m64"],
+    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "decode70b", "decode70b_m4",
+                             "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -22,8 +22,10 @@
  * nibble position (e >> 1) + 4 * (e & 1).  qzeros and scales are used as they
  * are on disk.
  *
- * Shape rules for every compute entry point: K % 128 == 0, N % 8 == 0,
- * G % 128 == 0 and K % G == 0; all pointers 16-byte aligned.
+ * Shape rules for every compute entry point: K % 128 == 0, N % 8 == 0, K % G == 0 and G a multiple of
+ * 128, or 32 / 64 for the entry points that build the exact fp16 weight per element (awq_b200_gemm*,
+ * awq_b200_skinny, awq_b200_dequant*, and awq_b200_linear*, which routes such groups to those two kernels);
+ * all pointers 16-byte aligned.
  */
 #ifndef AWQ_B200_H_
 #define AWQ_B200_H_
@@ -233,19 +235,21 @@ AWQ_B200_API int awq_b200_skinny(const void* x, const void* packed, const void* 
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
 
-/* Decode rows (1 <= M <= 16) of a large matrix on the tensor-memory path with the cheapest possible unpack:
- * same split-K stream of 256-column x 128-k units as awq_b200_skinny, but the nibbles go to tensor memory as
- * unscaled codes (1024 + q or 64 + q: five logic operations per packed word) and the kernel applies
- * s * (sum x*code - H - z * sum x) in fp32 once per unit when it reads the unit's accumulator back, H and
- * sum x coming from a warp that adds up the activation tile.  The weights are therefore multiplied
- * un-rounded, as in the reference's GEMV (LLMQRT/runtime_refact/csrc/awq/gemv.cu:138): results are within
- * the 2e-3 layer bound of the fp16-weight path, not bit-equal to awq_b200_skinny.  Deterministic; a row's bits
- * do not depend on M.  Same arguments, workspace rules and flags as awq_b200_skinny; replaces the same
+/* Decode rows (1 <= M <= 4) of a large matrix on the INTEGER tensor-core path (tcgen05.mma kind::i8): the packed
+ * words are only masked (word & 0xf0f0f0f0, word & 0x0f0f0f0f: one logic operation per word and nibble position)
+ * and multiplied as unsigned bytes with the activations in block-fixed-point form (per row and 128-k block:
+ * x ~ sx * t, t a 15-bit integer held as two signed-byte planes); all sums are exact int32 and the kernel applies
+ * s * sx * (sum - z * sum t) in fp32 once per 128-k unit.  Weights are applied un-rounded, as in the reference's
+ * GEMV (LLMQRT/runtime_refact/csrc/awq/gemv.cu:138); the activations carry a relative error below the fp16
+ * spacing of the largest activation of their block.  Results are within the 2e-3 layer bound of the fp16-weight
+ * path, not bit-equal to it.  Deterministic; a row's bits do not depend on M.  Same split-K stream of 256-column
+ * x 128-k units, arguments and flags as awq_b200_skinny; the workspace must hold
+ * awq_b200_decode_workspace_bytes(M, K, N) bytes, start zero-initialised and is left clean.  Replaces the same
  * reference calls as awq_b200_gemv. */
 AWQ_B200_API size_t awq_b200_decode_workspace_bytes(int M, int K, int N);
-AWQ_B200_API int awq_b200_decode(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
-                    const void* bias, void* y, int M, int K, int N, int group_size,
-                    void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
+AWQ_B200_API int awq_b200_decode_i8(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                       const void* bias, void* y, int M, int K, int N, int group_size,
+                       void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
 
 /* Tuning hook: awq_b200_gemm_wtm with the activation-row tile forced (64, 128, 192; 0 = by M). */
 AWQ_B200_API int awq_b200_gemm_wtm_tile(const void* x, const void* packed, const void* scales,
@@ -302,12 +306,15 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
-/* Picks the kernel from the row count and the shape: M <= 16 -> awq_b200_gemv, or awq_b200_decode
- * once the packed weights reach 16 MiB (a choice that depends on K and N only, so a row's bits do
- * not change with the number of rows decoded together); 17 <= M <= 64 -> awq_b200_skinny where the
- * GEMM would leave most SMs idle (N <= 18944 and K >= 4096); awq_b200_gemm otherwise.  Mirrors the
- * row-count switch in AWQLinearMMFunction.forward
- * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185). */
+/* Picks the kernel from the row count and the shape.  M <= 16 -> awq_b200_gemv, except for large weights:
+ * from 48 MiB of packed weights M <= 4 -> awq_b200_decode_i8 and 5 <= M <= 8 -> awq_b200_skinny, and from 16 MiB
+ * 9 <= M <= 16 -> awq_b200_skinny (beyond 8 rows the GEMV does its unpacking twice).  The thresholds depend on K
+ * and N only, so within a row-count class a row's bits do not change with the number of rows decoded together.
+ * 17 <= M <= 64 -> awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
+ * awq_b200_gemm otherwise.  Group sizes 32 and 64 always take awq_b200_skinny (M <= 64) or awq_b200_gemm.
+ * Mirrors the row-count switch in AWQLinearMMFunction.forward
+ * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), which also changes kernel
+ * (and with it the order of additions) between row counts. */
 AWQ_B200_API int awq_b200_linear(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream);
@@ -349,6 +356,28 @@ AWQ_B200_API int awq_b200_linear_fused(const void* x, const void* packed, const 
  * a gated epilogue expects.  Load-time utility. */
 AWQ_B200_API int awq_b200_interleave_columns(const int32_t* a, const int32_t* b, int32_t* out, int rows,
                                 int words_per_row, awq_b200_stream_t stream);
+
+/* ---- decode-time plumbing between the linears of a decoder layer -------------- */
+
+/* One token's fused qkv row [(H + 2 KV) * D] fp16 -> per-head RMSNorm of the q and k heads (q_weight / k_weight
+ * [D] fp16, both NULL for models without q/k norms), rotary embedding of q and k with row `*pos` of cos_tab /
+ * sin_tab [max_len, D] (the layout of Hugging Face's rotary module: both halves of a row hold the same D/2
+ * angles), q to q_out [H, D], k and v into row `*pos` of k_cache / v_cache [KV, max_len, D].  `pos` points to an
+ * int64 in DEVICE memory, so the launch is the same for every token (CUDA-graph friendly).  D is 64 or 128.
+ * Each fp16 step rounds where the reference's separate tensor operations round
+ * (LLMQRT/runtime_refact/nn_models/modules/nonlinear/attention.py:299-330: q_norm / k_norm, rope, cache
+ * update).  A position outside [0, max_len) writes nothing. */
+AWQ_B200_API int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                                const void* cos_tab, const void* sin_tab, const int64_t* pos, void* q_out,
+                                void* k_cache, void* v_cache, int H, int KV, int D, int max_len,
+                                awq_b200_stream_t stream);
+
+/* out [H * D] fp16 = softmax(scale * q . K[0..*pos]^T) . V[0..*pos] for one query token of H heads against a cache
+ * of KV heads (grouped-query attention, H % KV == 0); fp32 online softmax.  Stands in, at decode time, for the
+ * attention call of the reference's attention block (attention.py:331-380), which is outside the quantized-linear
+ * path; it exists so that a whole decode step is a fixed sequence of launches. */
+AWQ_B200_API int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
+                         void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -44,7 +44,7 @@ SIGNATURES = {
     "awq_b200_skinny_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_skinny": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_decode_workspace_bytes": (_Z, [_I, _I, _I]),
-    "awq_b200_decode": (_I, _COMPUTE + [C.c_uint]),
+    "awq_b200_decode_i8": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_peer_allreduce_flag_bytes": (_Z, []),
     "awq_b200_peer_allreduce": (_I, [_P, _P, _P, _P, _Z, _I, _I, _I, _P]),
     "awq_b200_peer_allreduce_push": (_I, [_P, _P, _P, _P, _P, _Z, _I, _Z, _I, _I, _P]),
@@ -53,6 +53,8 @@ SIGNATURES = {
     "awq_b200_linear": (_I, _COMPUTE),
     "awq_b200_linear_fused": (_I, _COMPUTE + [C.c_uint]),   # 5th argument: const awq_b200_epilogue*
     "awq_b200_interleave_columns": (_I, [_P, _P, _P, _I, _I, _P]),
+    "awq_b200_qk_norm_rope_cache": (_I, [_P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "awq_b200_attn_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P]),
 }
 
 

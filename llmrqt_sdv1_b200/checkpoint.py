@@ -83,15 +83,38 @@ def checkpoint_files(path: str) -> list[str]:
     return [path]
 
 
+def _assign(model: torch.nn.Module, name: str, tensor: torch.Tensor) -> None:
+    """Replace the parameter or buffer `name` of `model` by `tensor` (used for destinations on the meta device)."""
+    mod_name, _, leaf = name.rpartition(".")
+    mod = model.get_submodule(mod_name) if mod_name else model
+    if leaf in mod._parameters:
+        mod._parameters[leaf] = torch.nn.Parameter(tensor, requires_grad=False)
+    else:
+        mod._buffers[leaf] = tensor
+
+
 @torch.no_grad()
-def load_checkpoint(model: torch.nn.Module, path: str, strict: bool = True, prepare: bool = True) -> dict:
-    """Copy every checkpoint tensor that names a parameter or buffer of `model` into it (on the device it
-    already lives on; shapes and dtypes must match, except that floating tensors are cast to the
-    destination's dtype), then repack each `AWQLinear_GEMM` into the kernel layout.  Returns
-    {"loaded": [...], "missing": [...], "unexpected": [...]}; with `strict`, missing or unexpected names raise."""
+def load_checkpoint(model: torch.nn.Module, path: str, strict: bool = True, prepare: bool = True,
+                    device: torch.device | str | None = None, release_qweight: bool = False) -> dict:
+    """Copy every checkpoint tensor that names a parameter or buffer of `model` into it, then repack each
+    `AWQLinear_GEMM` into the kernel layout.  Shapes and dtypes must match, except that floating tensors are
+    cast to the destination's dtype.  A destination that lives on the meta device (a model built without
+    storage, as the reference builds it under `init_empty_weights`, LLMQRT/runtime_refact/core/base.py:132-151)
+    is created on `device`; every other destination is filled where it already lives.
+
+    `release_qweight=True` repacks every quantized linear as soon as its three tensors are in and gives its
+    on-disk `qweight` back at once, so the device never holds more than one layer's int4 weights twice: after
+    the load it holds 1.0 x the packed bytes plus scales and zeros (`state_dict()` still returns the on-disk
+    tensors, rebuilt on demand by the inverse repack).
+
+    Returns {"loaded": [...], "missing": [...], "unexpected": [...]}; with `strict`, missing or unexpected
+    names raise."""
     import warnings
     dest = dict(model.named_parameters())
     dest.update(dict(model.named_buffers()))
+    target = torch.device(device) if device is not None else None
+    awq_modules = {n: m for n, m in model.named_modules() if isinstance(m, AWQLinear_GEMM)}
+    pending = {n: {"qweight", "qzeros", "scales"} for n in awq_modules} if release_qweight else {}
     loaded, unexpected = [], []
     with warnings.catch_warnings():
         warnings.filterwarnings("ignore", message=".*not writable.*")
@@ -105,8 +128,21 @@ def load_checkpoint(model: torch.nn.Module, path: str, strict: bool = True, prep
                     raise ValueError(f"{name}: checkpoint shape {tuple(src.shape)} != module shape {tuple(d.shape)}")
                 if d.dtype != src.dtype and not (d.dtype.is_floating_point and src.dtype.is_floating_point):
                     raise ValueError(f"{name}: checkpoint dtype {src.dtype} cannot fill a {d.dtype} tensor")
-                d.copy_(src)          # pageable host memory -> device: one staged copy, cast on the device side
+                if d.device.type == "meta":
+                    if target is None:
+                        raise ValueError(f"{name} lives on the meta device: pass device= to say where to create it")
+                    _assign(model, name, src.to(device=target, dtype=d.dtype))
+                else:
+                    d.copy_(src)      # pageable host memory -> device: one staged copy, cast on the device side
                 loaded.append(name)
+                mod_name, _, leaf = name.rpartition(".")
+                todo = pending.get(mod_name)
+                if todo is not None:
+                    todo.discard(leaf)
+                    m = awq_modules[mod_name]
+                    if not todo and m.qweight.is_cuda:
+                        m.release_qweight()          # repack now, keep the kernel layout only
+                        del pending[mod_name]
     missing = sorted(set(dest) - set(loaded))
     if strict and (missing or unexpected):
         raise KeyError(f"checkpoint does not match the model: missing {missing[:8]}{'...' if len(missing) > 8 else ''}, "

@@ -30,10 +30,13 @@ inline int cuda_fail(cudaError_t e) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Shape rules shared by every compute entry point.
-inline int check_shape(int K, int N, int group_size) {
+// Shape rules shared by every compute entry point.  Group sizes: any multiple of 128, and 32 or 64 for the
+// kernels that build the exact fp16 weight per element (`small_groups`: the tensor-memory GEMMs and the
+// exact-weight split-K kernel); the decode kernels that rescale once per 128-k block need whole blocks.
+inline int check_shape(int K, int N, int group_size, bool small_groups = false) {
   if (K <= 0 || N <= 0 || K % kBlockK != 0 || N % 8 != 0) return AWQ_B200_ERR_SHAPE;
-  if (group_size <= 0 || group_size % kBlockK != 0) return AWQ_B200_ERR_GROUP;
+  const bool small = small_groups && (group_size == 32 || group_size == 64);
+  if (group_size <= 0 || (group_size % kBlockK != 0 && !small)) return AWQ_B200_ERR_GROUP;
   if (K % group_size != 0) return AWQ_B200_ERR_SHAPE;
   return AWQ_B200_OK;
 }
@@ -65,9 +68,9 @@ int gemv_run(const void* x, const void* packed, const void* scales, const int32_
 int skinny_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                     void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream, unsigned flags);
-int decode_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
-                    void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
-                    cudaStream_t stream, unsigned flags);
+int decode_i8_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream, unsigned flags);
 int wtm_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream, int m_tile);

@@ -1,0 +1,702 @@
+// Decode path for 1 <= M <= 4 rows of a large matrix on the integer tensor-core path (tcgen05.mma kind::i8):
+// the packed nibbles reach the tensor core with ONE logic operation per packed word and nibble position, no
+// conversion to floating point at all.
+//
+// A byte of the packed weights holds two nibbles of one column, q_hi (bits 4..7) and q_lo (bits 0..3), for two
+// different k of the same 128-k block.  Masking gives two unsigned 8-bit operands,
+//     hi = word & 0xf0f0f0f0   (bytes 16 * q_hi)          lo = word & 0x0f0f0f0f   (bytes q_lo),
+// which go to tensor memory as they are (lane = output column, one byte per k slot).  The activations of a
+// block are turned into block-fixed-point integers once per unit by four helper warps:
+//     x[m, k] ~ sx[m] * t[m, k],   t = rint(x / sx) in [-16256, 16256],   sx = max_k |x[m, k]| / 16256
+//     t = 128 * p1 + p2,  p1 in [-127, 127], p2 in [-64, 63]                  (two signed 8-bit planes)
+// and laid out as the B operand: plane 1 of row m in row m of the tile, plane 2 in row MR + m, the k slots in
+// the order of the bytes they meet (one tile for the k of the high nibbles, one for the low nibbles).  Then
+//     D_hi[n, .] = sum_slots hi * Xhi      D_lo[n, .] = sum_slots lo * Xlo            (int32, exact)
+//     y[m, n] += s[n] * sx[m] * ( (128 * D_hi[m] + D_hi[MR + m]) / 16 + 128 * D_lo[m] + D_lo[MR + m] - z[n] * T[m] )
+// with T[m] = sum_k t[m, k]; everything inside the parenthesis is exact integer arithmetic, so the only
+// roundings are the quantisation of x (15 bits below the largest activation of the row's 128-k block, i.e.
+// finer than the fp16 spacing of that activation) and one fp32 multiply-add per unit.  Like the reference's
+// GEMV (LLMQRT/runtime_refact/csrc/awq/gemv.cu:138) the weights are applied un-rounded, s * (q - z).
+//
+// Work distribution is the split-K stream of the exact-weight kernel (awq_skinny.cu): unit = 256 columns x 128 k
+// (16 KiB of packed weights), CTA b owns units [b*U/G, (b+1)*U/G) of the flattened (column tile, k block)
+// sequence, one CTA per SM, one copy pipeline that never drains; a column tile that straddles CTAs is finished
+// through fp32 partials added in CTA (= k) order by the last contributor.  Warps 0 / 18 copy producers, 1 / 19 MMA issuers (one per 128-column half), 2..17 four groups
+// of four warps that mask the words into tensor memory and fold the finished accumulators, 20..23 activation
+// helpers (every fourth unit each).  TMEM columns: [0, 256) four accumulator windows of 64 (2 halves x {hi, lo}
+// x 16), [256, 512) four operand slots of 64 (2 halves x {hi, lo} x 16 columns = 64 k slots).  Per unit and half
+// the tensor core runs 4 instructions (2 k steps of 32 slots x {hi, lo}).  Deterministic; a row's bits do not
+// depend on M.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+#include "awq_gemv_common.cuh"
+#include "awq_tcgen05.cuh"
+
+namespace awq {
+
+constexpr int kD8UnpackWarps = 16;
+constexpr int kD8UnpackThreads = kD8UnpackWarps * 32;
+constexpr int kD8Groups = 4;
+constexpr int kD8HelperWarps = 4;
+constexpr int kD8Threads = 64 + kD8UnpackThreads + 64 + kD8HelperWarps * 32;   // 24 warps
+constexpr int kD8Producer2Warp = 18, kD8Issuer2Warp = 19, kD8HelperWarp0 = 20;
+constexpr int kD8BN = 256;
+constexpr int kD8RawBytes = kD8BN * 64;            // [256 columns][64 bytes], 64-byte swizzle
+constexpr int kD8XTileBytes = 16 * 64;             // B operand tile: 16 rows x 64 k slots, 64-byte swizzle
+constexpr int kD8RawOff = 0;
+constexpr int kD8SzOff = kD8RawOff + kD8RawBytes;  // 256 fp16 scales, then 32 qzeros words
+constexpr int kD8XhiOff = kD8SzOff + 1024;
+constexpr int kD8XloOff = kD8XhiOff + kD8XTileBytes;
+constexpr int kD8StageBytes = kD8XloOff + kD8XTileBytes;   // 19 KiB + 512... see static_assert
+constexpr int kD8Stages = 8;                       // measured: 10 stages are no faster (the copy pipeline is not the limit)
+constexpr int kD8Windows = 4;
+constexpr int kD8ABase = kD8Windows * 64;          // 256
+constexpr int kD8AStages = 4;
+constexpr int kD8MetaSlots = 16;                   // ring of per-unit (sx, T) rows; must be >= kD8Stages + 2
+constexpr int kD8MaxRows = 4;                      // beyond that the per-row fold costs more than the exact-weight kernel's unpack
+constexpr int kD8Range = 16256;                    // 127 * 128: largest |t|
+static_assert(kD8StageBytes % 1024 == 0, "every stage starts on a swizzle-atom boundary");
+static_assert(kD8ABase + kD8AStages * 64 == 512, "tensor memory is used in full");
+static_assert(kD8MetaSlots >= kD8Stages + 2 && kD8Stages % 2 == 0, "see the meta ring / two producers");
+
+template <int MR> struct D8Cfg {
+  static_assert(MR == 1 || MR == 2 || MR == 4, "rows per call class");
+  static constexpr int kCombBytes = (kD8Groups - 1) * kD8BN * MR * 4;
+  static constexpr int kMetaBytes = kD8MetaSlots * MR * 8;
+  static constexpr int kCombOff = kD8Stages * kD8StageBytes;
+  static constexpr int kMetaOff = kCombOff + kCombBytes;
+  static constexpr int kBarOff = kMetaOff + ((kMetaBytes + 15) / 16) * 16;
+  static constexpr int kNumBars = 3 * kD8Stages + 2 * kD8AStages + 4 * kD8Windows + kD8MetaSlots;
+  static constexpr int kSmemBytes = kBarOff + kNumBars * 8 + 1024 /*align*/;
+};
+
+struct D8Params {
+  const uint16_t* x;
+  const uint16_t* scales;
+  const uint32_t* qzeros;
+  Epilogue epi;
+  uint16_t* y;
+  float* partial;
+  unsigned* counters;
+  unsigned* status;
+  int M, K, N;
+  int group_size;
+  int ntiles;
+  int nblk;
+  long long units;
+};
+
+__device__ __forceinline__ void d8_unpack_warps_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kD8UnpackThreads) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand of 8-bit elements, 64-byte rows, 64-byte swizzle, 8-row
+// groups 512 bytes apart.
+__device__ __forceinline__ uint64_t make_sw64_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(512 >> 4) << 32;                     // stride byte offset: next 8-row group
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(4) << 61;                            // SWIZZLE_64B
+  return d;
+}
+
+// Instruction descriptor for kind::i8: D int32, A unsigned 8-bit, B signed 8-bit, both K-major.
+__host__ __device__ constexpr uint32_t make_i8_idesc(int m, int n) {
+  return (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// The four integer MMAs of one unit and half - {hi, lo} x two k steps of 32 slots - into fresh accumulators,
+// then three commits, under one election.  a_hi / a_lo: operand columns in tensor memory (8 columns per step);
+// b_hi / b_lo: descriptors of the activation tiles (a step advances 32 bytes = 2 units of 16 bytes).
+__device__ __forceinline__ void tcgen05_mma_i8_unit_commit3_warp(uint32_t d_hi, uint32_t d_lo, uint32_t a_hi, uint32_t a_lo,
+                                                                 uint64_t b_hi, uint64_t b_lo, uint32_t idesc,
+                                                                 uint32_t bar0, uint32_t bar1, uint32_t bar2) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [%3], %5, %6, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
+      "add.u32 a, %3, 8;\n\t  mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [a], d, %6, p;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n\t}"
+      ::"r"(d_hi), "r"(d_lo), "r"(a_hi), "r"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(bar0), "r"(bar1), "r"(bar2)
+      : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void d8_tmem_ld(uint32_t taddr, uint32_t (&v)[N]) {
+  static_assert(N == 2 || N == 4 || N == 8 || N == 16, "columns per load");
+  if constexpr (N == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "r"(taddr) : "memory");
+  } else if constexpr (N == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+  } else if constexpr (N == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr) : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+  }
+}
+
+template <int MR>
+__global__ void __launch_bounds__(kD8Threads, 1)
+decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
+  using Cfg = D8Cfg<MR>;
+  constexpr int NT = kD8Stages, NA = kD8AStages, NW = kD8Windows, NS = kD8MetaSlots;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ int s_last;
+  __shared__ uint32_t s_tmem_base;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  auto stage_addr = [&](int t) { return base + t * kD8StageBytes; };
+  float* comb = reinterpret_cast<float*>(base_ptr + Cfg::kCombOff);          // [3][MR][256]
+  int2* meta = reinterpret_cast<int2*>(base_ptr + Cfg::kMetaOff);            // [NS][MR]: (bits of sx, T)
+  const uint32_t bar_base = base + Cfg::kBarOff;
+  auto bar_full_tma = [&](int t) { return bar_base + 8u * t; };             // weights, scales, zeros landed
+  auto bar_empty = [&](int t) { return bar_base + 8u * (NT + t); };         // 4 unpack warps + 2 MMA commits
+  auto bar_xq_full = [&](int t) { return bar_base + 8u * (2 * NT + t); };   // activation tiles written
+  auto bar_a_full = [&](int a) { return bar_base + 8u * (3 * NT + a); };
+  auto bar_a_empty = [&](int a) { return bar_base + 8u * (3 * NT + NA + a); };
+  auto bar_win_full = [&](int h, int w) { return bar_base + 8u * (3 * NT + 2 * NA + h * NW + w); };
+  auto bar_win_empty = [&](int h, int w) { return bar_base + 8u * (3 * NT + 2 * NA + 2 * NW + h * NW + w); };
+  auto bar_meta_full = [&](int s) { return bar_base + 8u * (3 * NT + 2 * NA + 4 * NW + s); };
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int t = 0; t < NT; ++t) {
+      mbar_init(bar_full_tma(t), 1);
+      mbar_init(bar_empty(t), kD8UnpackWarps / kD8Groups + 2);
+      mbar_init(bar_xq_full(t), 1);
+    }
+    for (int a = 0; a < NA; ++a) {
+      mbar_init(bar_a_full(a), kD8UnpackWarps / kD8Groups);
+      mbar_init(bar_a_empty(a), 2);
+    }
+    for (int h = 0; h < 2; ++h) {
+      for (int w = 0; w < NW; ++w) {
+        mbar_init(bar_win_full(h, w), 1);
+        mbar_init(bar_win_empty(h, w), 4);
+      }
+    }
+    for (int s = 0; s < NS; ++s) mbar_init(bar_meta_full(s), 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  const long long U = p.units, G = gridDim.x;
+  const long long u0 = stream_first_unit(blockIdx.x, U, G), u1 = stream_first_unit(blockIdx.x + 1, U, G);
+  const int my_units = static_cast<int>(u1 - u0);
+  const int nblk = p.nblk;
+  constexpr uint32_t kIdesc = make_i8_idesc(128, 16);
+  const bool sz_by_copy = (p.N & 31) == 0;
+
+  if (warp == 0 || warp == kD8Producer2Warp) {
+    // ------------------------------ copy producers ----------------------------
+    // Weights, scales and zero words are constant data: the first ring fill starts before the wait on the
+    // previous kernel of the stream.
+    const int my_parity = warp == 0 ? 0 : 1;
+    if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    int tile, kb;
+    {
+      const long long u = u0 + my_parity;
+      tile = static_cast<int>(u / nblk);
+      kb = static_cast<int>(u - static_cast<long long>(tile) * nblk);
+    }
+    const int group_blocks = p.group_size / kBlockK;
+    auto advance = [&]() {
+      kb += 2;
+      while (kb >= nblk) { kb -= nblk; ++tile; }
+    };
+    auto issue = [&](int gs, int tile_, int kb_) {
+      const int n0 = tile_ * kD8BN;
+      const int ncols = min(kD8BN, p.N - n0);
+      const int t = gs % NT;
+      const uint32_t bar = bar_full_tma(t);
+      const uint32_t dst = stage_addr(t);
+      if (lane == 0) mbar_expect_tx(bar, kD8RawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0));
+      if (lane == 2) tma_load_3d(dst + kD8RawOff, &map_w, 0, n0, kb_, bar);
+      if (sz_by_copy && (lane == 3 || lane == 4)) {
+        const int grp = group_blocks == 1 ? kb_ : kb_ / group_blocks;
+        if (lane == 3) bulk_load(dst + kD8SzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar);
+        else bulk_load(dst + kD8SzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3), ncols / 2, bar);
+      }
+    };
+    int next = my_parity;
+    for (; next < NT && next < my_units; next += 2) { issue(next, tile, kb); advance(); }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    for (; next < my_units; next += 2) {
+      if (!mbar_wait(bar_empty(next % NT), static_cast<uint32_t>(next / NT - 1) & 1u, abort_flag, 1)) break;
+      issue(next, tile, kb);
+      advance();
+    }
+    const int issued_end = next < my_units ? next : my_units;
+    for (int gs = my_parity; gs < issued_end; gs += 2)
+      if (gs + NT >= issued_end) mbar_wait_timed(bar_full_tma(gs % NT), static_cast<uint32_t>(gs / NT) & 1u);
+    __syncwarp();
+  } else if (warp == 1 || warp == kD8Issuer2Warp) {
+    // ------------------------------ MMA issuers --------------------------------
+    const int h = warp == 1 ? 0 : 1;
+    for (int gs = 0; gs < my_units; ++gs) {
+      const int t = gs % NT, a = gs % NA, w = gs % NW;
+      if (!mbar_wait(bar_win_empty(h, w), (static_cast<uint32_t>(gs / NW) & 1u) ^ 1u, abort_flag, 2)) break;
+      if (!mbar_wait(bar_xq_full(t), static_cast<uint32_t>(gs / NT) & 1u, abort_flag, 3)) break;
+      if (!mbar_wait(bar_a_full(a), static_cast<uint32_t>(gs / NA) & 1u, abort_flag, 4)) break;
+      tcgen05_fence_after();
+      const uint32_t win = tmem_base + static_cast<uint32_t>(w * 64 + h * 32);
+      const uint32_t opd = tmem_base + static_cast<uint32_t>(kD8ABase + a * 64 + h * 32);
+      tcgen05_mma_i8_unit_commit3_warp(win, win + 16, opd, opd + 16, make_sw64_desc(stage_addr(t) + kD8XhiOff),
+                                       make_sw64_desc(stage_addr(t) + kD8XloOff), kIdesc, bar_empty(t), bar_a_empty(a),
+                                       bar_win_full(h, w));
+    }
+    __syncwarp();
+  } else if (warp >= kD8HelperWarp0) {
+    // ------------------------------ activation helpers -------------------------
+    // Unit by unit (every fourth unit per warp): the M rows of this unit's 128 activations -> two planes of
+    // signed bytes in the order of the weight bytes they multiply.  Word j of a column holds k = 8j + e at
+    // nibble (e >> 1) + 4 (e & 1), so byte b of that word carries k = 8j + {0, 4, 1, 5}[b] in its low nibble and
+    // k = 8j + {2, 6, 3, 7}[b] in its high nibble.  Lane = (row parity, word j): 16 lanes share a row.
+    asm volatile("griddepcontrol.wait;" ::: "memory");        // the activations belong to the previous kernel until here
+    const int jw = lane & 15, rsel = lane >> 4;
+    constexpr int RP = (MR + 1) / 2;                          // row pairs
+    auto load_x = [&](int gs, uint4 (&xv)[RP]) {
+      const long long u = u0 + gs;
+      const int tile = static_cast<int>(u / nblk);
+      const int kb = static_cast<int>(u - static_cast<long long>(tile) * nblk);
+#pragma unroll
+      for (int r = 0; r < RP; ++r) {
+        const int m = 2 * r + rsel;
+        xv[r] = make_uint4(0u, 0u, 0u, 0u);
+        if (m < p.M && gs < my_units)
+          xv[r] = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.K + kb * kBlockK + jw * 8));
+      }
+    };
+    uint4 xnext[RP];
+    const int first = warp - kD8HelperWarp0;
+    load_x(first, xnext);
+    for (int gs = first; gs < my_units; gs += kD8HelperWarps) {
+      const int t = gs % NT, s = gs % NS;
+      uint4 xv[RP];
+#pragma unroll
+      for (int r = 0; r < RP; ++r) xv[r] = xnext[r];
+      load_x(gs + kD8HelperWarps, xnext);                     // the next unit's rows travel while this one is processed
+      if (gs >= NT && !mbar_wait(bar_empty(t), static_cast<uint32_t>(gs / NT - 1) & 1u, abort_flag, 8)) break;
+      unsigned char* st = base_ptr + t * kD8StageBytes;
+#pragma unroll
+      for (int r = 0; r < RP; ++r) {
+        const int m = 2 * r + rsel;
+        float f[8];
+        {
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].y));
+          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].z));
+          const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].w));
+          f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y; f[4] = f2.x; f[5] = f2.y; f[6] = f3.x; f[7] = f3.y;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        // Inf / NaN activations have no integer image: the row's scale becomes 0 * inf = NaN and so does its output.
+        const float sx = amax * (1.0f / kD8Range);
+        const float inv = amax > 0.f ? static_cast<float>(kD8Range) / amax : 0.f;
+        int tq[8], tsum = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          int v = __float2int_rn(f[e] * inv);
+          v = max(-kD8Range, min(kD8Range, v));
+          tq[e] = v;
+          tsum += v;
+        }
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, off);
+        // planes: t = 128 * p1 + p2
+        uint32_t hi1 = 0u, hi2 = 0u, lo1 = 0u, lo2 = 0u;
+        constexpr int kLoK[4] = {0, 4, 1, 5}, kHiK[4] = {2, 6, 3, 7};
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int th = tq[kHiK[b]], tl = tq[kLoK[b]];
+          const int h1 = (th + 64) >> 7, l1 = (tl + 64) >> 7;
+          hi1 |= static_cast<uint32_t>(h1 & 0xff) << (8 * b);
+          hi2 |= static_cast<uint32_t>((th - (h1 << 7)) & 0xff) << (8 * b);
+          lo1 |= static_cast<uint32_t>(l1 & 0xff) << (8 * b);
+          lo2 |= static_cast<uint32_t>((tl - (l1 << 7)) & 0xff) << (8 * b);
+        }
+        if (m < MR) {
+          // tile row r: 64 bytes, 16-byte chunk c at chunk position c ^ ((r >> 1) & 3)
+          const int r1 = m, r2 = MR + m;
+          const uint32_t o1 = static_cast<uint32_t>(r1 * 64 + (((jw >> 2) ^ ((r1 >> 1) & 3)) << 4) + (jw & 3) * 4);
+          const uint32_t o2 = static_cast<uint32_t>(r2 * 64 + (((jw >> 2) ^ ((r2 >> 1) & 3)) << 4) + (jw & 3) * 4);
+          *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o1) = hi1;
+          *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o2) = hi2;
+          *reinterpret_cast<uint32_t*>(st + kD8XloOff + o1) = lo1;
+          *reinterpret_cast<uint32_t*>(st + kD8XloOff + o2) = lo2;
+          if (jw == 0) meta[s * MR + m] = make_int2(__float_as_int(sx), tsum);
+        }
+      }
+      fence_proxy_async();            // the tiles are read by the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar_meta_full(s));
+        mbar_arrive(bar_xq_full(t));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------- mask into tensor memory, then fold accumulators ---------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // y and the workspace belong to the previous kernel until here
+    const int id = tid - 64;                  // 0..511
+    const int dq_warp = id >> 5;              // 0..15
+    const int lane_q = warp & 3;              // TMEM lane quarter this warp may touch
+    const int grp = dq_warp >> 2;             // 0..3; four consecutive warps cover the four quarters
+    const int cl0 = lane_q * 32 + lane;       // column within a 128-column half
+    const uint32_t lane_addr = static_cast<uint32_t>(lane_q * 32) << 16;
+    const int zcols = p.N >> 3;
+    bool ok = true;
+    int gs = 0;
+    while (gs < my_units) {
+      const long long u = u0 + gs;
+      const int tile = static_cast<int>(u / nblk);
+      const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * nblk);
+      const int seg_units = min(nblk - kb0, my_units - gs);
+      const int n0 = tile * kD8BN;
+      int ncol[2];
+      bool nval[2];
+      uint32_t zsh[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        ncol[h] = n0 + h * 128 + cl0;
+        nval[h] = ncol[h] < p.N;
+        zsh[h] = awq_slot_shift(static_cast<uint32_t>(ncol[h] & 7));
+      }
+      uint32_t sc[2] = {0u, 0u}, zw[2] = {0u, 0u};
+      int sz_group = -1;
+      float acc[2][MR];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) acc[h][m] = 0.f;
+      int pend = -1;
+      float pend_s[2] = {0.f, 0.f};
+      int pend_z[2] = {0, 0};
+
+      // acc[h][m] += s * sx[m] * ((128 Dhi[m] + Dhi[MR + m]) / 16 + 128 Dlo[m] + Dlo[MR + m] - z T[m])
+      auto fold_pending = [&]() {
+        if (pend < 0) return;
+        const int w = pend % NW, s = pend % NS;
+        if (ok && !mbar_wait(bar_meta_full(s), static_cast<uint32_t>(pend / NS) & 1u, abort_flag, 9)) ok = false;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (ok && !mbar_wait(bar_win_full(h, w), static_cast<uint32_t>(pend / NW) & 1u, abort_flag, 6)) ok = false;
+          if (!ok) continue;
+          tcgen05_fence_after();
+          uint32_t vh[2 * MR], vl[2 * MR];
+          const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * 64 + h * 32);
+          d8_tmem_ld<2 * MR>(win, vh);
+          d8_tmem_ld<2 * MR>(win + 16, vl);
+          tcgen05_wait_ld();
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_win_empty(h, w));
+#pragma unroll
+          for (int m = 0; m < MR; ++m) {
+            const int2 mt = meta[s * MR + m];                  // same address in every lane: a broadcast
+            const int dhi = (static_cast<int>(vh[m]) << 7) + static_cast<int>(vh[MR + m]);    // a multiple of 16
+            const int dlo = (static_cast<int>(vl[m]) << 7) + static_cast<int>(vl[MR + m]);
+            const int val = (dhi >> 4) + dlo - pend_z[h] * mt.y;
+            acc[h][m] = fmaf(pend_s[h] * __int_as_float(mt.x), static_cast<float>(val), acc[h][m]);
+          }
+        }
+        pend = -1;
+      };
+
+      for (int j = 0; j < seg_units; ++j, ++gs) {
+        if ((gs & (kD8Groups - 1)) != grp) continue;             // another group's unit
+        const int t = gs % NT, a = gs % NA;
+        const uint32_t ph = static_cast<uint32_t>(gs / NT) & 1u, pha = static_cast<uint32_t>(gs / NA) & 1u;
+        fold_pending();                                          // this group's previous unit, four units back
+        if (!sz_by_copy) {
+          const int qgrp = ((kb0 + j) * kBlockK) / p.group_size;
+          if (qgrp != sz_group) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              sc[h] = nval[h] ? __ldg(p.scales + static_cast<size_t>(qgrp) * p.N + ncol[h]) : 0u;
+              zw[h] = nval[h] ? __ldg(p.qzeros + static_cast<size_t>(qgrp) * zcols + (ncol[h] >> 3)) : 0u;
+            }
+            sz_group = qgrp;
+          }
+        }
+        if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
+        if (!ok) continue;
+        const unsigned char* stage = base_ptr + t * kD8StageBytes;
+        if (sz_by_copy) {
+          // Columns beyond N read stale shared memory here; their lanes of the product are never stored.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            sc[h] = reinterpret_cast<const uint16_t*>(stage + kD8SzOff)[h * 128 + cl0];
+            zw[h] = reinterpret_cast<const uint32_t*>(stage + kD8SzOff + 512)[(h * 128 + cl0) >> 3];
+          }
+        }
+        if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) {
+          ok = false;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_empty(t));
+          continue;
+        }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int cl = h * 128 + cl0;
+          uint4 r[4];
+          const uint32_t swz = static_cast<uint32_t>((cl >> 1) & 3);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            r[c] = *reinterpret_cast<const uint4*>(stage + kD8RawOff + cl * 64 + ((static_cast<uint32_t>(c) ^ swz) << 4));
+          if (h == 1) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(t));            // the stage's packed weights are in registers
+          }
+          const uint32_t a_addr = tmem_base + lane_addr + static_cast<uint32_t>(kD8ABase + a * 64 + h * 32);
+          uint32_t o[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            o[4 * c + 0] = r[c].x & 0xf0f0f0f0u; o[4 * c + 1] = r[c].y & 0xf0f0f0f0u;
+            o[4 * c + 2] = r[c].z & 0xf0f0f0f0u; o[4 * c + 3] = r[c].w & 0xf0f0f0f0u;
+          }
+          tcgen05_st_32x32b_x16(a_addr, o);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            o[4 * c + 0] = r[c].x & 0x0f0f0f0fu; o[4 * c + 1] = r[c].y & 0x0f0f0f0fu;
+            o[4 * c + 2] = r[c].z & 0x0f0f0f0fu; o[4 * c + 3] = r[c].w & 0x0f0f0f0fu;
+          }
+          tcgen05_st_32x32b_x16(a_addr + 16u, o);
+        }
+        tcgen05_wait_st();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_a_full(a));
+        pend = gs;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          pend_s[h] = __half2float(__ushort_as_half(static_cast<unsigned short>(sc[h])));
+          pend_z[h] = static_cast<int>((zw[h] >> zsh[h]) & 0xFu);
+        }
+      }
+      fold_pending();
+
+      // ------------------------------ segment epilogue ------------------------
+      d8_unpack_warps_sync();
+      if (grp != 0) {
+        float* cb = comb + (grp - 1) * (MR * kD8BN);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int m = 0; m < MR; ++m) cb[m * kD8BN + h * 128 + cl0] = acc[h][m];
+      }
+      d8_unpack_warps_sync();
+      const long long tile_u0 = static_cast<long long>(tile) * nblk;
+      const int c_first = stream_cta_of(tile_u0, U, G);
+      const int c_last = stream_cta_of(tile_u0 + nblk - 1, U, G);
+      const int nc = c_last - c_first + 1;
+      const int slot = static_cast<int>(blockIdx.x) - c_first;
+      const bool direct = (nc == 1);
+      if (grp == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int m = 0; m < MR; ++m) {
+            if (m < p.M) {                                 // warp-uniform
+              const float* cb = comb + m * kD8BN + h * 128 + cl0;
+              const float val = ((acc[h][m] + cb[0]) + cb[MR * kD8BN]) + cb[2 * MR * kD8BN];
+              if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, ncol[h], val, nval[h]);
+              else if (nval[h]) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + ncol[h], val);
+            }
+          }
+        }
+      }
+      if (!direct) {
+        __threadfence();
+        d8_unpack_warps_sync();
+        if (id == 0) {
+          const unsigned prev = atomicAdd(&p.counters[tile], 1u);
+          const int last = (prev == static_cast<unsigned>(nc - 1));
+          if (last) p.counters[tile] = 0u;   // every contributor has arrived: leave the counter clean
+          s_last = last;
+        }
+        d8_unpack_warps_sync();
+        if (s_last) {
+          __threadfence();
+          const int ncols = min(kD8BN, p.N - n0);
+          const int pairs = ncols >> 1;
+          const size_t slot_stride = static_cast<size_t>(p.M) * p.N;
+          for (int i = id; i < p.M * pairs; i += kD8UnpackThreads) {
+            const int row = i / pairs;
+            const int col = n0 + 2 * (i - row * pairs);
+            const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
+            float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
+            for (int s = 1; s < nc; ++s) {
+              const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * slot_stride));
+              sum.x += v.x;
+              sum.y += v.y;
+            }
+            epilogue_store_pair(p.y, p.epi, row, p.N, col, sum.x, sum.y);
+          }
+        }
+        d8_unpack_warps_sync();   // s_last is rewritten by the next straddling segment
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, 0x400u | static_cast<unsigned>(s_abort));
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+// Largest number of CTAs that share one column tile (= partial slots needed).
+static int decode_slots(int K, int N, int sm_count) {
+  const int nblk = K / kBlockK, ntiles = (N + kD8BN - 1) / kD8BN;
+  const long long U = static_cast<long long>(ntiles) * nblk;
+  const long long G = U < sm_count ? U : sm_count;
+  int worst = 1;
+  for (int t = 0; t < ntiles; ++t) {
+    const long long a = static_cast<long long>(t) * nblk;
+    const int nc = stream_cta_of(a + nblk - 1, U, G) - stream_cta_of(a, U, G) + 1;
+    if (nc > worst) worst = nc;
+  }
+  return worst;
+}
+
+size_t decode_workspace_bytes(int M, int K, int N, int sm_count) {
+  if (M < 1 || K < kBlockK || N < 8) return 0;
+  const int slots = decode_slots(K, N, sm_count);
+  return kGemvMaxCounters * sizeof(unsigned) + (slots > 1 ? static_cast<size_t>(slots) * M * N * sizeof(float) : 0);
+}
+
+template <int MR>
+static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTiledFn encode, cudaStream_t stream,
+                            bool overlap_previous, int max_smem_optin) {
+  using Cfg = D8Cfg<MR>;
+  if (Cfg::kSmemBytes > max_smem_optin) return AWQ_B200_ERR_TOO_LARGE;
+  CUtensorMap mw;
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(p.N), static_cast<cuuint64_t>(p.K / kBlockK)};
+    const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(p.N) * 64};
+    const cuuint32_t box[3] = {64, kD8BN, 1};
+    const CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_64B;
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(packed), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  }
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kD8Threads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (overlap_previous) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_i8_kernel<MR>, mw, p));
+  return AWQ_B200_OK;
+}
+
+int decode_i8_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream, unsigned flags) {
+  if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
+  if (int st = check_shape(K, N, group_size)) return st;
+  if (M < 1 || M > kD8MaxRows) return AWQ_B200_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
+    return AWQ_B200_ERR_ALIGN;
+  if (int st = check_epilogue(epi, N)) return st;
+  DeviceInfo di;
+  if (int st = device_info(&di)) return st;
+  if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
+  EncodeTiledFn encode;
+  if (int st = get_encode(&encode)) return st;
+  const int ntiles = (N + kD8BN - 1) / kD8BN;
+  if (ntiles > kGemvMaxCounters - 1) return AWQ_B200_ERR_TOO_LARGE;
+  if (!workspace || workspace_bytes < decode_workspace_bytes(M, K, N, di.sm_count)) return AWQ_B200_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
+  D8Params p;
+  p.x = static_cast<const uint16_t*>(x);
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.qzeros = reinterpret_cast<const uint32_t*>(qzeros);
+  p.epi = epi;
+  p.y = static_cast<uint16_t*>(y);
+  p.counters = static_cast<unsigned*>(workspace);
+  p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kGemvMaxCounters * sizeof(unsigned));
+  p.status = static_cast<unsigned*>(workspace) + (kGemvMaxCounters - 1);
+  p.M = M; p.K = K; p.N = N;
+  p.group_size = group_size;
+  p.ntiles = ntiles;
+  p.nblk = K / kBlockK;
+  p.units = static_cast<long long>(ntiles) * p.nblk;
+  const int grid = static_cast<int>(p.units < di.sm_count ? p.units : di.sm_count);
+  const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
+  if (M <= 1) return launch_decode_i8<1>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  if (M <= 2) return launch_decode_i8<2>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  return launch_decode_i8<4>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+}
+
+}  // namespace awq
+
+extern "C" {
+
+size_t awq_b200_decode_workspace_bytes(int M, int K, int N) {
+  awq::DeviceInfo di;
+  int sm = 148;
+  if (awq::device_info(&di) == AWQ_B200_OK) sm = di.sm_count;
+  return awq::decode_workspace_bytes(M, K, N, sm);
+}
+
+int awq_b200_decode_i8(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const void* bias,
+                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                       awq_b200_stream_t stream, unsigned flags) {
+  return awq::decode_i8_dispatch(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0},
+                                 y, M, K, N, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), flags);
+}
+
+}  // extern "C"

@@ -204,7 +204,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
       const uint32_t zshift = awq_slot_shift(static_cast<uint32_t>(nA & 7));
 
       auto load_sz = [&](int ks, uint32_t& sA, uint32_t& zA) {
-        const int grp = (ks * kBK) / p.group_size;
+        const int grp = (ks * kBK + hh * 32) / p.group_size;     // this thread's 32 k of the stage
         sA = vA ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + nA) : 0u;
         zA = vA ? __ldg(p.qzeros + static_cast<size_t>(grp) * zcols + (nA >> 3)) : 0u;
       };
@@ -341,7 +341,7 @@ int gemm_dispatch(const void* x, const void* packed, const void* scales, const i
                   void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                   cudaStream_t stream, int variant) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
-  if (int st = check_shape(K, N, group_size)) return st;
+  if (int st = check_shape(K, N, group_size, true)) return st;
   if (M < 1) return AWQ_B200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;

@@ -1,5 +1,5 @@
 // Row-count and shape dispatch between the linear kernels: the mma.sync decode GEMV, the two tensor-memory
-// split-K kernels for few rows of a large matrix (unscaled codes up to 16 rows, exact fp16 weights up to 64),
+// split-K kernels for few rows of a large matrix (integer path up to 4 rows, exact fp16 weights up to 64),
 // and the prefill GEMM.
 #include "awq_common.cuh"
 
@@ -7,17 +7,27 @@ namespace {
 constexpr size_t kGemmStatusBytes = 256;  // leading slot of the shared workspace: GEMM status word
 constexpr int kSkinnyMaxRows = 64;
 
-// Which kernel serves M rows of a K x N linear.
-//   rows <= 16: the GEMV, or the tensor-memory decode kernel (unscaled codes, awq_decode.cu) once the packed
-//               weights reach 16 MiB.  The choice depends on (K, N) only, so a row's bits do not change with
-//               the number of rows decoded together.
+// Which kernel serves M rows of a K x N linear (all thresholds are on (K, N) only, so within a row-count class
+// a row's bits do not change with the number of rows decoded together).
+//   rows <= 4:  the GEMV, or from 48 MiB of packed weights the integer tensor-core decode kernel
+//               (awq_decode_i8.cu; 70B-class gate_up at one row: 49 us against 72 us).
+//   5..8:       the GEMV, or from 48 MiB the exact-weight split-K tensor-memory kernel.
+//   9..16:      the same with the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice).
 //   17..64:     the exact-weight tensor-memory kernel where the GEMM would leave most SMs idle (at most 74
 //               column tiles of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
-enum class Route { kGemv, kDecode, kSkinny, kGemm };
-constexpr long long kDecodeFromBytes = 16ll << 20;
-Route route(int M, int K, int N) {
+// Like the reference's own switch from its GEMV to its GEMM at 8 rows (linear_awq.py:167-185), a switch of
+// kernel changes the order of additions.
+enum class Route { kGemv, kDecodeI8, kSkinny, kGemm };
+constexpr int kDecodeI8MaxRows = 4;
+Route route(int M, int K, int N, int group_size) {
+  // Groups of 32 or 64: only the kernels that build the exact fp16 weight per element take them.
+  if (group_size < 128) return M <= kSkinnyMaxRows ? Route::kSkinny : Route::kGemm;
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
-  if (M <= awq_b200_gemv_max_rows()) return packed_bytes >= kDecodeFromBytes ? Route::kDecode : Route::kGemv;
+  if (M <= awq_b200_gemv_max_rows()) {
+    const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
+    if (packed_bytes < from_bytes) return Route::kGemv;
+    return M <= kDecodeI8MaxRows ? Route::kDecodeI8 : Route::kSkinny;
+  }
   if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
   return Route::kGemm;
 }
@@ -27,12 +37,17 @@ extern "C" {
 
 size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
   if (M < 1) M = 1;
+  // The group size is not known here: take the larger of what the two possible routes of these rows need.
   size_t need = 0;
-  switch (route(M, K, N)) {
+  switch (route(M, K, N, 128)) {
     case Route::kGemv: need = awq_b200_gemv_workspace_bytes(M, K, N); break;
-    case Route::kDecode: need = awq_b200_decode_workspace_bytes(M, K, N); break;
+    case Route::kDecodeI8: need = awq_b200_decode_workspace_bytes(M, K, N); break;
     case Route::kSkinny: need = awq_b200_skinny_workspace_bytes(M, K, N); break;
     case Route::kGemm: return awq_b200_gemm_workspace_bytes(M, K, N);   // status word first there too
+  }
+  if (M <= kSkinnyMaxRows) {
+    const size_t small = awq_b200_skinny_workspace_bytes(M, K, N);
+    if (small > need) need = small;
   }
   return kGemmStatusBytes + need;
 }
@@ -48,11 +63,11 @@ static int linear_run(const void* x, const void* packed, const void* scales, con
   unsigned char* rest = static_cast<unsigned char*>(workspace) + kGemmStatusBytes;
   const size_t rest_bytes = workspace_bytes - kGemmStatusBytes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (route(M, K, N)) {
+  switch (route(M, K, N, group_size)) {
     case Route::kGemv:
       return awq::gemv_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
-    case Route::kDecode:
-      return awq::decode_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
+    case Route::kDecodeI8:
+      return awq::decode_i8_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kSkinny:
       return awq::skinny_dispatch(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kGemm:

@@ -197,7 +197,7 @@ const char* awq_b200_status_string(int status) {
     case AWQ_B200_ERR_NULL: return "required pointer is NULL";
     case AWQ_B200_ERR_SHAPE: return "unsupported shape (need K % 128 == 0, N % 8 == 0, K % group_size == 0, M in range)";
     case AWQ_B200_ERR_ALIGN: return "pointer not 16-byte aligned";
-    case AWQ_B200_ERR_GROUP: return "unsupported group size (need a positive multiple of 128)";
+    case AWQ_B200_ERR_GROUP: return "unsupported group size (need a multiple of 128; 32 and 64 are served by the exact-weight kernels only)";
     case AWQ_B200_ERR_WORKSPACE: return "workspace missing or too small";
     case AWQ_B200_ERR_CUDA: return "CUDA call failed";
     case AWQ_B200_ERR_ARCH: return "device is not compute capability 10.x (B200)";
@@ -272,7 +272,7 @@ int awq_b200_dequant(const int32_t* qweight, const int32_t* qzeros, const void* 
 int awq_b200_dequant_packed(const void* packed, const int32_t* qzeros, const void* scales, void* W,
                             int K, int N, int group_size, awq_b200_stream_t stream) {
   if (!packed || !qzeros || !scales || !W) return AWQ_B200_ERR_NULL;
-  if (int st = check_shape(K, N, group_size)) return st;
+  if (int st = check_shape(K, N, group_size, true)) return st;
   if (!aligned16(packed) || !aligned16(scales) || !aligned16(W) || !aligned16(qzeros))
     return AWQ_B200_ERR_ALIGN;
   const long long words = static_cast<long long>(K / 8) * N;

@@ -128,8 +128,10 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   const int my_units = static_cast<int>(u1 - u0);
   const int nblk = p.nblk;
   constexpr uint32_t kIdesc = make_f16_idesc(128, MT);
-  // Bulk copies need 16-byte aligned, 16-byte sized row segments of scales and qzeros: N % 32 == 0.
-  const bool sz_by_copy = (p.N & 31) == 0;
+  // Bulk copies need 16-byte aligned, 16-byte sized row segments of scales and qzeros: N % 32 == 0.  Groups
+  // of 32 or 64 put several scale rows into one 128-k unit: those are read per thread instead.
+  const bool sz_by_copy = (p.N & 31) == 0 && p.group_size >= kBlockK;
+  const bool small_groups = p.group_size < kBlockK;
 
   if (warp == 0 || warp == kSkProducer2Warp) {
     // ------------------------------ copy producers ----------------------------
@@ -148,7 +150,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       tile = static_cast<int>(u / nblk);
       kb = static_cast<int>(u - static_cast<long long>(tile) * nblk);
     }
-    const int group_blocks = p.group_size / kBlockK;
+    const int group_blocks = p.group_size >= kBlockK ? p.group_size / kBlockK : 1;   // only used with sz_by_copy
     auto advance = [&]() {
       kb += 2;
       while (kb >= nblk) { kb -= nblk; ++tile; }
@@ -261,7 +263,20 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if ((gs & 1) != grp) continue;                           // the other group's unit
         const int t = gs % NT, a = gs % NA;
         const uint32_t ph = static_cast<uint32_t>(gs / NT) & 1u, pha = static_cast<uint32_t>(gs / NA) & 1u;
-        if (!sz_by_copy) {
+        uint32_t sc_sub[4] = {0u, 0u, 0u, 0u}, zw_sub[4] = {0u, 0u, 0u, 0u};   // per 32 k of the unit (small groups)
+        if (small_groups) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int qgrp = ((kb0 + j) * kBlockK + 32 * c) / p.group_size;
+            if (c > 0 && qgrp == ((kb0 + j) * kBlockK + 32 * (c - 1)) / p.group_size) {
+              sc_sub[c] = sc_sub[c - 1];
+              zw_sub[c] = zw_sub[c - 1];
+            } else {
+              sc_sub[c] = nvalid ? __ldg(p.scales + static_cast<size_t>(qgrp) * p.N + n) : 0u;
+              zw_sub[c] = nvalid ? __ldg(p.qzeros + static_cast<size_t>(qgrp) * zcols + (n >> 3)) : 0u;
+            }
+          }
+        } else if (!sz_by_copy) {
           const int qgrp = ((kb0 + j) * kBlockK) / p.group_size;
           if (qgrp != sz_group) {
             sc = nvalid ? __ldg(p.scales + static_cast<size_t>(qgrp) * p.N + n) : 0u;
@@ -285,11 +300,15 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if (lane == 0) mbar_arrive(bar_empty_tma(t));            // packed weights are in registers
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) { ok = false; continue; }
         tcgen05_fence_after();
-        const ZeroPair zp = make_zero_pair((zw >> zsh) & 0xFu);
-        const uint32_t s2 = sc * 0x00010001u;
+        ZeroPair zp = make_zero_pair((zw >> zsh) & 0xFu);
+        uint32_t s2 = sc * 0x00010001u;
         const uint32_t a_addr = tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + a * 128 + h * 64);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
+          if (small_groups) {                                    // warp-uniform
+            zp = make_zero_pair((zw_sub[c] >> zsh) & 0xFu);
+            s2 = sc_sub[c] * 0x00010001u;
+          }
           const uint32_t w[4] = {r[c].x, r[c].y, r[c].z, r[c].w};
           uint32_t o[16];
 #pragma unroll
@@ -464,7 +483,7 @@ int skinny_dispatch(const void* x, const void* packed, const void* scales, const
                     void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                     cudaStream_t stream, unsigned flags) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
-  if (int st = check_shape(K, N, group_size)) return st;
+  if (int st = check_shape(K, N, group_size, true)) return st;
   if (M < 1 || M > 64) return AWQ_B200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;

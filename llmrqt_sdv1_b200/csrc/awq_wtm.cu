@@ -156,7 +156,10 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   const int num_tiles = p.mtiles * p.ntiles;
   constexpr uint32_t kIdesc = make_f16_idesc(128, MT);
   // Bulk copies need 16-byte aligned, 16-byte sized row segments of scales and qzeros: N % 32 == 0.
-  const bool sz_by_copy = (p.N & 31) == 0;
+  // Scales and zero words ride in the stage by bulk copy when their row segments are 16-byte aligned and sized
+  // (N % 32 == 0) and a 64-k stage lies within one quantisation group; groups of 32 are read per thread.
+  const bool sz_by_copy = (p.N & 31) == 0 && p.group_size >= kWtBK;
+  const bool half_stage_groups = p.group_size < kWtBK;
 
   if (warp == 0 || warp == kWtProducer2Warp) {
     // ------------------------------ TMA producers -----------------------------
@@ -170,7 +173,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     }
-    const int stages_per_group = p.group_size / kWtBK;
+    const int stages_per_group = p.group_size >= kWtBK ? p.group_size / kWtBK : 1;   // only used with sz_by_copy
     uint32_t it = 0;
     int t = 0;
     uint32_t ph = 0;
@@ -285,8 +288,8 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         nval[hh] = ncol[hh] < p.N;
         zsh[hh] = awq_slot_shift(static_cast<uint32_t>(ncol[hh] & 7));
       }
-      auto load_sz = [&](int ks, uint32_t (&s)[NH], uint32_t (&z)[NH]) {
-        const int grp = (ks * kWtBK) / p.group_size;
+      auto load_sz = [&](int ks, int kh, uint32_t (&s)[NH], uint32_t (&z)[NH]) {
+        const int grp = (ks * kWtBK + kh * 32) / p.group_size;
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) {
           s[hh] = nval[hh] ? __ldg(p.scales + static_cast<size_t>(grp) * p.N + ncol[hh]) : 0u;
@@ -294,6 +297,7 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         }
       };
       uint32_t sc[NH], zw[NH];
+      uint32_t sc_hi[NH], zw_hi[NH];          // second 32 k of a stage when groups are 32 wide
       int sz_group = -1;
 
       for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
@@ -302,7 +306,8 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         const uint32_t ph = (it / NT) & 1u, pha = (it / NA) & 1u;
         if (!sz_by_copy) {
           const int qgrp = (ks * kWtBK) / p.group_size;
-          if (qgrp != sz_group) { load_sz(ks, sc, zw); sz_group = qgrp; }
+          if (half_stage_groups) { load_sz(ks, 0, sc, zw); load_sz(ks, 1, sc_hi, zw_hi); }
+          else if (qgrp != sz_group) { load_sz(ks, 0, sc, zw); sz_group = qgrp; }
         }
         if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
         if (!ok) continue;
@@ -331,10 +336,14 @@ wtm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
 #pragma unroll
         for (int hh = 0; hh < NH; ++hh) {
           const int h = (NH == 2) ? hh : sub;
-          const ZeroPair zp = make_zero_pair((zw[hh] >> zsh[hh]) & 0xFu);
-          const uint32_t s2 = sc[hh] * 0x00010001u;
+          ZeroPair zp = make_zero_pair((zw[hh] >> zsh[hh]) & 0xFu);
+          uint32_t s2 = sc[hh] * 0x00010001u;
 #pragma unroll
           for (int kh = 0; kh < 2; ++kh) {
+            if (half_stage_groups && kh == 1) {                  // warp-uniform
+              zp = make_zero_pair((zw_hi[hh] >> zsh[hh]) & 0xFu);
+              s2 = sc_hi[hh] * 0x00010001u;
+            }
             const uint32_t w[4] = {r[hh][kh].x, r[hh][kh].y, r[hh][kh].z, r[hh][kh].w};
             uint32_t o[16];
 #pragma unroll
@@ -539,7 +548,7 @@ int wtm_dispatch(const void* x, const void* packed, const void* scales, const in
                  void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream, int m_tile) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
-  if (int st = check_shape(K, N, group_size)) return st;
+  if (int st = check_shape(K, N, group_size, true)) return st;
   if (M < 1) return AWQ_B200_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(packed) || !aligned16(scales) || !aligned16(qzeros) || !aligned16(y))
     return AWQ_B200_ERR_ALIGN;

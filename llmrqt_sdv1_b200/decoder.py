@@ -66,6 +66,7 @@ class GraphedDecoder:
         self.cos_tab = cos[0].to(self.dtype).contiguous()                              # [max_len, head_dim]
         # rotate_half(x) * sin == roll(x, head_dim / 2) * sin_signed with the first half of sin negated
         self.sin_signed_tab = torch.cat((-sin[0, :, :half], sin[0, :, half:]), dim=-1).to(self.dtype).contiguous()
+        self.sin_tab = sin[0].to(self.dtype).contiguous()
         # per-head q / k norm weights as one [heads + kv_heads, head_dim] tensor (ones where a model has none)
         self.qk_weights = []
         for layer in self.layers:
@@ -84,6 +85,21 @@ class GraphedDecoder:
         self.last_logits = None
         self.graph = None
         self._capture = (dev.type == "cuda") if capture is None else capture
+        # On the GPU the step's attention-side plumbing (per-head q/k norm, rotary embedding, cache write, the
+        # single-query attention) runs as two small library kernels instead of a dozen tensor operations.
+        self._glue = dev.type == "cuda" and self.dtype == torch.float16 and self.head_dim in (64, 128)
+        if self._glue:
+            self._q_buf = torch.empty((self.n_heads, self.head_dim), dtype=self.dtype, device=dev)
+            self._attn_buf = torch.empty((1, 1, self.n_heads * self.head_dim), dtype=self.dtype, device=dev)
+            self._qk_norm = []
+            for layer in self.layers:
+                qn, kn = getattr(layer.self_attn, "q_norm", None), getattr(layer.self_attn, "k_norm", None)
+                if qn is None or kn is None:
+                    self._qk_norm.append((None, None, 0.0))
+                else:
+                    self._qk_norm.append((qn.weight.detach().to(self.dtype).contiguous(),
+                                          kn.weight.detach().to(self.dtype).contiguous(),
+                                          float(getattr(qn, "variance_epsilon", 1e-6))))
 
     # ------------------------------------------------------------------ pieces of a step
     def _qkv(self, attn, x):
@@ -144,7 +160,17 @@ class GraphedDecoder:
         mask = (self.positions <= pos).view(1, 1, 1, self.max_len)              # attend to cache slots 0..pos
         for li, layer in enumerate(self.layers):
             x = _rms(h, layer.input_layernorm)
-            q, k, v = self._qk_norm_rope(li, self._qkv(layer.self_attn, x), cos, sin_signed)
+            qkv = self._qkv(layer.self_attn, x)
+            if self._glue:
+                from . import kernels
+                qw, kw, eps = self._qk_norm[li]
+                kernels.qk_norm_rope_cache(qkv, qw, kw, eps, self.cos_tab, self.sin_tab, pos, self._q_buf,
+                                           self.k_cache[li], self.v_cache[li])
+                kernels.attn_decode(self._q_buf, self.k_cache[li], self.v_cache[li], pos, self._attn_buf,
+                                    layer.self_attn.scaling if hasattr(layer.self_attn, "scaling") else self.head_dim ** -0.5)
+                h = self._layer_tail(layer, h, self._attn_buf)
+                continue
+            q, k, v = self._qk_norm_rope(li, qkv, cos, sin_signed)
             self.k_cache[li].index_copy_(2, pos, k)
             self.v_cache[li].index_copy_(2, pos, v)
             a = F.scaled_dot_product_attention(q, self.k_cache[li], self.v_cache[li], attn_mask=mask,

@@ -194,9 +194,9 @@ def skinny(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
 
-def decode(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
-    """Decode rows (1 <= M <= 16) on the tensor-memory path with unscaled codes (split-K over all SMs)."""
-    return _run(lib.awq_b200_decode, "awq_b200_decode", x, pw, bias,
+def decode_i8(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """Decode rows (1 <= M <= 4) on the integer tensor-core path (masked nibbles x block-fixed-point activations)."""
+    return _run(lib.awq_b200_decode_i8, "awq_b200_decode", x, pw, bias,
                 lib.awq_b200_decode_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))
 
@@ -370,6 +370,41 @@ def peer_allreduce_push(partial: torch.Tensor, recv_dev: int, flags_dev: int, sl
                                            bias.data_ptr() if bias is not None else None, M * N, N, slot_elems,
                                            rank, world, _stream(partial)), "awq_b200_peer_allreduce_push")
     return y
+
+
+def qk_norm_rope_cache(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, q_out, k_cache, v_cache) -> None:
+    """One token's fused qkv row -> q (normalised per head, rotated) into `q_out` [H, D], k (likewise) and v into row
+    `pos` of `k_cache` / `v_cache` [KV, max_len, D].  `pos` is an int64 tensor on the device (one element)."""
+    KV, max_len, D = k_cache.shape[-3], k_cache.shape[-2], k_cache.shape[-1]
+    H = q_out.numel() // D
+    for t in (qkv, cos_tab, sin_tab, q_out, k_cache, v_cache):
+        if t.dtype != torch.float16 or not t.is_contiguous():
+            raise ValueError("qk_norm_rope_cache needs contiguous fp16 tensors")
+    if qkv.numel() != (H + 2 * KV) * D or v_cache.shape != k_cache.shape or pos.dtype != torch.int64:
+        raise ValueError("qk_norm_rope_cache: inconsistent shapes")
+    if tuple(cos_tab.shape) != (max_len, D) or tuple(sin_tab.shape) != (max_len, D):
+        raise ValueError(f"rotary tables must be [{max_len}, {D}]")
+    dev = _prep(qkv, cos_tab, sin_tab, pos, q_out, k_cache, v_cache)
+    check(lib.awq_b200_qk_norm_rope_cache(
+        qkv.data_ptr(), q_weight.data_ptr() if q_weight is not None else None,
+        k_weight.data_ptr() if k_weight is not None else None, float(eps), cos_tab.data_ptr(), sin_tab.data_ptr(),
+        pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), H, KV, D, max_len,
+        torch.cuda.current_stream(dev).cuda_stream), "awq_b200_qk_norm_rope_cache")
+
+
+def attn_decode(q, k_cache, v_cache, pos, out, scale: float) -> None:
+    """`out` [H * D] = attention of one query token `q` [H, D] over rows 0..pos of the caches [KV, max_len, D]."""
+    KV, max_len, D = k_cache.shape[-3], k_cache.shape[-2], k_cache.shape[-1]
+    H = q.numel() // D
+    for t in (q, k_cache, v_cache, out):
+        if t.dtype != torch.float16 or not t.is_contiguous():
+            raise ValueError("attn_decode needs contiguous fp16 tensors")
+    if out.numel() != H * D or v_cache.shape != k_cache.shape or pos.dtype != torch.int64:
+        raise ValueError("attn_decode: inconsistent shapes")
+    dev = _prep(q, k_cache, v_cache, pos, out)
+    check(lib.awq_b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                   H, KV, D, max_len, float(scale), torch.cuda.current_stream(dev).cuda_stream),
+          "awq_b200_attn_decode")
 
 
 def gemv_status(dev: torch.device | None = None) -> int:

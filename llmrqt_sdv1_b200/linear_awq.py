@@ -93,6 +93,7 @@ class AWQLinear_GEMM(nn.Module):
             self.register_buffer("bias", torch.zeros((out_features,), dtype=torch.float16, device=dev))
         else:
             self.bias = None
+        self._released = None       # the kernel-layout weight while `qweight` is released
 
     @classmethod
     def from_linear(cls, linear, w_bit, group_size, init_only=False, dtype=torch.bfloat16, scales=None,
@@ -119,9 +120,66 @@ class AWQLinear_GEMM(nn.Module):
 
     def prepare(self):
         """Repack now instead of on the first forward (call after any buffer surgery)."""
+        if getattr(self, "_released", None) is not None:
+            return self
         _, ext = _kernels()
         ext.packed_for(self.qweight, self.qzeros, self.scales, self.group_size)
         return self
+
+    def packed(self):
+        """The kernel-layout weight of this module (repacked on first use, or the one kept by `release_qweight`)."""
+        pw = getattr(self, "_released", None)
+        if pw is not None:
+            return pw
+        _, ext = _kernels()
+        return ext.packed_for(self.qweight, self.qzeros, self.scales, self.group_size)
+
+    # The kernels read the repacked weight only.  A module that serves and is not being edited can therefore
+    # give the on-disk `qweight` back: `release_qweight` keeps the kernel-layout copy alone (half the int4
+    # bytes of a layer that otherwise holds both), and `state_dict()` / `restore_qweight` rebuild the on-disk
+    # tensor bit for bit with the inverse repack (awq_b200_unpack) whenever it is asked for.
+    def release_qweight(self):
+        """Free the on-disk `qweight` buffer; forward keeps working from the kernel-layout weight."""
+        if getattr(self, "_released", None) is not None:
+            return self
+        _, ext = _kernels()
+        pw = ext.packed_for(self.qweight, self.qzeros, self.scales, self.group_size)
+        self._released = pw
+        self.qweight = torch.empty((0, self.out_features // (32 // self.w_bit)), dtype=torch.int32,
+                                   device=pw.packed.device)
+        return self
+
+    def adopt_packed(self, pw):
+        """Take a kernel-layout weight built elsewhere (a loader that repacks straight from the file) as this
+        module's weight, with `qweight` released.  `pw.qzeros` / `pw.scales` become the module's buffers."""
+        if (pw.K, pw.N, pw.group_size) != (self.in_features, self.out_features, self.group_size):
+            raise ValueError("packed weight does not match the module's shape / group size")
+        self.qzeros, self.scales = pw.qzeros, pw.scales
+        self._released = pw
+        self.qweight = torch.empty((0, self.out_features // (32 // self.w_bit)), dtype=torch.int32,
+                                   device=pw.packed.device)
+        return self
+
+    def restore_qweight(self):
+        """Bring the on-disk `qweight` buffer back (needed before editing buffers, e.g. q/k/v fusion)."""
+        pw = getattr(self, "_released", None)
+        if pw is not None:
+            kernels, _ = _kernels()
+            self.qweight = kernels.unpack(pw.packed)
+            self._released = None
+        return self
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        pw = getattr(self, "_released", None)
+        if pw is not None:       # the checkpoint format is the on-disk one, whatever the module holds
+            kernels, _ = _kernels()
+            destination[prefix + "qweight"] = kernels.unpack(pw.packed)
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        if getattr(self, "_released", None) is not None and prefix + "qweight" in state_dict:
+            self.restore_qweight()
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
     def forward(self, x, residual=None):
         """`residual` (optional, not in the reference's signature): a tensor of the result's shape that the
@@ -132,11 +190,16 @@ class AWQLinear_GEMM(nn.Module):
         assert x.device == dev, "when awq linear fwd, input and qweight must be same device!"
         assert qzeros.device == dev, "when awq linear fwd, qzeros and qweight must be same device!"
         assert scales.device == dev, "when awq linear fwd, scales and qweight must be same device!"
+        released = self.__dict__.get("_released")
+        if released is not None and self.impl_mode != "auto":
+            # the explicit reference path materialises the fp16 weight from the on-disk tensors
+            self.restore_qweight()
+            qweight, released = self._buffers["qweight"], None
         if x.dtype == torch.float16 and self.impl_mode == "auto" and x.dim() >= 2 and x.numel() != 0:
             # The per-token path: straight to the library's dispatcher.  Nothing here records autograd
             # state (the result is a fresh tensor written by the kernel), so no no_grad block is needed.
             kernels, ext = _kernels()
-            pw = ext.packed_for(qweight, qzeros, scales, self.group_size)
+            pw = released if released is not None else ext.packed_for(qweight, qzeros, scales, self.group_size)
             overlap, pw.fresh = not pw.fresh, False   # first call after a repack: no weight prefetch
             shape = x.shape[:-1] + (self.out_features,)
             shape = (1,) + tuple(shape) if len(shape) == 2 else shape
@@ -146,6 +209,14 @@ class AWQLinear_GEMM(nn.Module):
         out_shape = x.shape[:-1] + (self.out_features,)
         if x.shape[0] == 0:
             return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
+        if released is not None:
+            if self.impl_mode not in {"auto", "dequant_matmul"}:
+                raise ValueError(f"AWQ impl_mode must be 'auto' or 'dequant_matmul', got {self.impl_mode!r}")
+            x16 = x.to(torch.float16)
+            y = self.forward(x16 if x16.dim() >= 2 else x16.unsqueeze(0),
+                             residual.to(torch.float16) if residual is not None else None)
+            y = y if x.dim() >= 2 else y.reshape(out_shape)
+            return y if x.dtype == torch.float16 else y.to(x.dtype)
         input_dtype = x.dtype
         if input_dtype != torch.float16:
             x = x.to(torch.float16)

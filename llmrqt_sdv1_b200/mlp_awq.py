@@ -73,6 +73,7 @@ class AWQGatedMLP(nn.Module):
             if self.gate_up_bias is not None:
                 y = y + self.gate_up_bias
             h = F.silu(y[..., 0::2]) * y[..., 1::2]
+            down.restore_qweight()
             out = torch.matmul(h, kernels.dequantize(down.qweight, down.qzeros, down.scales, down.group_size))
             if down.bias is not None:
                 out = out + down.bias
@@ -83,7 +84,7 @@ class AWQGatedMLP(nn.Module):
             pw_gu = ext.packed_for(self.gate_up_qweight, self.gate_up_qzeros, self.gate_up_scales, self.group_size)
             overlap, pw_gu.fresh = not pw_gu.fresh, False
             h = kernels.linear_fused(x2, pw_gu, bias=self.gate_up_bias, gated=True, overlap=overlap)
-            pw_d = ext.packed_for(down.qweight, down.qzeros, down.scales, down.group_size)
+            pw_d = down.packed()
             overlap, pw_d.fresh = not pw_d.fresh, False
             out = kernels.linear_fused(h, pw_d, bias=down.bias, residual=residual, overlap=overlap,
                                        out_shape=lead + (down.out_features,))

@@ -87,8 +87,7 @@ def _local_linear(qw, qz, sc, bias, group_size, device) -> AWQLinear_GEMM:
 
 
 def _packed(lin: AWQLinear_GEMM):
-    from .sq_fp8_kernels import packed_for
-    return packed_for(lin.qweight, lin.qzeros, lin.scales, lin.group_size)
+    return lin.packed()
 
 
 class ColumnParallelAWQLinear(nn.Module):

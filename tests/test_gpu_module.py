@@ -116,3 +116,66 @@ def test_load_checkpoint_fills_and_repacks(tmp_path):
     x = torch.randn((1, 5, 256), device="cuda").half()
     assert torch.equal(dst(x), src(x))
     assert kernels.gemv_status() == 0
+
+
+def test_release_qweight_keeps_one_copy_and_state_dict_round_trips(tmp_path):
+    """`release_qweight` frees the on-disk tensor (the module then holds the int4 weights once, in the kernel
+    layout), forward results do not change, `state_dict()` still yields the on-disk tensors bit for bit, and a
+    checkpoint loaded with `release_qweight=True` into a model built on the meta device ends up the same way."""
+    import os
+    from llmrqt_sdv1_b200 import AWQLinear_GEMM, checkpoint, kernels, quantize
+    K, N = 2048, 4096
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated()
+    m = AWQLinear_GEMM(4, 128, K, N, True, "cuda")
+    m.qweight, m.qzeros, m.scales = quantize.random_awq_tensors(K, N, 128, seed=5, device="cuda")
+    m.bias = (torch.randn(N, device="cuda") * 0.1).half()
+    qweight = m.qweight.clone()
+    x1, x9 = torch.randn((1, 1, K), device="cuda").half(), torch.randn((1, 9, K), device="cuda").half()
+    y1, y9 = m(x1), m(x9)
+    y9_bf16 = m(x9.to(torch.bfloat16))
+    sd = {k: v.clone() for k, v in m.state_dict().items()}
+    both = torch.cuda.memory_allocated()
+    m.release_qweight()
+    assert m.qweight.numel() == 0
+    torch.cuda.synchronize()
+    assert both - torch.cuda.memory_allocated() >= K * N // 2          # the on-disk copy is gone
+    assert torch.equal(m(x1), y1) and torch.equal(m(x9), y9)
+    assert torch.equal(m(x9.to(torch.bfloat16)), y9_bf16)           # other input dtypes: cast in, cast back
+    for k, v in m.state_dict().items():
+        assert torch.equal(v, sd[k]), k
+    m.impl_mode = "dequant_matmul"                                      # needs the on-disk tensors: they come back
+    yd = m(x9)
+    assert torch.equal(m.qweight, qweight)
+    assert float((yd.float() - y9.float()).abs().max() / y9.float().abs().max()) <= 2e-3
+    m.impl_mode = "auto"
+    m.release_qweight()
+    m.load_state_dict(sd)                                               # loading restores, then overwrites
+    assert torch.equal(m.qweight, qweight) and torch.equal(m(x1), y1)
+
+    # a model built without storage, filled straight from the file
+    class Block(torch.nn.Module):
+        def __init__(self, dev):
+            super().__init__()
+            self.a = AWQLinear_GEMM(4, 128, K, N, True, dev)
+
+    src = Block("cuda")
+    src.a.load_state_dict(sd)
+    path = os.path.join(tmp_path, "one.safetensors")
+    checkpoint.save_checkpoint(src.state_dict(), path)
+    del src, m, sd, qweight
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    dst = Block("meta")
+    report = checkpoint.load_checkpoint(dst, path, device="cuda", release_qweight=True)
+    assert not report["missing"] and not report["unexpected"]
+    torch.cuda.synchronize()
+    held = torch.cuda.memory_allocated() - before
+    packed_bytes = K * N // 2
+    extras = (K // 128) * N * 2 + (K // 128) * (N // 8) * 4 + N * 2     # scales, zeros, bias
+    assert held <= packed_bytes + extras + (1 << 20), (held, packed_bytes, extras)
+    assert dst.a.qweight.numel() == 0 and dst.a.qzeros.is_cuda
+    assert torch.equal(dst.a(x1), y1)
+    back = dst.state_dict()
+    assert back["a.qweight"].shape == (K, N // 8)
+    assert kernels.gemv_status() == 0

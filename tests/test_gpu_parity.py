@@ -391,3 +391,45 @@ def test_gemm_full_size_vs_device_dequant_matmul(K_, K, N, M):
     y = K_.gemm(x, pw)
     assert K_.gemm_status() == 0
     assert (y.float() - ref).abs().max() / ref.abs().max() <= TOL
+
+
+# --------------------------------------------------------------------------- group sizes 32 and 64
+@pytest.mark.parametrize("G", [32, 64])
+@pytest.mark.parametrize("K,N", [(256, 264), (1024, 1096), (4096, 512)])
+def test_small_groups_every_row_count(K_, K, N, G):
+    """The reference module takes any group size that divides K (linear_awq.py:228-236).  Groups of 32 and 64
+    put several scale rows into one 128-k block: the kernels that build the exact fp16 weight per element serve
+    them (dequant bit-exact; the split-K tensor-memory kernel up to 64 rows, the GEMMs beyond), and `linear`
+    routes there for every row count."""
+    qw, qz, sc = tensors(K, N, G, seed=K + N + G)
+    pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
+    assert np.array_equal(bits(K_.dequantize_packed(pw)), orc.dequantize(qw, qz, sc, G).view(np.uint16))
+    assert np.array_equal(bits(K_.dequantize(dev(qw), dev(qz), dev(sc), G)), orc.dequantize(qw, qz, sc, G).view(np.uint16))
+    x = orc.make_activations(300, K, seed=G)
+    ref = orc.linear_forward(x, qw, qz, sc, G)
+    for M in (1, 8, 16, 40, 64, 65, 300):
+        y = K_.linear(dev(x[:M]), pw)
+        assert orc.max_normalised_error(y.cpu().numpy(), ref[:M]) <= TOL, (M, G)
+    ys = K_.skinny(dev(x[:33]), pw)
+    assert torch.equal(ys, K_.linear(dev(x[:33]), pw))
+    for fn in (K_.gemm, K_.gemm_smem, K_.gemm_wtm):
+        yg = fn(dev(x), pw)
+        assert orc.max_normalised_error(yg.cpu().numpy(), ref) <= TOL, (fn.__name__, G)
+    assert torch.equal(K_.gemm_smem(dev(x), pw), K_.gemm_wtm_unsplit(dev(x), pw))
+    with pytest.raises(ValueError):
+        K_.gemv(dev(x[:1]), pw)            # the per-block decode kernels need whole 128-k groups
+    with pytest.raises(ValueError):
+        K_.decode_i8(dev(x[:1]), pw)
+    assert K_.gemm_status() == 0 and K_.gemv_status() == 0
+
+
+def test_small_groups_through_the_module(K_):
+    from llmrqt_sdv1_b200 import AWQLinear_GEMM
+    K, N, G = 512, 384, 64
+    qw, qz, sc = tensors(K, N, G, seed=77)
+    m = AWQLinear_GEMM(4, G, K, N, False, "cuda")
+    m.load_state_dict({"qweight": torch.from_numpy(qw), "qzeros": torch.from_numpy(qz), "scales": torch.from_numpy(sc)})
+    for M in (1, 70):
+        x = orc.make_activations(M, K, seed=M)
+        y = m(dev(x))[0].cpu().numpy()
+        assert orc.max_normalised_error(y, orc.linear_forward(x, qw, qz, sc, G)) <= TOL
