@@ -49,7 +49,7 @@ PREFILL_SHAPES = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of a decode kernel, from one ncu capture of that
 # kernel on that shape (None where no capture exists).
-NCU_TRAFFIC_BYTES = {"gemv_2048x12288_m1": 13_117_440, "decode_8192x57344_m1": None}
+NCU_TRAFFIC_BYTES = {"gemv_2048x12288_m1": 13_117_440, "decode_8192x57344_m1": 250_596_608}
 
 
 def gemv_bytes(M, K, N, G=GROUP):
@@ -832,7 +832,9 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                      "frac": per_gpu / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["decode_8192x57344_m1"],
                      "traffic_of": "one launch of the decode kernel on the unsharded gate_up (8192 x 57344, M = 1)",
                      "peak_source": peaks["source"], "frac_of_nominal_8tbs": per_gpu / 8000.0,
-                     "kernel": "the decode kernel awq_b200_linear routes these shards to (+ the all-reduce named in allreduce.used)",
+                     "kernel": ("awq::decode_i8_kernel" if world <= 2 else "awq::decode_i8_kernel / awq::gemv_kernel by shard size")
+                               + (" (+ the all-reduce named in allreduce.used)" if world > 1 else ""),
+                     "algorithmic_bytes_per_launch": gemv_bytes(M, Kg, Ng),
                      "per_gpu": True},
         "e2e": {"value": step_bytes_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (hxg.numel() + hxd.numel()) * 2, "d2h_bytes_per_step": hy.numel() * 2,
@@ -848,8 +850,9 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     else:
         # One GPU: the Qwen3-1.7B decode step (the small shapes, where per-launch latency decides), the per-shape
         # tables and the whole-model leg ride on the same line.
-        line["qwen3_decode"] = qwen3_decode_measure(args, torch, peaks)
-        if not args.no_detail:
+        if not args.headline_only:
+            line["qwen3_decode"] = qwen3_decode_measure(args, torch, peaks)
+        if not args.no_detail and not args.headline_only:
             detail_tables(line, args, torch, peaks)
             try:
                 line["config5"] = config5_block(torch)
@@ -1010,6 +1013,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, "qwen3_decode", "ffn70b_tp", "qwen3_e2e"])
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape decode / prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="time the headline workload only (no qwen3_decode block, no tables): for launch-list captures")
     ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "decode70b", "decode70b_m4",
                              "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")

@@ -20,42 +20,56 @@
 //
 // Work distribution is the split-K stream of the exact-weight kernel (awq_skinny.cu): unit = 256 columns x 128 k
 // (16 KiB of packed weights), CTA b owns units [b*U/G, (b+1)*U/G) of the flattened (column tile, k block)
-// sequence, one CTA per SM, one copy pipeline that never drains; a column tile that straddles CTAs is finished
-// through fp32 partials added in CTA (= k) order by the last contributor.  Warps 0 / 18 copy producers, 1 / 19 MMA issuers (one per 128-column half), 2..17 four groups
-// of four warps that mask the words into tensor memory and fold the finished accumulators, 20..23 activation
-// helpers (every fourth unit each).  TMEM columns: [0, 256) four accumulator windows of 64 (2 halves x {hi, lo}
-// x 16), [256, 512) four operand slots of 64 (2 halves x {hi, lo} x 16 columns = 64 k slots).  Per unit and half
-// the tensor core runs 4 instructions (2 k steps of 32 slots x {hi, lo}).  Deterministic; a row's bits do not
-// depend on M.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+// sequence, one copy pipeline per CTA that never drains; a column tile that straddles CTAs is finished through
+// fp32 partials added in CTA (= k) order by the last contributor.  Deterministic; a row's bits do not depend on M.
+//
+// TWO CTAs per SM (384 threads, 256 tensor-memory columns, ~100 KB of shared memory each).  In steady state the
+// kernel moves what the memory system delivers to such a stream (measured 5.6 - 5.7 TB/s); what a launch costs
+// beyond that is its start (barriers, tensor-memory allocation, first copies in flight, pipeline fill) and its
+// end (last accumulators, partial tiles).  With two small CTAs per SM the next kernel of the stream
+// (programmatic dependent launch) takes over an SM half as soon as one CTA has left, and its first copies
+// overlap the other CTA's tail; one CTA that fills the SM makes every launch pay start and end in full.
+//
+// Warps: 0 copy producer, 1 MMA issuer, 2..9 two groups of four warps that mask the words into tensor memory
+// (a thread serves one column in each 128-column half) and fold the finished accumulators, 10..11 activation
+// helpers (alternate units).  TMEM columns: [0, 128) two accumulator windows of 64 (2 halves x {hi, lo} x 16),
+// [128, 256) two operand slots of 64 (2 halves x {hi, lo} x 16 columns = 64 k slots).  Per unit the tensor core
+// runs 8 instructions (2 halves x 2 k steps of 32 slots x {hi, lo}).  A group folds unit u when it starts on
+// unit u + 2.  Every mbarrier wait is bounded (see awq_ptx.cuh).
 #include "awq_gemv_common.cuh"
 #include "awq_tcgen05.cuh"
 
 namespace awq {
 
-constexpr int kD8UnpackWarps = 16;
+constexpr int kD8UnpackWarps = 8;
 constexpr int kD8UnpackThreads = kD8UnpackWarps * 32;
-constexpr int kD8Groups = 4;
-constexpr int kD8HelperWarps = 4;
-constexpr int kD8Threads = 64 + kD8UnpackThreads + 64 + kD8HelperWarps * 32;   // 24 warps
-constexpr int kD8Producer2Warp = 18, kD8Issuer2Warp = 19, kD8HelperWarp0 = 20;
+constexpr int kD8Groups = 2;
+constexpr int kD8HelperWarps = 2;
+constexpr int kD8Threads = 64 + kD8UnpackThreads + kD8HelperWarps * 32;   // 12 warps
+constexpr int kD8HelperWarp0 = 2 + kD8UnpackWarps;
+constexpr int kD8CtasPerSm = 2;
 constexpr int kD8BN = 256;
 constexpr int kD8RawBytes = kD8BN * 64;            // [256 columns][64 bytes], 64-byte swizzle
-constexpr int kD8XTileBytes = 16 * 64;             // B operand tile: 16 rows x 64 k slots, 64-byte swizzle
+// B operand tiles: 16 rows x 64 k slots, 64-byte swizzle.  Only rows 0 .. 2 MR - 1 <= 7 carry data (two planes
+// of up to four rows); the tensor core also reads rows 8..15, whose products land in accumulator columns nobody
+// looks at, so those rows may be whatever lies behind the tile: a tile takes 512 bytes.
+constexpr int kD8XTileBytes = 8 * 64;
 constexpr int kD8RawOff = 0;
-constexpr int kD8SzOff = kD8RawOff + kD8RawBytes;  // 256 fp16 scales, then 32 qzeros words
-constexpr int kD8XhiOff = kD8SzOff + 1024;
+constexpr int kD8XhiOff = kD8RawOff + kD8RawBytes;
 constexpr int kD8XloOff = kD8XhiOff + kD8XTileBytes;
-constexpr int kD8StageBytes = kD8XloOff + kD8XTileBytes;   // 19 KiB + 512... see static_assert
-constexpr int kD8Stages = 8;                       // measured: 10 stages are no faster (the copy pipeline is not the limit)
-constexpr int kD8Windows = 4;
-constexpr int kD8ABase = kD8Windows * 64;          // 256
-constexpr int kD8AStages = 4;
-constexpr int kD8MetaSlots = 16;                   // ring of per-unit (sx, T) rows; must be >= kD8Stages + 2
+constexpr int kD8SzOff = kD8XloOff + kD8XTileBytes;    // 256 fp16 scales, then 32 qzeros words
+constexpr int kD8StageBytes = 18 * 1024;
+constexpr int kD8Stages = 5;                       // per CTA; two CTAs per SM
+constexpr int kD8Windows = 2;
+constexpr int kD8ABase = kD8Windows * 64;          // 128
+constexpr int kD8AStages = 2;
+constexpr int kD8TmemCols = 256;
+constexpr int kD8MetaSlots = 8;                    // ring of per-unit (sx, T) rows (see the helpers for why 8 is enough)
 constexpr int kD8MaxRows = 4;                      // beyond that the per-row fold costs more than the exact-weight kernel's unpack
 constexpr int kD8Range = 16256;                    // 127 * 128: largest |t|
-static_assert(kD8StageBytes % 1024 == 0, "every stage starts on a swizzle-atom boundary");
-static_assert(kD8ABase + kD8AStages * 64 == 512, "tensor memory is used in full");
-static_assert(kD8MetaSlots >= kD8Stages + 2 && kD8Stages % 2 == 0, "see the meta ring / two producers");
+static_assert(kD8SzOff + 512 + 128 <= kD8StageBytes && kD8StageBytes % 1024 == 0, "stage layout");
+static_assert(kD8XloOff + 1024 <= kD8StageBytes, "the rows the tensor core reads behind a tile stay inside the stage");
+static_assert(kD8ABase + kD8AStages * 64 == kD8TmemCols, "tensor memory columns");
 
 template <int MR> struct D8Cfg {
   static_assert(MR == 1 || MR == 2 || MR == 4, "rows per call class");
@@ -64,7 +78,7 @@ template <int MR> struct D8Cfg {
   static constexpr int kCombOff = kD8Stages * kD8StageBytes;
   static constexpr int kMetaOff = kCombOff + kCombBytes;
   static constexpr int kBarOff = kMetaOff + ((kMetaBytes + 15) / 16) * 16;
-  static constexpr int kNumBars = 3 * kD8Stages + 2 * kD8AStages + 4 * kD8Windows + kD8MetaSlots;
+  static constexpr int kNumBars = 3 * kD8Stages + 2 * kD8AStages + 2 * kD8Windows + kD8MetaSlots;
   static constexpr int kSmemBytes = kBarOff + kNumBars * 8 + 1024 /*align*/;
 };
 
@@ -129,6 +143,24 @@ __device__ __forceinline__ void tcgen05_mma_i8_unit_commit3_warp(uint32_t d_hi, 
       : "memory");
 }
 
+// The same four MMAs without commits (the first half of a unit).
+__device__ __forceinline__ void tcgen05_mma_i8_half_warp(uint32_t d_hi, uint32_t d_lo, uint32_t a_hi, uint32_t a_lo,
+                                                         uint64_t b_hi, uint64_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [%3], %5, %6, p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
+      "add.u32 a, %3, 8;\n\t  mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [a], d, %6, p;\n\t}"
+      ::"r"(d_hi), "r"(d_lo), "r"(a_hi), "r"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc)
+      : "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void d8_tmem_ld(uint32_t taddr, uint32_t (&v)[N]) {
   static_assert(N == 2 || N == 4 || N == 8 || N == 16, "columns per load");
@@ -151,7 +183,7 @@ __device__ __forceinline__ void d8_tmem_ld(uint32_t taddr, uint32_t (&v)[N]) {
 }
 
 template <int MR>
-__global__ void __launch_bounds__(kD8Threads, 1)
+__global__ void __launch_bounds__(kD8Threads, kD8CtasPerSm)
 decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   using Cfg = D8Cfg<MR>;
   constexpr int NT = kD8Stages, NA = kD8AStages, NW = kD8Windows, NS = kD8MetaSlots;
@@ -163,17 +195,17 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   auto stage_addr = [&](int t) { return base + t * kD8StageBytes; };
-  float* comb = reinterpret_cast<float*>(base_ptr + Cfg::kCombOff);          // [3][MR][256]
+  float* comb = reinterpret_cast<float*>(base_ptr + Cfg::kCombOff);          // [MR][256]: group 1's sums
   int2* meta = reinterpret_cast<int2*>(base_ptr + Cfg::kMetaOff);            // [NS][MR]: (bits of sx, T)
   const uint32_t bar_base = base + Cfg::kBarOff;
   auto bar_full_tma = [&](int t) { return bar_base + 8u * t; };             // weights, scales, zeros landed
-  auto bar_empty = [&](int t) { return bar_base + 8u * (NT + t); };         // 4 unpack warps + 2 MMA commits
+  auto bar_empty = [&](int t) { return bar_base + 8u * (NT + t); };         // 4 unpack warps + the MMA commit
   auto bar_xq_full = [&](int t) { return bar_base + 8u * (2 * NT + t); };   // activation tiles written
   auto bar_a_full = [&](int a) { return bar_base + 8u * (3 * NT + a); };
   auto bar_a_empty = [&](int a) { return bar_base + 8u * (3 * NT + NA + a); };
-  auto bar_win_full = [&](int h, int w) { return bar_base + 8u * (3 * NT + 2 * NA + h * NW + w); };
-  auto bar_win_empty = [&](int h, int w) { return bar_base + 8u * (3 * NT + 2 * NA + 2 * NW + h * NW + w); };
-  auto bar_meta_full = [&](int s) { return bar_base + 8u * (3 * NT + 2 * NA + 4 * NW + s); };
+  auto bar_win_full = [&](int w) { return bar_base + 8u * (3 * NT + 2 * NA + w); };
+  auto bar_win_empty = [&](int w) { return bar_base + 8u * (3 * NT + 2 * NA + NW + w); };
+  auto bar_meta_full = [&](int s) { return bar_base + 8u * (3 * NT + 2 * NA + 2 * NW + s); };
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -182,25 +214,23 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
     s_abort = 0;
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_full_tma(t), 1);
-      mbar_init(bar_empty(t), kD8UnpackWarps / kD8Groups + 2);
+      mbar_init(bar_empty(t), kD8UnpackWarps / kD8Groups + 1);
       mbar_init(bar_xq_full(t), 1);
     }
     for (int a = 0; a < NA; ++a) {
       mbar_init(bar_a_full(a), kD8UnpackWarps / kD8Groups);
-      mbar_init(bar_a_empty(a), 2);
+      mbar_init(bar_a_empty(a), 1);
     }
-    for (int h = 0; h < 2; ++h) {
-      for (int w = 0; w < NW; ++w) {
-        mbar_init(bar_win_full(h, w), 1);
-        mbar_init(bar_win_empty(h, w), 4);
-      }
+    for (int w = 0; w < NW; ++w) {
+      mbar_init(bar_win_full(w), 1);
+      mbar_init(bar_win_empty(w), kD8UnpackWarps / kD8Groups);
     }
     for (int s = 0; s < NS; ++s) mbar_init(bar_meta_full(s), 1);
     mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
-                 "r"(512u)
+                 "r"(static_cast<uint32_t>(kD8TmemCols))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -217,68 +247,61 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   constexpr uint32_t kIdesc = make_i8_idesc(128, 16);
   const bool sz_by_copy = (p.N & 31) == 0;
 
-  if (warp == 0 || warp == kD8Producer2Warp) {
-    // ------------------------------ copy producers ----------------------------
+  if (warp == 0) {
+    // ------------------------------ copy producer ------------------------------
     // Weights, scales and zero words are constant data: the first ring fill starts before the wait on the
-    // previous kernel of the stream.
-    const int my_parity = warp == 0 ? 0 : 1;
+    // previous kernel of the stream.  Lanes 2, 3, 4 each issue one of a unit's three copies.
     if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-    int tile, kb;
-    {
-      const long long u = u0 + my_parity;
-      tile = static_cast<int>(u / nblk);
-      kb = static_cast<int>(u - static_cast<long long>(tile) * nblk);
-    }
+    int tile = static_cast<int>(u0 / nblk);
+    int kb = static_cast<int>(u0 - static_cast<long long>(tile) * nblk);
     const int group_blocks = p.group_size / kBlockK;
-    auto advance = [&]() {
-      kb += 2;
-      while (kb >= nblk) { kb -= nblk; ++tile; }
-    };
-    auto issue = [&](int gs, int tile_, int kb_) {
-      const int n0 = tile_ * kD8BN;
+    auto issue = [&](int gs) {
+      const int n0 = tile * kD8BN;
       const int ncols = min(kD8BN, p.N - n0);
       const int t = gs % NT;
       const uint32_t bar = bar_full_tma(t);
       const uint32_t dst = stage_addr(t);
       if (lane == 0) mbar_expect_tx(bar, kD8RawBytes + (sz_by_copy ? ncols * 2 + ncols / 2 : 0));
-      if (lane == 2) tma_load_3d(dst + kD8RawOff, &map_w, 0, n0, kb_, bar);
+      if (lane == 2) tma_load_3d(dst + kD8RawOff, &map_w, 0, n0, kb, bar);
       if (sz_by_copy && (lane == 3 || lane == 4)) {
-        const int grp = group_blocks == 1 ? kb_ : kb_ / group_blocks;
+        const int grp = group_blocks == 1 ? kb : kb / group_blocks;
         if (lane == 3) bulk_load(dst + kD8SzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar);
         else bulk_load(dst + kD8SzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3), ncols / 2, bar);
       }
+      if (++kb == nblk) { kb = 0; ++tile; }
     };
-    int next = my_parity;
-    for (; next < NT && next < my_units; next += 2) { issue(next, tile, kb); advance(); }
+    int next = 0;
+    for (; next < NT && next < my_units; ++next) issue(next);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    for (; next < my_units; next += 2) {
+    for (; next < my_units; ++next) {
       if (!mbar_wait(bar_empty(next % NT), static_cast<uint32_t>(next / NT - 1) & 1u, abort_flag, 1)) break;
-      issue(next, tile, kb);
-      advance();
+      issue(next);
     }
-    const int issued_end = next < my_units ? next : my_units;
-    for (int gs = my_parity; gs < issued_end; gs += 2)
-      if (gs + NT >= issued_end) mbar_wait_timed(bar_full_tma(gs % NT), static_cast<uint32_t>(gs / NT) & 1u);
+    // Do not leave while a copy may still be writing shared memory: wait (bounded) for the last ring's worth.
+    for (int gs = max(0, next - NT); gs < next; ++gs)
+      mbar_wait_timed(bar_full_tma(gs % NT), static_cast<uint32_t>(gs / NT) & 1u);
     __syncwarp();
-  } else if (warp == 1 || warp == kD8Issuer2Warp) {
-    // ------------------------------ MMA issuers --------------------------------
-    const int h = warp == 1 ? 0 : 1;
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    // Warp-uniform loop, one elected lane issues.  Every unit gets fresh accumulators in window gs % 2, which
+    // its group has read back (for unit gs - 2) before it signalled this unit's operands.
     for (int gs = 0; gs < my_units; ++gs) {
       const int t = gs % NT, a = gs % NA, w = gs % NW;
-      if (!mbar_wait(bar_win_empty(h, w), (static_cast<uint32_t>(gs / NW) & 1u) ^ 1u, abort_flag, 2)) break;
+      if (!mbar_wait(bar_win_empty(w), (static_cast<uint32_t>(gs / NW) & 1u) ^ 1u, abort_flag, 2)) break;
       if (!mbar_wait(bar_xq_full(t), static_cast<uint32_t>(gs / NT) & 1u, abort_flag, 3)) break;
       if (!mbar_wait(bar_a_full(a), static_cast<uint32_t>(gs / NA) & 1u, abort_flag, 4)) break;
       tcgen05_fence_after();
-      const uint32_t win = tmem_base + static_cast<uint32_t>(w * 64 + h * 32);
-      const uint32_t opd = tmem_base + static_cast<uint32_t>(kD8ABase + a * 64 + h * 32);
-      tcgen05_mma_i8_unit_commit3_warp(win, win + 16, opd, opd + 16, make_sw64_desc(stage_addr(t) + kD8XhiOff),
-                                       make_sw64_desc(stage_addr(t) + kD8XloOff), kIdesc, bar_empty(t), bar_a_empty(a),
-                                       bar_win_full(h, w));
+      const uint32_t win = tmem_base + static_cast<uint32_t>(w * 64);
+      const uint32_t opd = tmem_base + static_cast<uint32_t>(kD8ABase + a * 64);
+      const uint64_t b_hi = make_sw64_desc(stage_addr(t) + kD8XhiOff), b_lo = make_sw64_desc(stage_addr(t) + kD8XloOff);
+      tcgen05_mma_i8_half_warp(win, win + 16, opd, opd + 16, b_hi, b_lo, kIdesc);
+      tcgen05_mma_i8_unit_commit3_warp(win + 32, win + 48, opd + 32, opd + 48, b_hi, b_lo, kIdesc, bar_empty(t),
+                                       bar_a_empty(a), bar_win_full(w));
     }
     __syncwarp();
   } else if (warp >= kD8HelperWarp0) {
     // ------------------------------ activation helpers -------------------------
-    // Unit by unit (every fourth unit per warp): the M rows of this unit's 128 activations -> two planes of
+    // Unit by unit (alternate units per warp): the M rows of this unit's 128 activations -> two planes of
     // signed bytes in the order of the weight bytes they multiply.  Word j of a column holds k = 8j + e at
     // nibble (e >> 1) + 4 (e & 1), so byte b of that word carries k = 8j + {0, 4, 1, 5}[b] in its low nibble and
     // k = 8j + {2, 6, 3, 7}[b] in its high nibble.  Lane = (row parity, word j): 16 lanes share a row.
@@ -350,7 +373,9 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
           lo2 |= static_cast<uint32_t>((tl - (l1 << 7)) & 0xff) << (8 * b);
         }
         if (m < MR) {
-          // tile row r: 64 bytes, 16-byte chunk c at chunk position c ^ ((r >> 1) & 3)
+          // tile row r: 64 bytes, 16-byte chunk c at chunk position c ^ ((r >> 1) & 3).  The (sx, T) ring: slot
+          // gs % 8 was last used by unit gs - 8, whose fold preceded MMA(gs - 6) (same accumulator window),
+          // which preceded the release of stage gs - 5 that this warp has just waited for.
           const int r1 = m, r2 = MR + m;
           const uint32_t o1 = static_cast<uint32_t>(r1 * 64 + (((jw >> 2) ^ ((r1 >> 1) & 3)) << 4) + (jw & 3) * 4);
           const uint32_t o2 = static_cast<uint32_t>(r2 * 64 + (((jw >> 2) ^ ((r2 >> 1) & 3)) << 4) + (jw & 3) * 4);
@@ -372,10 +397,10 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   } else {
     // ---------------------- mask into tensor memory, then fold accumulators ---------------
     asm volatile("griddepcontrol.wait;" ::: "memory");   // y and the workspace belong to the previous kernel until here
-    const int id = tid - 64;                  // 0..511
-    const int dq_warp = id >> 5;              // 0..15
+    const int id = tid - 64;                  // 0..255
+    const int dq_warp = id >> 5;              // 0..7
     const int lane_q = warp & 3;              // TMEM lane quarter this warp may touch
-    const int grp = dq_warp >> 2;             // 0..3; four consecutive warps cover the four quarters
+    const int grp = dq_warp >> 2;             // 0..1; four consecutive warps cover the four quarters
     const int cl0 = lane_q * 32 + lane;       // column within a 128-column half
     const uint32_t lane_addr = static_cast<uint32_t>(lane_q * 32) << 16;
     const int zcols = p.N >> 3;
@@ -412,26 +437,31 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
         if (pend < 0) return;
         const int w = pend % NW, s = pend % NS;
         if (ok && !mbar_wait(bar_meta_full(s), static_cast<uint32_t>(pend / NS) & 1u, abort_flag, 9)) ok = false;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (ok && !mbar_wait(bar_win_full(h, w), static_cast<uint32_t>(pend / NW) & 1u, abort_flag, 6)) ok = false;
-          if (!ok) continue;
+        if (ok && !mbar_wait(bar_win_full(w), static_cast<uint32_t>(pend / NW) & 1u, abort_flag, 6)) ok = false;
+        if (ok) {
           tcgen05_fence_after();
-          uint32_t vh[2 * MR], vl[2 * MR];
-          const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * 64 + h * 32);
-          d8_tmem_ld<2 * MR>(win, vh);
-          d8_tmem_ld<2 * MR>(win + 16, vl);
+          uint32_t vh[2][2 * MR], vl[2][2 * MR];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * 64 + h * 32);
+            d8_tmem_ld<2 * MR>(win, vh[h]);
+            d8_tmem_ld<2 * MR>(win + 16, vl[h]);
+          }
           tcgen05_wait_ld();
           tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_win_empty(h, w));
+          if (lane == 0) mbar_arrive(bar_win_empty(w));
 #pragma unroll
           for (int m = 0; m < MR; ++m) {
             const int2 mt = meta[s * MR + m];                  // same address in every lane: a broadcast
-            const int dhi = (static_cast<int>(vh[m]) << 7) + static_cast<int>(vh[MR + m]);    // a multiple of 16
-            const int dlo = (static_cast<int>(vl[m]) << 7) + static_cast<int>(vl[MR + m]);
-            const int val = (dhi >> 4) + dlo - pend_z[h] * mt.y;
-            acc[h][m] = fmaf(pend_s[h] * __int_as_float(mt.x), static_cast<float>(val), acc[h][m]);
+            const float sx = __int_as_float(mt.x);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int dhi = (static_cast<int>(vh[h][m]) << 7) + static_cast<int>(vh[h][MR + m]);    // a multiple of 16
+              const int dlo = (static_cast<int>(vl[h][m]) << 7) + static_cast<int>(vl[h][MR + m]);
+              const int val = (dhi >> 4) + dlo - pend_z[h] * mt.y;
+              acc[h][m] = fmaf(pend_s[h] * sx, static_cast<float>(val), acc[h][m]);
+            }
           }
         }
         pend = -1;
@@ -441,7 +471,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
         if ((gs & (kD8Groups - 1)) != grp) continue;             // another group's unit
         const int t = gs % NT, a = gs % NA;
         const uint32_t ph = static_cast<uint32_t>(gs / NT) & 1u, pha = static_cast<uint32_t>(gs / NA) & 1u;
-        fold_pending();                                          // this group's previous unit, four units back
+        fold_pending();                                          // this group's previous unit, two units back
         if (!sz_by_copy) {
           const int qgrp = ((kb0 + j) * kBlockK) / p.group_size;
           if (qgrp != sz_group) {
@@ -514,7 +544,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       // ------------------------------ segment epilogue ------------------------
       d8_unpack_warps_sync();
       if (grp != 0) {
-        float* cb = comb + (grp - 1) * (MR * kD8BN);
+        float* cb = comb;
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -534,7 +564,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
           for (int m = 0; m < MR; ++m) {
             if (m < p.M) {                                 // warp-uniform
               const float* cb = comb + m * kD8BN + h * 128 + cl0;
-              const float val = ((acc[h][m] + cb[0]) + cb[MR * kD8BN]) + cb[2 * MR * kD8BN];
+              const float val = acc[h][m] + cb[0];
               if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, ncol[h], val, nval[h]);
               else if (nval[h]) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + ncol[h], val);
             }
@@ -578,7 +608,9 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(kD8TmemCols))
+                 : "memory");
   }
   if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, 0x400u | static_cast<unsigned>(s_abort));
 }
@@ -586,11 +618,16 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
+static long long decode_grid(int sm_count, long long units) {
+  const long long ctas = static_cast<long long>(kD8CtasPerSm) * sm_count;
+  return units < ctas ? units : ctas;
+}
+
 // Largest number of CTAs that share one column tile (= partial slots needed).
 static int decode_slots(int K, int N, int sm_count) {
   const int nblk = K / kBlockK, ntiles = (N + kD8BN - 1) / kD8BN;
   const long long U = static_cast<long long>(ntiles) * nblk;
-  const long long G = U < sm_count ? U : sm_count;
+  const long long G = decode_grid(sm_count, U);
   int worst = 1;
   for (int t = 0; t < ntiles; ++t) {
     const long long a = static_cast<long long>(t) * nblk;
@@ -624,6 +661,9 @@ static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTile
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
   }
   AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  // two CTAs of ~100 KB per SM: ask for the largest shared-memory carve-out
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kD8Threads);
@@ -674,7 +714,7 @@ int decode_i8_dispatch(const void* x, const void* packed, const void* scales, co
   p.ntiles = ntiles;
   p.nblk = K / kBlockK;
   p.units = static_cast<long long>(ntiles) * p.nblk;
-  const int grid = static_cast<int>(p.units < di.sm_count ? p.units : di.sm_count);
+  const int grid = static_cast<int>(decode_grid(di.sm_count, p.units));
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
   if (M <= 1) return launch_decode_i8<1>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   if (M <= 2) return launch_decode_i8<2>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
