@@ -379,6 +379,55 @@ AWQ_B200_API int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weig
 AWQ_B200_API int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
                          void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * The reference extension's other quantized linears: FP8 (e4m3) and SmoothQuant INT8, 8-bit x 8-bit GEMMs with a
+ * scaling epilogue.  Operands arrive quantised, as they do in the reference: activations xq [M, K] row-major with
+ * a row pitch of ldx bytes; weights wq [N, K] row-major with a row pitch of ldw bytes (the memory behind the
+ * `[K, N]`, stride `[1, K]` view the reference passes).  Pitches are multiples of 16 bytes and >= K; xq and wq
+ * are 16-byte aligned.  bias_kind: 0 none (bias NULL), 1 bf16, 2 fp16, 3 fp32.  `status` (optional, device word)
+ * receives a non-zero code if a bounded wait inside the kernel ran out.
+ * --------------------------------------------------------------------------------------------------------------- */
+
+/* y[M, N] = alpha' * (xq . wq^T) + beta * bias, fp32 accumulation, y bf16 (out_bf16 != 0) or fp16.
+ * alpha' = alpha * (*alpha_dev) * (*alpha_dev2); either pointer may be NULL.  They let a dynamic activation scale
+ * and a weight-scale parameter stay on the device: the reference multiplies the two on the device and reads the
+ * product back to pass it as a float (linear_fp8.py:216-225).
+ * Replaces cutlass_f8f8bf16_tensorwise_sm89(XQ, WQ, bias, alpha, beta, dtype_str)
+ * (LLMQRT/runtime_refact/csrc/bindings.cpp:15-17; csrc/fp8/sm89_fp8_tensorwise_cutlassgemm.cu:30-160, :316-328). */
+AWQ_B200_API int awq_b200_fp8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias,
+                                 int bias_kind, void* y, int M, int N, int K, float alpha, const float* alpha_dev,
+                                 const float* alpha_dev2, float beta, int out_bf16, unsigned* status,
+                                 awq_b200_stream_t stream);
+
+/* y[M, N] bf16 = ((xq . wq^T) * x_scale[m]) * w_scale[n] + bias[n]; xq e4m3 or e5m2 (x_is_e5m2), wq e4m3.
+ * Replaces cutlass_f8f8bf16_rowwise_sm89(XQ, WQ, bias, x_scale, w_scale, use_fast_accum)
+ * (csrc/bindings.cpp:18-20; csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:425-2248).  The accumulator is always fp32 in
+ * tensor memory, so use_fast_accum has nothing to select. */
+AWQ_B200_API int awq_b200_fp8_gemm_rowwise(const void* xq, int ldx, int x_is_e5m2, const void* wq, int ldw,
+                              const void* bias, int bias_kind, const float* x_scale, const float* w_scale, void* y,
+                              int M, int N, int K, unsigned* status, awq_b200_stream_t stream);
+
+/* y[M, N] = alpha' * float(int32(xq . wq^T)) + beta * bias; xq, wq int8; exact int32 accumulation.
+ * Replaces w8a8_int8_linear_bbf16_obf16_per_tensor(input, weight, bias, alpha, beta)
+ * (csrc/bindings.cpp:12-14; csrc/smoothquant/sq_gemm.cu:30-190), whose output element type is fp16. */
+AWQ_B200_API int awq_b200_int8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias,
+                                  int bias_kind, void* y, int M, int N, int K, float alpha, const float* alpha_dev,
+                                  const float* alpha_dev2, float beta, int out_bf16, unsigned* status,
+                                  awq_b200_stream_t stream);
+
+/* Activation quantisation in front of those GEMMs, with the roundings of the reference's torch expressions run on
+ * a GPU.  x [M, K] fp16 or bf16 (x_is_bf16), contiguous, 16-byte aligned, K % 8 == 0; xq [M, K] bytes.
+ *   mode 0  e4m3, one dynamic scale:  per_tensor_quantize        (linear_fp8.py:11-33)     scale_out[0] = scale
+ *   mode 1  e4m3, one scale per row:  per_token_quantize         (linear_fp8.py:41-64)     scale_out[m] = scale
+ *   mode 2  e4m3, given fp32 scale *static_scale: static_per_tensor_quantize (linear_fp8.py:35-38)
+ *   mode 3  int8, one dynamic scale:  quantize_activation_per_tensor_absmax (linear_sq.py:19-28)
+ *           scale_out[0] = scale, scale_out[1] = scale * weight_scale rounded to x's type (linear_sq.py:97)
+ * amax_ws: one device word of scratch (modes 0 and 3).  An all-zero fp16 tensor, which the reference turns into
+ * NaNs (its scale underflows to 0), quantises to zeros here. */
+AWQ_B200_API int awq_b200_q8_quantize(const void* x, int x_is_bf16, int M, int K, int mode, const float* static_scale,
+                         float weight_scale, void* xq, float* scale_out, unsigned* amax_ws,
+                         awq_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

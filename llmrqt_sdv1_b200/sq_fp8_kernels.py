@@ -4,8 +4,8 @@ order and return shapes for the five AWQ entry points, backed by the sm_100a
 kernels.  The arguments are the ON-DISK tensors; the kernel-layout repack is
 done once per weight tensor and cached on the tensor's identity.
 
-The three non-AWQ names exist only so that the reference's `linear` package
-imports (linear_fp8.py:7-8, linear_sq.py:14); calling them raises.
+The three non-AWQ entry points (FP8 tensorwise / rowwise, SmoothQuant INT8) keep the
+reference's names, `_sm89` included, and run 8-bit tensor-memory GEMMs.
 """
 from __future__ import annotations
 
@@ -13,7 +13,7 @@ import weakref
 
 import torch
 
-from . import kernels
+from . import kernels, q8
 
 _cache: dict[int, tuple] = {}
 
@@ -85,13 +85,34 @@ def awq_gemm_cutlass(in_feats, kernel, scaling_factors, zeros, split_k_iters=8):
     return awq_gemm(in_feats, kernel, scaling_factors, zeros, split_k_iters)
 
 
-def _not_awq(name):
-    def fn(*_a, **_k):
-        raise NotImplementedError(f"{name}: only the AWQ W4A16 path is implemented for sm_100a")
-    fn.__name__ = name
-    return fn
+_DTYPE_STR = {"bfloat16": torch.bfloat16, "float16": torch.float16}
 
 
-cutlass_f8f8bf16_tensorwise_sm89 = _not_awq("cutlass_f8f8bf16_tensorwise_sm89")
-cutlass_f8f8bf16_rowwise_sm89 = _not_awq("cutlass_f8f8bf16_rowwise_sm89")
-w8a8_int8_linear_bbf16_obf16_per_tensor = _not_awq("w8a8_int8_linear_bbf16_obf16_per_tensor")
+def cutlass_f8f8bf16_tensorwise_sm89(XQ, WQ, bias, alpha, beta, dtype_str):
+    """[M, K] e4m3 x [K, N] e4m3 (stride [1, K]) -> [M, N] `dtype_str`: alpha * (XQ @ WQ) + beta * bias
+    (csrc/fp8/sm89_fp8_tensorwise_cutlassgemm.cu:316-328; checks :272-311, dtype dispatch :228-262).  The name is
+    the reference's; the kernel is an sm_100a one.  `alpha` may also be a one-element CUDA tensor, which is then
+    read on the device instead of being converted to a python float (the reference's binding forces that read)."""
+    if dtype_str not in _DTYPE_STR:
+        raise RuntimeError(f"currently only support bf16 or fp16 output dtype, the passed dtype is {dtype_str}")
+    out_dtype = _DTYPE_STR[dtype_str]
+    if bias is not None and bias.dtype != out_dtype:
+        raise RuntimeError("if bias has value, dtype passed in should same as bias dtype")
+    return q8.gemm_tensorwise(XQ, WQ, bias, alpha, beta, out_dtype)
+
+
+def cutlass_f8f8bf16_rowwise_sm89(XQ, WQ, bias, x_scale, w_scale, use_fast_accum=True):
+    """[M, K] e4m3 / e5m2 x [K, N] e4m3 -> [M, N] bf16: (XQ @ WQ) * x_scale[M, 1] * w_scale[1, N] + bias
+    (csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:2222-2248; checks :2170-2218).  `use_fast_accum` selected between two
+    accumulation schemes of the sm_89 kernel; here the accumulator is always fp32 in tensor memory."""
+    return q8.gemm_rowwise(XQ, WQ, bias, x_scale, w_scale)
+
+
+def w8a8_int8_linear_bbf16_obf16_per_tensor(input, weight, bias, alpha, beta):
+    """[M, K] int8 x [K, N] int8 (stride [1, K]) -> [M, N]: alpha * int32(input @ weight) + beta * bias
+    (csrc/smoothquant/sq_gemm.cu:30-190).  The reference requires a bias tensor (zeros when the layer has none),
+    writes fp16 whatever the bias dtype and reads a bf16 bias as if it were fp16; here the output takes the
+    bias's dtype (fp16 or bf16) and a bf16 bias is read as bf16."""
+    if bias is None:
+        raise RuntimeError("w8a8_int8_linear_bbf16_obf16_per_tensor: bias is required (pass zeros)")
+    return q8.gemm_tensorwise(input, weight, bias, alpha, beta, bias.dtype, int8=True)
