@@ -288,6 +288,68 @@ def decode_detail(torch, kernels, quantize, peaks):
     return rows
 
 
+def q8_detail(torch, peaks):
+    """The other quantized linears of the reference extension (FP8 e4m3, SmoothQuant INT8) on 70B-sized layers.
+    Decode rows (M in {1, 16}) against the HBM peak: bytes = 8-bit weights + activations + 16-bit output, weights
+    rotated over more than 2x L2.  Prefill rows (M in {2048, 8192}) in TFLOP/s; MEASURED_PEAKS holds no 8-bit
+    figure, so the fraction is of twice the measured bf16 burst (the ratio of the two nominal dense peaks), with
+    the library's own FP8 GEMM (torch._scaled_mm) timed beside it.  `module_us` is a whole FP8DynamicLinear forward
+    (activation quantisation + GEMM)."""
+    from llmrqt_sdv1_b200 import q8
+    from llmrqt_sdv1_b200.linear_fp8 import FP8NativeDynamicLinear
+    rows = []
+    one = torch.tensor(1.0, device="cuda")
+    for name, N, K in (("qkvo", 8192, 8192), ("gate_up", 57344, 8192), ("down", 8192, 28672)):
+        copies = max(2, min(8, (300 << 20) // (N * K) + 1))
+        wf = [torch.randn(N, K, device="cuda").mul_(0.5).to(torch.float8_e4m3fn) for _ in range(copies)]
+        wi = [w.view(torch.int8) for w in wf]
+        mod = FP8NativeDynamicLinear(K, N, False, dev="cuda", dtype=torch.bfloat16)
+        mod.weight.data = wf[0]
+        mod.weight_scale.data.fill_(0.01)
+        for M in (1, 16, 2048, 8192):
+            xb = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            xf = xb.to(torch.float8_e4m3fn)
+            xi = xf.view(torch.int8)
+            ob = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            oh = torch.empty(M, N, device="cuda", dtype=torch.float16)
+            bias = torch.zeros(N, device="cuda", dtype=torch.float16)
+            min_ms = 50.0 if M >= 2048 else 4.0
+
+            def run_fp8():
+                for w in wf:
+                    q8.gemm_tensorwise(xf, w.t(), None, 0.5, 1.0, torch.bfloat16, out=ob)
+
+            def run_int8():
+                for w in wi:
+                    q8.gemm_tensorwise(xi, w.t(), bias, 1e-4, 1.0, torch.float16, int8=True, out=oh)
+
+            def run_lib():
+                for w in wf:
+                    torch._scaled_mm(xf, w.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            t_f = time_graph(torch, run_fp8, iters=3, min_ms=min_ms) / copies
+            t_i = time_graph(torch, run_int8, iters=3, min_ms=min_ms) / copies
+            t_m = time_graph(torch, lambda: mod(xb), iters=3, min_ms=min_ms)
+            try:
+                t_l = time_graph(torch, run_lib, iters=3, min_ms=min_ms) / copies if M >= 16 else None
+            except Exception:
+                t_l = None
+            flops, nbytes = 2.0 * M * N * K, N * K + M * K + 2 * M * N
+            row = {"linear": name, "N": N, "K": K, "M": M, "fp8_us": round(t_f * 1e3, 2), "int8_us": round(t_i * 1e3, 2),
+                   "module_us": round(t_m * 1e3, 2), "scaled_mm_us": round(t_l * 1e3, 2) if t_l else None}
+            if M <= 16:
+                row.update(fp8_gbs=round(nbytes / t_f / 1e6, 1), int8_gbs=round(nbytes / t_i / 1e6, 1),
+                           fp8_frac_hbm=round(nbytes / t_f / 1e6 / peaks["hbm_gbs"], 4))
+            else:
+                row.update(fp8_tflops=round(flops / t_f / 1e9, 1), int8_tops=round(flops / t_i / 1e9, 1),
+                           scaled_mm_tflops=round(flops / t_l / 1e9, 1) if t_l else None,
+                           fp8_frac_2x_bf16_burst=round(flops / t_f / 1e9 / (2 * peaks["tflops"]), 4))
+            rows.append(row)
+        require_clean(torch, "q8_detail", q8=q8.status())
+        del wf, wi, mod
+        torch.cuda.empty_cache()
+    return rows
+
+
 def mlp_fusion_detail(torch, kernels, quantize):
     """The MLP of the decode configuration (hidden 2048, intermediate 6144) over 28 layers of distinct weights
     (0.5 GB > L2), `h = h + down(silu(gate(h)) * up(h))`, as the three linears plus separate elementwise
@@ -498,6 +560,7 @@ def detail_tables(line, args, torch, peaks):
     require_clean(torch, "decode_detail", gemv=kernels.gemv_status(), gemm=kernels.gemm_status())
     line["prefill_detail"] = prefill_detail(torch, kernels, quantize, peaks)
     line["mlp_fusion"] = mlp_fusion_detail(torch, kernels, quantize)
+    line["q8_detail"] = q8_detail(torch, peaks)
     require_clean(torch, "prefill_detail / mlp_fusion", gemv=kernels.gemv_status(), gemm=kernels.gemm_status())
     best = max(line["prefill_detail"], key=lambda r: r["tflops"])
     # Each shape is timed in repetitions of back-to-back launches, i.e. under the power cap: the sustained

@@ -9,12 +9,17 @@
 //   rowwise     y = (x . w^T) * x_scale[m] * w_scale[n] + bias    cutlass_f8f8bf16_rowwise_sm89
 //                                                            (LLMQRT/runtime_refact/csrc/fp8/sm89_fp8_rowwise_fbgemm.cu:425-2248)
 //
-// One persistent kernel: CTA tile = 256 weight rows (two tcgen05 M = 128 halves: the weights are the A operand, so
-// a thread's tensor-memory lane is an output column) x MT activation rows (the MMA's N), K walked in stages of 128
-// bytes.  Warp 0 copies both operands with TMA (128-byte swizzle), warp 1 issues the MMAs (K = 32 per instruction,
-// 8 per stage), warps 2..9 drain the accumulators: two accumulator sets in tensor memory, so the epilogue of a tile
-// overlaps the MMAs of the next.  No quantisation happens here: the operands arrive quantised, as in the reference.
-// Every mbarrier wait is bounded (see awq_ptx.cuh).
+// One persistent kernel: CTA tile = 128 or 256 weight rows (one or two tcgen05 M = 128 halves: the weights are the A
+// operand, so a thread's tensor-memory lane is an output column) x MT activation rows (the MMA's N), K walked in
+// stages of 128 bytes.  Warp 0 copies both operands with TMA (128-byte swizzle), warp 1 issues the MMAs (K = 32 per
+// instruction), warps 2..9 drain the accumulators: two accumulator sets in tensor memory, so the epilogue of a work
+// item overlaps the MMAs of the next.  No quantisation happens here: the operands arrive quantised, as in the
+// reference.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+//
+// Few rows make few tiles (a decode step has N / 128 of them), so a tile's K range can be split over several CTAs:
+// each writes its 32-bit partial sums to a workspace, takes a ticket on the tile's counter, and the CTA that draws
+// the last ticket adds the partials IN SPLIT ORDER (its own included, re-read from the workspace), so the result
+// does not depend on which CTA finished last; int32 partials are exact in any order.  The counter goes back to 0.
 #include <cuda_bf16.h>
 
 #include "awq_common.cuh"
@@ -24,17 +29,24 @@
 namespace awq {
 
 constexpr int kQ8Threads = 64 + 256;         // producer, issuer, 8 epilogue warps
-constexpr int kQ8BN = 256;                   // weight rows (output columns) per tile
 constexpr int kQ8BK = 128;                   // bytes of K per stage
-constexpr int kQ8ABytes = kQ8BN * kQ8BK;     // 32 KiB
+constexpr int kQ8CounterBytes = 4096;        // workspace head: one ticket counter per split tile
+constexpr int kQ8MaxSplitTiles = kQ8CounterBytes / 4;
 
-template <int MT> struct Q8Cfg {
+// MT activation rows and HALVES x 128 weight rows per tile.
+template <int MT, int HALVES> struct Q8Cfg {
   static_assert(MT == 32 || MT == 128, "activation rows per tile");
+  static_assert(HALVES == 1 || HALVES == 2, "weight rows per tile: 128 or 256");
+  static constexpr int kBN = 128 * HALVES;
+  static constexpr int kABytes = kBN * kQ8BK;
   static constexpr int kBBytes = MT * kQ8BK;
-  static constexpr int kStageBytes = kQ8ABytes + kBBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes >= 6 ? 6 : (200 * 1024) / kStageBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  // small tiles: two CTAs per SM (one drains / reduces while the other streams); large tiles: one
+  static constexpr int kCtasPerSm = (MT == 32 && HALVES == 1) ? 2 : 1;
+  static constexpr int kBudget = kCtasPerSm == 2 ? 104 * 1024 : 200 * 1024;
+  static constexpr int kStages = kBudget / kStageBytes >= 6 ? 6 : kBudget / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-  static constexpr int kAccCols = 2 * MT;                       // one accumulator set: two halves
+  static constexpr int kAccCols = HALVES * MT;                  // one accumulator set
   static constexpr int kTmemCols = 2 * kAccCols <= 32 ? 32 : (2 * kAccCols <= 64 ? 64 : (2 * kAccCols <= 128 ? 128 : (2 * kAccCols <= 256 ? 256 : 512)));
 };
 
@@ -49,6 +61,9 @@ struct Q8Params {
   unsigned* status;
   int M, N, K;
   int mtiles, ntiles;
+  int splits, kper;        // K split: work item = (tile, split), split s walks stages [s * kper, (s + 1) * kper)
+  unsigned* counters;      // [tiles] tickets (splits > 1)
+  uint32_t* partials;      // [tiles][splits][MT][BN] 32-bit partial sums (splits > 1)
   int ldx, ldw;            // row pitches of the activations and of the weights, in bytes
   int rowwise;             // 0 tensorwise, 1 rowwise
   int out_bf16;            // 1 bf16, 0 fp16
@@ -103,18 +118,20 @@ __device__ __forceinline__ void q8_mma_stage_warp(uint32_t d_tmem, uint64_t a_de
   }
 }
 
-template <bool INT8, int MT>
-__global__ void __launch_bounds__(kQ8Threads, 1)
+template <bool INT8, int MT, int HALVES>
+__global__ void __launch_bounds__(kQ8Threads, Q8Cfg<MT, HALVES>::kCtasPerSm)
 q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Q8Params p) {
-  using Cfg = Q8Cfg<MT>;
+  using Cfg = Q8Cfg<MT, HALVES>;
   constexpr int NT = Cfg::kStages;
+  constexpr int BN = Cfg::kBN;
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
+  __shared__ int s_last;
   __shared__ uint32_t s_tmem_base;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   auto a_addr = [&](int t) { return base + t * Cfg::kStageBytes; };
-  auto b_addr = [&](int t) { return base + t * Cfg::kStageBytes + kQ8ABytes; };
+  auto b_addr = [&](int t) { return base + t * Cfg::kStageBytes + Cfg::kABytes; };
   const uint32_t bar_base = base + NT * Cfg::kStageBytes;
   auto bar_full = [&](int t) { return bar_base + 8u * t; };
   auto bar_empty = [&](int t) { return bar_base + 8u * (NT + t); };
@@ -125,6 +142,7 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
+    s_last = 0;
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_full(t), 1);
       mbar_init(bar_empty(t), 1);
@@ -147,8 +165,16 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
   const int nks = (p.K + kQ8BK - 1) / kQ8BK;          // the copy zero-fills the last stage beyond K
-  const int num_tiles = p.mtiles * p.ntiles;
+  const int num_items = p.mtiles * p.ntiles * p.splits;
   const uint32_t kIdesc = p.idesc;
+  // work item -> (column tile, row tile, split); the splits of a tile are neighbours, so they run at the same time
+  auto decode = [&](int item, int* tn, int* tm, int* k0, int* k1) {
+    const int tile = item / p.splits, split = item - tile * p.splits;
+    *tn = tile / p.mtiles;
+    *tm = tile - *tn * p.mtiles;           // row tiles fastest: a wave shares weight tiles
+    *k0 = split * p.kper;
+    *k1 = min(nks, *k0 + p.kper);
+  };
 
   if (warp == 0) {
     // ------------------------------ copy producer ------------------------------
@@ -158,15 +184,16 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int tn = tile / p.mtiles, tm = tile - tn * p.mtiles;     // row tiles fastest: a wave shares weight tiles
-      for (int ks = 0; ks < nks; ++ks, ++it) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      int tn, tm, k0, k1;
+      decode(item, &tn, &tm, &k0, &k1);
+      for (int ks = k0; ks < k1; ++ks, ++it) {
         const int t = it % NT;
         if (it >= static_cast<uint32_t>(NT) &&
             !mbar_wait(bar_empty(t), ((it / NT) - 1u) & 1u, abort_flag, 1)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(bar_full(t), Cfg::kStageBytes);
-          tma_load_2d(a_addr(t), &map_w, ks * kQ8BK, tn * kQ8BN, bar_full(t));
+          tma_load_2d(a_addr(t), &map_w, ks * kQ8BK, tn * BN, bar_full(t));
           tma_load_2d(b_addr(t), &map_x, ks * kQ8BK, tm * MT, bar_full(t));
         }
         __syncwarp();
@@ -179,20 +206,23 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
-    uint32_t it = 0, tile_it = 0;
+    uint32_t it = 0, item_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
-      const uint32_t set = tile_it & 1u;
-      if (!mbar_wait(bar_acc_empty(set), ((tile_it >> 1) & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++item_it) {
+      int tn, tm, k0, k1;
+      decode(item, &tn, &tm, &k0, &k1);
+      const uint32_t set = item_it & 1u;
+      if (!mbar_wait(bar_acc_empty(set), ((item_it >> 1) & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + set * Cfg::kAccCols;
-      for (int ks = 0; ks < nks; ++ks, ++it) {
+      for (int ks = k0; ks < k1; ++ks, ++it) {
         const int t = it % NT;
         if (!mbar_wait(bar_full(t), (it / NT) & 1u, abort_flag, 3)) { ok = false; break; }
         tcgen05_fence_after();
         const uint64_t bd = make_sw128_desc(b_addr(t));
-        q8_mma_stage_warp<INT8>(acc, make_sw128_desc(a_addr(t)), bd, kIdesc, ks != 0 ? 1u : 0u);
-        q8_mma_stage_warp<INT8>(acc + MT, make_sw128_desc(a_addr(t) + 128 * kQ8BK), bd, kIdesc, ks != 0 ? 1u : 0u);
+        q8_mma_stage_warp<INT8>(acc, make_sw128_desc(a_addr(t)), bd, kIdesc, ks != k0 ? 1u : 0u);
+        if constexpr (HALVES == 2)
+          q8_mma_stage_warp<INT8>(acc + MT, make_sw128_desc(a_addr(t) + 128 * kQ8BK), bd, kIdesc, ks != k0 ? 1u : 0u);
         tcgen05_commit_warp(bar_empty(t));
       }
       if (ok) tcgen05_commit_warp(bar_acc_full(set));
@@ -200,21 +230,38 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncwarp();
   } else {
     // ------------------------------ epilogue ------------------------------------
-    // Warp (quarter q, half h): lanes = output columns n0 + h*128 + 32q + lane; 32 accumulator columns (activation
-    // rows) per tensor-memory load.
+    // Warp (quarter q, part h): lanes = output columns n0 + 32q + lane of half h (HALVES == 2: warps 2..5 take half 0,
+    // 6..9 half 1; HALVES == 1: the two warps of a quarter share the accumulator's columns, i.e. the rows of x).
     const int ew = warp - 2;                 // 0..7
     const int lane_q = warp & 3;
-    const int h = ew >> 2;
+    const int part = ew >> 2;                // 0 or 1
+    const int h = HALVES == 2 ? part : 0;
+    constexpr int kRowStep = HALVES == 2 ? 32 : 64;          // rows of x between this warp's 32-row loads
+    const int row_first = HALVES == 2 ? 0 : part * 32;
     const uint32_t lane_addr = static_cast<uint32_t>(lane_q * 32) << 16;
-    uint32_t tile_it = 0;
+    const int col = h * 128 + lane_q * 32 + lane;            // column inside the tile
+    uint32_t item_it = 0;
     bool ok = true;
     float alpha = p.alpha;
     if (!p.rowwise && p.alpha_dev != nullptr) alpha = __fmul_rn(alpha, __ldg(p.alpha_dev));
     if (!p.rowwise && p.alpha_dev2 != nullptr) alpha = __fmul_rn(alpha, __ldg(p.alpha_dev2));
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_it) {
-      const int tn = tile / p.mtiles, tm = tile - tn * p.mtiles;
-      const uint32_t set = tile_it & 1u;
-      const int n = tn * kQ8BN + h * 128 + lane_q * 32 + lane;
+
+    auto finish = [&](uint32_t raw, int m, int n, float ws_n, float bias_n, float beta_bias) {
+      const float a = INT8 ? static_cast<float>(static_cast<int>(raw)) : __uint_as_float(raw);
+      float r;
+      if (p.rowwise) r = __fadd_rn(__fmul_rn(__fmul_rn(a, __ldg(p.x_scale + m)), ws_n), bias_n);
+      else r = fmaf(alpha, a, beta_bias);
+      const size_t at = static_cast<size_t>(m) * p.N + n;
+      if (p.out_bf16) static_cast<__nv_bfloat16*>(p.y)[at] = __float2bfloat16_rn(r);
+      else static_cast<__half*>(p.y)[at] = __float2half_rn(r);
+    };
+
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++item_it) {
+      int tn, tm, k0, k1;
+      decode(item, &tn, &tm, &k0, &k1);
+      const int tile = item / p.splits, split = item - tile * p.splits;
+      const uint32_t set = item_it & 1u;
+      const int n = tn * BN + col;
       const bool nvalid = n < p.N;
       float bias_n = 0.f, ws_n = 1.f;
       if (nvalid) {
@@ -224,33 +271,71 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (p.rowwise) ws_n = __ldg(p.w_scale + n);
       }
       const float beta_bias = __fmul_rn(p.beta, bias_n);
-      if (ok && !mbar_wait(bar_acc_full(set), (tile_it >> 1) & 1u, abort_flag, 4)) ok = false;
+      uint32_t* part_tile = p.partials + static_cast<size_t>(tile) * p.splits * (MT * BN);
+      if (ok && !mbar_wait(bar_acc_full(set), (item_it >> 1) & 1u, abort_flag, 4)) ok = false;
       if (ok) {
         tcgen05_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < MT; c0 += 32) {
+        for (int c0 = row_first; c0 < MT; c0 += kRowStep) {
           if (tm * MT + c0 >= p.M) break;                       // rows beyond M are padding (warp-uniform)
           uint32_t v[32];
           tcgen05_ld_32x32b_x32(tmem_base + lane_addr + set * Cfg::kAccCols + h * MT + c0, v);
           tcgen05_wait_ld();
+          if (p.splits == 1) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int m = tm * MT + c0 + j;
-            if (m < p.M && nvalid) {
-              const float a = INT8 ? static_cast<float>(static_cast<int>(v[j])) : __uint_as_float(v[j]);
-              float r;
-              if (p.rowwise) r = __fadd_rn(__fmul_rn(__fmul_rn(a, __ldg(p.x_scale + m)), ws_n), bias_n);
-              else r = fmaf(alpha, a, beta_bias);
-              const size_t at = static_cast<size_t>(m) * p.N + n;
-              if (p.out_bf16) static_cast<__nv_bfloat16*>(p.y)[at] = __float2bfloat16_rn(r);
-              else static_cast<__half*>(p.y)[at] = __float2half_rn(r);
+            for (int j = 0; j < 32; ++j) {
+              const int m = tm * MT + c0 + j;
+              if (m < p.M && nvalid) finish(v[j], m, n, ws_n, bias_n, beta_bias);
             }
+          } else {
+            uint32_t* dst = part_tile + (static_cast<size_t>(split) * MT + c0) * BN + col;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (tm * MT + c0 + j < p.M) __stcg(dst + static_cast<size_t>(j) * BN, v[j]);
           }
         }
         tcgen05_fence_before();
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty(set));
+      if (p.splits > 1) {
+        // ticket: the CTA that completes the tile adds the partials in split order
+        __threadfence();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ew == 0 && lane == 0) {
+          const unsigned ticket = atomicAdd(p.counters + tile, 1u);
+          s_last = (ticket == static_cast<unsigned>(p.splits) - 1u) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const bool last = s_last != 0;
+        if (last) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = row_first; c0 < MT; c0 += kRowStep) {
+            if (tm * MT + c0 >= p.M) break;
+#pragma unroll 4
+            for (int j = 0; j < 32; ++j) {
+              const int m = tm * MT + c0 + j;
+              if (m >= p.M) break;
+              const uint32_t* src = part_tile + static_cast<size_t>(c0 + j) * BN + col;
+              uint32_t sum;
+              if constexpr (INT8) {
+                int acc = 0;
+                for (int sp = 0; sp < p.splits; ++sp) acc += static_cast<int>(__ldcg(src + static_cast<size_t>(sp) * MT * BN));
+                sum = static_cast<uint32_t>(acc);
+              } else {
+                float acc = __uint_as_float(__ldcg(src));
+                for (int sp = 1; sp < p.splits; ++sp)
+                  acc = __fadd_rn(acc, __uint_as_float(__ldcg(src + static_cast<size_t>(sp) * MT * BN)));
+                sum = __float_as_uint(acc);
+              }
+              if (nvalid) finish(sum, m, n, ws_n, bias_n, beta_bias);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");          // s_last is rewritten by the next item
+        if (last && ew == 0 && lane == 0) p.counters[tile] = 0u;   // ready for the next launch
+      }
     }
   }
 
@@ -265,9 +350,39 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, 0x500u | static_cast<unsigned>(s_abort));
 }
 
-template <bool INT8, int MT>
-static int launch_q8(const void* x, const void* w, Q8Params p, int sm_count, EncodeTiledFn encode, cudaStream_t stream) {
-  using Cfg = Q8Cfg<MT>;
+// How a problem is cut: tile shape by row count, then a K split when the tiles alone would leave SMs idle.
+struct Q8Plan {
+  int mt, halves, mtiles, ntiles, splits, kper;
+  size_t workspace_bytes;
+};
+static Q8Plan q8_plan(int M, int N, int K, int sm_count, bool allow_split) {
+  Q8Plan pl{};
+  pl.mt = M <= 32 ? 32 : 128;
+  pl.halves = M <= 32 ? 1 : 2;
+  const int bn = 128 * pl.halves;
+  const int ctas = (M <= 32 ? 2 : 1) * sm_count;
+  pl.mtiles = (M + pl.mt - 1) / pl.mt;
+  pl.ntiles = (N + bn - 1) / bn;
+  const int tiles = pl.mtiles * pl.ntiles;
+  const int nks = (K + kQ8BK - 1) / kQ8BK;
+  int splits = 1;
+  if (allow_split && tiles * 4 < ctas * 3 && tiles <= kQ8MaxSplitTiles) {
+    splits = ctas / tiles;                                   // all work items resident at once
+    const int max_by_k = nks / 4 > 1 ? nks / 4 : 1;          // at least four stages per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 32) splits = 32;
+  }
+  pl.kper = (nks + splits - 1) / splits;
+  pl.splits = (nks + pl.kper - 1) / pl.kper;                 // no empty split
+  pl.workspace_bytes = pl.splits > 1
+      ? kQ8CounterBytes + static_cast<size_t>(tiles) * pl.splits * pl.mt * bn * sizeof(uint32_t) : 0;
+  return pl;
+}
+
+template <bool INT8, int MT, int HALVES>
+static int launch_q8(const void* x, const void* w, Q8Params p, const Q8Plan& pl, int sm_count, EncodeTiledFn encode,
+                     cudaStream_t stream) {
+  using Cfg = Q8Cfg<MT, HALVES>;
   CUtensorMap mx, mw;
   const cuuint32_t estr[2] = {1, 1};
   {
@@ -282,23 +397,30 @@ static int launch_q8(const void* x, const void* w, Q8Params p, int sm_count, Enc
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.K), static_cast<cuuint64_t>(p.N)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ldw)};
-    const cuuint32_t box[2] = {kQ8BK, kQ8BN};
+    const cuuint32_t box[2] = {kQ8BK, static_cast<cuuint32_t>(Cfg::kBN)};
     if (encode(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cuda_fail(cudaErrorInvalidValue);
   }
   p.idesc = make_q8_idesc(INT8, p.idesc != 0u, 128, MT);
-  p.mtiles = (p.M + MT - 1) / MT;
-  p.ntiles = (p.N + kQ8BN - 1) / kQ8BN;
-  const int tiles = p.mtiles * p.ntiles;
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_kernel<INT8, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  q8_gemm_kernel<INT8, MT><<<tiles < sm_count ? tiles : sm_count, kQ8Threads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
+  p.mtiles = pl.mtiles;
+  p.ntiles = pl.ntiles;
+  p.splits = pl.splits;
+  p.kper = pl.kper;
+  const int items = pl.mtiles * pl.ntiles * pl.splits;
+  const int resident = Cfg::kCtasPerSm * sm_count;
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_kernel<INT8, MT, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes));
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_kernel<INT8, MT, HALVES>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared));
+  q8_gemm_kernel<INT8, MT, HALVES><<<items < resident ? items : resident, kQ8Threads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
   AWQ_CUDA_TRY(cudaGetLastError());
   return AWQ_B200_OK;
 }
 
-static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, cudaStream_t stream) {
+static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
   if (!x || !w || !p.y) return AWQ_B200_ERR_NULL;
   if (p.M < 1 || p.N < 1 || p.K < 1) return AWQ_B200_ERR_SHAPE;
   // the bulk tensor copies want row pitches that are multiples of 16 bytes
@@ -306,51 +428,66 @@ static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, cu
   if (!aligned16(x) || !aligned16(w) || (reinterpret_cast<uintptr_t>(p.y) & 1u)) return AWQ_B200_ERR_ALIGN;
   if (p.rowwise && (!p.x_scale || !p.w_scale)) return AWQ_B200_ERR_NULL;
   if (p.bias_kind < 0 || p.bias_kind > 3 || ((p.bias_kind != 0) != (p.bias != nullptr))) return AWQ_B200_ERR_SHAPE;
+  if (workspace && !aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
   EncodeTiledFn encode;
   if (int st = get_encode(&encode)) return st;
-  if (is_int) {
-    if (p.M <= 32) return launch_q8<true, 32>(x, w, p, di.sm_count, encode, stream);
-    return launch_q8<true, 128>(x, w, p, di.sm_count, encode, stream);
+  Q8Plan pl = q8_plan(p.M, p.N, p.K, di.sm_count, workspace != nullptr);
+  if (pl.workspace_bytes > workspace_bytes) pl = q8_plan(p.M, p.N, p.K, di.sm_count, false);   // too small: no split
+  if (pl.splits > 1) {
+    p.counters = static_cast<unsigned*>(workspace);
+    p.partials = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + kQ8CounterBytes);
   }
-  if (p.M <= 32) return launch_q8<false, 32>(x, w, p, di.sm_count, encode, stream);
-  return launch_q8<false, 128>(x, w, p, di.sm_count, encode, stream);
+  if (is_int) {
+    if (pl.mt == 32) return launch_q8<true, 32, 1>(x, w, p, pl, di.sm_count, encode, stream);
+    return launch_q8<true, 128, 2>(x, w, p, pl, di.sm_count, encode, stream);
+  }
+  if (pl.mt == 32) return launch_q8<false, 32, 1>(x, w, p, pl, di.sm_count, encode, stream);
+  return launch_q8<false, 128, 2>(x, w, p, pl, di.sm_count, encode, stream);
 }
 
 }  // namespace awq
 
 extern "C" {
 
+size_t awq_b200_q8_workspace_bytes(int M, int N, int K) {
+  awq::DeviceInfo di;
+  if (M < 1 || N < 1 || K < 1 || awq::device_info(&di)) return 0;
+  return awq::q8_plan(M, N, K, di.sm_count, true).workspace_bytes;
+}
+
 int awq_b200_fp8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias, int bias_kind,
-                                 void* y, int M, int N, int K, float alpha, const float* alpha_dev, const float* alpha_dev2,
-                                 float beta, int out_bf16, unsigned* status, awq_b200_stream_t stream) {
+                                 void* y, int M, int N, int K, float alpha, const float* alpha_dev,
+                                 const float* alpha_dev2, float beta, int out_bf16, void* workspace,
+                                 size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
   awq::Q8Params p{};
-  p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha; p.beta = beta;
-  p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0; p.out_bf16 = out_bf16;
-  p.idesc = 0u;
-  return awq::q8_dispatch(false, xq, wq, p, static_cast<cudaStream_t>(stream));
+  p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha;
+  p.beta = beta; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0;
+  p.out_bf16 = out_bf16; p.idesc = 0u;
+  return awq::q8_dispatch(false, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int awq_b200_fp8_gemm_rowwise(const void* xq, int ldx, int x_is_e5m2, const void* wq, int ldw, const void* bias,
                               int bias_kind, const float* x_scale, const float* w_scale, void* y, int M, int N, int K,
-                              unsigned* status, awq_b200_stream_t stream) {
+                              void* workspace, size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
   awq::Q8Params p{};
   p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.x_scale = x_scale; p.w_scale = w_scale; p.alpha = 1.f;
   p.beta = 1.f; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 1; p.out_bf16 = 1;
   p.idesc = x_is_e5m2 ? 1u : 0u;
-  return awq::q8_dispatch(false, xq, wq, p, static_cast<cudaStream_t>(stream));
+  return awq::q8_dispatch(false, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int awq_b200_int8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias, int bias_kind,
-                                  void* y, int M, int N, int K, float alpha, const float* alpha_dev, const float* alpha_dev2,
-                                  float beta, int out_bf16, unsigned* status, awq_b200_stream_t stream) {
+                                  void* y, int M, int N, int K, float alpha, const float* alpha_dev,
+                                  const float* alpha_dev2, float beta, int out_bf16, void* workspace,
+                                  size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
   awq::Q8Params p{};
-  p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha; p.beta = beta;
-  p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0; p.out_bf16 = out_bf16;
-  p.idesc = 0u;
-  return awq::q8_dispatch(true, xq, wq, p, static_cast<cudaStream_t>(stream));
+  p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha;
+  p.beta = beta; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0;
+  p.out_bf16 = out_bf16; p.idesc = 0u;
+  return awq::q8_dispatch(true, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -86,6 +86,38 @@ def test_int8_extremes_and_device_alpha(q8):
     assert np.array_equal(_bits(y), want)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 8192, 8192), (4, 1024, 28672), (32, 2048, 4096), (48, 4096, 8192), (128, 2048, 8192)])
+def test_k_split_is_exact_for_int8_and_repeatable(q8, M, N, K):
+    """Few rows: K is split over CTAs and the 32-bit partial sums are added by the last CTA of a tile.  INT8: the
+    same bits as without the split and as the oracle.  FP8: the same bits on every call (the order of the additions
+    is fixed), within the accumulation bound of the unsplit result."""
+    from llmrqt_sdv1_b200._lib import lib
+    assert lib.awq_b200_q8_workspace_bytes(M, N, K) > 0              # these shapes do split
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+    w = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8).cuda()
+    bias = torch.randn(N, generator=g).half().cuda()
+    y0 = q8.gemm_tensorwise(x, w.t(), bias, 2e-5, 1.0, torch.float16, int8=True, split=False)
+    y1 = q8.gemm_tensorwise(x, w.t(), bias, 2e-5, 1.0, torch.float16, int8=True)
+    y2 = q8.gemm_tensorwise(x, w.t(), bias, 2e-5, 1.0, torch.float16, int8=True)
+    assert torch.equal(y0, y1) and torch.equal(y1, y2)
+    rows = slice(0, min(M, 4))
+    want = q8o.tensorwise(x[rows].cpu().numpy(), w[:512].cpu().numpy(), bias[:512].cpu().numpy(), 2e-5, 1.0, False,
+                          kind=q8o.KIND_INT8)
+    assert np.array_equal(_bits(y1[rows, :512]), want)
+    a = _rand_fp8((M, K), 3).cuda()
+    b = _rand_fp8((N, K), 4).cuda()
+    f0 = q8.gemm_tensorwise(a, b.t(), None, 1.0, 0.0, torch.bfloat16, split=False)
+    f1 = q8.gemm_tensorwise(a, b.t(), None, 1.0, 0.0, torch.bfloat16)
+    f2 = q8.gemm_tensorwise(a, b.t(), None, 1.0, 0.0, torch.bfloat16)
+    assert torch.equal(f1, f2)
+    want = q8o.tensorwise(_bits(a[rows]), _bits(b[:512]), None, 1.0, 0.0, True)
+    slack = 2e-6 * q8o.gemm_abs(_bits(a[rows]), _bits(b[:512]), q8o.KIND_E4M3)
+    _check_fp8(_bits(f1[rows, :512]), want, True, slack)
+    _check_fp8(_bits(f0[rows, :512]), want, True, slack)
+    assert q8.status() == 0
+
+
 def test_pitched_operands(q8):
     """Row pitches larger than K (views into wider buffers), as the reference's checks allow (stride >= K)."""
     M, N, K, LD = 37, 320, 256, 384
