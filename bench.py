@@ -1038,7 +1038,20 @@ def run_profile_case(args, torch):
     """Small, self-terminating cases for `ncu` captures (a few launches, a few hundred MB)."""
     from llmrqt_sdv1_b200 import kernels, quantize
     torch.cuda.set_device(0)
-    if args.profile_case.startswith(("gemv", "skinny", "decode")):
+    if args.profile_case.startswith("q8"):
+        # q8_decode: fp8 57344 x 8192 weights (470 MB > L2), 16 rows, three launches (two CTAs per SM, no K split)
+        # q8_decode_split: fp8 8192 x 28672 weights (235 MB), 16 rows, three launches (clusters of four along K)
+        # q8_prefill: fp8 8192 x 8192 weights, 4096 rows, three launches
+        from llmrqt_sdv1_b200 import q8
+        M, N, K = {"q8_decode": (16, 57344, 8192), "q8_decode_split": (16, 8192, 28672)}.get(args.profile_case, (4096, 8192, 8192))
+        w = torch.randn(N, K, device="cuda").mul_(0.5).to(torch.float8_e4m3fn)
+        x = torch.randn(M, K, device="cuda").to(torch.float8_e4m3fn)
+        y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            q8.gemm_tensorwise(x, w.t(), None, 0.5, 1.0, torch.bfloat16, out=y)
+        torch.cuda.synchronize()
+        assert q8.status() == 0
+    elif args.profile_case.startswith(("gemv", "skinny", "decode")):
         # gemv / gemv16: 24 distinct 2048x12288 weights (13 MB each, 314 MB > L2), two passes
         # gemv70b / skinny70b[_m16] / decode70b[_m4]: one 8192x57344 weight (235 MB > L2), three launches
         M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else (4 if args.profile_case == "decode70b_m4" else 1)
@@ -1079,6 +1092,7 @@ def main():
     ap.add_argument("--headline-only", action="store_true",
                     help="time the headline workload only (no qwen3_decode block, no tables): for launch-list captures")
     ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "decode70b", "decode70b_m4",
+                                                       "q8_decode", "q8_decode_split", "q8_prefill",
                              "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")
     args = ap.parse_args()

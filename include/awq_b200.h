@@ -386,12 +386,13 @@ AWQ_B200_API int awq_b200_attn_decode(const void* q, const void* k_cache, const 
  * `[K, N]`, stride `[1, K]` view the reference passes).  Pitches are multiples of 16 bytes and >= K; xq and wq
  * are 16-byte aligned.  bias_kind: 0 none (bias NULL), 1 bf16, 2 fp16, 3 fp32.  `status` (optional, device word)
  * receives a non-zero code if a bounded wait inside the kernel ran out.
- * `workspace` (optional): device memory of awq_b200_q8_workspace_bytes(M, N, K) bytes, 16-byte aligned, whose first
- * 4096 bytes are ZERO before the first call (the kernels leave them zero) and which no other stream uses at the same
- * time.  With it, problems of few rows split K over otherwise idle SMs; the partial sums are added in a fixed order,
- * so results do not depend on timing, and for INT8 not on the split either.  Without it (NULL) nothing is split.
+ * Problems of few rows split K over the CTAs of a thread-block cluster, which add their partial sums over
+ * distributed shared memory in a fixed order: results do not depend on timing, and for INT8 not on the split
+ * either.  `flags`: AWQ_B200_Q8_NO_SPLIT forbids the split (tests, tuning).
  * --------------------------------------------------------------------------------------------------------------- */
-AWQ_B200_API size_t awq_b200_q8_workspace_bytes(int M, int N, int K);
+#define AWQ_B200_Q8_NO_SPLIT 1u
+/* Number of K splits (1..8) the GEMMs below use for this problem on the current device. */
+AWQ_B200_API int awq_b200_q8_splits(int M, int N, int K);
 
 /* y[M, N] = alpha' * (xq . wq^T) + beta * bias, fp32 accumulation, y bf16 (out_bf16 != 0) or fp16.
  * alpha' = alpha * (*alpha_dev) * (*alpha_dev2); either pointer may be NULL.  They let a dynamic activation scale
@@ -401,8 +402,8 @@ AWQ_B200_API size_t awq_b200_q8_workspace_bytes(int M, int N, int K);
  * (LLMQRT/runtime_refact/csrc/bindings.cpp:15-17; csrc/fp8/sm89_fp8_tensorwise_cutlassgemm.cu:30-160, :316-328). */
 AWQ_B200_API int awq_b200_fp8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias,
                                  int bias_kind, void* y, int M, int N, int K, float alpha, const float* alpha_dev,
-                                 const float* alpha_dev2, float beta, int out_bf16, void* workspace,
-                                 size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream);
+                                 const float* alpha_dev2, float beta, int out_bf16, unsigned flags,
+                                 unsigned* status, awq_b200_stream_t stream);
 
 /* y[M, N] bf16 = ((xq . wq^T) * x_scale[m]) * w_scale[n] + bias[n]; xq e4m3 or e5m2 (x_is_e5m2), wq e4m3.
  * Replaces cutlass_f8f8bf16_rowwise_sm89(XQ, WQ, bias, x_scale, w_scale, use_fast_accum)
@@ -410,16 +411,15 @@ AWQ_B200_API int awq_b200_fp8_gemm_tensorwise(const void* xq, int ldx, const voi
  * tensor memory, so use_fast_accum has nothing to select. */
 AWQ_B200_API int awq_b200_fp8_gemm_rowwise(const void* xq, int ldx, int x_is_e5m2, const void* wq, int ldw,
                               const void* bias, int bias_kind, const float* x_scale, const float* w_scale, void* y,
-                              int M, int N, int K, void* workspace, size_t workspace_bytes, unsigned* status,
-                              awq_b200_stream_t stream);
+                              int M, int N, int K, unsigned flags, unsigned* status, awq_b200_stream_t stream);
 
 /* y[M, N] = alpha' * float(int32(xq . wq^T)) + beta * bias; xq, wq int8; exact int32 accumulation.
  * Replaces w8a8_int8_linear_bbf16_obf16_per_tensor(input, weight, bias, alpha, beta)
  * (csrc/bindings.cpp:12-14; csrc/smoothquant/sq_gemm.cu:30-190), whose output element type is fp16. */
 AWQ_B200_API int awq_b200_int8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias,
                                   int bias_kind, void* y, int M, int N, int K, float alpha, const float* alpha_dev,
-                                  const float* alpha_dev2, float beta, int out_bf16, void* workspace,
-                                  size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream);
+                                  const float* alpha_dev2, float beta, int out_bf16, unsigned flags,
+                                  unsigned* status, awq_b200_stream_t stream);
 
 /* Activation quantisation in front of those GEMMs, with the roundings of the reference's torch expressions run on
  * a GPU.  x [M, K] fp16 or bf16 (x_is_bf16), contiguous, 16-byte aligned, K % 8 == 0; xq [M, K] bytes.

@@ -16,13 +16,15 @@
 // item overlaps the MMAs of the next.  No quantisation happens here: the operands arrive quantised, as in the
 // reference.  Every mbarrier wait is bounded (see awq_ptx.cuh).
 //
-// Few rows make few tiles (a decode step has N / 128 of them), so a tile's K range can be split over several CTAs:
-// each writes its 32-bit partial sums to a workspace, takes a ticket on the tile's counter, and the CTA that draws
-// the last ticket adds the partials IN SPLIT ORDER (its own included, re-read from the workspace), so the result
-// does not depend on which CTA finished last; int32 partials are exact in any order.  The counter goes back to 0.
+// Few rows make few tiles (a decode step has N / 128 of them), so a tile's K range can be split over the CTAs of
+// one thread-block cluster (2..8): each leaves its 32-bit partial sums in its own shared memory (the operand ring
+// is free by then), and after a cluster barrier every CTA adds, IN SPLIT ORDER, the partials of its share of the
+// tile's rows out of all the peers' shared memory and writes those rows.  The order is fixed, so fp8 results
+// are the same on every call; int32 partials are exact in any order.  No workspace, no atomics.
 #include <cuda_bf16.h>
 
 #include "awq_common.cuh"
+#include "awq_gemv_common.cuh"
 #include "awq_ptx.cuh"
 #include "awq_tcgen05.cuh"
 
@@ -30,8 +32,7 @@ namespace awq {
 
 constexpr int kQ8Threads = 64 + 256;         // producer, issuer, 8 epilogue warps
 constexpr int kQ8BK = 128;                   // bytes of K per stage
-constexpr int kQ8CounterBytes = 4096;        // workspace head: one ticket counter per split tile
-constexpr int kQ8MaxSplitTiles = kQ8CounterBytes / 4;
+constexpr int kQ8MaxSplits = 8;              // portable cluster size
 
 // MT activation rows and HALVES x 128 weight rows per tile.
 template <int MT, int HALVES> struct Q8Cfg {
@@ -62,8 +63,6 @@ struct Q8Params {
   int M, N, K;
   int mtiles, ntiles;
   int splits, kper;        // K split: work item = (tile, split), split s walks stages [s * kper, (s + 1) * kper)
-  unsigned* counters;      // [tiles] tickets (splits > 1)
-  uint32_t* partials;      // [tiles][splits][MT][BN] 32-bit partial sums (splits > 1)
   int ldx, ldw;            // row pitches of the activations and of the weights, in bytes
   int rowwise;             // 0 tensorwise, 1 rowwise
   int out_bf16;            // 1 bf16, 0 fp16
@@ -118,7 +117,8 @@ __device__ __forceinline__ void q8_mma_stage_warp(uint32_t d_tmem, uint64_t a_de
   }
 }
 
-template <bool INT8, int MT, int HALVES>
+// CLUSTER: one work item per CTA, the p.splits CTAs of a cluster share a tile (cluster rank = split).
+template <bool INT8, int MT, int HALVES, bool CLUSTER>
 __global__ void __launch_bounds__(kQ8Threads, Q8Cfg<MT, HALVES>::kCtasPerSm)
 q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Q8Params p) {
   using Cfg = Q8Cfg<MT, HALVES>;
@@ -126,7 +126,6 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   constexpr int BN = Cfg::kBN;
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
-  __shared__ int s_last;
   __shared__ uint32_t s_tmem_base;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -142,7 +141,6 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_abort = 0;
-    s_last = 0;
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_full(t), 1);
       mbar_init(bar_empty(t), 1);
@@ -259,7 +257,6 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++item_it) {
       int tn, tm, k0, k1;
       decode(item, &tn, &tm, &k0, &k1);
-      const int tile = item / p.splits, split = item - tile * p.splits;
       const uint32_t set = item_it & 1u;
       const int n = tn * BN + col;
       const bool nvalid = n < p.N;
@@ -271,7 +268,6 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (p.rowwise) ws_n = __ldg(p.w_scale + n);
       }
       const float beta_bias = __fmul_rn(p.beta, bias_n);
-      uint32_t* part_tile = p.partials + static_cast<size_t>(tile) * p.splits * (MT * BN);
       if (ok && !mbar_wait(bar_acc_full(set), (item_it >> 1) & 1u, abort_flag, 4)) ok = false;
       if (ok) {
         tcgen05_fence_after();
@@ -281,62 +277,84 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           uint32_t v[32];
           tcgen05_ld_32x32b_x32(tmem_base + lane_addr + set * Cfg::kAccCols + h * MT + c0, v);
           tcgen05_wait_ld();
-          if (p.splits == 1) {
+          if constexpr (!CLUSTER) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int m = tm * MT + c0 + j;
               if (m < p.M && nvalid) finish(v[j], m, n, ws_n, bias_n, beta_bias);
             }
           } else {
-            uint32_t* dst = part_tile + (static_cast<size_t>(split) * MT + c0) * BN + col;
+            // partial sums of this split: [row][column] words at the start of the (now idle) operand ring
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (tm * MT + c0 + j < p.M) __stcg(dst + static_cast<size_t>(j) * BN, v[j]);
+              if (tm * MT + c0 + j < p.M)
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(base + 4u * ((c0 + j) * BN + col)), "r"(v[j]) : "memory");
           }
         }
         tcgen05_fence_before();
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty(set));
-      if (p.splits > 1) {
-        // ticket: the CTA that completes the tile adds the partials in split order
-        __threadfence();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ew == 0 && lane == 0) {
-          const unsigned ticket = atomicAdd(p.counters + tile, 1u);
-          s_last = (ticket == static_cast<unsigned>(p.splits) - 1u) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const bool last = s_last != 0;
-        if (last) {
-          __threadfence();
-#pragma unroll 1
-          for (int c0 = row_first; c0 < MT; c0 += kRowStep) {
-            if (tm * MT + c0 >= p.M) break;
-#pragma unroll 4
-            for (int j = 0; j < 32; ++j) {
-              const int m = tm * MT + c0 + j;
-              if (m >= p.M) break;
-              const uint32_t* src = part_tile + static_cast<size_t>(c0 + j) * BN + col;
-              uint32_t sum;
-              if constexpr (INT8) {
-                int acc = 0;
-                for (int sp = 0; sp < p.splits; ++sp) acc += static_cast<int>(__ldcg(src + static_cast<size_t>(sp) * MT * BN));
-                sum = static_cast<uint32_t>(acc);
-              } else {
-                float acc = __uint_as_float(__ldcg(src));
-                for (int sp = 1; sp < p.splits; ++sp)
-                  acc = __fadd_rn(acc, __uint_as_float(__ldcg(src + static_cast<size_t>(sp) * MT * BN)));
-                sum = __float_as_uint(acc);
-              }
-              if (nvalid) finish(sum, m, n, ws_n, bias_n, beta_bias);
+    }
+  }
+
+  if constexpr (CLUSTER) {
+    // Every thread of every CTA of the cluster: partials are in place.
+    cluster_sync_all();
+    if (warp >= 2) {
+      int tn, tm, k0, k1;
+      decode(blockIdx.x, &tn, &tm, &k0, &k1);
+      const int rank = blockIdx.x % p.splits;
+      const int et = tid - 64;                                   // 0..255
+      const int col = et % BN;
+      const int rows_valid = min(MT, p.M - tm * MT);
+      const int n = tn * BN + col;
+      if (n < p.N) {
+        float bias_n = 0.f, ws_n = 1.f;
+        if (p.bias_kind == 1) bias_n = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+        else if (p.bias_kind == 2) bias_n = __half2float(static_cast<const __half*>(p.bias)[n]);
+        else if (p.bias_kind == 3) bias_n = static_cast<const float*>(p.bias)[n];
+        if (p.rowwise) ws_n = __ldg(p.w_scale + n);
+        const float beta_bias = __fmul_rn(p.beta, bias_n);
+        float alpha = p.alpha;
+        if (!p.rowwise && p.alpha_dev != nullptr) alpha = __fmul_rn(alpha, __ldg(p.alpha_dev));
+        if (!p.rowwise && p.alpha_dev2 != nullptr) alpha = __fmul_rn(alpha, __ldg(p.alpha_dev2));
+        // this CTA's share: rows rank, rank + splits, ... ; the thread walks them 256 / BN apart
+        for (int row = rank + (et / BN) * p.splits; row < rows_valid; row += (256 / BN) * p.splits) {
+          const uint32_t local = base + 4u * (row * BN + col);
+          uint32_t part[kQ8MaxSplits];
+#pragma unroll
+          for (int sp = 0; sp < kQ8MaxSplits; ++sp) {
+            if (sp < p.splits) {
+              uint32_t remote;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(sp));
+              asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(part[sp]) : "r"(remote) : "memory");
             }
           }
+          float a;
+          if constexpr (INT8) {
+            int acc = 0;
+#pragma unroll
+            for (int sp = 0; sp < kQ8MaxSplits; ++sp)
+              if (sp < p.splits) acc += static_cast<int>(part[sp]);
+            a = static_cast<float>(acc);
+          } else {
+            a = __uint_as_float(part[0]);
+#pragma unroll
+            for (int sp = 1; sp < kQ8MaxSplits; ++sp)
+              if (sp < p.splits) a = __fadd_rn(a, __uint_as_float(part[sp]));
+          }
+          const int m = tm * MT + row;
+          float r;
+          if (p.rowwise) r = __fadd_rn(__fmul_rn(__fmul_rn(a, __ldg(p.x_scale + m)), ws_n), bias_n);
+          else r = fmaf(alpha, a, beta_bias);
+          const size_t at = static_cast<size_t>(m) * p.N + n;
+          if (p.out_bf16) static_cast<__nv_bfloat16*>(p.y)[at] = __float2bfloat16_rn(r);
+          else static_cast<__half*>(p.y)[at] = __float2half_rn(r);
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");          // s_last is rewritten by the next item
-        if (last && ew == 0 && lane == 0) p.counters[tile] = 0u;   // ready for the next launch
       }
     }
+    cluster_sync_all();                                          // nobody leaves while its shared memory may be read
   }
 
   tcgen05_fence_before();
@@ -353,7 +371,6 @@ q8_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // How a problem is cut: tile shape by row count, then a K split when the tiles alone would leave SMs idle.
 struct Q8Plan {
   int mt, halves, mtiles, ntiles, splits, kper;
-  size_t workspace_bytes;
 };
 static Q8Plan q8_plan(int M, int N, int K, int sm_count, bool allow_split) {
   Q8Plan pl{};
@@ -366,16 +383,14 @@ static Q8Plan q8_plan(int M, int N, int K, int sm_count, bool allow_split) {
   const int tiles = pl.mtiles * pl.ntiles;
   const int nks = (K + kQ8BK - 1) / kQ8BK;
   int splits = 1;
-  if (allow_split && tiles * 4 < ctas * 3 && tiles <= kQ8MaxSplitTiles) {
+  if (allow_split && tiles * 4 < ctas * 3) {
     splits = ctas / tiles;                                   // all work items resident at once
     const int max_by_k = nks / 4 > 1 ? nks / 4 : 1;          // at least four stages per split
     if (splits > max_by_k) splits = max_by_k;
-    if (splits > 32) splits = 32;
+    if (splits > kQ8MaxSplits) splits = kQ8MaxSplits;
   }
   pl.kper = (nks + splits - 1) / splits;
   pl.splits = (nks + pl.kper - 1) / pl.kper;                 // no empty split
-  pl.workspace_bytes = pl.splits > 1
-      ? kQ8CounterBytes + static_cast<size_t>(tiles) * pl.splits * pl.mt * bn * sizeof(uint32_t) : 0;
   return pl;
 }
 
@@ -410,17 +425,35 @@ static int launch_q8(const void* x, const void* w, Q8Params p, const Q8Plan& pl,
   p.kper = pl.kper;
   const int items = pl.mtiles * pl.ntiles * pl.splits;
   const int resident = Cfg::kCtasPerSm * sm_count;
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_kernel<INT8, MT, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg::kSmemBytes));
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(q8_gemm_kernel<INT8, MT, HALVES>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    cudaSharedmemCarveoutMaxShared));
-  q8_gemm_kernel<INT8, MT, HALVES><<<items < resident ? items : resident, kQ8Threads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
+  if (pl.splits > 1) {
+    // one work item per CTA; the splits of a tile are the CTAs of one cluster
+    auto kernel = q8_gemm_kernel<INT8, MT, HALVES, true>;
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    AWQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(items);
+    cfg.blockDim = dim3(kQ8Threads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(pl.splits);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, mx, mw, p));
+    return AWQ_B200_OK;
+  }
+  auto kernel = q8_gemm_kernel<INT8, MT, HALVES, false>;
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  kernel<<<items < resident ? items : resident, kQ8Threads, Cfg::kSmemBytes, stream>>>(mx, mw, p);
   AWQ_CUDA_TRY(cudaGetLastError());
   return AWQ_B200_OK;
 }
 
-static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, void* workspace, size_t workspace_bytes,
-                       cudaStream_t stream) {
+static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, unsigned flags, cudaStream_t stream) {
   if (!x || !w || !p.y) return AWQ_B200_ERR_NULL;
   if (p.M < 1 || p.N < 1 || p.K < 1) return AWQ_B200_ERR_SHAPE;
   // the bulk tensor copies want row pitches that are multiples of 16 bytes
@@ -428,18 +461,12 @@ static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, vo
   if (!aligned16(x) || !aligned16(w) || (reinterpret_cast<uintptr_t>(p.y) & 1u)) return AWQ_B200_ERR_ALIGN;
   if (p.rowwise && (!p.x_scale || !p.w_scale)) return AWQ_B200_ERR_NULL;
   if (p.bias_kind < 0 || p.bias_kind > 3 || ((p.bias_kind != 0) != (p.bias != nullptr))) return AWQ_B200_ERR_SHAPE;
-  if (workspace && !aligned16(workspace)) return AWQ_B200_ERR_ALIGN;
   DeviceInfo di;
   if (int st = device_info(&di)) return st;
   if (di.cc_major != 10) return AWQ_B200_ERR_ARCH;
   EncodeTiledFn encode;
   if (int st = get_encode(&encode)) return st;
-  Q8Plan pl = q8_plan(p.M, p.N, p.K, di.sm_count, workspace != nullptr);
-  if (pl.workspace_bytes > workspace_bytes) pl = q8_plan(p.M, p.N, p.K, di.sm_count, false);   // too small: no split
-  if (pl.splits > 1) {
-    p.counters = static_cast<unsigned*>(workspace);
-    p.partials = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + kQ8CounterBytes);
-  }
+  const Q8Plan pl = q8_plan(p.M, p.N, p.K, di.sm_count, (flags & AWQ_B200_Q8_NO_SPLIT) == 0);
   if (is_int) {
     if (pl.mt == 32) return launch_q8<true, 32, 1>(x, w, p, pl, di.sm_count, encode, stream);
     return launch_q8<true, 128, 2>(x, w, p, pl, di.sm_count, encode, stream);
@@ -452,42 +479,42 @@ static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, vo
 
 extern "C" {
 
-size_t awq_b200_q8_workspace_bytes(int M, int N, int K) {
+int awq_b200_q8_splits(int M, int N, int K) {
   awq::DeviceInfo di;
   if (M < 1 || N < 1 || K < 1 || awq::device_info(&di)) return 0;
-  return awq::q8_plan(M, N, K, di.sm_count, true).workspace_bytes;
+  return awq::q8_plan(M, N, K, di.sm_count, true).splits;
 }
 
 int awq_b200_fp8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias, int bias_kind,
                                  void* y, int M, int N, int K, float alpha, const float* alpha_dev,
-                                 const float* alpha_dev2, float beta, int out_bf16, void* workspace,
-                                 size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
+                                 const float* alpha_dev2, float beta, int out_bf16, unsigned flags, unsigned* status,
+                                 awq_b200_stream_t stream) {
   awq::Q8Params p{};
   p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha;
   p.beta = beta; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0;
   p.out_bf16 = out_bf16; p.idesc = 0u;
-  return awq::q8_dispatch(false, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  return awq::q8_dispatch(false, xq, wq, p, flags, static_cast<cudaStream_t>(stream));
 }
 
 int awq_b200_fp8_gemm_rowwise(const void* xq, int ldx, int x_is_e5m2, const void* wq, int ldw, const void* bias,
                               int bias_kind, const float* x_scale, const float* w_scale, void* y, int M, int N, int K,
-                              void* workspace, size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
+                              unsigned flags, unsigned* status, awq_b200_stream_t stream) {
   awq::Q8Params p{};
   p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.x_scale = x_scale; p.w_scale = w_scale; p.alpha = 1.f;
   p.beta = 1.f; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 1; p.out_bf16 = 1;
   p.idesc = x_is_e5m2 ? 1u : 0u;
-  return awq::q8_dispatch(false, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  return awq::q8_dispatch(false, xq, wq, p, flags, static_cast<cudaStream_t>(stream));
 }
 
 int awq_b200_int8_gemm_tensorwise(const void* xq, int ldx, const void* wq, int ldw, const void* bias, int bias_kind,
                                   void* y, int M, int N, int K, float alpha, const float* alpha_dev,
-                                  const float* alpha_dev2, float beta, int out_bf16, void* workspace,
-                                  size_t workspace_bytes, unsigned* status, awq_b200_stream_t stream) {
+                                  const float* alpha_dev2, float beta, int out_bf16, unsigned flags, unsigned* status,
+                                  awq_b200_stream_t stream) {
   awq::Q8Params p{};
   p.y = y; p.bias = bias; p.bias_kind = bias_kind; p.alpha_dev = alpha_dev; p.alpha_dev2 = alpha_dev2; p.alpha = alpha;
   p.beta = beta; p.status = status; p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldw = ldw; p.rowwise = 0;
   p.out_bf16 = out_bf16; p.idesc = 0u;
-  return awq::q8_dispatch(true, xq, wq, p, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+  return awq::q8_dispatch(true, xq, wq, p, flags, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

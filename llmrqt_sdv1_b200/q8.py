@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ._lib import check, lib
-from .kernels import _prep, _workspace
+from .kernels import _prep
 
 _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 _BIAS_KIND = {torch.bfloat16: 1, torch.float16: 2, torch.float32: 3}
@@ -28,17 +28,6 @@ def _scratch_words(dev: torch.device, stream: int) -> torch.Tensor:
         t = torch.zeros(128, dtype=torch.int32, device=dev)
         _scratch[key] = t
     return t
-
-
-def _split_workspace(dev: torch.device, stream: int, M: int, N: int, K: int, split: bool):
-    """(pointer, bytes) of this stream's K-split workspace (zero-initialised; the kernels leave its counters zero)."""
-    if not split:
-        return None, 0
-    need = lib.awq_b200_q8_workspace_bytes(M, N, K)
-    if need == 0:
-        return None, 0
-    ws = _workspace(dev, stream, need, "awq_b200_q8")
-    return ws.data_ptr(), ws.numel()
 
 
 def status(dev: torch.device | None = None) -> int:
@@ -125,10 +114,9 @@ def gemm_tensorwise(XQ, WQ, bias, alpha, beta, out_dtype: torch.dtype, alpha2=No
     stream = torch.cuda.current_stream(dev).cuda_stream
     st = _scratch_words(dev, stream)
     fn = lib.awq_b200_int8_gemm_tensorwise if int8 else lib.awq_b200_fp8_gemm_tensorwise
-    ws_ptr, ws_bytes = _split_workspace(dev, stream, M, N, K, split)
     check(fn(XQ.data_ptr(), ldx, WQ.data_ptr(), ldw, bias.data_ptr() if bias is not None else None, kind,
              out.data_ptr(), M, N, K, a_host * a2_host, a_ptr or None, a2_ptr or None, float(beta),
-             1 if out_dtype == torch.bfloat16 else 0, ws_ptr, ws_bytes, st.data_ptr(), stream), "awq_b200_" + what)
+             1 if out_dtype == torch.bfloat16 else 0, 0 if split else 1, st.data_ptr(), stream), "awq_b200_" + what)
     del keep1, keep2
     return out
 
@@ -158,10 +146,9 @@ def gemm_rowwise(XQ, WQ, bias, x_scale, w_scale, out: torch.Tensor | None = None
         raise RuntimeError(f"{what}: K = 0")
     stream = torch.cuda.current_stream(dev).cuda_stream
     st = _scratch_words(dev, stream)
-    ws_ptr, ws_bytes = _split_workspace(dev, stream, M, N, K, split)
     check(lib.awq_b200_fp8_gemm_rowwise(XQ.data_ptr(), ldx, 1 if XQ.dtype == torch.float8_e5m2 else 0, WQ.data_ptr(), ldw,
                                         bias.data_ptr() if bias is not None else None, kind, x_scale.data_ptr(),
-                                        w_scale.data_ptr(), out.data_ptr(), M, N, K, ws_ptr, ws_bytes, st.data_ptr(),
+                                        w_scale.data_ptr(), out.data_ptr(), M, N, K, 0 if split else 1, st.data_ptr(),
                                         stream),
           "awq_b200_fp8_gemm_rowwise")
     return out

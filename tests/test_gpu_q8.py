@@ -88,11 +88,11 @@ def test_int8_extremes_and_device_alpha(q8):
 
 @pytest.mark.parametrize("M,N,K", [(1, 8192, 8192), (4, 1024, 28672), (32, 2048, 4096), (48, 4096, 8192), (128, 2048, 8192)])
 def test_k_split_is_exact_for_int8_and_repeatable(q8, M, N, K):
-    """Few rows: K is split over CTAs and the 32-bit partial sums are added by the last CTA of a tile.  INT8: the
-    same bits as without the split and as the oracle.  FP8: the same bits on every call (the order of the additions
-    is fixed), within the accumulation bound of the unsplit result."""
+    """Few rows: K is split over the CTAs of a cluster, which add the 32-bit partial sums over distributed shared
+    memory.  INT8: the same bits as without the split and as the oracle.  FP8: the same bits on every call (the
+    order of the additions is fixed), within the accumulation bound of the unsplit result."""
     from llmrqt_sdv1_b200._lib import lib
-    assert lib.awq_b200_q8_workspace_bytes(M, N, K) > 0              # these shapes do split
+    assert lib.awq_b200_q8_splits(M, N, K) > 1                       # these shapes do split
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).cuda()
     w = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8).cuda()
