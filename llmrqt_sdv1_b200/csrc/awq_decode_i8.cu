@@ -1,18 +1,21 @@
 // Decode path for 1 <= M <= 4 rows of a large matrix on the integer tensor-core path (tcgen05.mma kind::i8):
-// the packed nibbles reach the tensor core with ONE logic operation per packed word and nibble position, no
-// conversion to floating point at all.
+// the packed nibbles reach the tensor core with ONE logic operation per packed word, no conversion to floating
+// point at all, and half of them with no operation.
 //
 // A byte of the packed weights holds two nibbles of one column, q_hi (bits 4..7) and q_lo (bits 0..3), for two
-// different k of the same 128-k block.  Masking gives two unsigned 8-bit operands,
-//     hi = word & 0xf0f0f0f0   (bytes 16 * q_hi)          lo = word & 0x0f0f0f0f   (bytes q_lo),
-// which go to tensor memory as they are (lane = output column, one byte per k slot).  The activations of a
-// block are turned into block-fixed-point integers once per unit by four helper warps:
+// different k of the same 128-k block.  Two unsigned 8-bit operands are used:
+//     raw = the packed bytes as the copy engine left them in shared memory (16 * q_hi + q_lo),
+//     hi  = word & 0xf0f0f0f0 (bytes 16 * q_hi), written to tensor memory (lane = output column, one byte per slot).
+// The activations of a block are turned into block-fixed-point integers once per unit by two helper warps:
 //     x[m, k] ~ sx[m] * t[m, k],   t = rint(x / sx) in [-16256, 16256],   sx = max_k |x[m, k]| / 16256
 //     t = 128 * p1 + p2,  p1 in [-127, 127], p2 in [-64, 63]                  (two signed 8-bit planes)
-// and laid out as the B operand: plane 1 of row m in row m of the tile, plane 2 in row MR + m, the k slots in
-// the order of the bytes they meet (one tile for the k of the high nibbles, one for the low nibbles).  Then
-//     D_hi[n, .] = sum_slots hi * Xhi      D_lo[n, .] = sum_slots lo * Xlo            (int32, exact)
-//     y[m, n] += s[n] * sx[m] * ( (128 * D_hi[m] + D_hi[MR + m]) / 16 + 128 * D_lo[m] + D_lo[MR + m] - z[n] * T[m] )
+// and laid out as the B operand, the k slots in the order of the bytes they meet: tile Xhi (rows 0..7) for the k of
+// the high nibbles, tile Xlo (rows 8..15, directly behind) for the k of the low nibbles; plane 1 of row m in row m
+// of a tile, plane 2 in row MR + m.  One MMA of N = 16 over [Xhi; Xlo] and one over Xlo give (int32, exact)
+//     D_hi[n, 0..7]  = sum_slots hi * Xhi      D_hi[n, 8..15] = sum_slots hi * Xlo      D_raw[n, 0..7] = sum_slots raw * Xlo
+// and, since raw - hi = q_lo byte by byte, D_raw - D_hi[8..] = sum_slots q_lo * Xlo:
+//     y[m, n] += s[n] * sx[m] * ( (128 * D_hi[m] + D_hi[MR + m]) / 16
+//                                 + 128 * (D_raw[m] - D_hi[8 + m]) + (D_raw[MR + m] - D_hi[8 + MR + m]) - z[n] * T[m] )
 // with T[m] = sum_k t[m, k]; everything inside the parenthesis is exact integer arithmetic, so the only
 // roundings are the quantisation of x (15 bits below the largest activation of the row's 128-k block, i.e.
 // finer than the fp16 spacing of that activation) and one fp32 multiply-add per unit.  Like the reference's
@@ -23,19 +26,16 @@
 // sequence, one copy pipeline per CTA that never drains; a column tile that straddles CTAs is finished through
 // fp32 partials added in CTA (= k) order by the last contributor.  Deterministic; a row's bits do not depend on M.
 //
-// TWO CTAs per SM (384 threads, 256 tensor-memory columns, ~100 KB of shared memory each).  In steady state the
-// kernel moves what the memory system delivers to such a stream (measured 5.6 - 5.7 TB/s); what a launch costs
-// beyond that is its start (barriers, tensor-memory allocation, first copies in flight, pipeline fill) and its
-// end (last accumulators, partial tiles).  With two small CTAs per SM the next kernel of the stream
-// (programmatic dependent launch) takes over an SM half as soon as one CTA has left, and its first copies
-// overlap the other CTA's tail; one CTA that fills the SM makes every launch pay start and end in full.
+// TWO CTAs per SM (384 threads, 256 tensor-memory columns, ~100 KB of shared memory each).  With two small CTAs
+// per SM the next kernel of the stream (programmatic dependent launch) takes over an SM half as soon as one CTA
+// has left, and its first copies overlap the other CTA's tail.
 //
 // Warps: 0 copy producer, 1 MMA issuer, 2..9 two groups of four warps that mask the words into tensor memory
 // (a thread serves one column in each 128-column half) and fold the finished accumulators, 10..11 activation
-// helpers (alternate units).  TMEM columns: [0, 128) two accumulator windows of 64 (2 halves x {hi, lo} x 16),
-// [128, 256) two operand slots of 64 (2 halves x {hi, lo} x 16 columns = 64 k slots).  Per unit the tensor core
-// runs 8 instructions (2 halves x 2 k steps of 32 slots x {hi, lo}).  A group folds unit u when it starts on
-// unit u + 2.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+// helpers (alternate units).  TMEM columns: [0, 128) two accumulator windows of 64 (2 halves x {hi, raw} x 16),
+// [128, 256) two operand slots of 64 (2 halves x 32, of which the hi bytes take 16 columns = 64 k slots).  Per
+// unit the tensor core runs 8 instructions (2 halves x 2 k steps of 32 slots x {hi, raw}).  A group folds unit u
+// when it starts on unit u + 2.  Every mbarrier wait is bounded (see awq_ptx.cuh).
 #include "awq_gemv_common.cuh"
 #include "awq_tcgen05.cuh"
 
@@ -119,45 +119,48 @@ __host__ __device__ constexpr uint32_t make_i8_idesc(int m, int n) {
   return (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// The four integer MMAs of one unit and half - {hi, lo} x two k steps of 32 slots - into fresh accumulators,
-// then three commits, under one election.  a_hi / a_lo: operand columns in tensor memory (8 columns per step);
-// b_hi / b_lo: descriptors of the activation tiles (a step advances 32 bytes = 2 units of 16 bytes).
-__device__ __forceinline__ void tcgen05_mma_i8_unit_commit3_warp(uint32_t d_hi, uint32_t d_lo, uint32_t a_hi, uint32_t a_lo,
+// The four integer MMAs of one unit and half - {hi from tensor memory, raw from shared memory} x two k steps of
+// 32 slots - into fresh accumulators, then three commits, under one election.  a_hi: operand columns in tensor
+// memory (8 columns per step); a_raw: descriptor of the half's packed bytes as they arrived; b_hi / b_lo:
+// descriptors of the activation tiles (a step advances 32 bytes = 2 units of 16 bytes).
+__device__ __forceinline__ void tcgen05_mma_i8_unit_commit3_warp(uint32_t d_hi, uint32_t d_raw, uint32_t a_hi, uint64_t a_raw,
                                                                  uint64_t b_hi, uint64_t b_lo, uint32_t idesc,
                                                                  uint32_t bar0, uint32_t bar1, uint32_t bar2) {
   asm volatile(
-      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d;\n\t"
+      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d, da;\n\t"
       "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, 0, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [%3], %5, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %6, p;\n\t"
       "setp.eq.b32 p, 0, 0;\n\t"
       "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
-      "add.u32 a, %3, 8;\n\t  mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [a], d, %6, p;\n\t"
+      "mov.b64 {lo, hi}, %3;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 da, {lo, hi};\n\t"
+      "mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %6, p;\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n\t}"
-      ::"r"(d_hi), "r"(d_lo), "r"(a_hi), "r"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(bar0), "r"(bar1), "r"(bar2)
+      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(bar0), "r"(bar1), "r"(bar2)
       : "memory");
 }
 
 // The same four MMAs without commits (the first half of a unit).
-__device__ __forceinline__ void tcgen05_mma_i8_half_warp(uint32_t d_hi, uint32_t d_lo, uint32_t a_hi, uint32_t a_lo,
+__device__ __forceinline__ void tcgen05_mma_i8_half_warp(uint32_t d_hi, uint32_t d_raw, uint32_t a_hi, uint64_t a_raw,
                                                          uint64_t b_hi, uint64_t b_lo, uint32_t idesc) {
   asm volatile(
-      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d;\n\t"
+      "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d, da;\n\t"
       "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, 0, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [%3], %5, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %6, p;\n\t"
       "setp.eq.b32 p, 0, 0;\n\t"
       "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
-      "add.u32 a, %3, 8;\n\t  mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], [a], d, %6, p;\n\t}"
-      ::"r"(d_hi), "r"(d_lo), "r"(a_hi), "r"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc)
+      "mov.b64 {lo, hi}, %3;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 da, {lo, hi};\n\t"
+      "mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %6, p;\n\t}"
+      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc)
       : "memory");
 }
 
@@ -290,12 +293,14 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       if (!mbar_wait(bar_win_empty(w), (static_cast<uint32_t>(gs / NW) & 1u) ^ 1u, abort_flag, 2)) break;
       if (!mbar_wait(bar_xq_full(t), static_cast<uint32_t>(gs / NT) & 1u, abort_flag, 3)) break;
       if (!mbar_wait(bar_a_full(a), static_cast<uint32_t>(gs / NA) & 1u, abort_flag, 4)) break;
+      if (!mbar_wait(bar_full_tma(t), static_cast<uint32_t>(gs / NT) & 1u, abort_flag, 10)) break;   // the raw bytes are an operand
       tcgen05_fence_after();
       const uint32_t win = tmem_base + static_cast<uint32_t>(w * 64);
       const uint32_t opd = tmem_base + static_cast<uint32_t>(kD8ABase + a * 64);
       const uint64_t b_hi = make_sw64_desc(stage_addr(t) + kD8XhiOff), b_lo = make_sw64_desc(stage_addr(t) + kD8XloOff);
-      tcgen05_mma_i8_half_warp(win, win + 16, opd, opd + 16, b_hi, b_lo, kIdesc);
-      tcgen05_mma_i8_unit_commit3_warp(win + 32, win + 48, opd + 32, opd + 48, b_hi, b_lo, kIdesc, bar_empty(t),
+      const uint64_t a_raw0 = make_sw64_desc(stage_addr(t) + kD8RawOff), a_raw1 = make_sw64_desc(stage_addr(t) + kD8RawOff + 128 * 64);
+      tcgen05_mma_i8_half_warp(win, win + 16, opd, a_raw0, b_hi, b_lo, kIdesc);
+      tcgen05_mma_i8_unit_commit3_warp(win + 32, win + 48, opd + 32, a_raw1, b_hi, b_lo, kIdesc, bar_empty(t),
                                        bar_a_empty(a), bar_win_full(w));
     }
     __syncwarp();
@@ -440,12 +445,13 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
         if (ok && !mbar_wait(bar_win_full(w), static_cast<uint32_t>(pend / NW) & 1u, abort_flag, 6)) ok = false;
         if (ok) {
           tcgen05_fence_after();
-          uint32_t vh[2][2 * MR], vl[2][2 * MR];
+          uint32_t vh[2][2 * MR], vx[2][2 * MR], vr[2][2 * MR];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * 64 + h * 32);
-            d8_tmem_ld<2 * MR>(win, vh[h]);
-            d8_tmem_ld<2 * MR>(win + 16, vl[h]);
+            d8_tmem_ld<2 * MR>(win, vh[h]);             // hi x (activations of the high nibbles)
+            d8_tmem_ld<2 * MR>(win + 8, vx[h]);         // hi x (activations of the low nibbles): rows 8.. of the B tile
+            d8_tmem_ld<2 * MR>(win + 16, vr[h]);        // raw x (activations of the low nibbles)
           }
           tcgen05_wait_ld();
           tcgen05_fence_before();
@@ -458,7 +464,9 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int dhi = (static_cast<int>(vh[h][m]) << 7) + static_cast<int>(vh[h][MR + m]);    // a multiple of 16
-              const int dlo = (static_cast<int>(vl[h][m]) << 7) + static_cast<int>(vl[h][MR + m]);
+              // raw = hi + lo byte by byte, so (raw - hi) . x = lo . x, plane by plane
+              const int dlo = ((static_cast<int>(vr[h][m]) - static_cast<int>(vx[h][m])) << 7) +
+                              (static_cast<int>(vr[h][MR + m]) - static_cast<int>(vx[h][MR + m]));
               const int val = (dhi >> 4) + dlo - pend_z[h] * mt.y;
               acc[h][m] = fmaf(pend_s[h] * sx, static_cast<float>(val), acc[h][m]);
             }
@@ -521,12 +529,6 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
             o[4 * c + 2] = r[c].z & 0xf0f0f0f0u; o[4 * c + 3] = r[c].w & 0xf0f0f0f0u;
           }
           tcgen05_st_32x32b_x16(a_addr, o);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            o[4 * c + 0] = r[c].x & 0x0f0f0f0fu; o[4 * c + 1] = r[c].y & 0x0f0f0f0fu;
-            o[4 * c + 2] = r[c].z & 0x0f0f0f0fu; o[4 * c + 3] = r[c].w & 0x0f0f0f0fu;
-          }
-          tcgen05_st_32x32b_x16(a_addr + 16u, o);
         }
         tcgen05_wait_st();
         tcgen05_fence_before();

@@ -83,8 +83,14 @@ def test_extension_function_api():
         y = fn(torch.from_numpy(x).cuda(), dq, ds, dz, 128)
         assert y.shape == (M, N)
         assert orc.max_normalised_error(y.cpu().numpy(), orc.linear_forward(x, qw, qz, sc, 128)) <= TOL
-    with pytest.raises(NotImplementedError):
-        ext.cutlass_f8f8bf16_rowwise_sm89()
+    # the three non-AWQ names of the extension are real functions too (tests/test_gpu_q8.py covers their results)
+    a = torch.zeros(2, 64, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.zeros(32, 64, device="cuda").to(torch.float8_e4m3fn)
+    assert ext.cutlass_f8f8bf16_tensorwise_sm89(a, b.t(), None, 1.0, 1.0, "bfloat16").shape == (2, 32)
+    assert ext.cutlass_f8f8bf16_rowwise_sm89(a, b.t(), None, torch.ones(2, 1, device="cuda"),
+                                             torch.ones(1, 32, device="cuda"), True).dtype == torch.bfloat16
+    assert ext.w8a8_int8_linear_bbf16_obf16_per_tensor(a.view(torch.int8), b.view(torch.int8).t(),
+                                                       torch.zeros(32, device="cuda", dtype=torch.float16), 1.0, 1.0).dtype == torch.float16
 
 
 def test_load_checkpoint_fills_and_repacks(tmp_path):
