@@ -307,9 +307,10 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
 /* Picks the kernel from the row count and the shape.  M <= 16 -> awq_b200_gemv, except for large weights:
- * from 48 MiB of packed weights M <= 4 -> awq_b200_decode_i8 and 5 <= M <= 8 -> awq_b200_skinny, and from 16 MiB
- * 9 <= M <= 16 -> awq_b200_skinny (beyond 8 rows the GEMV does its unpacking twice).  The thresholds depend on K
- * and N only, so within a row-count class a row's bits do not change with the number of rows decoded together.
+ * awq_b200_decode_i8 for M = 1 from 20 MiB of packed weights and for 2 <= M <= 4 from 36 MiB; awq_b200_skinny for
+ * 5 <= M <= 8 from 48 MiB and for 9 <= M <= 16 from 16 MiB (beyond 8 rows the GEMV does its unpacking twice).  The
+ * thresholds depend on K and N only, so within a row-count class (1, 2..4, 5..8, 9..16, 17..64) a row's bits do not
+ * change with the number of rows decoded together.
  * 17 <= M <= 64 -> awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
  * awq_b200_gemm otherwise.  Group sizes 32 and 64 always take awq_b200_skinny (M <= 64) or awq_b200_gemm.
  * Mirrors the row-count switch in AWQLinearMMFunction.forward

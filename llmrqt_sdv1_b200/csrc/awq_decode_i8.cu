@@ -620,16 +620,24 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-static long long decode_grid(int sm_count, long long units) {
+// Number of CTAs.  Two per SM, except that when a slightly smaller grid is a whole multiple of the column tiles,
+// that grid is taken: every tile is then shared by the same number of CTAs and no CTA straddles two tiles (one
+// epilogue per CTA instead of two; measured 27.4 -> 25.7 us on 28672 -> 8192, 13.7 -> 10.7 us on 7168 -> 8192).
+static long long decode_grid(int sm_count, long long units, int ntiles) {
   const long long ctas = static_cast<long long>(kD8CtasPerSm) * sm_count;
-  return units < ctas ? units : ctas;
+  if (units <= ctas) return units;
+  if (ntiles <= ctas) {
+    const long long g = (ctas / ntiles) * ntiles;
+    if (g * 10 >= ctas * 9) return g;
+  }
+  return ctas;
 }
 
 // Largest number of CTAs that share one column tile (= partial slots needed).
 static int decode_slots(int K, int N, int sm_count) {
   const int nblk = K / kBlockK, ntiles = (N + kD8BN - 1) / kD8BN;
   const long long U = static_cast<long long>(ntiles) * nblk;
-  const long long G = decode_grid(sm_count, U);
+  const long long G = decode_grid(sm_count, U, ntiles);
   int worst = 1;
   for (int t = 0; t < ntiles; ++t) {
     const long long a = static_cast<long long>(t) * nblk;
@@ -716,7 +724,7 @@ int decode_i8_dispatch(const void* x, const void* packed, const void* scales, co
   p.ntiles = ntiles;
   p.nblk = K / kBlockK;
   p.units = static_cast<long long>(ntiles) * p.nblk;
-  const int grid = static_cast<int>(decode_grid(di.sm_count, p.units));
+  const int grid = static_cast<int>(decode_grid(di.sm_count, p.units, ntiles));
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
   if (M <= 1) return launch_decode_i8<1>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   if (M <= 2) return launch_decode_i8<2>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);

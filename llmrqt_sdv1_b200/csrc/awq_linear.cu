@@ -9,8 +9,9 @@ constexpr int kSkinnyMaxRows = 64;
 
 // Which kernel serves M rows of a K x N linear (all thresholds are on (K, N) only, so within a row-count class
 // a row's bits do not change with the number of rows decoded together).
-//   rows <= 4:  the GEMV, or from 48 MiB of packed weights the integer tensor-core decode kernel
-//               (awq_decode_i8.cu; 70B-class gate_up at one row: 49 us against 72 us).
+//   one row:    the GEMV, or from 20 MiB of packed weights the integer tensor-core decode kernel
+//               (awq_decode_i8.cu; 70B-class gate_up: 45 us against 72 us).
+//   2..4:       the same with the switch at 36 MiB.
 //   5..8:       the GEMV, or from 48 MiB the exact-weight split-K tensor-memory kernel.
 //   9..16:      the same with the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice).
 //   17..64:     the exact-weight tensor-memory kernel where the GEMM would leave most SMs idle (at most 74
@@ -24,9 +25,15 @@ Route route(int M, int K, int N, int group_size) {
   if (group_size < 128) return M <= kSkinnyMaxRows ? Route::kSkinny : Route::kGemm;
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
   if (M <= awq_b200_gemv_max_rows()) {
+    // Measured crossovers against the GEMV (us, graph replay, weights from HBM): the integer kernel wins from
+    // ~16-20 MiB at one row (28 MiB: 10.8-11.2 against 12.5-12.9) and from ~36 MiB at four rows.
+    if (M <= kDecodeI8MaxRows) {
+      const long long from_bytes = M == 1 ? (20ll << 20) : (36ll << 20);
+      return packed_bytes < from_bytes ? Route::kGemv : Route::kDecodeI8;
+    }
     const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
     if (packed_bytes < from_bytes) return Route::kGemv;
-    return M <= kDecodeI8MaxRows ? Route::kDecodeI8 : Route::kSkinny;
+    return Route::kSkinny;
   }
   if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
   return Route::kGemm;

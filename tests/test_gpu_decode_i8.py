@@ -135,4 +135,10 @@ def test_decode_i8_fused_epilogues_and_routing(K_):
     x2 = torch.randn((8, K2), device="cuda", dtype=torch.float16)
     assert torch.equal(K_.linear(x2, pw2), K_.gemv(x2, pw2))
     assert torch.equal(K_.linear(x2[:2].contiguous(), pw2), K_.gemv(x2[:2].contiguous(), pw2))
+    K3, N3 = 6144, 8192                                        # 24 MiB: this kernel at one row, the GEMV at 2..4
+    qw, qz, sc = _random_packed_inputs(K3, N3, 128, seed=43)
+    pw3 = K_.make_packed(qw, qz, sc, 128)
+    x4 = torch.randn((4, K3), device="cuda", dtype=torch.float16)
+    assert torch.equal(K_.linear(x4[:1].contiguous(), pw3), K_.decode_i8(x4[:1].contiguous(), pw3))
+    assert torch.equal(K_.linear(x4, pw3), K_.gemv(x4, pw3))
     assert K_.gemv_status() == 0
