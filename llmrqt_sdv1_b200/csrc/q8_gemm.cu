@@ -14,7 +14,9 @@
 // stages of 128 bytes.  Warp 0 copies both operands with TMA (128-byte swizzle), warp 1 issues the MMAs (K = 32 per
 // instruction), warps 2..9 drain the accumulators: two accumulator sets in tensor memory, so the epilogue of a work
 // item overlaps the MMAs of the next.  No quantisation happens here: the operands arrive quantised, as in the
-// reference.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+// reference.  Every mbarrier wait is bounded (see awq_ptx.cuh).  Up to 128 rows: tiles of 128 weight rows x
+// 32 / 64 / 128 activation rows, two CTAs per SM (the weights are streamed once: bytes in flight and overlapped
+// epilogues matter, not the tile's arithmetic intensity); more rows: 256 x 128 tiles, one CTA per SM.
 //
 // Few rows make few tiles (a decode step has N / 128 of them), so a tile's K range can be split over the CTAs of
 // one thread-block cluster (2..8): each leaves its 32-bit partial sums in its own shared memory (the operand ring
@@ -36,14 +38,14 @@ constexpr int kQ8MaxSplits = 8;              // portable cluster size
 
 // MT activation rows and HALVES x 128 weight rows per tile.
 template <int MT, int HALVES> struct Q8Cfg {
-  static_assert(MT == 32 || MT == 128, "activation rows per tile");
+  static_assert(MT == 32 || MT == 64 || MT == 128, "activation rows per tile");
   static_assert(HALVES == 1 || HALVES == 2, "weight rows per tile: 128 or 256");
   static constexpr int kBN = 128 * HALVES;
   static constexpr int kABytes = kBN * kQ8BK;
   static constexpr int kBBytes = MT * kQ8BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // small tiles: two CTAs per SM (one drains / reduces while the other streams); large tiles: one
-  static constexpr int kCtasPerSm = (MT == 32 && HALVES == 1) ? 2 : 1;
+  // 128-wide tiles: two CTAs per SM (one drains / reduces while the other streams); 256-wide tiles: one
+  static constexpr int kCtasPerSm = HALVES == 1 ? 2 : 1;
   static constexpr int kBudget = kCtasPerSm == 2 ? 104 * 1024 : 200 * 1024;
   static constexpr int kStages = kBudget / kStageBytes >= 6 ? 6 : kBudget / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
@@ -374,10 +376,11 @@ struct Q8Plan {
 };
 static Q8Plan q8_plan(int M, int N, int K, int sm_count, bool allow_split) {
   Q8Plan pl{};
-  pl.mt = M <= 32 ? 32 : 128;
-  pl.halves = M <= 32 ? 1 : 2;
+  // up to 128 rows: many small CTAs (128 weight rows each), two per SM; beyond that the tile is 256 x 128
+  pl.mt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  pl.halves = M <= 128 ? 1 : 2;
   const int bn = 128 * pl.halves;
-  const int ctas = (M <= 32 ? 2 : 1) * sm_count;
+  const int ctas = (pl.halves == 1 ? 2 : 1) * sm_count;
   pl.mtiles = (M + pl.mt - 1) / pl.mt;
   pl.ntiles = (N + bn - 1) / bn;
   const int tiles = pl.mtiles * pl.ntiles;
@@ -469,9 +472,13 @@ static int q8_dispatch(bool is_int, const void* x, const void* w, Q8Params p, un
   const Q8Plan pl = q8_plan(p.M, p.N, p.K, di.sm_count, (flags & AWQ_B200_Q8_NO_SPLIT) == 0);
   if (is_int) {
     if (pl.mt == 32) return launch_q8<true, 32, 1>(x, w, p, pl, di.sm_count, encode, stream);
+    if (pl.mt == 64) return launch_q8<true, 64, 1>(x, w, p, pl, di.sm_count, encode, stream);
+    if (pl.halves == 1) return launch_q8<true, 128, 1>(x, w, p, pl, di.sm_count, encode, stream);
     return launch_q8<true, 128, 2>(x, w, p, pl, di.sm_count, encode, stream);
   }
   if (pl.mt == 32) return launch_q8<false, 32, 1>(x, w, p, pl, di.sm_count, encode, stream);
+  if (pl.mt == 64) return launch_q8<false, 64, 1>(x, w, p, pl, di.sm_count, encode, stream);
+  if (pl.halves == 1) return launch_q8<false, 128, 1>(x, w, p, pl, di.sm_count, encode, stream);
   return launch_q8<false, 128, 2>(x, w, p, pl, di.sm_count, encode, stream);
 }
 

@@ -138,10 +138,63 @@ q8_quant_kernel(const void* x, int M, int K, const unsigned* amax_bits, const fl
   }
 }
 
+// A tensor-wide dynamic scale for a few rows (a decode step): one CTA keeps the tensor in registers between the
+// maximum and the quantisation - one launch, no scratch word.  Up to kSmallVecs vectors of 8 elements per thread.
+constexpr int kSmallVecs = 16;
+template <bool BF16, int MODE>
+__global__ void __launch_bounds__(kQuantThreads)
+q8_quant_small_kernel(const void* x, int vecs, float aux, uint8_t* xq, float* scale_out) {
+  static_assert(MODE == 0 || MODE == 3, "tensor-wide dynamic scales only");
+  __shared__ float red[kQuantThreads / 32];
+  const uint4* xv = static_cast<const uint4*>(x);
+  uint4 v[kSmallVecs];
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < kSmallVecs; ++i) {
+    const int at = i * kQuantThreads + threadIdx.x;
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (at < vecs) {
+      v[i] = __ldg(xv + at);
+      float f[8];
+      unpack8<BF16>(v[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    }
+  }
+  m = block_max(m, red);
+  const float scale = scale_from_amax<BF16, MODE == 3>(m);
+  if (threadIdx.x == 0) {
+    scale_out[0] = scale;
+    if constexpr (MODE == 3) scale_out[1] = round_t<BF16>(__fmul_rn(scale, aux));
+  }
+  uint2* q = reinterpret_cast<uint2*>(xq);
+#pragma unroll
+  for (int i = 0; i < kSmallVecs; ++i) {
+    const int at = i * kQuantThreads + threadIdx.x;
+    if (at < vecs) {
+      float f[8];
+      unpack8<BF16>(v[i], f);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= static_cast<uint32_t>(quant_one<BF16, MODE>(f[j], scale)) << (8 * j);
+        hi |= static_cast<uint32_t>(quant_one<BF16, MODE>(f[4 + j], scale)) << (8 * j);
+      }
+      q[at] = make_uint2(lo, hi);
+    }
+  }
+}
+
 template <bool BF16>
 static int quantize_launch(const void* x, int M, int K, int mode, const float* static_scale, float aux, uint8_t* xq,
                            float* scale_out, unsigned* amax_ws, int sm_count, cudaStream_t stream) {
   const size_t vecs = static_cast<size_t>(M) * K / 8;
+  if ((mode == 0 || mode == 3) && vecs <= static_cast<size_t>(kSmallVecs) * kQuantThreads) {
+    if (mode == 0) q8_quant_small_kernel<BF16, 0><<<1, kQuantThreads, 0, stream>>>(x, static_cast<int>(vecs), aux, xq, scale_out);
+    else q8_quant_small_kernel<BF16, 3><<<1, kQuantThreads, 0, stream>>>(x, static_cast<int>(vecs), aux, xq, scale_out);
+    AWQ_CUDA_TRY(cudaGetLastError());
+    return AWQ_B200_OK;
+  }
   if (mode == 0 || mode == 3) {
     AWQ_CUDA_TRY(cudaMemsetAsync(amax_ws, 0, sizeof(unsigned), stream));
     const size_t want = (vecs + kQuantThreads - 1) / kQuantThreads;
