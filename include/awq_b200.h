@@ -101,7 +101,7 @@ AWQ_B200_API int awq_b200_dequant(const int32_t* qweight, const int32_t* qzeros,
 AWQ_B200_API int awq_b200_dequant_packed(const void* packed, const int32_t* qzeros, const void* scales,
                             void* W, int K, int N, int group_size, awq_b200_stream_t stream);
 
-/* ---- decode: split-K GEMV, M <= 16 -------------------------------------- */
+/* ---- decode: split-K GEMV, M <= 64 (8 rows per CTA) ---------------------- */
 
 /* Bytes of scratch awq_b200_gemv needs for (M, K, N).  The first
  * awq_b200_gemv_counter_bytes(N) bytes (a constant, 16 KiB) hold arrival
@@ -112,8 +112,8 @@ AWQ_B200_API int awq_b200_dequant_packed(const void* packed, const int32_t* qzer
 AWQ_B200_API size_t awq_b200_gemv_workspace_bytes(int M, int K, int N);
 AWQ_B200_API size_t awq_b200_gemv_counter_bytes(int N);
 
-/* y[M, N] = x[M, K] . W (+ bias), 1 <= M <= 16, one pass over the weights for
- * all rows.  Replaces awq_gemv / awq_gemv_coalesced
+/* y[M, N] = x[M, K] . W (+ bias), 1 <= M <= 64 (awq_b200_gemv_static: 16), one pass over the weights per 8
+ * rows.  Replaces awq_gemv / awq_gemv_coalesced
  * (LLMQRT/runtime_refact/csrc/awq/gemv.cu:171-208, gemv_coalesced.cu:263-303).
  * A row's result does not depend on M or on the other rows, and repeated calls
  * give identical bits.  Calls sharing one workspace must not overlap on the GPU. */
@@ -301,7 +301,7 @@ AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* 
 
 /* ---- dispatch ------------------------------------------------------------ */
 
-/* Largest M routed to the GEMV kernel by awq_b200_linear (16). */
+/* Largest M the GEMV entry points accept (64). */
 AWQ_B200_API int awq_b200_gemv_max_rows(void);
 
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
@@ -311,7 +311,8 @@ AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
  * 5 <= M <= 8 from 48 MiB and for 9 <= M <= 16 from 16 MiB (beyond 8 rows the GEMV does its unpacking twice).  The
  * thresholds depend on K and N only, so within a row-count class (1, 2..4, 5..8, 9..16, 17..64) a row's bits do not
  * change with the number of rows decoded together.
- * 17 <= M <= 64 -> awq_b200_skinny where the GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
+ * 17 <= M <= 64 -> awq_b200_gemv for small matrices (packed MiB x ceil(M / 8) <= 32), else awq_b200_skinny where the
+ * GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
  * awq_b200_gemm otherwise.  Group sizes 32 and 64 always take awq_b200_skinny (M <= 64) or awq_b200_gemm.
  * Mirrors the row-count switch in AWQLinearMMFunction.forward
  * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:167-185), which also changes kernel

@@ -1,6 +1,7 @@
-// Decode path: split-K W4A16 GEMV for 1 <= M <= 16 rows.
+// Decode path: split-K W4A16 GEMV for 1 <= M <= 64 rows (8 rows per CTA).
 //
-// One pass over the packed weights serves all rows.  Work unit = one 128-k
+// One pass over the packed weights serves 8 rows; more rows run as more CTAs per (column group, split), which
+// read the same weights at about the same time (L2 hits) and unpack them once each.  Work unit = one 128-k
 // block x one tile of 8 output columns = 512 contiguous bytes, read by a warp
 // as one 128-bit load per lane.  Lane (g = lane / 4, c = lane % 4) owns column
 // 8*tile + g and the four words 4c..4c+3 of that column (32 consecutive k).
@@ -494,8 +495,9 @@ int gemv_dispatch(const void* x, const void* packed, const void* scales, const i
   bool use_stream = force_bps < 1 && stream_by_default(plan, nblk, ntiles, di.sm_count);
   if (flags & AWQ_B200_GEMV_STREAM) use_stream = true;
   if (flags & AWQ_B200_GEMV_PER_SPLIT) use_stream = false;
+  if (M > kGemvStreamMaxRows) use_stream = false;
   if (M > 8 && force_ntw == 0 && use_stream) plan.ntw = 2;
-  const int row_halves = (!use_stream && M > 8) ? 2 : 1;
+  const int row_halves = (!use_stream && M > 8) ? (M + 7) / 8 : 1;
   plan.S = (nblk + plan.bps - 1) / plan.bps;
   plan.ncol = plan_ncol(ntiles, plan.ntw, plan.w, plan.kw);
   unsigned* p_status = nullptr;
@@ -601,7 +603,7 @@ size_t awq_b200_gemv_workspace_bytes(int M, int K, int N) {
   if (M > 8) plan.ntw = 2;
   plan.ncol = plan_ncol(N / 8, plan.ntw, plan.w, plan.kw);
   size_t slots = static_cast<size_t>(plan.S);
-  if (stream_by_default(plan, K / kBlockK, N / 8, sm)) slots = static_cast<size_t>(gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, sm));
+  if (M <= kGemvStreamMaxRows && stream_by_default(plan, K / kBlockK, N / 8, sm)) slots = static_cast<size_t>(gemv_stream_slots(K, N, plan.ntw, plan.w, plan.kw, sm));
   return counter_bytes(N) + slots * M * N * sizeof(float);
 }
 
@@ -687,7 +689,7 @@ int awq_b200_gemv_static_status(unsigned* status_out, awq_b200_stream_t stream) 
 int awq_b200_gemv_static(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
                          const void* bias, void* y, int M, int K, int N, int group_size,
                          awq_b200_stream_t stream) {
-  if (M < 1 || M > kGemvMaxRows) return AWQ_B200_ERR_SHAPE;
+  if (M < 1 || M > 16) return AWQ_B200_ERR_SHAPE;
   if (int st = check_shape(K, N, group_size)) return st;
   // Worst case the planner can ask for at this shape; refuse rather than overrun the fixed array.
   if (awq_b200_gemv_workspace_bytes(M, K, N) > kGemvStaticScratchBytes) return AWQ_B200_ERR_TOO_LARGE;

@@ -8,7 +8,8 @@ namespace awq {
 
 // A CTA has W compute warps (8 or 16) plus one warp that only issues bulk copies.
 constexpr int kGemvMaxBps = 32;   // per warp  // 128-k blocks per split (bounds the activation slice in smem)
-constexpr int kGemvMaxRows = 16;
+constexpr int kGemvMaxRows = 64;          // 8 rows per CTA; more rows = more CTAs per (column group, split)
+constexpr int kGemvStreamMaxRows = 16;    // the persistent stream form holds at most 16 rows per CTA
 // Arrival counters at the start of the workspace (fixed size; the last slot is the status word).
 constexpr int kGemvMaxCounters = 4096;
 // 128-k blocks in flight per CTA (bulk copies): 5 x 17 KiB or 6 x 8.5 KiB of shared memory.

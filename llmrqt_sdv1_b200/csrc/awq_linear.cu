@@ -14,8 +14,9 @@ constexpr int kSkinnyMaxRows = 64;
 //   2..4:       the same with the switch at 36 MiB.
 //   5..8:       the GEMV, or from 48 MiB the exact-weight split-K tensor-memory kernel.
 //   9..16:      the same with the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice).
-//   17..64:     the exact-weight tensor-memory kernel where the GEMM would leave most SMs idle (at most 74
-//               column tiles of 256) and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
+//   17..64:     small matrices (packed MiB x ceil(rows / 8) <= 32): the GEMV, 8 rows per CTA; else the exact-weight
+//               tensor-memory kernel where the GEMM would leave most SMs idle (at most 74 column tiles of 256)
+//               and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
 // Like the reference's own switch from its GEMV to its GEMM at 8 rows (linear_awq.py:167-185), a switch of
 // kernel changes the order of additions.
 enum class Route { kGemv, kDecodeI8, kSkinny, kGemm };
@@ -24,7 +25,7 @@ Route route(int M, int K, int N, int group_size) {
   // Groups of 32 or 64: only the kernels that build the exact fp16 weight per element take them.
   if (group_size < 128) return M <= kSkinnyMaxRows ? Route::kSkinny : Route::kGemm;
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
-  if (M <= awq_b200_gemv_max_rows()) {
+  if (M <= 16) {
     // Measured crossovers against the GEMV (us, graph replay, weights from HBM): the integer kernel wins from
     // ~16-20 MiB at one row (28 MiB: 10.8-11.2 against 12.5-12.9) and from ~36 MiB at four rows.
     if (M <= kDecodeI8MaxRows) {
@@ -35,7 +36,13 @@ Route route(int M, int K, int N, int group_size) {
     if (packed_bytes < from_bytes) return Route::kGemv;
     return Route::kSkinny;
   }
-  if (M <= kSkinnyMaxRows && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
+  // 17..64 rows of a small matrix: the GEMV again, one CTA per 8 rows and column group (the weights are re-read
+  // through L2 and unpacked once per 8 rows: ~0.6 us per MiB and 8 rows, against ~20 us of fixed cost in the
+  // tensor-memory kernels).  Measured win up to packed MiB x ceil(M / 8) = 32.
+  if (M <= kSkinnyMaxRows && packed_bytes * ((M + 7) / 8) <= (32ll << 20)) return Route::kGemv;
+  // The split-K kernel's cost grows with the rows, the GEMM's hardly: below 16 MiB the GEMM wins from ~40 rows.
+  const bool small_and_many = packed_bytes < (16ll << 20) && M > 32;
+  if (M <= kSkinnyMaxRows && !small_and_many && (N + 255) / 256 <= 74 && K / 128 >= 32) return Route::kSkinny;
   return Route::kGemm;
 }
 }  // namespace

@@ -169,7 +169,7 @@ def _gemv_flags(overlap: bool, no_cluster: bool, mode) -> int:
 
 def gemv(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, no_cluster: bool = False,
          mode=None) -> torch.Tensor:
-    """Decode kernel, 1 <= M <= 16.  `overlap=True` lets the kernel prefetch its weights while the
+    """Decode kernel, 1 <= M <= 64 (8 rows per CTA).  `overlap=True` lets the kernel prefetch its weights while the
     previous kernel of the stream drains; pass it only when the weights are not being written by
     work still queued on that stream (i.e. not right after `repack`).  `mode` forces the persistent
     stream ("stream") or the one-CTA-per-split grid ("per_split"); None lets the library choose."""

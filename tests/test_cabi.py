@@ -36,7 +36,7 @@ def test_stateless_queries():
     assert lib.awq_b200_status_string(0) == b"ok"
     assert b"128" in lib.awq_b200_status_string(4)
     assert lib.awq_b200_packed_bytes(2048, 6144) == 2048 * 6144 // 2
-    assert lib.awq_b200_gemv_max_rows() == 16
+    assert lib.awq_b200_gemv_max_rows() == 64
     assert lib.awq_b200_gemv_counter_bytes(6144) == lib.awq_b200_gemv_counter_bytes(57344) == 16384
     ws1 = lib.awq_b200_gemv_workspace_bytes(1, 2048, 6144)
     ws16 = lib.awq_b200_gemv_workspace_bytes(16, 2048, 6144)
@@ -51,5 +51,5 @@ def test_argument_errors_need_no_gpu():
     assert lib.awq_b200_repack(16, 32, 100, 8, None) == ERR_SHAPE
     assert lib.awq_b200_repack(16, 36, 128, 8, None) == ERR_ALIGN
     assert lib.awq_b200_gemv(16, 16, 16, 16, None, 16, 1, 128, 8, 64, None, 0, None) == ERR_GROUP
-    assert lib.awq_b200_gemv(16, 16, 16, 16, None, 16, 17, 128, 8, 128, None, 0, None) == ERR_SHAPE
+    assert lib.awq_b200_gemv(16, 16, 16, 16, None, 16, 65, 128, 8, 128, None, 0, None) == ERR_SHAPE
     assert lib.awq_b200_gemm(16, 16, 16, 16, None, 16, 0, 128, 8, 128, None, 0, None) == ERR_SHAPE

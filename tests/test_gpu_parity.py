@@ -91,7 +91,7 @@ GEMV_SHAPES = [(128, 8), (256, 72), (2048, 2048), (2048, 6144), (6144, 2048), (1
 
 
 @pytest.mark.parametrize("K,N", GEMV_SHAPES)
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 23, 40, 64])
 def test_gemv_vs_oracle(K_, K, N, M):
     qw, qz, sc = tensors(K, N, 128, seed=1)
     x = orc.make_activations(M, K, seed=M)
@@ -178,11 +178,12 @@ def test_gemv_row_result_independent_of_batch(K_):
     K, N = 2048, 4096
     qw, qz, sc = tensors(K, N, 128, seed=4)
     pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
-    x16 = dev(orc.make_activations(16, K, seed=9))
-    y16 = K_.gemv(x16, pw)
-    for M in (1, 2, 7, 8, 9, 15):
-        yM = K_.gemv(x16[:M].contiguous(), pw)
-        assert torch.equal(yM, y16[:M]), f"rows differ between M={M} and M=16"
+    x64 = dev(orc.make_activations(64, K, seed=9))
+    y64 = K_.gemv(x64, pw)
+    x16, y16 = x64[:16].contiguous(), y64[:16]
+    for M in (1, 2, 7, 8, 9, 15, 16, 17, 33):
+        yM = K_.gemv(x64[:M].contiguous(), pw)
+        assert torch.equal(yM, y64[:M]), f"rows differ between M={M} and M=64"
     for r in (3, 12):
         assert torch.equal(K_.gemv(x16[r:r + 1].contiguous(), pw)[0], y16[r])
     for _ in range(50):
@@ -209,7 +210,7 @@ def test_gemv_rejects_bad_arguments(K_):
     qw, qz, sc = tensors(256, 72, 128, seed=5)
     pw = K_.make_packed(dev(qw), dev(qz), dev(sc), 128)
     with pytest.raises(ValueError):
-        K_.gemv(torch.zeros(17, 256, dtype=torch.float16, device="cuda"), pw)
+        K_.gemv(torch.zeros(65, 256, dtype=torch.float16, device="cuda"), pw)
     with pytest.raises(ValueError):
         K_.gemv(torch.zeros(1, 128, dtype=torch.float16, device="cuda"), pw)
     with pytest.raises(ValueError):
