@@ -647,10 +647,14 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
             st[name] = ps.status()
         return st
 
+    fused = False          # the down kernel's epilogue does the push exchange itself (one launch less per layer)
+
     def step():
         for i in range(FFN70B_LAYERS):
             kernels.linear(x_g, pw_g[i], out=y_g[i], overlap=True)
-            if peer is not None:
+            if peer is not None and fused:
+                peer.linear_push(x_d, pw_d[i], out=y_d[i], overlap=True)
+            elif peer is not None:
                 kernels.linear(x_d, pw_d[i], out=peer.partial(M, Nd), overlap=True)
                 peer.reduce(M, Nd, out=y_d[i])
             else:
@@ -669,18 +673,24 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
     # same number of replays on every rank) and the fastest is the configuration that is measured.
     allreduce, calib = "none", {}
     if world > 1:
-        for name in list(peers) + ["nccl"]:
-            peer = peers.get(name)
+        names = list(peers) + ["nccl"]
+        if "peer_push" in peers and peers["peer_push"].can_fuse(M, pw_d[0]):
+            names.insert(0, "peer_push_fused")
+        for name in names:
+            peer = peers.get("peer_push" if name == "peer_push_fused" else name)
+            fused = name == "peer_push_fused"
             dist.barrier()
             tc = torch.tensor([time_graph(torch, step_nccl if name == "nccl" else step, iters=5)], device=dev)
             dist.all_reduce(tc, op=dist.ReduceOp.MAX)
             calib[name] = float(tc.item())
             require_clean(torch, f"calibration of {name}", **statuses())
         allreduce = min(calib, key=calib.get)
-        peer = peers.get(allreduce)
+        fused = allreduce == "peer_push_fused"
+        peer = peers.get("peer_push" if fused else allreduce)
         if peer is not None:
             for m in down:
                 m.use_peer_sum(peer)
+                m.fuse_exchange = fused
     step_timed = step_nccl if allreduce == "nccl" else step
     # the exchange that is timed against the library collective on the same partials (fp32 sum of fp16
     # partials vs NCCL's fp16 additions: equal to a few fp16 places)
@@ -877,8 +887,9 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         return
     value = step_bytes_total / (ms * 1e-3) / 1e9
     per_gpu = value / world
-    launches_per_layer = (3 if allreduce.startswith("peer") else 2)
-    exchange = ("one-shot all-reduce over peer memory (NVLink)" if allreduce.startswith("peer")
+    launches_per_layer = 2 if (fused or not allreduce.startswith("peer")) else 3
+    exchange = ("push exchange over peer memory (NVLink) inside the down kernel's epilogue" if fused
+                else "one-shot all-reduce over peer memory (NVLink)" if allreduce.startswith("peer")
                 else ("NCCL all-reduce" if world > 1 else "no exchange (one GPU)"))
     line = {
         "metric": "W4A16 GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,

@@ -299,6 +299,22 @@ AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* 
                                  const void* bias, size_t count, int ncols, size_t slot_elems, int rank,
                                  int world, awq_b200_stream_t stream);
 
+/* awq_b200_decode_i8 for this rank's ROW shard of a row-parallel linear, with the push form of the exchange done by
+ * the kernel's own epilogue: each finished pair of results is stored, in the wire format of
+ * awq_b200_peer_allreduce_push, into this rank's slot on every peer; the same threads then collect the peers' words
+ * for that position out of this rank's receive area, add all ranks' values in rank order in fp32 and write the SUM to
+ * y[M, N] - the bits awq_b200_decode_i8 followed by awq_b200_peer_allreduce_push give, in one launch less.
+ * recv / flags / slot_elems / rank / world (2..8) as for awq_b200_peer_allreduce_push, and the calls of the two entry
+ * points may be mixed freely (they share the call counter), as long as every rank makes the same sequence of calls.
+ * bias (this rank's, normally rank 0 only) is added to the partial before the exchange.  Waits on peers are bounded
+ * (AWQ_B200_PEER_WAIT_LIMIT_WORD); on expiry the status word (AWQ_B200_PEER_STATUS_WORD) becomes 3.
+ * Plays the part of the all-reduce that follows a row-parallel linear in the reference's tensor-parallel layers
+ * (spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:195-199). */
+AWQ_B200_API int awq_b200_decode_i8_push(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                            const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                            size_t workspace_bytes, void* const* recv, void* const* flags, size_t slot_elems,
+                            int rank, int world, awq_b200_stream_t stream, unsigned call_flags);
+
 /* ---- dispatch ------------------------------------------------------------ */
 
 /* Largest M the GEMV entry points accept (64). */

@@ -45,6 +45,7 @@ SIGNATURES = {
     "awq_b200_skinny": (_I, _COMPUTE + [C.c_uint]),
     "awq_b200_decode_workspace_bytes": (_Z, [_I, _I, _I]),
     "awq_b200_decode_i8": (_I, _COMPUTE + [C.c_uint]),
+    "awq_b200_decode_i8_push": (_I, _COMPUTE[:-1] + [_P, _P, _Z, _I, _I, _P, C.c_uint]),
     "awq_b200_peer_allreduce_flag_bytes": (_Z, []),
     "awq_b200_peer_allreduce": (_I, [_P, _P, _P, _P, _Z, _I, _I, _I, _P]),
     "awq_b200_peer_allreduce_push": (_I, [_P, _P, _P, _P, _P, _Z, _I, _Z, _I, _I, _P]),

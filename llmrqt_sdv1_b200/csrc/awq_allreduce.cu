@@ -22,27 +22,9 @@
 // in the number of calls) the ranks' call counters disagree and every later call expires too, until the flag
 // arrays and receive areas have been zeroed again on every rank with no call in flight (a collective reset;
 // the wait-limit word may be kept).
-#include "awq_common.cuh"
+#include "awq_peer.cuh"
 
 namespace awq {
-
-constexpr int kArMaxWorld = 16;
-constexpr unsigned long long kArWaitLimitCycles = 4000000000ull;   // default limit of a wait on a peer: ~2 s at 2 GHz
-
-// Flag array layout (uint32 words) in each rank's symmetric flag buffer:
-//   [0, 16)   ready[r]   written by rank r
-//   [16, 32)  done[r]    written by rank r
-//   [32]      epoch of the last completed call (local)
-//   [33]      blocks of the current call that finished summing (local)
-//   [34]      status: 0, or 1 / 2 when the ready / done wait expired, 3 for the push variant's wait (local, sticky)
-//   [35], [36] epoch and finished-block counter of the push variant (local)
-//   [37]      limit of a wait on a peer in units of 1024 SM cycles; 0 = the default of ~2 s (local, set by the host)
-constexpr int kArReadyOff = 0, kArDoneOff = 16, kArEpochOff = 32, kArBlocksOff = 33, kArStatusOff = 34;
-constexpr int kArPushEpochOff = 35, kArPushBlocksOff = 36, kArLimitOff = 37;
-static_assert(kArStatusOff == AWQ_B200_PEER_STATUS_WORD && kArLimitOff == AWQ_B200_PEER_WAIT_LIMIT_WORD,
-              "the header documents these two words");
-constexpr int kArMaxBlocks = 64;
-constexpr int kArFlagWords = 64;
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -63,11 +45,6 @@ __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
                : "l"(p)
                : "memory");
   return v;
-}
-
-__device__ __forceinline__ unsigned long long wait_limit_cycles(const unsigned* my_flags) {
-  const unsigned kcycles = my_flags[kArLimitOff];
-  return kcycles != 0u ? static_cast<unsigned long long>(kcycles) << 10 : kArWaitLimitCycles;
 }
 
 // Waits until flags[off + r] == epoch for every r < world.  Returns false on expiry.
@@ -175,19 +152,6 @@ peer_allreduce_kernel(const uint16_t* const* bufs, unsigned* const* flags, uint1
 // call e + 1, which a peer sends only after its own call e has completed (calls on a stream do not overlap:
 // each kernel of the chain waits for its predecessor before touching anything).
 // ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void st_wire_16(void* p, uint32_t d0, uint32_t d1, uint32_t flag) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
-               : "memory");
-}
-__device__ __forceinline__ uint4 ld_wire_16(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
 // recv[r]: rank r's receive area, 2 parities x world slots x (4 * slot_elems) bytes (wire format).
 __global__ void __launch_bounds__(kArThreads)
 peer_allreduce_push_kernel(const uint16_t* partial, unsigned char* const* recv, unsigned* const* flags, uint16_t* out,

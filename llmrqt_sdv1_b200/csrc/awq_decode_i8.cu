@@ -37,6 +37,7 @@
 // unit the tensor core runs 8 instructions (2 halves x 2 k steps of 32 slots x {hi, raw}).  A group folds unit u
 // when it starts on unit u + 2.  Every mbarrier wait is bounded (see awq_ptx.cuh).
 #include "awq_gemv_common.cuh"
+#include "awq_peer.cuh"
 #include "awq_tcgen05.cuh"
 
 namespace awq {
@@ -96,6 +97,11 @@ struct D8Params {
   int ntiles;
   int nblk;
   long long units;
+  // Row-parallel shard: the epilogue performs the push form of the peer exchange itself (PUSH kernels only).
+  unsigned char* const* recv;   // per rank: receive area, 2 parities x world slots x slot_bytes (wire format)
+  unsigned* const* pflags;      // per rank: flag array (awq_peer.cuh)
+  size_t slot_bytes;
+  int rank, world;
 };
 
 __device__ __forceinline__ void d8_unpack_warps_sync() {
@@ -185,7 +191,56 @@ __device__ __forceinline__ void d8_tmem_ld(uint32_t taddr, uint32_t (&v)[N]) {
   }
 }
 
-template <int MR>
+// Push form of the row-parallel exchange, per payload word (two adjacent fp16 results of this rank's shard; word w
+// of a slot sits at byte 8 w).  d8_push_word stores {payload, epoch} into this rank's slot on every peer;
+// d8_collect_word gathers the peers' words for the same position out of this rank's own receive area, adds all
+// ranks' values in rank order in fp32 (the arithmetic of peer_allreduce_push_kernel: identical bits on every rank)
+// and returns the rounded pair.  Waits are bounded by one limit per call (t_call); on expiry *fail is raised and
+// the result is meaningless.  A thread pushes all its words before it collects the first.
+constexpr int kD8PushMaxWorld = 8;
+__device__ __forceinline__ void d8_push_word(const D8Params& p, unsigned epoch, size_t word, uint32_t payload) {
+  const size_t par_off = static_cast<size_t>(epoch & 1u) * p.world;
+#pragma unroll
+  for (int r = 0; r < kD8PushMaxWorld; ++r)
+    if (r < p.world && r != p.rank) st_wire_8(p.recv[r] + (par_off + p.rank) * p.slot_bytes + word * 8, payload, epoch);
+}
+__device__ __forceinline__ uint32_t d8_collect_word(const D8Params& p, unsigned epoch, unsigned long long t_call,
+                                                    unsigned long long limit, volatile int* fail, size_t word,
+                                                    uint32_t payload) {
+  const size_t par_off = static_cast<size_t>(epoch & 1u) * p.world;
+  const unsigned char* slots = p.recv[p.rank] + par_off * p.slot_bytes + word * 8;
+  uint2 v[kD8PushMaxWorld];
+#pragma unroll
+  for (int r = 0; r < kD8PushMaxWorld; ++r) {
+    v[r] = make_uint2(payload, epoch);
+    if (r < p.world && r != p.rank) v[r] = ld_wire_8(slots + static_cast<size_t>(r) * p.slot_bytes);
+  }
+  bool ok = true;
+#pragma unroll
+  for (int r = 0; r < kD8PushMaxWorld; ++r) {
+    if (r < p.world && r != p.rank && ok) {
+      unsigned spins = 0;
+      while (v[r].y != epoch) {
+        if ((++spins & 15u) == 0u && (*fail != 0 || clock64() - t_call > limit)) { ok = false; break; }
+        v[r] = ld_wire_8(slots + static_cast<size_t>(r) * p.slot_bytes);
+      }
+    }
+  }
+  if (!ok) *fail = 1;
+  float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < kD8PushMaxWorld; ++r) {
+    if (r < p.world) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[r].x));
+      acc.x += f.x;
+      acc.y += f.y;
+    }
+  }
+  const __half2 o = __floats2half2_rn(acc.x, acc.y);
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+
+template <int MR, bool PUSH>
 __global__ void __launch_bounds__(kD8Threads, kD8CtasPerSm)
 decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   using Cfg = D8Cfg<MR>;
@@ -193,6 +248,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
   __shared__ int s_last;
+  __shared__ int s_push_fail;
   __shared__ uint32_t s_tmem_base;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -215,6 +271,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 
   if (tid == 0) {
     s_abort = 0;
+    s_push_fail = 0;
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar_full_tma(t), 1);
       mbar_init(bar_empty(t), kD8UnpackWarps / kD8Groups + 1);
@@ -402,6 +459,22 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   } else {
     // ---------------------- mask into tensor memory, then fold accumulators ---------------
     asm volatile("griddepcontrol.wait;" ::: "memory");   // y and the workspace belong to the previous kernel until here
+    // PUSH: the call's epoch (advanced by the last CTA of the previous exchange, which has completed by now)
+    unsigned push_epoch = 0u;
+    unsigned long long push_limit = 0ull, push_t0 = 0ull;
+    volatile int* push_fail = &s_push_fail;
+    if constexpr (PUSH) {
+      const unsigned* my_flags = p.pflags[p.rank];
+      push_epoch = my_flags[kArPushEpochOff] + 1u;
+      push_limit = wait_limit_cycles(my_flags);
+      push_t0 = clock64();
+    }
+    // This rank's rounded pair (col even) of row m, bias included: what the unfused kernel would have stored.
+    auto pair_bits = [&](int col, float a, float b) -> uint32_t {
+      __half2 h = __floats2half2_rn(a, b);
+      if (p.epi.bias != nullptr) h = __hadd2(h, *reinterpret_cast<const __half2*>(p.epi.bias + col));
+      return *reinterpret_cast<const uint32_t*>(&h);
+    };
     const int id = tid - 64;                  // 0..255
     const int dq_warp = id >> 5;              // 0..7
     const int lane_q = warp & 3;              // TMEM lane quarter this warp may touch
@@ -560,15 +633,47 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       const int slot = static_cast<int>(blockIdx.x) - c_first;
       const bool direct = (nc == 1);
       if (grp == 0) {
+        if (PUSH && direct) {
+          // Exchange in the epilogue: an even lane owns the pair (its column, its neighbour's); all of a thread's
+          // words leave for the peers before it collects the first of theirs.
+          uint32_t pay[2][MR];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < 2; ++h) {
 #pragma unroll
-          for (int m = 0; m < MR; ++m) {
-            if (m < p.M) {                                 // warp-uniform
-              const float* cb = comb + m * kD8BN + h * 128 + cl0;
-              const float val = acc[h][m] + cb[0];
-              if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, ncol[h], val, nval[h]);
-              else if (nval[h]) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + ncol[h], val);
+            for (int m = 0; m < MR; ++m) {
+              pay[h][m] = 0u;
+              if (m < p.M) {                               // warp-uniform
+                const float val = acc[h][m] + comb[m * kD8BN + h * 128 + cl0];
+                const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                if (nval[h] && (lane & 1) == 0) {
+                  pay[h][m] = pair_bits(ncol[h], val, other);
+                  d8_push_word(p, push_epoch, (static_cast<size_t>(m) * p.N + ncol[h]) >> 1, pay[h][m]);
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+              if (m < p.M && nval[h] && (lane & 1) == 0) {
+                const size_t at = static_cast<size_t>(m) * p.N + ncol[h];
+                *reinterpret_cast<uint32_t*>(p.y + at) =
+                    d8_collect_word(p, push_epoch, push_t0, push_limit, push_fail, at >> 1, pay[h][m]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+              if (m < p.M) {                                 // warp-uniform
+                const float* cb = comb + m * kD8BN + h * 128 + cl0;
+                const float val = acc[h][m] + cb[0];
+                if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, ncol[h], val, nval[h]);
+                else if (nval[h]) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + ncol[h], val);
+              }
             }
           }
         }
@@ -598,7 +703,15 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
               sum.x += v.x;
               sum.y += v.y;
             }
-            epilogue_store_pair(p.y, p.epi, row, p.N, col, sum.x, sum.y);
+            if constexpr (PUSH) {
+              const uint32_t mine = pair_bits(col, sum.x, sum.y);
+              const size_t at = static_cast<size_t>(row) * p.N + col;
+              d8_push_word(p, push_epoch, at >> 1, mine);
+              *reinterpret_cast<uint32_t*>(p.y + at) =
+                  d8_collect_word(p, push_epoch, push_t0, push_limit, push_fail, at >> 1, mine);
+            } else {
+              epilogue_store_pair(p.y, p.epi, row, p.N, col, sum.x, sum.y);
+            }
           }
         }
         d8_unpack_warps_sync();   // s_last is rewritten by the next straddling segment
@@ -615,6 +728,21 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
                  : "memory");
   }
   if (tid == 0 && s_abort != 0 && p.status != nullptr) atomicCAS(p.status, 0u, 0x400u | static_cast<unsigned>(s_abort));
+  if constexpr (PUSH) {
+    // The last CTA closes the exchange: the epoch advances once per call (device memory: graphs replay).  Every
+    // CTA read the old epoch after the barrier above at the latest, and the last one writes after all have counted.
+    if (tid == 0) {
+      unsigned* my_flags = p.pflags[p.rank];
+      const unsigned epoch = my_flags[kArPushEpochOff] + 1u;
+      if (s_push_fail != 0 || s_abort != 0) atomicCAS(my_flags + kArStatusOff, 0u, 3u);
+      __threadfence();
+      const unsigned prev = atomicAdd(my_flags + kArPushBlocksOff, 1u);
+      if (prev == gridDim.x - 1) {
+        my_flags[kArPushBlocksOff] = 0u;
+        my_flags[kArPushEpochOff] = epoch;
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -653,7 +781,7 @@ size_t decode_workspace_bytes(int M, int K, int N, int sm_count) {
   return kGemvMaxCounters * sizeof(unsigned) + (slots > 1 ? static_cast<size_t>(slots) * M * N * sizeof(float) : 0);
 }
 
-template <int MR>
+template <int MR, bool PUSH>
 static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTiledFn encode, cudaStream_t stream,
                             bool overlap_previous, int max_smem_optin) {
   using Cfg = D8Cfg<MR>;
@@ -670,9 +798,9 @@ static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTile
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
   }
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   // two CTAs of ~100 KB per SM: ask for the largest shared-memory carve-out
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -688,13 +816,20 @@ static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTile
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_i8_kernel<MR>, mw, p));
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_i8_kernel<MR, PUSH>, mw, p));
   return AWQ_B200_OK;
 }
 
-int decode_i8_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
-                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
-                       cudaStream_t stream, unsigned flags) {
+struct D8PushArgs {
+  void* const* recv;
+  void* const* flags;
+  size_t slot_elems;
+  int rank, world;
+};
+
+static int decode_i8_run(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                         void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                         cudaStream_t stream, unsigned flags, const D8PushArgs* push) {
   if (!x || !packed || !scales || !qzeros || !y) return AWQ_B200_ERR_NULL;
   if (int st = check_shape(K, N, group_size)) return st;
   if (M < 1 || M > kD8MaxRows) return AWQ_B200_ERR_SHAPE;
@@ -726,9 +861,31 @@ int decode_i8_dispatch(const void* x, const void* packed, const void* scales, co
   p.units = static_cast<long long>(ntiles) * p.nblk;
   const int grid = static_cast<int>(decode_grid(di.sm_count, p.units, ntiles));
   const bool overlap = (flags & AWQ_B200_OVERLAP_PREVIOUS) != 0;
-  if (M <= 1) return launch_decode_i8<1>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-  if (M <= 2) return launch_decode_i8<2>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-  return launch_decode_i8<4>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  p.recv = nullptr; p.pflags = nullptr; p.slot_bytes = 0; p.rank = 0; p.world = 0;
+  if (push != nullptr) {
+    if (!push->recv || !push->flags) return AWQ_B200_ERR_NULL;
+    if (push->world < 2 || push->world > 8 || push->rank < 0 || push->rank >= push->world) return AWQ_B200_ERR_SHAPE;
+    if (static_cast<size_t>(M) * N > push->slot_elems) return AWQ_B200_ERR_TOO_LARGE;
+    if (epi.residual != nullptr || epi.gated) return AWQ_B200_ERR_SHAPE;      // the exchanged value is the plain sum
+    p.recv = reinterpret_cast<unsigned char* const*>(push->recv);
+    p.pflags = reinterpret_cast<unsigned* const*>(push->flags);
+    p.slot_bytes = push->slot_elems * 4;
+    p.rank = push->rank;
+    p.world = push->world;
+    if (M <= 1) return launch_decode_i8<1, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    if (M <= 2) return launch_decode_i8<2, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    return launch_decode_i8<4, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  }
+  if (M <= 1) return launch_decode_i8<1, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  if (M <= 2) return launch_decode_i8<2, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  return launch_decode_i8<4, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+}
+
+int decode_i8_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,
+                       void* y, int M, int K, int N, int group_size, void* workspace, size_t workspace_bytes,
+                       cudaStream_t stream, unsigned flags) {
+  return decode_i8_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, workspace, workspace_bytes, stream, flags,
+                       nullptr);
 }
 
 }  // namespace awq
@@ -747,6 +904,18 @@ int awq_b200_decode_i8(const void* x, const void* packed, const void* scales, co
                        awq_b200_stream_t stream, unsigned flags) {
   return awq::decode_i8_dispatch(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0},
                                  y, M, K, N, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), flags);
+}
+
+// awq_b200_decode_i8 for a row-parallel shard, with the push form of the peer exchange (awq_b200_peer_allreduce_push)
+// performed by the kernel's epilogue: y receives the SUM over the ranks.
+int awq_b200_decode_i8_push(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
+                            const void* bias, void* y, int M, int K, int N, int group_size, void* workspace,
+                            size_t workspace_bytes, void* const* recv, void* const* flags, size_t slot_elems, int rank,
+                            int world, awq_b200_stream_t stream, unsigned call_flags) {
+  const awq::D8PushArgs push{recv, flags, slot_elems, rank, world};
+  return awq::decode_i8_run(x, packed, scales, qzeros, awq::Epilogue{static_cast<const uint16_t*>(bias), nullptr, 0}, y, M,
+                            K, N, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), call_flags,
+                            &push);
 }
 
 }  // extern "C"

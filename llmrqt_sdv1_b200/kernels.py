@@ -372,6 +372,24 @@ def peer_allreduce_push(partial: torch.Tensor, recv_dev: int, flags_dev: int, sl
     return y
 
 
+def decode_i8_push(x, pw: PackedWeight, recv_dev: int, flags_dev: int, slot_elems: int, rank: int, world: int,
+                   bias=None, out=None, overlap: bool = False) -> torch.Tensor:
+    """`decode_i8` on this rank's row shard with the push form of the peer exchange done by the kernel's epilogue:
+    returns the SUM over the ranks (see `sharded.PeerSum.linear_push`).  1 <= M <= 4, 2 <= world <= 8."""
+    x = _check_x(x, pw)
+    M = x.shape[0]
+    _check_out(out, None, M, pw.N, x.device)
+    dev = _prep(x, pw.packed, pw.qzeros, pw.scales, bias)
+    y = out if out is not None else torch.empty((M, pw.N), dtype=torch.float16, device=dev)
+    stream = _stream(x)
+    ws = _workspace(dev, stream, lib.awq_b200_decode_workspace_bytes(max(M, 1), pw.K, pw.N), "awq_b200_decode")
+    check(lib.awq_b200_decode_i8_push(x.data_ptr(), pw.packed.data_ptr(), pw.scales.data_ptr(), pw.qzeros.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, y.data_ptr(), M, pw.K, pw.N,
+                                      pw.group_size, ws.data_ptr(), ws.numel(), recv_dev, flags_dev, slot_elems, rank,
+                                      world, stream, _lib.OVERLAP_PREVIOUS if overlap else 0), "awq_b200_decode_i8_push")
+    return y
+
+
 def qk_norm_rope_cache(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, q_out, k_cache, v_cache) -> None:
     """One token's fused qkv row -> q (normalised per head, rotated) into `q_out` [H, D], k (likewise) and v into row
     `pos` of `k_cache` / `v_cache` [KV, max_len, D].  `pos` is an int64 tensor on the device (one element)."""

@@ -173,6 +173,25 @@ class PeerSum:
         return kernels.peer_allreduce(self._h_buf.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev, self.buf,
                                       M, N, self.rank, self.world, out=out, bias=bias)
 
+    # The fused form: one to four rows of a shard whose weights are large enough for the integer decode kernel
+    # (about what that kernel needs to beat the GEMV plus a separate exchange launch).
+    FUSED_MAX_ROWS, FUSED_MIN_PACKED_BYTES = 4, 12 << 20
+
+    def can_fuse(self, M: int, pw) -> bool:
+        """Whether `linear_push` serves M rows of this packed shard (push mode, 2..8 ranks, group size >= 128)."""
+        return (self.mode == "push" and 2 <= self.world <= 8 and 1 <= M <= self.FUSED_MAX_ROWS
+                and pw.group_size % 128 == 0 and pw.K * pw.N // 2 >= self.FUSED_MIN_PACKED_BYTES
+                and self.fits(M, pw.N))
+
+    def linear_push(self, x2d: torch.Tensor, pw, bias=None, out: torch.Tensor | None = None,
+                    overlap: bool = False) -> torch.Tensor:
+        """This rank's row shard times its activations AND the sum over the ranks, in one launch: the decode
+        kernel's epilogue pushes each finished pair of results to the peers and collects theirs.  Same bits as
+        `kernels.decode_i8` into `partial()` followed by `reduce()`; counts as one call of the exchange."""
+        from . import kernels
+        return kernels.decode_i8_push(x2d, pw, self._h_recv.buffer_ptrs_dev, self._h_flags.buffer_ptrs_dev,
+                                      self.max_elems, self.rank, self.world, bias=bias, out=out, overlap=overlap)
+
     STATUS_WORD, WAIT_LIMIT_WORD = 34, 37      # AWQ_B200_PEER_STATUS_WORD / AWQ_B200_PEER_WAIT_LIMIT_WORD
 
     def status(self) -> int:
@@ -255,6 +274,9 @@ class RowParallelAWQLinear(nn.Module):
                 from . import kernels
                 pw = self.packed()
                 overlap, pw.fresh = not pw.fresh, False     # first call after a repack: no weight prefetch
+                if getattr(self, "fuse_exchange", True) and ps.can_fuse(rows, pw):
+                    y = ps.linear_push(x.reshape(rows, -1), pw, bias=self.linear.bias, overlap=overlap)
+                    return y.view(*x.shape[:-1], N) if x.dim() > 2 else y.view(1, rows, N)
                 kernels.linear(x.reshape(rows, -1), pw, bias=self.linear.bias, out=ps.partial(rows, N),
                                overlap=overlap)
                 y = ps.reduce(rows, N)

@@ -65,6 +65,45 @@ def _check_mode(mode, rank, world, dev, dist, quantize, PeerSum, RowParallelAWQL
         y_peer = mod(x)
         rel = ((y_peer.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max()).item()
         ok = ok and y_peer.shape == y_nccl.shape and rel <= 2e-3
+        # the exchange inside the decode kernel's epilogue: same bits as decode kernel + push kernel, and the two
+        # forms may alternate (one call counter)
+        if mode == "push":
+            from llmrqt_sdv1_b200 import kernels
+            K2, N2 = 4096 * world, 8192                                  # 16 MiB per rank
+            qw, qz, sc = quantize.random_awq_tensors(K2 // world, N2, 128, seed=7 + rank, device=dev)
+            bias = torch.randn(N2, device=dev, generator=torch.Generator(device=dev).manual_seed(8)).half()
+            mod2 = RowParallelAWQLinear.from_local(qw, qz, sc, bias, 128)
+            mod2.use_peer_sum(ps)
+            pw2 = mod2.packed()
+            for M2 in (1, 4, 2):
+                x2 = torch.randn((M2, K2 // world), device=dev, generator=torch.Generator(device=dev).manual_seed(20 + rank + M2)).half()
+                ok = ok and ps.can_fuse(M2, pw2)
+                mod2.fuse_exchange = True
+                y_fused = mod2(x2).view(M2, N2)
+                kernels.decode_i8(x2, pw2, bias=mod2.linear.bias, out=ps.partial(M2, N2))
+                y_two = ps.reduce(M2, N2)
+                ok = ok and torch.equal(y_fused, y_two)
+                ys = [torch.empty_like(y_fused) for _ in range(world)]
+                dist.all_gather(ys, y_fused)
+                ok = ok and all(torch.equal(ys[0], t) for t in ys)
+            # in a graph, alternating with the standalone form
+            x2 = torch.randn((1, K2 // world), device=dev, generator=torch.Generator(device=dev).manual_seed(40 + rank)).half()
+            o1 = torch.empty((1, N2), dtype=torch.float16, device=dev)
+            o2 = torch.empty((1, N2), dtype=torch.float16, device=dev)
+            def both():
+                ps.linear_push(x2, pw2, bias=mod2.linear.bias, out=o1)
+                kernels.decode_i8(x2, pw2, bias=mod2.linear.bias, out=ps.partial(1, N2))
+                ps.reduce(1, N2, out=o2)
+            both()
+            gr2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr2):
+                both()
+                both()
+                ps.linear_push(x2, pw2, bias=mod2.linear.bias, out=o1)
+            for _ in range(3):
+                gr2.replay()
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(o1, o2)
         # a graph with an odd number of calls replays correctly (the epoch, and with it the receive slot in
         # use, lives in device memory)
         outs = [torch.empty((1, 4096), dtype=torch.float16, device=dev) for _ in range(3)]

@@ -64,6 +64,12 @@ class _Rig:
         return kernels.peer_allreduce_push(part, self.recv_tab.data_ptr(), self.flags_tab.data_ptr(),
                                            self.slot_elems, M, N, 0, WORLD, out=out, bias=bias)
 
+    def fused(self, x, pw, out=None, bias=None, overlap=False):
+        """Rank 0's row shard through the decode kernel whose epilogue does the push exchange itself."""
+        from llmrqt_sdv1_b200 import kernels
+        return kernels.decode_i8_push(x, pw, self.recv_tab.data_ptr(), self.flags_tab.data_ptr(), self.slot_elems, 0,
+                                      WORLD, bias=bias, out=out, overlap=overlap)
+
     def pull(self, M, N, out=None, bias=None):
         from llmrqt_sdv1_b200 import kernels
         return kernels.peer_allreduce(self.bufs_tab.data_ptr(), self.flags_tab.data_ptr(), self.bufs[0], M, N, 0,
@@ -188,3 +194,106 @@ def test_pull_wait_runs_out_sets_status():
     y = rig.pull(1, 4096)
     torch.cuda.synchronize()
     assert bool((y == 3.0).all()) and int(rig.flags[0][STATUS].item()) == 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The decode kernel that performs the push exchange in its epilogue (awq_b200_decode_i8_push)
+# ---------------------------------------------------------------------------------------------------------------
+def _packed(K, N, seed):
+    from llmrqt_sdv1_b200 import kernels, quantize
+    qw, qz, sc = quantize.random_awq_tensors(K, N, 128, seed=seed, device="cuda")
+    return kernels.make_packed(qw, qz, sc, 128)
+
+
+@pytest.mark.parametrize("K,N", [(1024, 2048),        # 8 column tiles x 8 blocks = 64 units: one CTA per unit, shared tiles
+                                 (8192, 8192),        # 32 tiles x 64 blocks: several CTAs per tile, all through partials
+                                 (128, 80 * 256)])    # 80 tiles x 1 block: every CTA owns its tile (direct stores)
+def test_fused_exchange_equals_decode_then_push(K, N):
+    """Same bits as the decode kernel into a partial followed by the push kernel; the words sent to the peer are
+    this rank's partial in wire format; the call counter advances once per call; bias goes into the partial."""
+    from llmrqt_sdv1_b200 import kernels
+    pw = _packed(K, N, seed=K + N)
+    rig = _Rig(4 * N)
+    epoch = 0
+    for call, M in enumerate((1, 2, 4, 3, 1)):
+        epoch += 1
+        x = _rand((M, K), 50 + call)
+        bias = _rand((N,), 60 + call) if call % 2 else None
+        theirs = _rand((M, N), 70 + call)
+        mine = kernels.decode_i8(x, pw, bias=bias)                 # what the unfused path would push
+        rig.peer_pushes(theirs, epoch)
+        y = rig.fused(x, pw, bias=bias, overlap=(call % 2 == 0))
+        torch.cuda.synchronize()
+        assert torch.equal(y, _fp32_sum(mine, theirs)), f"call {call}: wrong sum"
+        sent, counters_ok = rig.sent_by_rank0(M * N, epoch)
+        assert counters_ok and torch.equal(sent.view(M, N), mine), f"call {call}: wire words sent to the peer are wrong"
+        assert int(rig.flags[0][35].item()) == epoch
+    # the standalone push kernel continues the same call sequence (shared counter and slots)
+    epoch += 1
+    mine, theirs = _rand((1, N), 1), _rand((1, N), 2)
+    rig.peer_pushes(theirs, epoch)
+    assert torch.equal(rig.push(mine, 1, N), _fp32_sum(mine, theirs))
+    torch.cuda.synchronize()
+    assert int(rig.flags[0][STATUS].item()) == 0
+    assert kernels.gemv_status() == 0
+
+
+def test_fused_exchange_inside_a_replayed_graph():
+    from llmrqt_sdv1_b200 import kernels
+    K, N = 4096, 4096
+    pw = _packed(K, N, seed=9)
+    rig = _Rig(N)
+    x = [_rand((1, K), 20), _rand((1, K), 21), _rand((1, K), 22)]
+    mine = [kernels.decode_i8(xi, pw) for xi in x]
+    outs = [torch.empty((1, N), dtype=torch.float16, device="cuda") for _ in x]
+    epoch = 0
+
+    def fill(seed):
+        theirs = [_rand((1, N), seed + j) for j in range(3)]
+        # three calls per replay: the third reuses the parity of the first, so the host writes it after the
+        # first two slots have been consumed - here all three are written up front into distinct epochs' words
+        for j, t in enumerate(theirs[:2]):
+            rig.peer_pushes(t, epoch + 1 + j)
+        return theirs
+
+    theirs = fill(200)
+    for o, xi in zip(outs[:2], x[:2]):
+        rig.fused(xi, pw, out=o)
+    torch.cuda.synchronize()
+    epoch += 2
+    for j in range(2):
+        assert torch.equal(outs[j], _fp32_sum(mine[j], theirs[j]))
+    g = torch.cuda.CUDAGraph()
+    theirs = fill(300)
+    with torch.cuda.graph(g):
+        for o, xi in zip(outs[:2], x[:2]):
+            rig.fused(xi, pw, out=o)
+    for rep in range(3):
+        theirs = fill(400 + 10 * rep)
+        g.replay()
+        torch.cuda.synchronize()
+        epoch += 2
+        for j in range(2):
+            assert torch.equal(outs[j], _fp32_sum(mine[j], theirs[j])), f"replay {rep}, call {j}"
+    assert int(rig.flags[0][35].item()) == epoch and int(rig.flags[0][STATUS].item()) == 0
+
+
+def test_fused_exchange_wait_runs_out_sets_status_and_reset_recovers():
+    """Nothing arrives from the peer and the limit is ~1 ms: the kernel returns, status 3, the context stays usable;
+    after a reset the next matched call is correct."""
+    from llmrqt_sdv1_b200 import kernels
+    K, N = 2048, 4096
+    pw = _packed(K, N, seed=3)
+    rig = _Rig(N)
+    rig.flags[0][LIMIT] = 2000                      # x 1024 cycles: about a millisecond
+    x = _rand((1, K), 5)
+    rig.fused(x, pw)
+    torch.cuda.synchronize()
+    assert int(rig.flags[0][STATUS].item()) == 3
+    rig.reset()
+    theirs = _rand((1, N), 6)
+    rig.peer_pushes(theirs, 1)
+    y = rig.fused(x, pw)
+    torch.cuda.synchronize()
+    assert torch.equal(y, _fp32_sum(kernels.decode_i8(x, pw), theirs))
+    assert int(rig.flags[0][STATUS].item()) == 0
