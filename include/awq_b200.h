@@ -142,7 +142,13 @@ enum awq_b200_flags {
   AWQ_B200_GEMV_PER_SPLIT = 8,
   /* awq_b200_linear_fused only: where the call takes the GEMM route, use the kernel that stages the
    * dequantised weights in shared memory (as awq_b200_gemm_smem does).  For tests. */
-  AWQ_B200_GEMM_SMEM = 16
+  AWQ_B200_GEMM_SMEM = 16,
+  /* awq_b200_linear_ex / awq_b200_linear_fused: serve every call of fewer than 8 rows with ONE kernel (the GEMV)
+   * whatever the weight's size, as the reference does so that decode (1 row) and speculative verification
+   * (2..7 rows) add in the same order and cannot flip an argmax near a tie
+   * (LLMQRT/runtime_refact/nn_models/modules/linear/linear_awq.py:161-166).  Without the flag rows 1..4 share a
+   * kernel and rows 5..8 share a kernel, and large weights take faster kernels that differ between those classes. */
+  AWQ_B200_ONE_KERNEL_BELOW_8 = 32
 };
 
 /* awq_b200_gemv with call flags.  No reference counterpart (the reference launches on the
@@ -323,10 +329,10 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
 /* Picks the kernel from the row count and the shape.  M <= 16 -> awq_b200_gemv, except for large weights:
- * awq_b200_decode_i8 for M = 1 from 20 MiB of packed weights and for 2 <= M <= 4 from 36 MiB; awq_b200_skinny for
- * 5 <= M <= 8 from 48 MiB and for 9 <= M <= 16 from 16 MiB (beyond 8 rows the GEMV does its unpacking twice).  The
- * thresholds depend on K and N only, so within a row-count class (1, 2..4, 5..8, 9..16, 17..64) a row's bits do not
- * change with the number of rows decoded together.
+ * awq_b200_decode_i8 for M <= 4 from 24 MiB of packed weights; awq_b200_skinny for 5 <= M <= 8 from 48 MiB and for
+ * 9 <= M <= 16 from 16 MiB (beyond 8 rows the GEMV does its unpacking twice).  The thresholds depend on K and N
+ * only, so within a row-count class (1..4, 5..8, 9..16, 17..64) a row's bits do not change with the number of rows
+ * decoded together; AWQ_B200_ONE_KERNEL_BELOW_8 (awq_b200_linear_ex) makes 1..7 rows one class.
  * 17 <= M <= 64 -> awq_b200_gemv for small matrices (packed MiB x ceil(M / 8) <= 32), else awq_b200_skinny where the
  * GEMM would leave most SMs idle (N <= 18944 and K >= 4096);
  * awq_b200_gemm otherwise.  Group sizes 32 and 64 always take awq_b200_skinny (M <= 64) or awq_b200_gemm.

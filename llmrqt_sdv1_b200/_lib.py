@@ -93,6 +93,7 @@ NO_CLUSTER = 2
 GEMV_STREAM = 4
 GEMV_PER_SPLIT = 8
 GEMM_SMEM = 16
+ONE_KERNEL_BELOW_8 = 32
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_WORKSPACE, ERR_CUDA, ERR_ARCH, ERR_TOO_LARGE = range(1, 9)
 _VALUE_ERRORS = {ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_GROUP, ERR_TOO_LARGE}
 

@@ -9,9 +9,8 @@ constexpr int kSkinnyMaxRows = 64;
 
 // Which kernel serves M rows of a K x N linear (all thresholds are on (K, N) only, so within a row-count class
 // a row's bits do not change with the number of rows decoded together).
-//   one row:    the GEMV, or from 20 MiB of packed weights the integer tensor-core decode kernel
-//               (awq_decode_i8.cu; 70B-class gate_up: 45 us against 72 us).
-//   2..4:       the same with the switch at 36 MiB.
+//   rows <= 4:  the GEMV, or from 24 MiB of packed weights the integer tensor-core decode kernel
+//               (awq_decode_i8.cu; 70B-class gate_up at one row: 45 us against 72 us).
 //   5..8:       the GEMV, or from 48 MiB the exact-weight split-K tensor-memory kernel.
 //   9..16:      the same with the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice).
 //   17..64:     small matrices (packed MiB x ceil(rows / 8) <= 32): the GEMV, 8 rows per CTA; else the exact-weight
@@ -21,17 +20,16 @@ constexpr int kSkinnyMaxRows = 64;
 // kernel changes the order of additions.
 enum class Route { kGemv, kDecodeI8, kSkinny, kGemm };
 constexpr int kDecodeI8MaxRows = 4;
-Route route(int M, int K, int N, int group_size) {
+Route route(int M, int K, int N, int group_size, bool one_kernel_below_8 = false) {
   // Groups of 32 or 64: only the kernels that build the exact fp16 weight per element take them.
   if (group_size < 128) return M <= kSkinnyMaxRows ? Route::kSkinny : Route::kGemm;
   const long long packed_bytes = static_cast<long long>(K) * N / 2;
+  if (one_kernel_below_8 && M < 8) return Route::kGemv;
   if (M <= 16) {
     // Measured crossovers against the GEMV (us, graph replay, weights from HBM): the integer kernel wins from
-    // ~16-20 MiB at one row (28 MiB: 10.8-11.2 against 12.5-12.9) and from ~36 MiB at four rows.
-    if (M <= kDecodeI8MaxRows) {
-      const long long from_bytes = M == 1 ? (20ll << 20) : (36ll << 20);
-      return packed_bytes < from_bytes ? Route::kGemv : Route::kDecodeI8;
-    }
+    // ~16-20 MiB at one row (28 MiB: 10.8-11.2 against 12.5-12.9) and from ~36 MiB at four rows.  One threshold
+    // for the class: decode (1 row) and a short verification (2..4 rows) must take the same kernel.
+    if (M <= kDecodeI8MaxRows) return packed_bytes < (24ll << 20) ? Route::kGemv : Route::kDecodeI8;
     const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
     if (packed_bytes < from_bytes) return Route::kGemv;
     return Route::kSkinny;
@@ -63,6 +61,10 @@ size_t awq_b200_linear_workspace_bytes(int M, int K, int N) {
     const size_t small = awq_b200_skinny_workspace_bytes(M, K, N);
     if (small > need) need = small;
   }
+  if (M < 8) {                      // AWQ_B200_ONE_KERNEL_BELOW_8 sends these rows to the GEMV whatever the size
+    const size_t gemv = awq_b200_gemv_workspace_bytes(M, K, N);
+    if (gemv > need) need = gemv;
+  }
   return kGemmStatusBytes + need;
 }
 
@@ -77,7 +79,7 @@ static int linear_run(const void* x, const void* packed, const void* scales, con
   unsigned char* rest = static_cast<unsigned char*>(workspace) + kGemmStatusBytes;
   const size_t rest_bytes = workspace_bytes - kGemmStatusBytes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (route(M, K, N, group_size)) {
+  switch (route(M, K, N, group_size, (flags & AWQ_B200_ONE_KERNEL_BELOW_8) != 0)) {
     case Route::kGemv:
       return awq::gemv_run(x, packed, scales, qzeros, epi, y, M, K, N, group_size, rest, rest_bytes, s, flags);
     case Route::kDecodeI8:

@@ -225,9 +225,11 @@ def gemm_wtm(x, pw: PackedWeight, bias=None, out=None, m_tile: int = 0) -> torch
                 lib.awq_b200_gemm_workspace_bytes(x.shape[0], pw.K, pw.N), out, (m_tile,))
 
 
-def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_shape=None) -> torch.Tensor:
+def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_shape=None,
+           one_kernel_below_8: bool = False) -> torch.Tensor:
     """The library's dispatcher (decode GEMV, split-K tensor-memory kernel or GEMM by rows and shape).
-    `overlap` as in `gemv`.  `x` is fp16 [..., K]; its leading dimensions are the rows.  The result is
+    `overlap` as in `gemv`.  `one_kernel_below_8` serves every call of fewer than 8 rows with the GEMV, so that
+    decode and speculative verification add in the same order (the reference's rule, linear_awq.py:161-166).  `x` is fp16 [..., K]; its leading dimensions are the rows.  The result is
     `out`, or a new tensor of `out_shape` (default [M, N]).  This is the per-token call of the module, so
     the wrapper keeps its own work to a minimum: cached pointers and workspace sizes, one ctypes call."""
     wp, sp, zp, dev = pw._ptrs
@@ -261,7 +263,8 @@ def linear(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False, out_
         y = torch.empty(out_shape if out_shape is not None else (M, pw.N), dtype=torch.float16, device=dev)
     st = lib.awq_b200_linear_ex(x.data_ptr(), wp, sp, zp, bias.data_ptr() if bias is not None else None,
                                 y.data_ptr(), M, pw.K, pw.N, pw.group_size, ws.data_ptr(), ws.numel(), stream,
-                                _lib.OVERLAP_PREVIOUS if overlap else 0)
+                                (_lib.OVERLAP_PREVIOUS if overlap else 0) |
+                                (_lib.ONE_KERNEL_BELOW_8 if one_kernel_below_8 else 0))
     if st != 0:
         check(st, "awq_b200_linear")
     return y

@@ -81,6 +81,10 @@ class AWQLinear_GEMM(nn.Module):
         self.group_size = group_size if group_size != -1 else in_features
         self.training = training
         self.impl_mode = "auto"     # or "dequant_matmul"
+        # True: every call of fewer than 8 rows takes one kernel whatever the weight's size, so decode (1 row) and
+        # speculative verification (2..7 rows) add in the same order (the reference's rule, linear_awq.py:161-166).
+        # False (default): rows 1..4 share a kernel, rows 5..8 share a kernel, large weights take the faster ones.
+        self.one_kernel_below_8 = False
         assert self.in_features % self.group_size == 0
         assert out_features % (32 // self.w_bit) == 0
         pack = 32 // self.w_bit
@@ -204,7 +208,8 @@ class AWQLinear_GEMM(nn.Module):
             shape = x.shape[:-1] + (self.out_features,)
             shape = (1,) + tuple(shape) if len(shape) == 2 else shape
             if residual is None:
-                return kernels.linear(x, pw, bias=self.bias, overlap=overlap, out_shape=shape)
+                return kernels.linear(x, pw, bias=self.bias, overlap=overlap, out_shape=shape,
+                                      one_kernel_below_8=self.one_kernel_below_8)
             return kernels.linear_fused(x, pw, bias=self.bias, residual=residual, overlap=overlap, out_shape=shape)
         out_shape = x.shape[:-1] + (self.out_features,)
         if x.shape[0] == 0:

@@ -135,10 +135,18 @@ def test_decode_i8_fused_epilogues_and_routing(K_):
     x2 = torch.randn((8, K2), device="cuda", dtype=torch.float16)
     assert torch.equal(K_.linear(x2, pw2), K_.gemv(x2, pw2))
     assert torch.equal(K_.linear(x2[:2].contiguous(), pw2), K_.gemv(x2[:2].contiguous(), pw2))
-    K3, N3 = 6144, 8192                                        # 24 MiB: this kernel at one row, the GEMV at 2..4
+    K3, N3 = 6144, 8192                                        # 24 MiB: this kernel at 1..4 rows
     qw, qz, sc = _random_packed_inputs(K3, N3, 128, seed=43)
     pw3 = K_.make_packed(qw, qz, sc, 128)
-    x4 = torch.randn((4, K3), device="cuda", dtype=torch.float16)
-    assert torch.equal(K_.linear(x4[:1].contiguous(), pw3), K_.decode_i8(x4[:1].contiguous(), pw3))
-    assert torch.equal(K_.linear(x4, pw3), K_.gemv(x4, pw3))
+    x7 = torch.randn((7, K3), device="cuda", dtype=torch.float16)
+    x4 = x7[:4].contiguous()
+    y4 = K_.linear(x4, pw3)
+    assert torch.equal(y4, K_.decode_i8(x4, pw3))
+    assert torch.equal(K_.linear(x4[:1].contiguous(), pw3), y4[:1])       # decode and a short verification agree
+    # one kernel for every call of fewer than 8 rows, as the reference dispatches: rows agree between 1, 2 and 7 rows
+    y7 = K_.linear(x7, pw3, one_kernel_below_8=True)
+    assert torch.equal(y7, K_.gemv(x7, pw3))
+    for M in (1, 2, 5):
+        assert torch.equal(K_.linear(x7[:M].contiguous(), pw3, one_kernel_below_8=True), y7[:M])
+    assert torch.equal(K_.linear(x3, pw_gu, bias=bias, one_kernel_below_8=True), K_.gemv(x3, pw_gu, bias=bias))
     assert K_.gemv_status() == 0
