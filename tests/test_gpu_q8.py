@@ -222,6 +222,32 @@ def test_fp8_linearity_at_full_size(q8):
     assert q8.status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 57344, 8192), (16, 8192, 28672), (4096, 8192, 8192), (2048, 8192, 28672)])
+def test_full_size_against_library_gemms_on_the_gpu(q8, M, N, K):
+    """70B-class layers at full size, where the CPU oracle would take minutes: INT8 against the exact int32 product
+    of the library (bit for bit: the scale is a power of two), FP8 against the library's FP8 GEMM within one output
+    step plus the two kernels' accumulation bound."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    xi = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8, device="cuda")
+    wi = torch.randint(-128, 128, (N, K), generator=g, dtype=torch.int8, device="cuda")
+    zero = torch.zeros(N, dtype=torch.float16, device="cuda")
+    y = q8.gemm_tensorwise(xi, wi.t(), zero, 2.0 ** -18, 1.0, torch.float16, int8=True)
+    rows = xi if M > 16 else torch.cat([xi, torch.zeros((32 - M, K), dtype=torch.int8, device="cuda")])
+    acc = torch._int_mm(rows, wi.t())[:M]                       # int32, exact
+    assert torch.equal(y, (acc.float() * 2.0 ** -18).half())
+    xf = (torch.randn((M, K), generator=g, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+    wf = (torch.randn((N, K), generator=g, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+    yf = q8.gemm_tensorwise(xf, wf.t(), None, 1.0, 0.0, torch.bfloat16)
+    one = torch.tensor(1.0, device="cuda")
+    rowsf = xf if M >= 16 else torch.cat([xf, torch.zeros((16 - M, K), device="cuda").to(torch.float8_e4m3fn)])
+    ref = torch._scaled_mm(rowsf, wf.t(), scale_a=one, scale_b=one, out_dtype=torch.float32)[:M]
+    err = (yf.float() - ref).abs()
+    # one bf16 step of the reference value + both kernels' fp32 accumulation noise (K products of magnitude <= ~1)
+    bound = ref.abs().clamp_min(2.0 ** -126).log2().floor().exp2() * 2.0 ** -7 + 4e-6 * K ** 0.5 * 8
+    assert bool((err <= bound).all()), float((err - bound).max())
+    assert q8.status() == 0
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # quantisers
 # ---------------------------------------------------------------------------------------------------------------
