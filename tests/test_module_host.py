@@ -102,3 +102,37 @@ def test_out_tensor_is_validated_before_the_call():
         kernels.linear(x, pw, out_shape=(1, 2, N + 8))
     with pytest.raises(RuntimeError):
         kernels.linear(x, pw, out=torch.zeros((2, N), dtype=torch.float16))
+
+
+def test_fp8_and_smoothquant_module_surface():
+    """Names, shapes and dtypes of the parameters / buffers a reference checkpoint fills
+    (LLMQRT/runtime_refact/nn_models/modules/linear/linear_fp8.py:134-454, linear_sq.py:44-147), the quant_method map
+    of the reference's linear package, and no CPU fallback."""
+    import llmrqt_sdv1_b200 as pkg
+    assert sorted(pkg.method_to_linear) == ["awq", "fp8_dynamic_quant", "fp8_native_dynamic_quant",
+                                            "fp8_native_static_quant", "fp8_static_quant", "sq"]
+    assert pkg.get_concrete_linear_module("awq") is AWQLinear_GEMM
+    d = pkg.FP8DynamicLinear(64, 32, True, dev="cpu", dtype=torch.bfloat16, per_tensor=True)
+    assert d.weight.shape == (32, 64) and d.weight.dtype == torch.bfloat16 and d.weight_scale.shape == (1,)
+    assert d.bias.shape == (32,) and d.bias.dtype == torch.bfloat16
+    assert set(d.state_dict()) == {"weight", "weight_scale", "bias"}
+    t = pkg.FP8DynamicLinear(64, 32, False, dev="cpu", per_tensor=False)
+    assert t.weight_scale.shape == (32, 1) and t.bias is None
+    s = pkg.FP8StaticLinear(64, 32, False, dev="cpu")
+    assert set(s.state_dict()) == {"weight", "weight_scale", "input_scale", "output_scale"}
+    n = pkg.FP8NativeStaticLinear(64, 32, False, dev="cpu")
+    assert n.weight.dtype == torch.float8_e4m3fn
+    lin = torch.nn.Linear(64, 32, bias=True)
+    f = pkg.FP8NativeDynamicLinear.from_linear(lin, init_only=True, dtype=torch.float16, per_tensor=False)
+    assert f.weight.dtype == torch.float8_e4m3fn and f.weight_scale.shape == (32, 1) and f.dtype == torch.float16
+    with pytest.raises(AssertionError):
+        pkg.FP8DynamicLinear.from_linear(lin, group_size=128)
+    with pytest.raises(AssertionError):
+        pkg.FP8DynamicLinear(64, 32, False, dev="cpu", impl_mode="other")
+    q = pkg.SqW8A8BBF16OBF16PerTensor(8, 0, 64, 32, True, dev="cpu", dtype=torch.float16, weight_scale=0.02)
+    assert q.qweight.shape == (32, 64) and q.qweight.dtype == torch.int8
+    assert set(q.state_dict()) == {"qweight", "bias", "weight_scale", "input_scale"}
+    assert abs(float(q.weight_scale) - 0.02) < 1e-8
+    for mod in (d, q):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            mod(torch.zeros(2, 64, dtype=mod.dtype))
