@@ -403,6 +403,20 @@ AWQ_B200_API int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weig
 AWQ_B200_API int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
                          void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
 
+/* y[M, D] fp16 = RMSNorm(x[M, D]) * weight[D]: fp32 arithmetic, one rounding (torch.nn.functional.rms_norm's); D even.
+ * The norms between the linears of a decoder layer (LLMQRT/runtime_refact/nn_models/modules/nonlinear/
+ * transformer_layer.py:139-151) as one launch that may overlap its predecessor's tail. */
+AWQ_B200_API int awq_b200_rmsnorm(const void* x, const void* weight, float eps, void* y, int M, int D,
+                     awq_b200_stream_t stream);
+
+/* awq_b200_qk_norm_rope_cache followed by awq_b200_attn_decode as ONE launch (one CTA per query head): qkv
+ * [(H + 2 KV) * D] fp16 is the fused qkv linear's output row; every CTA normalises / rotates its query head and its
+ * group's key head itself, attends over cache rows 0 .. *pos - 1 plus the fresh key / value, and the first CTA of a
+ * group appends the fresh key / value to row *pos of the caches.  out [H * D] fp16; same bits as the two calls. */
+AWQ_B200_API int awq_b200_attn_step(const void* qkv, const void* q_weight, const void* k_weight, float eps,
+                       const void* cos_tab, const void* sin_tab, const int64_t* pos, void* k_cache, void* v_cache,
+                       void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * The reference extension's other quantized linears: FP8 (e4m3) and SmoothQuant INT8, 8-bit x 8-bit GEMMs with a
  * scaling epilogue.  Operands arrive quantised, as they do in the reference: activations xq [M, K] row-major with

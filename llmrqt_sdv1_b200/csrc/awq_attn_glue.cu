@@ -177,6 +177,223 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
   }
 }
 
+// The two kernels above as ONE launch per layer: CTA h first turns its own query head and the key / value head of its
+// group into their final fp16 values (warps 0, 1, 2: per-head RMSNorm, rotary embedding - the arithmetic of
+// qk_norm_rope_cache_kernel), keeps them in shared memory, and then attends over the cached positions 0..pos-1 plus
+// the fresh key / value.  The first CTA of a group also writes the fresh key / value into row `pos` of the cache for
+// the tokens to come; no CTA reads that row in this launch, so CTAs never wait for one another.  Same bits as the
+// two-kernel sequence (the positions are visited in the same batches).
+template <int V>
+__device__ __forceinline__ void norm_rope_head(const __half* __restrict__ src, const __half* __restrict__ w, float eps,
+                                               const __half* __restrict__ cs, const __half* __restrict__ sn, bool rope,
+                                               int lane, __half (&out)[V]) {
+  constexpr int D = 32 * V;
+  __half x[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) x[i] = src[lane * V + i];
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float f = __half2float(x[i]); ss = fmaf(f, f, ss); }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float r = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int i = 0; i < V; ++i) x[i] = __hmul_rn(w[lane * V + i], __float2half_rn(__half2float(x[i]) * r));
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    if (rope) {
+      const unsigned partner = __shfl_xor_sync(0xffffffffu, static_cast<unsigned>(__half_as_ushort(x[i])), 16);
+      __half rot = __ushort_as_half(static_cast<unsigned short>(partner));
+      if (lane < 16) rot = __hneg(rot);
+      out[i] = __hadd_rn(__hmul_rn(x[i], cs[lane * V + i]), __hmul_rn(rot, sn[lane * V + i]));
+    } else {
+      out[i] = x[i];
+    }
+  }
+}
+
+template <int V>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_weight, const __half* __restrict__ k_weight,
+                 float eps, const __half* __restrict__ cos_tab, const __half* __restrict__ sin_tab,
+                 const long long* __restrict__ pos_ptr, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                 __half* __restrict__ out, int H, int KV, int max_len, float scale) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  static_assert(V == 2 || V == 4, "head dimension 64 or 128");
+  constexpr int D = 32 * V;
+  constexpr int W = kAttnWarps, B = kAttnBatch;
+  __shared__ float s_m[W], s_l[W], s_acc[W][D];
+  __shared__ __half s_q[D], s_k[D], s_v[D];
+  const int head = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = H / KV;
+  const int kv = head / group;
+  const long long pos = *pos_ptr;
+  if (pos < 0 || pos >= max_len) return;              // out of range: leave everything untouched (CTA-uniform)
+  if (warp < 3) {
+    const __half* cs = cos_tab + static_cast<size_t>(pos) * D;
+    const __half* sn = sin_tab + static_cast<size_t>(pos) * D;
+    __half o[V];
+    if (warp == 0) {
+      norm_rope_head<V>(qkv + static_cast<size_t>(head) * D, q_weight, eps, cs, sn, true, lane, o);
+#pragma unroll
+      for (int i = 0; i < V; ++i) s_q[lane * V + i] = o[i];
+    } else {
+      const bool is_k = warp == 1;
+      norm_rope_head<V>(qkv + static_cast<size_t>(is_k ? H + kv : H + KV + kv) * D, is_k ? k_weight : nullptr, eps, cs, sn,
+                        is_k, lane, o);
+      __half* keep = is_k ? s_k : s_v;
+#pragma unroll
+      for (int i = 0; i < V; ++i) keep[lane * V + i] = o[i];
+      if (head == kv * group) {                          // one CTA per group appends to the cache
+        __half* dst = (is_k ? k_cache : v_cache) + (static_cast<size_t>(kv) * max_len + pos) * D + lane * V;
+#pragma unroll
+        for (int i = 0; i < V; ++i) dst[i] = o[i];
+      }
+    }
+  }
+  __syncthreads();
+  float qf[V], knew[V], vnew[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    qf[i] = __half2float(s_q[lane * V + i]) * scale;
+    knew[i] = __half2float(s_k[lane * V + i]);
+    vnew[i] = __half2float(s_v[lane * V + i]);
+  }
+  const __half* kb = k_cache + static_cast<size_t>(kv) * max_len * D + lane * V;
+  const __half* vb = v_cache + static_cast<size_t>(kv) * max_len * D + lane * V;
+  float m = -INFINITY, l = 0.f, acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  for (long long j0 = static_cast<long long>(warp) * B; j0 <= pos; j0 += W * B) {
+    float kf[B][V], vf[B][V];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const long long j = j0 + b;
+      if (j < pos) {                                              // warp-uniform
+        load_row<V>(kb + j * D, kf[b]);
+        load_row<V>(vb + j * D, vf[b]);
+      } else {                                                    // the fresh row (and the masked slots behind it)
+#pragma unroll
+        for (int i = 0; i < V; ++i) { kf[b][i] = knew[i]; vf[b][i] = vnew[i]; }
+      }
+    }
+    float s[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      s[b] = 0.f;
+#pragma unroll
+      for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
+    }
+    float m_new = m;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (j0 + b > pos) s[b] = -INFINITY;
+      m_new = fmaxf(m_new, s[b]);
+    }
+    const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
+      l += pj;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
+    }
+    m = m_new;
+  }
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < V; ++i) s_acc[warp][lane * V + i] = acc[i];
+  __syncthreads();
+  if (warp == 0) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < W; ++w) M = fmaxf(M, s_m[w]);
+    float L = 0.f, o[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) o[i] = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const float c = (s_m[w] == -INFINITY) ? 0.f : __expf(s_m[w] - M);
+      L = fmaf(s_l[w], c, L);
+#pragma unroll
+      for (int i = 0; i < V; ++i) o[i] = fmaf(s_acc[w][lane * V + i], c, o[i]);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[static_cast<size_t>(head) * D + lane * V + i] = __float2half_rn(o[i] * inv);
+  }
+}
+
+// RMSNorm of M rows of width D (fp16 in, fp16 weight, fp16 out): y = fp16( (x * rsqrt(mean(x^2) + eps)) * w ), all
+// in fp32 with ONE rounding at the end, as torch.nn.functional.rms_norm computes it (the reference's decoder layers
+// call their norm modules between the linears: LLMQRT/runtime_refact/nn_models/modules/nonlinear/
+// transformer_layer.py:139-151).  One CTA per row; a launch that can overlap its predecessor's tail.
+constexpr int kNormThreads = 256;
+constexpr int kNormKeep = 8;          // pairs a thread keeps in registers between the two passes (rows up to 4096 wide)
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, float eps, __half* __restrict__ y, int D) {
+  // the weight is constant data: fetch it while the predecessor still runs
+  const int pairs = D >> 1;
+  float2 g[kNormKeep];
+#pragma unroll
+  for (int j = 0; j < kNormKeep; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    g[j] = make_float2(0.f, 0.f);
+    if (i < pairs) g[j] = __half22float2(*reinterpret_cast<const __half2*>(w + 2 * i));
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float red[kNormThreads / 32];
+  const __half* xr = x + static_cast<size_t>(blockIdx.x) * D;
+  __half* yr = y + static_cast<size_t>(blockIdx.x) * D;
+  float2 f[kNormKeep];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kNormKeep; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    f[j] = make_float2(0.f, 0.f);
+    if (i < pairs) f[j] = __half22float2(*reinterpret_cast<const __half2*>(xr + 2 * i));
+  }
+#pragma unroll
+  for (int j = 0; j < kNormKeep; ++j) {            // fixed order of additions, whatever the row's width
+    ss = fmaf(f[j].x, f[j].x, ss);
+    ss = fmaf(f[j].y, f[j].y, ss);
+  }
+  for (int i = threadIdx.x + kNormKeep * kNormThreads; i < pairs; i += kNormThreads) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + 2 * i));
+    ss = fmaf(v.x, v.x, ss);
+    ss = fmaf(v.y, v.y, ss);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
+  const float r = rsqrtf(tot / D + eps);
+#pragma unroll
+  for (int j = 0; j < kNormKeep; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < pairs) *reinterpret_cast<__half2*>(yr + 2 * i) = __floats2half2_rn((f[j].x * r) * g[j].x, (f[j].y * r) * g[j].y);
+  }
+  for (int i = threadIdx.x + kNormKeep * kNormThreads; i < pairs; i += kNormThreads) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + 2 * i));
+    const float2 gw = __half22float2(*reinterpret_cast<const __half2*>(w + 2 * i));
+    *reinterpret_cast<__half2*>(yr + 2 * i) = __floats2half2_rn((v.x * r) * gw.x, (v.y * r) * gw.y);
+  }
+}
+
 template <typename... Args>
 static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -228,6 +445,33 @@ int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache
   __half* o = static_cast<__half*>(out);
   if (D == 128) return launch_pdl(attn_decode_kernel<4>, dim3(H), dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale);
   return launch_pdl(attn_decode_kernel<2>, dim3(H), dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale);
+}
+
+int awq_b200_attn_step(const void* qkv, const void* q_weight, const void* k_weight, float eps, const void* cos_tab,
+                       const void* sin_tab, const int64_t* pos, void* k_cache, void* v_cache, void* out, int H, int KV,
+                       int D, int max_len, float scale, awq_b200_stream_t stream) {
+  using namespace awq;
+  if (!qkv || !cos_tab || !sin_tab || !pos || !k_cache || !v_cache || !out) return AWQ_B200_ERR_NULL;
+  if ((q_weight == nullptr) != (k_weight == nullptr)) return AWQ_B200_ERR_NULL;
+  if (H < 1 || KV < 1 || H % KV != 0 || max_len < 1 || (D != 64 && D != 128)) return AWQ_B200_ERR_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* a = static_cast<const __half*>(qkv);
+  const __half *qw = static_cast<const __half*>(q_weight), *kw = static_cast<const __half*>(k_weight);
+  const __half *ct = static_cast<const __half*>(cos_tab), *st = static_cast<const __half*>(sin_tab);
+  const long long* pp = reinterpret_cast<const long long*>(pos);
+  __half *kc = static_cast<__half*>(k_cache), *vc = static_cast<__half*>(v_cache), *o = static_cast<__half*>(out);
+  if (D == 128) return launch_pdl(attn_step_kernel<4>, dim3(H), dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale);
+  return launch_pdl(attn_step_kernel<2>, dim3(H), dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale);
+}
+
+int awq_b200_rmsnorm(const void* x, const void* weight, float eps, void* y, int M, int D, awq_b200_stream_t stream) {
+  using namespace awq;
+  if (!x || !weight || !y) return AWQ_B200_ERR_NULL;
+  if (M < 1 || D < 2 || (D & 1)) return AWQ_B200_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 3u)
+    return AWQ_B200_ERR_ALIGN;
+  return launch_pdl(rmsnorm_kernel, dim3(M), dim3(kNormThreads), static_cast<cudaStream_t>(stream),
+                    static_cast<const __half*>(x), static_cast<const __half*>(weight), eps, static_cast<__half*>(y), D);
 }
 
 }  // extern "C"

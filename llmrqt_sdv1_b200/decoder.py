@@ -30,6 +30,9 @@ def _rms(x: torch.Tensor, norm: nn.Module) -> torch.Tensor:
     eps = getattr(norm, "variance_epsilon", None)
     if eps is None:
         eps = getattr(norm, "eps", 1e-6)
+    if x.is_cuda and x.dtype == torch.float16 and norm.weight.dtype == torch.float16 and x.is_contiguous():
+        from . import kernels
+        return kernels.rmsnorm(x, norm.weight, eps)       # one launch (F.rms_norm's arithmetic and rounding)
     return F.rms_norm(x, (x.shape[-1],), norm.weight, eps)
 
 
@@ -156,18 +159,19 @@ class GraphedDecoder:
         """One decode step on the device-side state: consumes `token` at `pos`, appends the arg-max token."""
         pos = self.pos
         h = self.core.embed_tokens(self.token)                                  # [1, 1, hidden]
-        cos, sin_signed = self.cos_tab.index_select(0, pos), self.sin_signed_tab.index_select(0, pos)
-        mask = (self.positions <= pos).view(1, 1, 1, self.max_len)              # attend to cache slots 0..pos
+        if not self._glue:
+            cos, sin_signed = self.cos_tab.index_select(0, pos), self.sin_signed_tab.index_select(0, pos)
+            mask = (self.positions <= pos).view(1, 1, 1, self.max_len)          # attend to cache slots 0..pos
         for li, layer in enumerate(self.layers):
             x = _rms(h, layer.input_layernorm)
             qkv = self._qkv(layer.self_attn, x)
             if self._glue:
                 from . import kernels
                 qw, kw, eps = self._qk_norm[li]
-                kernels.qk_norm_rope_cache(qkv, qw, kw, eps, self.cos_tab, self.sin_tab, pos, self._q_buf,
-                                           self.k_cache[li], self.v_cache[li])
-                kernels.attn_decode(self._q_buf, self.k_cache[li], self.v_cache[li], pos, self._attn_buf,
-                                    layer.self_attn.scaling if hasattr(layer.self_attn, "scaling") else self.head_dim ** -0.5)
+                # q/k norm + rope + cache append + attention of the one new token: one launch
+                kernels.attn_step(qkv, qw, kw, eps, self.cos_tab, self.sin_tab, pos, self.k_cache[li], self.v_cache[li],
+                                  self._attn_buf,
+                                  layer.self_attn.scaling if hasattr(layer.self_attn, "scaling") else self.head_dim ** -0.5)
                 h = self._layer_tail(layer, h, self._attn_buf)
                 continue
             q, k, v = self._qk_norm_rope(li, qkv, cos, sin_signed)

@@ -428,6 +428,42 @@ def attn_decode(q, k_cache, v_cache, pos, out, scale: float) -> None:
           "awq_b200_attn_decode")
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm over the last dimension of fp16 `x` times `weight` (fp32 arithmetic, one rounding), one launch."""
+    D = x.shape[-1]
+    if x.dtype != torch.float16 or weight.dtype != torch.float16 or not x.is_contiguous() or weight.numel() != D:
+        raise ValueError("rmsnorm needs contiguous fp16 x [..., D] and an fp16 weight [D]")
+    dev = _prep(x, weight)
+    y = out if out is not None else torch.empty_like(x)
+    if y.dtype != torch.float16 or not y.is_contiguous() or y.numel() != x.numel():
+        raise ValueError("rmsnorm: out must be a contiguous fp16 tensor of x's size")
+    if x.numel() == 0:
+        return y
+    check(lib.awq_b200_rmsnorm(x.data_ptr(), weight.data_ptr(), float(eps), y.data_ptr(), x.numel() // D, D,
+                               torch.cuda.current_stream(dev).cuda_stream), "awq_b200_rmsnorm")
+    return y
+
+
+def attn_step(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, k_cache, v_cache, out, scale: float) -> None:
+    """`qk_norm_rope_cache` + `attn_decode` in one launch: the fused qkv row in, the attention output [H * D] out,
+    row `pos` of the caches appended.  Same bits as the two calls."""
+    KV, max_len, D = k_cache.shape[-3], k_cache.shape[-2], k_cache.shape[-1]
+    H = out.numel() // D
+    for t in (qkv, cos_tab, sin_tab, out, k_cache, v_cache):
+        if t.dtype != torch.float16 or not t.is_contiguous():
+            raise ValueError("attn_step needs contiguous fp16 tensors")
+    if qkv.numel() != (H + 2 * KV) * D or v_cache.shape != k_cache.shape or pos.dtype != torch.int64:
+        raise ValueError("attn_step: inconsistent shapes")
+    if tuple(cos_tab.shape) != (max_len, D) or tuple(sin_tab.shape) != (max_len, D):
+        raise ValueError(f"rotary tables must be [{max_len}, {D}]")
+    dev = _prep(qkv, cos_tab, sin_tab, pos, out, k_cache, v_cache)
+    check(lib.awq_b200_attn_step(
+        qkv.data_ptr(), q_weight.data_ptr() if q_weight is not None else None,
+        k_weight.data_ptr() if k_weight is not None else None, float(eps), cos_tab.data_ptr(), sin_tab.data_ptr(),
+        pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), H, KV, D, max_len, float(scale),
+        torch.cuda.current_stream(dev).cuda_stream), "awq_b200_attn_step")
+
+
 def gemv_status(dev: torch.device | None = None) -> int:
     """Status word of the decode kernels (GEMV and split-K tensor-memory kernel) in this stream's workspaces (0 = no device-side wait expired).
     Synchronises."""

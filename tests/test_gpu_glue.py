@@ -80,3 +80,51 @@ def test_attn_decode(H, KV, D):
         torch.cuda.synchronize()
         err = (out.view(H, D).float() - ref.view(H, D)).abs().max() / ref.abs().max()
         assert err <= 2e-3, (p, float(err))
+
+
+@pytest.mark.parametrize("H,KV,D,with_norm", [(16, 8, 128, True), (32, 8, 128, False), (8, 2, 64, True), (4, 4, 128, True)])
+def test_attn_step_equals_the_two_kernel_sequence(H, KV, D, with_norm):
+    """`awq_b200_attn_step` (one launch per layer) against `qk_norm_rope_cache` followed by `attn_decode`: the same
+    output bits and the same cache contents, token after token, including position 0 and the last cache row; a
+    position outside the cache changes nothing."""
+    from llmrqt_sdv1_b200 import kernels
+    max_len, eps, scale = 160, 1e-6, D ** -0.5
+    qw, kw = (_rand((D,), 2, 0.3) + 1.0, _rand((D,), 3, 0.3) + 1.0) if with_norm else (None, None)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos = torch.cat((ang.cos(), ang.cos()), -1).half().contiguous()
+    sin = torch.cat((ang.sin(), ang.sin()), -1).half().contiguous()
+    caches = [[_rand((KV, max_len, D), 5, 0.5), _rand((KV, max_len, D), 6, 0.5)] for _ in range(2)]   # same prefill in both
+    q_buf = torch.empty((H, D), dtype=torch.float16, device="cuda")
+    out_a = torch.empty((H * D,), dtype=torch.float16, device="cuda")
+    out_b = torch.empty_like(out_a)
+    for step, p in enumerate([0, 1, 2, 3, 4, 63, 64, 65, 128, max_len - 1]):
+        pos = torch.tensor([p], dtype=torch.long, device="cuda")
+        qkv = _rand((1, 1, (H + 2 * KV) * D), 10 + step)
+        kernels.qk_norm_rope_cache(qkv, qw, kw, eps, cos, sin, pos, q_buf, caches[0][0], caches[0][1])
+        kernels.attn_decode(q_buf, caches[0][0], caches[0][1], pos, out_a, scale)
+        kernels.attn_step(qkv, qw, kw, eps, cos, sin, pos, caches[1][0], caches[1][1], out_b, scale)
+        assert torch.equal(out_a, out_b), f"position {p}"
+        assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1]), f"position {p}"
+    before = (caches[1][0].clone(), caches[1][1].clone(), out_b.clone())
+    kernels.attn_step(qkv, qw, kw, eps, cos, sin, torch.tensor([max_len], dtype=torch.long, device="cuda"),
+                      caches[1][0], caches[1][1], out_b, scale)
+    torch.cuda.synchronize()
+    assert torch.equal(caches[1][0], before[0]) and torch.equal(caches[1][1], before[1]) and torch.equal(out_b, before[2])
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 2048), (1, 128, 2048), (7, 4096), (3, 130)])
+def test_rmsnorm_against_torch(shape):
+    """`awq_b200_rmsnorm`: fp32 arithmetic, one rounding - within one fp16 step of torch.nn.functional.rms_norm (the
+    order in which the squares are added is not part of either contract), and of a float64 evaluation."""
+    from llmrqt_sdv1_b200 import kernels
+    x = _rand(shape, 1, 2.0)
+    w = _rand((shape[-1],), 2, 0.2) + 1.0
+    y = kernels.rmsnorm(x, w, 1e-6)
+    ref = F.rms_norm(x, (shape[-1],), w, 1e-6)
+    v = x.double()
+    exact = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * w.double())
+    step = exact.abs().clamp_min(2.0 ** -14).log2().floor().exp2() * 2.0 ** -10
+    assert bool(((y.double() - exact).abs() <= 0.51 * step + 1e-6 * exact.abs()).all())
+    assert bool(((y.double() - ref.double()).abs() <= step).all())
+    assert float((y != ref).float().mean()) < 0.01
