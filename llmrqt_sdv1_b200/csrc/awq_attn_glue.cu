@@ -23,6 +23,7 @@ qk_norm_rope_cache_kernel(const __half* __restrict__ qkv, const __half* __restri
                           const __half* __restrict__ sin_tab, const long long* __restrict__ pos_ptr,
                           __half* __restrict__ q_out, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                           int H, int KV, int max_len) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 32 * V;
   const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
                    const long long* __restrict__ pos_ptr, __half* __restrict__ out, int H, int KV, int max_len,
                    float scale) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   static_assert(V == 2 || V == 4, "head dimension 64 or 128");
   constexpr int D = 32 * V;
@@ -220,6 +222,7 @@ attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_we
                  float eps, const __half* __restrict__ cos_tab, const __half* __restrict__ sin_tab,
                  const long long* __restrict__ pos_ptr, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                  __half* __restrict__ out, int H, int KV, int max_len, float scale) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   static_assert(V == 2 || V == 4, "head dimension 64 or 128");
   constexpr int D = 32 * V;
@@ -352,6 +355,7 @@ rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, float
     g[j] = make_float2(0.f, 0.f);
     if (i < pairs) g[j] = __half22float2(*reinterpret_cast<const __half2*>(w + 2 * i));
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float red[kNormThreads / 32];
   const __half* xr = x + static_cast<size_t>(blockIdx.x) * D;
