@@ -241,14 +241,16 @@ AWQ_B200_API int awq_b200_skinny(const void* x, const void* packed, const void* 
                     const void* bias, void* y, int M, int K, int N, int group_size,
                     void* workspace, size_t workspace_bytes, awq_b200_stream_t stream, unsigned flags);
 
-/* Decode rows (1 <= M <= 4) of a large matrix on the INTEGER tensor-core path (tcgen05.mma kind::i8): the packed
- * words are only masked (word & 0xf0f0f0f0, word & 0x0f0f0f0f: one logic operation per word and nibble position)
- * and multiplied as unsigned bytes with the activations in block-fixed-point form (per row and 128-k block:
- * x ~ sx * t, t a 15-bit integer held as two signed-byte planes); all sums are exact int32 and the kernel applies
- * s * sx * (sum - z * sum t) in fp32 once per 128-k unit.  Weights are applied un-rounded, as in the reference's
+/* Decode rows (1 <= M <= 8) of a large matrix on the INTEGER tensor-core path (tcgen05.mma kind::i8): the packed
+ * bytes (16 q_hi + q_lo) are a tensor-core operand as they arrive, next to one masked copy (word & 0xf0f0f0f0: one
+ * logic operation per word), and are multiplied as unsigned bytes with the activations in block-fixed-point form
+ * (per row and 128-k block: x ~ sx * t, t a 15-bit integer held as two signed-byte planes); all sums are exact
+ * int32 and the kernel applies s * sx * (sum - z * sum t) in fp32 once per 128-k unit.  From 3 rows the planes of
+ * the call are written once by a small kernel launched in front (two launches per call; up to 2 rows every CTA
+ * builds the planes of its own units).  Weights are applied un-rounded, as in the reference's
  * GEMV (LLMQRT/runtime_refact/csrc/awq/gemv.cu:138); the activations carry a relative error below the fp16
  * spacing of the largest activation of their block.  Results are within the 2e-3 layer bound of the fp16-weight
- * path, not bit-equal to it.  Deterministic; a row's bits do not depend on M.  Same split-K stream of 256-column
+ * path, not bit-equal to it.  Deterministic; a row's bits do not depend on M within 1..4 and within 5..8 rows.  Same split-K stream of 256-column
  * x 128-k units, arguments and flags as awq_b200_skinny; the workspace must hold
  * awq_b200_decode_workspace_bytes(M, K, N) bytes, start zero-initialised and is left clean.  Replaces the same
  * reference calls as awq_b200_gemv. */
@@ -313,7 +315,7 @@ AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* 
  * recv / flags / slot_elems / rank / world (2..8) as for awq_b200_peer_allreduce_push, and the calls of the two entry
  * points may be mixed freely (they share the call counter), as long as every rank makes the same sequence of calls.
  * bias (this rank's, normally rank 0 only) is added to the partial before the exchange.  Waits on peers are bounded
- * (AWQ_B200_PEER_WAIT_LIMIT_WORD); on expiry the status word (AWQ_B200_PEER_STATUS_WORD) becomes 3.
+ * (AWQ_B200_PEER_WAIT_LIMIT_WORD); on expiry the status word (AWQ_B200_PEER_STATUS_WORD) becomes 3.  M <= 4.
  * Plays the part of the all-reduce that follows a row-parallel linear in the reference's tensor-parallel layers
  * (spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:195-199). */
 AWQ_B200_API int awq_b200_decode_i8_push(const void* x, const void* packed, const void* scales, const int32_t* qzeros,
@@ -329,7 +331,7 @@ AWQ_B200_API int awq_b200_gemv_max_rows(void);
 AWQ_B200_API size_t awq_b200_linear_workspace_bytes(int M, int K, int N);
 
 /* Picks the kernel from the row count and the shape.  M <= 16 -> awq_b200_gemv, except for large weights:
- * awq_b200_decode_i8 for M <= 4 from 24 MiB of packed weights; awq_b200_skinny for 5 <= M <= 8 from 48 MiB and for
+ * awq_b200_decode_i8 for M <= 4 from 24 MiB of packed weights and for 5 <= M <= 8 from 48 MiB; awq_b200_skinny for
  * 9 <= M <= 16 from 16 MiB (beyond 8 rows the GEMV does its unpacking twice).  The thresholds depend on K and N
  * only, so within a row-count class (1..4, 5..8, 9..16, 17..64) a row's bits do not change with the number of rows
  * decoded together; AWQ_B200_ONE_KERNEL_BELOW_8 (awq_b200_linear_ex) makes 1..7 rows one class.

@@ -1,4 +1,4 @@
-// Decode path for 1 <= M <= 4 rows of a large matrix on the integer tensor-core path (tcgen05.mma kind::i8):
+// Decode path for 1 <= M <= 8 rows of a large matrix on the integer tensor-core path (tcgen05.mma kind::i8):
 // the packed nibbles reach the tensor core with ONE logic operation per packed word, no conversion to floating
 // point at all, and half of them with no operation.
 //
@@ -36,6 +36,20 @@
 // [128, 256) two operand slots of 64 (2 halves x 32, of which the hi bytes take 16 columns = 64 k slots).  Per
 // unit the tensor core runs 8 instructions (2 halves x 2 k steps of 32 slots x {hi, raw}).  A group folds unit u
 // when it starts on unit u + 2.  Every mbarrier wait is bounded (see awq_ptx.cuh).
+//
+// 5..8 rows (MR = 8): the activation tiles have 16 rows (plane 1 of row m in tile row 2 m, plane 2 in 2 m + 1), the
+// hi MMA has N = 32 over [Xhi; Xlo] and the raw MMA N = 16 over Xlo; accumulator windows of 96 columns
+// (2 halves x {hi 32, raw 16}) at [0, 192), operand slots of 32 columns at [192, 256); stages of 19 KiB.
+//
+// Who builds the activation planes.  Up to 2 rows: the two helper warps of every CTA, for each of its units.  That
+// work is the same in every CTA that meets a k block (a 70B gate_up has 14,336 units and 64 k blocks), it grows
+// with the rows, and its latency (two shuffle reductions, a division, conversions: ~1 us per pair of rows and
+// unit) bounds the kernel from 3 rows on (measured on 8192 -> 57344 with the helpers' arithmetic taken out:
+// 4 rows 53 -> 48 us, 8 rows 89 -> 63 us).  From 3 rows (PREP kernels) d8_prep_kernel writes the planes and
+// (sx, T) of every k block once per call into the workspace, the copy producer fetches a unit's record with its
+// weights (two more bulk copies per unit) and the CTAs have no helper warps (320 threads): 4 rows 53.9 -> 50.7 us,
+// 8 rows 58.4 us (exact-weight kernel: 75 us).  At 1 and 2 rows the second launch costs more than it saves
+// (45.1 -> 45.7, 45.2 -> 47.0 us).  The bits are the same either way.
 #include "awq_gemv_common.cuh"
 #include "awq_peer.cuh"
 #include "awq_tcgen05.cuh"
@@ -51,32 +65,46 @@ constexpr int kD8HelperWarp0 = 2 + kD8UnpackWarps;
 constexpr int kD8CtasPerSm = 2;
 constexpr int kD8BN = 256;
 constexpr int kD8RawBytes = kD8BN * 64;            // [256 columns][64 bytes], 64-byte swizzle
-// B operand tiles: 16 rows x 64 k slots, 64-byte swizzle.  Only rows 0 .. 2 MR - 1 <= 7 carry data (two planes
-// of up to four rows); the tensor core also reads rows 8..15, whose products land in accumulator columns nobody
-// looks at, so those rows may be whatever lies behind the tile: a tile takes 512 bytes.
-constexpr int kD8XTileBytes = 8 * 64;
 constexpr int kD8RawOff = 0;
 constexpr int kD8XhiOff = kD8RawOff + kD8RawBytes;
-constexpr int kD8XloOff = kD8XhiOff + kD8XTileBytes;
-constexpr int kD8SzOff = kD8XloOff + kD8XTileBytes;    // 256 fp16 scales, then 32 qzeros words
-constexpr int kD8StageBytes = 18 * 1024;
 constexpr int kD8Stages = 5;                       // per CTA; two CTAs per SM
 constexpr int kD8Windows = 2;
-constexpr int kD8ABase = kD8Windows * 64;          // 128
 constexpr int kD8AStages = 2;
 constexpr int kD8TmemCols = 256;
 constexpr int kD8MetaSlots = 8;                    // ring of per-unit (sx, T) rows (see the helpers for why 8 is enough)
-constexpr int kD8MaxRows = 4;                      // beyond that the per-row fold costs more than the exact-weight kernel's unpack
+constexpr int kD8MaxRows = 8;                      // beyond that the per-row fold costs more than the exact-weight kernel's unpack
+constexpr int kD8PushMaxRows = 4;                  // the epilogue that exchanges with the peers exists for 1..4 rows
 constexpr int kD8Range = 16256;                    // 127 * 128: largest |t|
-static_assert(kD8SzOff + 512 + 128 <= kD8StageBytes && kD8StageBytes % 1024 == 0, "stage layout");
-static_assert(kD8XloOff + 1024 <= kD8StageBytes, "the rows the tensor core reads behind a tile stay inside the stage");
-static_assert(kD8ABase + kD8AStages * 64 == kD8TmemCols, "tensor memory columns");
 
 template <int MR> struct D8Cfg {
-  static_assert(MR == 1 || MR == 2 || MR == 4, "rows per call class");
+  static_assert(MR == 1 || MR == 2 || MR == 4 || MR == 8, "rows per call class");
+  // B operand tiles: kXRows rows x 64 k slots, 64-byte swizzle (8-row groups of 512 bytes).  Up to four rows: only
+  // tile rows 0 .. 2 MR - 1 <= 7 carry data (plane 1 of row m in row m, plane 2 in row MR + m) and a tile takes 512
+  // bytes; the instructions have N = 16 and also read the 8 rows behind the tile they start at, whose products
+  // land in accumulator columns nobody looks at.  Eight rows: 16-row tiles, plane 1 of row m in row 2 m, plane 2
+  // in row 2 m + 1; the hi MMA has N = 32.
+  static constexpr int kXRows = MR == 8 ? 16 : 8;
+  static constexpr int kXTileBytes = kXRows * 64;
+  static constexpr int kXloOff = kD8XhiOff + kXTileBytes;
+  static constexpr int kSzOff = kXloOff + kXTileBytes;       // 256 fp16 scales, then 32 qzeros words
+  static constexpr int kStageBytes = MR == 8 ? 19 * 1024 : 18 * 1024;
+  static constexpr int kHiN = MR == 8 ? 32 : 16;             // N of the MMA over [Xhi; Xlo]
+  static constexpr int kHalfCols = kHiN + 16;                // accumulator columns of a 128-column half: hi, then raw (N = 16)
+  static constexpr int kWinCols = 2 * kHalfCols;             // 64 / 96
+  static constexpr int kABase = kD8Windows * kWinCols;       // 128 / 192
+  static constexpr int kASlot = MR == 8 ? 32 : 64;           // operand slot; a half's 16 columns start at h * kASlot / 2
+  static_assert(kSzOff + 512 + 128 <= kStageBytes && kStageBytes % 1024 == 0, "stage layout");
+  static_assert(kXloOff + 1024 <= kStageBytes, "the rows the tensor core reads behind a tile stay inside the stage");
+  static_assert(kABase + kD8AStages * kASlot == kD8TmemCols, "tensor memory columns");
+  __host__ __device__ static constexpr int plane1_row(int m) { return MR == 8 ? 2 * m : m; }
+  __host__ __device__ static constexpr int plane2_row(int m) { return MR == 8 ? 2 * m + 1 : MR + m; }
+  // Record of one k block as d8_prep_kernel writes it: tile Xhi, tile Xlo, MR x (sx bits, T).
+  static constexpr int kPrepMetaBytes = MR * 8 < 16 ? 16 : MR * 8;
+  static constexpr int kPrepRecBytes = 2 * kXTileBytes + kPrepMetaBytes;
+  static constexpr int kMetaStride = kPrepMetaBytes / 8;     // int2 entries per ring slot
   static constexpr int kCombBytes = (kD8Groups - 1) * kD8BN * MR * 4;
-  static constexpr int kMetaBytes = kD8MetaSlots * MR * 8;
-  static constexpr int kCombOff = kD8Stages * kD8StageBytes;
+  static constexpr int kMetaBytes = kD8MetaSlots * kPrepMetaBytes;
+  static constexpr int kCombOff = kD8Stages * kStageBytes;
   static constexpr int kMetaOff = kCombOff + kCombBytes;
   static constexpr int kBarOff = kMetaOff + ((kMetaBytes + 15) / 16) * 16;
   static constexpr int kNumBars = 3 * kD8Stages + 2 * kD8AStages + 2 * kD8Windows + kD8MetaSlots;
@@ -92,6 +120,7 @@ struct D8Params {
   float* partial;
   unsigned* counters;
   unsigned* status;
+  const unsigned char* xprep;   // PREP kernels: K / 128 records written by d8_prep_kernel
   int M, K, N;
   int group_size;
   int ntiles;
@@ -131,42 +160,45 @@ __host__ __device__ constexpr uint32_t make_i8_idesc(int m, int n) {
 // descriptors of the activation tiles (a step advances 32 bytes = 2 units of 16 bytes).
 __device__ __forceinline__ void tcgen05_mma_i8_unit_commit3_warp(uint32_t d_hi, uint32_t d_raw, uint32_t a_hi, uint64_t a_raw,
                                                                  uint64_t b_hi, uint64_t b_lo, uint32_t idesc,
-                                                                 uint32_t bar0, uint32_t bar1, uint32_t bar2) {
+                                                                 uint32_t idesc_raw, uint32_t bar0, uint32_t bar1,
+                                                                 uint32_t bar2) {
   asm volatile(
       "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d, da;\n\t"
       "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, 0, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %10, p;\n\t"
       "setp.eq.b32 p, 0, 0;\n\t"
       "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
       "mov.b64 {lo, hi}, %3;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 da, {lo, hi};\n\t"
       "mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %10, p;\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%9];\n\t}"
-      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(bar0), "r"(bar1), "r"(bar2)
+      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(bar0), "r"(bar1), "r"(bar2),
+        "r"(idesc_raw)
       : "memory");
 }
 
 // The same four MMAs without commits (the first half of a unit).
 __device__ __forceinline__ void tcgen05_mma_i8_half_warp(uint32_t d_hi, uint32_t d_raw, uint32_t a_hi, uint64_t a_raw,
-                                                         uint64_t b_hi, uint64_t b_lo, uint32_t idesc) {
+                                                         uint64_t b_hi, uint64_t b_lo, uint32_t idesc,
+                                                         uint32_t idesc_raw) {
   asm volatile(
       "{\n\t.reg .pred p, e;\n\t.reg .b32 a, lo, hi;\n\t.reg .b64 d, da;\n\t"
       "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, 0, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [%2], %4, %6, p;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %6, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], %3, %5, %7, p;\n\t"
       "setp.eq.b32 p, 0, 0;\n\t"
       "add.u32 a, %2, 8;\n\t  mov.b64 {lo, hi}, %4;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
       "@e tcgen05.mma.cta_group::1.kind::i8 [%0], [a], d, %6, p;\n\t"
       "mov.b64 {lo, hi}, %3;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 da, {lo, hi};\n\t"
       "mov.b64 {lo, hi}, %5;\n\t  add.u32 lo, lo, 2;\n\t  mov.b64 d, {lo, hi};\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %6, p;\n\t}"
-      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc)
+      "@e tcgen05.mma.cta_group::1.kind::i8 [%1], da, d, %7, p;\n\t}"
+      ::"r"(d_hi), "r"(d_raw), "r"(a_hi), "l"(a_raw), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(idesc_raw)
       : "memory");
 }
 
@@ -240,8 +272,89 @@ __device__ __forceinline__ uint32_t d8_collect_word(const D8Params& p, unsigned 
   return *reinterpret_cast<const uint32_t*>(&o);
 }
 
-template <int MR, bool PUSH>
-__global__ void __launch_bounds__(kD8Threads, kD8CtasPerSm)
+// One row's 128 activations of a unit (16 lanes, 8 values each in xv: lane jw holds k = 8 jw .. 8 jw + 7) -> the two
+// planes of signed bytes in the order of the weight bytes they multiply, written into the stage's activation tiles,
+// and (sx, T) into meta_row[m].  Word j of a column holds k = 8j + e at nibble (e >> 1) + 4 (e & 1), so byte b of that
+// word carries k = 8j + {0, 4, 1, 5}[b] in its low nibble and k = 8j + {2, 6, 3, 7}[b] in its high nibble.
+template <int MR>
+__device__ __forceinline__ void d8_quantise_row(const uint4& xv, int m, int jw, unsigned char* st, int2* meta_row) {
+  using Cfg = D8Cfg<MR>;
+  float f[8];
+  {
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&xv.x));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&xv.y));
+    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&xv.z));
+    const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&xv.w));
+    f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y; f[4] = f2.x; f[5] = f2.y; f[6] = f3.x; f[7] = f3.y;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+  for (int off = 1; off < 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  // Inf / NaN activations have no integer image: the row's scale becomes 0 * inf = NaN and so does its output.
+  const float sx = amax * (1.0f / kD8Range);
+  const float inv = amax > 0.f ? static_cast<float>(kD8Range) / amax : 0.f;
+  int tq[8], tsum = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    int v = __float2int_rn(f[e] * inv);
+    v = max(-kD8Range, min(kD8Range, v));
+    tq[e] = v;
+    tsum += v;
+  }
+#pragma unroll
+  for (int off = 1; off < 16; off <<= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, off);
+  // planes: t = 128 * p1 + p2
+  uint32_t hi1 = 0u, hi2 = 0u, lo1 = 0u, lo2 = 0u;
+  constexpr int kLoK[4] = {0, 4, 1, 5}, kHiK[4] = {2, 6, 3, 7};
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int th = tq[kHiK[b]], tl = tq[kLoK[b]];
+    const int h1 = (th + 64) >> 7, l1 = (tl + 64) >> 7;
+    hi1 |= static_cast<uint32_t>(h1 & 0xff) << (8 * b);
+    hi2 |= static_cast<uint32_t>((th - (h1 << 7)) & 0xff) << (8 * b);
+    lo1 |= static_cast<uint32_t>(l1 & 0xff) << (8 * b);
+    lo2 |= static_cast<uint32_t>((tl - (l1 << 7)) & 0xff) << (8 * b);
+  }
+  if (m < MR) {
+    // tile row r: 64 bytes, 16-byte chunk c at chunk position c ^ ((r >> 1) & 3)
+    const int r1 = Cfg::plane1_row(m), r2 = Cfg::plane2_row(m);
+    const uint32_t o1 = static_cast<uint32_t>(r1 * 64 + (((jw >> 2) ^ ((r1 >> 1) & 3)) << 4) + (jw & 3) * 4);
+    const uint32_t o2 = static_cast<uint32_t>(r2 * 64 + (((jw >> 2) ^ ((r2 >> 1) & 3)) << 4) + (jw & 3) * 4);
+    *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o1) = hi1;
+    *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o2) = hi2;
+    *reinterpret_cast<uint32_t*>(st + Cfg::kXloOff + o1) = lo1;
+    *reinterpret_cast<uint32_t*>(st + Cfg::kXloOff + o2) = lo2;
+    if (jw == 0) meta_row[m] = make_int2(__float_as_int(sx), tsum);
+  }
+}
+
+// The activation planes of a call, once for all CTAs: block b writes the record of k block b (the layout the helper
+// warps produce inside a stage: tile Xhi, tile Xlo, then MR x (sx bits, T)).  Used from 5 rows, where the helper
+// warps of every CTA repeating this work for each of its units is what bounds the kernel.
+template <int MR>
+__global__ void __launch_bounds__(128) d8_prep_kernel(const uint16_t* __restrict__ x, unsigned char* __restrict__ out, int M,
+                                                      int K) {
+  using Cfg = D8Cfg<MR>;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");          // the activations belong to the previous kernel until here
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jw = lane & 15, rsel = lane >> 4;
+  const int kb = blockIdx.x;
+  unsigned char* rec = out + static_cast<size_t>(kb) * Cfg::kPrepRecBytes;
+  for (int r = warp; r < (MR + 1) / 2; r += 4) {
+    const int m = 2 * r + rsel;
+    uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) xv = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K + kb * kBlockK + jw * 8));
+    d8_quantise_row<MR>(xv, m, jw, rec - kD8XhiOff, reinterpret_cast<int2*>(rec + 2 * Cfg::kXTileBytes));
+  }
+}
+
+// PREP: the activation planes and (sx, T) of every k block were written by d8_prep_kernel (record layout below);
+// the copy producer fetches them with the weights and the helper warps have nothing to do.
+template <int MR, bool PUSH, bool PREP>
+__global__ void __launch_bounds__(PREP ? kD8Threads - kD8HelperWarps * 32 : kD8Threads, kD8CtasPerSm)
 decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   using Cfg = D8Cfg<MR>;
   constexpr int NT = kD8Stages, NA = kD8AStages, NW = kD8Windows, NS = kD8MetaSlots;
@@ -253,7 +366,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  auto stage_addr = [&](int t) { return base + t * kD8StageBytes; };
+  auto stage_addr = [&](int t) { return base + t * Cfg::kStageBytes; };
   float* comb = reinterpret_cast<float*>(base_ptr + Cfg::kCombOff);          // [MR][256]: group 1's sums
   int2* meta = reinterpret_cast<int2*>(base_ptr + Cfg::kMetaOff);            // [NS][MR]: (bits of sx, T)
   const uint32_t bar_base = base + Cfg::kBarOff;
@@ -304,7 +417,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   const long long u0 = stream_first_unit(blockIdx.x, U, G), u1 = stream_first_unit(blockIdx.x + 1, U, G);
   const int my_units = static_cast<int>(u1 - u0);
   const int nblk = p.nblk;
-  constexpr uint32_t kIdesc = make_i8_idesc(128, 16);
+  constexpr uint32_t kIdesc = make_i8_idesc(128, Cfg::kHiN), kIdescRaw = make_i8_idesc(128, 16);
   const bool sz_by_copy = (p.N & 31) == 0;
 
   if (warp == 0) {
@@ -325,21 +438,47 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       if (lane == 2) tma_load_3d(dst + kD8RawOff, &map_w, 0, n0, kb, bar);
       if (sz_by_copy && (lane == 3 || lane == 4)) {
         const int grp = group_blocks == 1 ? kb : kb / group_blocks;
-        if (lane == 3) bulk_load(dst + kD8SzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar);
-        else bulk_load(dst + kD8SzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3), ncols / 2, bar);
+        if (lane == 3) bulk_load(dst + Cfg::kSzOff, p.scales + static_cast<size_t>(grp) * p.N + n0, ncols * 2, bar);
+        else bulk_load(dst + Cfg::kSzOff + 512, p.qzeros + static_cast<size_t>(grp) * (p.N >> 3) + (n0 >> 3), ncols / 2, bar);
       }
       if (++kb == nblk) { kb = 0; ++tile; }
+    };
+    // PREP: the unit's activation tiles (one copy: Xhi and Xlo are adjacent in the record and in the stage) and
+    // its (sx, T) rows into ring slot gs % 8 (free for the reason given at the helpers).
+    int kbx = static_cast<int>(u0 % nblk);
+    auto issue_x = [&](int gs) {
+      const int t = gs % NT, s = gs % NS;
+      const unsigned char* rec = p.xprep + static_cast<size_t>(kbx) * Cfg::kPrepRecBytes;
+      if (lane == 5) {
+        mbar_expect_tx(bar_xq_full(t), 2 * Cfg::kXTileBytes);
+        bulk_load(stage_addr(t) + kD8XhiOff, rec, 2 * Cfg::kXTileBytes, bar_xq_full(t));
+      }
+      if (lane == 6) {
+        mbar_expect_tx(bar_meta_full(s), Cfg::kPrepMetaBytes);
+        bulk_load(base + Cfg::kMetaOff + s * Cfg::kPrepMetaBytes, rec + 2 * Cfg::kXTileBytes, Cfg::kPrepMetaBytes, bar_meta_full(s));
+      }
+      if (++kbx == nblk) kbx = 0;
     };
     int next = 0;
     for (; next < NT && next < my_units; ++next) issue(next);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if constexpr (PREP) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");      // the records are written by the kernel before this one
+      for (int gs = 0; gs < next; ++gs) issue_x(gs);
+    }
     for (; next < my_units; ++next) {
       if (!mbar_wait(bar_empty(next % NT), static_cast<uint32_t>(next / NT - 1) & 1u, abort_flag, 1)) break;
       issue(next);
+      if constexpr (PREP) issue_x(next);
     }
     // Do not leave while a copy may still be writing shared memory: wait (bounded) for the last ring's worth.
-    for (int gs = max(0, next - NT); gs < next; ++gs)
+    for (int gs = max(0, next - NT); gs < next; ++gs) {
       mbar_wait_timed(bar_full_tma(gs % NT), static_cast<uint32_t>(gs / NT) & 1u);
+      if constexpr (PREP) {
+        mbar_wait_timed(bar_xq_full(gs % NT), static_cast<uint32_t>(gs / NT) & 1u);
+        mbar_wait_timed(bar_meta_full(gs % NS), static_cast<uint32_t>(gs / NS) & 1u);
+      }
+    }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
@@ -352,16 +491,17 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       if (!mbar_wait(bar_a_full(a), static_cast<uint32_t>(gs / NA) & 1u, abort_flag, 4)) break;
       if (!mbar_wait(bar_full_tma(t), static_cast<uint32_t>(gs / NT) & 1u, abort_flag, 10)) break;   // the raw bytes are an operand
       tcgen05_fence_after();
-      const uint32_t win = tmem_base + static_cast<uint32_t>(w * 64);
-      const uint32_t opd = tmem_base + static_cast<uint32_t>(kD8ABase + a * 64);
-      const uint64_t b_hi = make_sw64_desc(stage_addr(t) + kD8XhiOff), b_lo = make_sw64_desc(stage_addr(t) + kD8XloOff);
+      const uint32_t win = tmem_base + static_cast<uint32_t>(w * Cfg::kWinCols);
+      const uint32_t opd = tmem_base + static_cast<uint32_t>(Cfg::kABase + a * Cfg::kASlot);
+      const uint64_t b_hi = make_sw64_desc(stage_addr(t) + kD8XhiOff), b_lo = make_sw64_desc(stage_addr(t) + Cfg::kXloOff);
       const uint64_t a_raw0 = make_sw64_desc(stage_addr(t) + kD8RawOff), a_raw1 = make_sw64_desc(stage_addr(t) + kD8RawOff + 128 * 64);
-      tcgen05_mma_i8_half_warp(win, win + 16, opd, a_raw0, b_hi, b_lo, kIdesc);
-      tcgen05_mma_i8_unit_commit3_warp(win + 32, win + 48, opd + 32, a_raw1, b_hi, b_lo, kIdesc, bar_empty(t),
-                                       bar_a_empty(a), bar_win_full(w));
+      tcgen05_mma_i8_half_warp(win, win + Cfg::kHiN, opd, a_raw0, b_hi, b_lo, kIdesc, kIdescRaw);
+      tcgen05_mma_i8_unit_commit3_warp(win + Cfg::kHalfCols, win + Cfg::kHalfCols + Cfg::kHiN, opd + Cfg::kASlot / 2, a_raw1,
+                                       b_hi, b_lo, kIdesc, kIdescRaw, bar_empty(t), bar_a_empty(a), bar_win_full(w));
     }
     __syncwarp();
   } else if (warp >= kD8HelperWarp0) {
+   if constexpr (!PREP) {
     // ------------------------------ activation helpers -------------------------
     // Unit by unit (alternate units per warp): the M rows of this unit's 128 activations -> two planes of
     // signed bytes in the order of the weight bytes they multiply.  Word j of a column holds k = 8j + e at
@@ -392,62 +532,11 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       for (int r = 0; r < RP; ++r) xv[r] = xnext[r];
       load_x(gs + kD8HelperWarps, xnext);                     // the next unit's rows travel while this one is processed
       if (gs >= NT && !mbar_wait(bar_empty(t), static_cast<uint32_t>(gs / NT - 1) & 1u, abort_flag, 8)) break;
-      unsigned char* st = base_ptr + t * kD8StageBytes;
+      // The (sx, T) ring: slot gs % 8 was last used by unit gs - 8, whose fold preceded MMA(gs - 6) (same
+      // accumulator window), which preceded the release of stage gs - 5 that this warp has just waited for.
+      unsigned char* st = base_ptr + t * Cfg::kStageBytes;
 #pragma unroll
-      for (int r = 0; r < RP; ++r) {
-        const int m = 2 * r + rsel;
-        float f[8];
-        {
-          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].x));
-          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].y));
-          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].z));
-          const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&xv[r].w));
-          f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y; f[4] = f2.x; f[5] = f2.y; f[6] = f3.x; f[7] = f3.y;
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
-#pragma unroll
-        for (int off = 1; off < 16; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        // Inf / NaN activations have no integer image: the row's scale becomes 0 * inf = NaN and so does its output.
-        const float sx = amax * (1.0f / kD8Range);
-        const float inv = amax > 0.f ? static_cast<float>(kD8Range) / amax : 0.f;
-        int tq[8], tsum = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          int v = __float2int_rn(f[e] * inv);
-          v = max(-kD8Range, min(kD8Range, v));
-          tq[e] = v;
-          tsum += v;
-        }
-#pragma unroll
-        for (int off = 1; off < 16; off <<= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, off);
-        // planes: t = 128 * p1 + p2
-        uint32_t hi1 = 0u, hi2 = 0u, lo1 = 0u, lo2 = 0u;
-        constexpr int kLoK[4] = {0, 4, 1, 5}, kHiK[4] = {2, 6, 3, 7};
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int th = tq[kHiK[b]], tl = tq[kLoK[b]];
-          const int h1 = (th + 64) >> 7, l1 = (tl + 64) >> 7;
-          hi1 |= static_cast<uint32_t>(h1 & 0xff) << (8 * b);
-          hi2 |= static_cast<uint32_t>((th - (h1 << 7)) & 0xff) << (8 * b);
-          lo1 |= static_cast<uint32_t>(l1 & 0xff) << (8 * b);
-          lo2 |= static_cast<uint32_t>((tl - (l1 << 7)) & 0xff) << (8 * b);
-        }
-        if (m < MR) {
-          // tile row r: 64 bytes, 16-byte chunk c at chunk position c ^ ((r >> 1) & 3).  The (sx, T) ring: slot
-          // gs % 8 was last used by unit gs - 8, whose fold preceded MMA(gs - 6) (same accumulator window),
-          // which preceded the release of stage gs - 5 that this warp has just waited for.
-          const int r1 = m, r2 = MR + m;
-          const uint32_t o1 = static_cast<uint32_t>(r1 * 64 + (((jw >> 2) ^ ((r1 >> 1) & 3)) << 4) + (jw & 3) * 4);
-          const uint32_t o2 = static_cast<uint32_t>(r2 * 64 + (((jw >> 2) ^ ((r2 >> 1) & 3)) << 4) + (jw & 3) * 4);
-          *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o1) = hi1;
-          *reinterpret_cast<uint32_t*>(st + kD8XhiOff + o2) = hi2;
-          *reinterpret_cast<uint32_t*>(st + kD8XloOff + o1) = lo1;
-          *reinterpret_cast<uint32_t*>(st + kD8XloOff + o2) = lo2;
-          if (jw == 0) meta[s * MR + m] = make_int2(__float_as_int(sx), tsum);
-        }
-      }
+      for (int r = 0; r < RP; ++r) d8_quantise_row<MR>(xv[r], 2 * r + rsel, jw, st, meta + s * Cfg::kMetaStride);
       fence_proxy_async();            // the tiles are read by the tensor core (async proxy)
       __syncwarp();
       if (lane == 0) {
@@ -456,6 +545,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
       }
     }
     __syncwarp();
+   }
   } else {
     // ---------------------- mask into tensor memory, then fold accumulators ---------------
     asm volatile("griddepcontrol.wait;" ::: "memory");   // y and the workspace belong to the previous kernel until here
@@ -516,12 +606,48 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
         const int w = pend % NW, s = pend % NS;
         if (ok && !mbar_wait(bar_meta_full(s), static_cast<uint32_t>(pend / NS) & 1u, abort_flag, 9)) ok = false;
         if (ok && !mbar_wait(bar_win_full(w), static_cast<uint32_t>(pend / NW) & 1u, abort_flag, 6)) ok = false;
-        if (ok) {
+        if constexpr (MR == 8) {
+          // Four rows at a time: the two planes of rows 4 c .. 4 c + 3 are eight adjacent accumulator columns.
+          if (ok) {
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              uint32_t vh[2][8], vx[2][8], vr[2][8];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * Cfg::kWinCols + h * Cfg::kHalfCols);
+                d8_tmem_ld<8>(win + 8 * c, vh[h]);                  // hi x (activations of the high nibbles)
+                d8_tmem_ld<8>(win + 16 + 8 * c, vx[h]);             // hi x (activations of the low nibbles)
+                d8_tmem_ld<8>(win + Cfg::kHiN + 8 * c, vr[h]);      // raw x (activations of the low nibbles)
+              }
+              tcgen05_wait_ld();
+              if (c == 1) {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_win_empty(w));
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int m = 4 * c + q;
+                const int2 mt = meta[s * Cfg::kMetaStride + m];                  // same address in every lane: a broadcast
+                const float sx = __int_as_float(mt.x);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int dhi = (static_cast<int>(vh[h][2 * q]) << 7) + static_cast<int>(vh[h][2 * q + 1]);
+                  const int dlo = ((static_cast<int>(vr[h][2 * q]) - static_cast<int>(vx[h][2 * q])) << 7) +
+                                  (static_cast<int>(vr[h][2 * q + 1]) - static_cast<int>(vx[h][2 * q + 1]));
+                  const int val = (dhi >> 4) + dlo - pend_z[h] * mt.y;
+                  acc[h][m] = fmaf(pend_s[h] * sx, static_cast<float>(val), acc[h][m]);
+                }
+              }
+            }
+          }
+        } else if (ok) {
           tcgen05_fence_after();
           uint32_t vh[2][2 * MR], vx[2][2 * MR], vr[2][2 * MR];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * 64 + h * 32);
+            const uint32_t win = tmem_base + lane_addr + static_cast<uint32_t>(w * Cfg::kWinCols + h * Cfg::kHalfCols);
             d8_tmem_ld<2 * MR>(win, vh[h]);             // hi x (activations of the high nibbles)
             d8_tmem_ld<2 * MR>(win + 8, vx[h]);         // hi x (activations of the low nibbles): rows 8.. of the B tile
             d8_tmem_ld<2 * MR>(win + 16, vr[h]);        // raw x (activations of the low nibbles)
@@ -532,7 +658,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
           if (lane == 0) mbar_arrive(bar_win_empty(w));
 #pragma unroll
           for (int m = 0; m < MR; ++m) {
-            const int2 mt = meta[s * MR + m];                  // same address in every lane: a broadcast
+            const int2 mt = meta[s * Cfg::kMetaStride + m];                  // same address in every lane: a broadcast
             const float sx = __int_as_float(mt.x);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -566,13 +692,13 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
         }
         if (ok && !mbar_wait(bar_full_tma(t), ph, abort_flag, 5)) ok = false;
         if (!ok) continue;
-        const unsigned char* stage = base_ptr + t * kD8StageBytes;
+        const unsigned char* stage = base_ptr + t * Cfg::kStageBytes;
         if (sz_by_copy) {
           // Columns beyond N read stale shared memory here; their lanes of the product are never stored.
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            sc[h] = reinterpret_cast<const uint16_t*>(stage + kD8SzOff)[h * 128 + cl0];
-            zw[h] = reinterpret_cast<const uint32_t*>(stage + kD8SzOff + 512)[(h * 128 + cl0) >> 3];
+            sc[h] = reinterpret_cast<const uint16_t*>(stage + Cfg::kSzOff)[h * 128 + cl0];
+            zw[h] = reinterpret_cast<const uint32_t*>(stage + Cfg::kSzOff + 512)[(h * 128 + cl0) >> 3];
           }
         }
         if (!mbar_wait(bar_a_empty(a), pha ^ 1u, abort_flag, 7)) {
@@ -594,7 +720,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(t));            // the stage's packed weights are in registers
           }
-          const uint32_t a_addr = tmem_base + lane_addr + static_cast<uint32_t>(kD8ABase + a * 64 + h * 32);
+          const uint32_t a_addr = tmem_base + lane_addr + static_cast<uint32_t>(Cfg::kABase + a * Cfg::kASlot + h * (Cfg::kASlot / 2));
           uint32_t o[16];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -669,8 +795,7 @@ decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
 #pragma unroll
             for (int m = 0; m < MR; ++m) {
               if (m < p.M) {                                 // warp-uniform
-                const float* cb = comb + m * kD8BN + h * 128 + cl0;
-                const float val = acc[h][m] + cb[0];
+                const float val = acc[h][m] + comb[m * kD8BN + h * 128 + cl0];
                 if (direct) epilogue_store_lane(p.y, p.epi, m, p.N, ncol[h], val, nval[h]);
                 else if (nval[h]) __stcg(p.partial + (static_cast<size_t>(slot) * p.M + m) * p.N + ncol[h], val);
               }
@@ -778,10 +903,11 @@ static int decode_slots(int K, int N, int sm_count) {
 size_t decode_workspace_bytes(int M, int K, int N, int sm_count) {
   if (M < 1 || K < kBlockK || N < 8) return 0;
   const int slots = decode_slots(K, N, sm_count);
-  return kGemvMaxCounters * sizeof(unsigned) + (slots > 1 ? static_cast<size_t>(slots) * M * N * sizeof(float) : 0);
+  const size_t prep = static_cast<size_t>(K / kBlockK) * D8Cfg<8>::kPrepRecBytes;   // the planes' records (largest form)
+  return kGemvMaxCounters * sizeof(unsigned) + (slots > 1 ? static_cast<size_t>(slots) * M * N * sizeof(float) : 0) + prep;
 }
 
-template <int MR, bool PUSH>
+template <int MR, bool PUSH, bool PREP>
 static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTiledFn encode, cudaStream_t stream,
                             bool overlap_previous, int max_smem_optin) {
   using Cfg = D8Cfg<MR>;
@@ -798,13 +924,13 @@ static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTile
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
   }
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH, PREP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   // two CTAs of ~100 KB per SM: ask for the largest shared-memory carve-out
-  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  AWQ_CUDA_TRY(cudaFuncSetAttribute(decode_i8_kernel<MR, PUSH, PREP>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kD8Threads);
+  cfg.blockDim = dim3(PREP ? kD8Threads - kD8HelperWarps * 32 : kD8Threads);   // no helper warps behind the planes' kernel
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -816,7 +942,19 @@ static int launch_decode_i8(const void* packed, D8Params p, int grid, EncodeTile
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_i8_kernel<MR, PUSH>, mw, p));
+  if constexpr (PREP) {
+    // The planes first (it takes the caller's overlap choice); the main kernel may always start early behind it:
+    // until its own wait it touches nothing but the weights, which the planes' kernel has waited for as well.
+    cudaLaunchConfig_t pc = cfg;
+    pc.gridDim = dim3(p.nblk);
+    pc.blockDim = dim3(128);
+    pc.dynamicSmemBytes = 0;
+    AWQ_CUDA_TRY(cudaLaunchKernelEx(&pc, d8_prep_kernel<MR>, p.x, const_cast<unsigned char*>(p.xprep), p.M, p.K));
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 1;
+  }
+  AWQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_i8_kernel<MR, PUSH, PREP>, mw, p));
   return AWQ_B200_OK;
 }
 
@@ -854,6 +992,10 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
   p.counters = static_cast<unsigned*>(workspace);
   p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kGemvMaxCounters * sizeof(unsigned));
   p.status = static_cast<unsigned*>(workspace) + (kGemvMaxCounters - 1);
+  {
+    const int slots = decode_slots(K, N, di.sm_count);
+    p.xprep = reinterpret_cast<const unsigned char*>(p.partial) + (slots > 1 ? static_cast<size_t>(slots) * M * N * sizeof(float) : 0);
+  }
   p.M = M; p.K = K; p.N = N;
   p.group_size = group_size;
   p.ntiles = ntiles;
@@ -865,6 +1007,7 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
   if (push != nullptr) {
     if (!push->recv || !push->flags) return AWQ_B200_ERR_NULL;
     if (push->world < 2 || push->world > 8 || push->rank < 0 || push->rank >= push->world) return AWQ_B200_ERR_SHAPE;
+    if (M > kD8PushMaxRows) return AWQ_B200_ERR_SHAPE;
     if (static_cast<size_t>(M) * N > push->slot_elems) return AWQ_B200_ERR_TOO_LARGE;
     if (epi.residual != nullptr || epi.gated) return AWQ_B200_ERR_SHAPE;      // the exchanged value is the plain sum
     p.recv = reinterpret_cast<unsigned char* const*>(push->recv);
@@ -872,13 +1015,14 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
     p.slot_bytes = push->slot_elems * 4;
     p.rank = push->rank;
     p.world = push->world;
-    if (M <= 1) return launch_decode_i8<1, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-    if (M <= 2) return launch_decode_i8<2, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-    return launch_decode_i8<4, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    if (M <= 1) return launch_decode_i8<1, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    if (M <= 2) return launch_decode_i8<2, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    return launch_decode_i8<4, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   }
-  if (M <= 1) return launch_decode_i8<1, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-  if (M <= 2) return launch_decode_i8<2, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-  return launch_decode_i8<4, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  if (M <= 1) return launch_decode_i8<1, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  if (M <= 2) return launch_decode_i8<2, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  if (M <= 4) return launch_decode_i8<4, false, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+  return launch_decode_i8<8, false, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
 }
 
 int decode_i8_dispatch(const void* x, const void* packed, const void* scales, const int32_t* qzeros, const Epilogue& epi,

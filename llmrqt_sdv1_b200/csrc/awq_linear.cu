@@ -1,5 +1,5 @@
 // Row-count and shape dispatch between the linear kernels: the mma.sync decode GEMV, the two tensor-memory
-// split-K kernels for few rows of a large matrix (integer path up to 4 rows, exact fp16 weights up to 64),
+// split-K kernels for few rows of a large matrix (integer path up to 8 rows, exact fp16 weights up to 64),
 // and the prefill GEMM.
 #include "awq_common.cuh"
 
@@ -11,8 +11,9 @@ constexpr int kSkinnyMaxRows = 64;
 // a row's bits do not change with the number of rows decoded together).
 //   rows <= 4:  the GEMV, or from 24 MiB of packed weights the integer tensor-core decode kernel
 //               (awq_decode_i8.cu; 70B-class gate_up at one row: 45 us against 72 us).
-//   5..8:       the GEMV, or from 48 MiB the exact-weight split-K tensor-memory kernel.
-//   9..16:      the same with the switch at 16 MiB (beyond 8 rows the GEMV does its unpacking twice).
+//   5..8:       the GEMV, or from 48 MiB the integer kernel again (its 8-row form).
+//   9..16:      the GEMV, or from 16 MiB the exact-weight split-K tensor-memory kernel (beyond 8 rows the GEMV
+//               does its unpacking twice).
 //   17..64:     small matrices (packed MiB x ceil(rows / 8) <= 32): the GEMV, 8 rows per CTA; else the exact-weight
 //               tensor-memory kernel where the GEMM would leave most SMs idle (at most 74 column tiles of 256)
 //               and k is long enough to split (at least 32 blocks of 128); the GEMM otherwise.
@@ -30,8 +31,10 @@ Route route(int M, int K, int N, int group_size, bool one_kernel_below_8 = false
     // ~16-20 MiB at one row (28 MiB: 10.8-11.2 against 12.5-12.9) and from ~36 MiB at four rows.  One threshold
     // for the class: decode (1 row) and a short verification (2..4 rows) must take the same kernel.
     if (M <= kDecodeI8MaxRows) return packed_bytes < (24ll << 20) ? Route::kGemv : Route::kDecodeI8;
-    const long long from_bytes = M <= 8 ? (48ll << 20) : (16ll << 20);
-    if (packed_bytes < from_bytes) return Route::kGemv;
+    // 5..8 rows: the integer kernel behind its planes' kernel (70B gate_up 58 us against 75 us of the exact-weight
+    // kernel; 56 MiB: 25.3 against 25.8 and 28.5 of the GEMV); the GEMV below 48 MiB (29 MiB: 12.8 against 16.7).
+    if (M <= 8) return packed_bytes < (48ll << 20) ? Route::kGemv : Route::kDecodeI8;
+    if (packed_bytes < (16ll << 20)) return Route::kGemv;
     return Route::kSkinny;
   }
   // 17..64 rows of a small matrix: the GEMV again, one CTA per 8 rows and column group (the weights are re-read

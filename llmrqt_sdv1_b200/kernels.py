@@ -195,7 +195,7 @@ def skinny(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> t
 
 
 def decode_i8(x, pw: PackedWeight, bias=None, out=None, overlap: bool = False) -> torch.Tensor:
-    """Decode rows (1 <= M <= 4) on the integer tensor-core path (masked nibbles x block-fixed-point activations)."""
+    """Decode rows (1 <= M <= 8) on the integer tensor-core path (packed bytes x block-fixed-point activations)."""
     return _run(lib.awq_b200_decode_i8, "awq_b200_decode", x, pw, bias,
                 lib.awq_b200_decode_workspace_bytes(max(x.shape[0], 1), pw.K, pw.N), out,
                 (_lib.OVERLAP_PREVIOUS if overlap else 0,))

@@ -1,4 +1,4 @@
-"""The integer tensor-core decode kernel (1..4 rows, `awq_b200_decode_i8`) against the CPU oracle at oracle-sized
+"""The integer tensor-core decode kernel (1..8 rows, `awq_b200_decode_i8`) against the CPU oracle at oracle-sized
 shapes and against device dequant + library matmul at full size; row results independent of the number of
 rows; run-to-run identical; activations with outliers and extreme zero points."""
 import numpy as np
@@ -35,16 +35,26 @@ def _random_packed_inputs(K, N, G, seed):
                                    (6144, 2048, 128), (4096, 4096, 128), (512, 384, 512)])
 def test_decode_i8_vs_oracle(K_, K, N, G):
     qw, qz, sc = orc.make_awq_tensors(K, N, G, seed=K + N)
-    x = orc.make_activations(4, K, seed=6)
-    ref = orc.linear_forward(x, qw, qz, sc, G)
+    x8 = orc.make_activations(8, K, seed=6)
+    x = x8[:4]
+    ref8 = orc.linear_forward(x8, qw, qz, sc, G)
     pw = K_.make_packed(dev(qw), dev(qz), dev(sc), G)
     y4 = K_.decode_i8(dev(x), pw)
     assert y4.shape == (4, N) and y4.dtype == torch.float16
-    assert orc.max_normalised_error(y4.cpu().numpy(), ref) <= TOL
+    assert orc.max_normalised_error(y4.cpu().numpy(), ref8[:4]) <= TOL
     for M in (1, 2, 3):
         yM = K_.decode_i8(dev(x[:M]), pw, overlap=(M % 2 == 1))
         assert torch.equal(yM, y4[:M]), f"rows differ between M={M} and M=4"
     assert torch.equal(K_.decode_i8(dev(x), pw), y4)          # run-to-run identical
+    # 5..8 rows: the 8-row form behind the kernel that writes the activation planes once per call
+    y8 = K_.decode_i8(dev(x8), pw)
+    assert y8.shape == (8, N)
+    assert orc.max_normalised_error(y8.cpu().numpy(), ref8) <= TOL
+    assert torch.equal(y8[:4], y4), "rows differ between M=4 and M=8"
+    for M in (5, 6, 7):
+        yM = K_.decode_i8(dev(x8[:M]), pw, overlap=(M % 2 == 1))
+        assert torch.equal(yM, y8[:M]), f"rows differ between M={M} and M=8"
+    assert torch.equal(K_.decode_i8(dev(x8), pw, overlap=True), y8)
     assert K_.gemv_status() == 0
 
 
@@ -58,7 +68,7 @@ def test_decode_i8_bias_and_bounds(K_):
     ref = orc.linear_forward(x, qw, qz, sc, 128, bias=bias)
     assert orc.max_normalised_error(y.cpu().numpy(), ref) <= TOL
     with pytest.raises(ValueError):
-        K_.decode_i8(dev(orc.make_activations(5, K, seed=1)), pw)
+        K_.decode_i8(dev(orc.make_activations(9, K, seed=1)), pw)
     assert K_.gemv_status() == 0
 
 
@@ -90,7 +100,8 @@ def test_decode_i8_outliers_zero_rows_and_extreme_zero_points(K_):
 
 
 @pytest.mark.parametrize("K,N,M", [(8192, 57344, 1), (8192, 57344, 4), (28672, 8192, 4), (28672, 8192, 1),
-                                   (8192, 7168, 3), (3584, 8192, 2), (2048, 12288, 2)])
+                                   (8192, 7168, 3), (3584, 8192, 2), (2048, 12288, 2), (8192, 57344, 8),
+                                   (28672, 8192, 5), (8192, 7168, 7), (7168, 8192, 6)])
 def test_decode_i8_full_size_vs_device_dequant_matmul(K_, K, N, M):
     qw, qz, sc = _random_packed_inputs(K, N, 128, seed=K + N)
     pw = K_.make_packed(qw, qz, sc, 128)
@@ -107,8 +118,8 @@ def test_decode_i8_full_size_vs_device_dequant_matmul(K_, K, N, M):
 
 def test_decode_i8_fused_epilogues_and_routing(K_):
     """Bias, SiLU(gate) * up over interleaved column pairs and the residual through `linear_fused` on a weight
-    large enough to be routed here (64 MiB); `linear` picks this kernel for 1..4 rows, the exact-weight
-    tensor-memory kernel for 5..16 rows, and the GEMV for every row count of a small weight."""
+    large enough to be routed here (64 MiB); `linear` picks this kernel for 1..8 rows, the exact-weight
+    tensor-memory kernel for 9..16 rows, and the GEMV for every row count of a small weight."""
     import torch.nn.functional as F
     K, n = 8192, 8192
     gate = _random_packed_inputs(K, n, 128, seed=1)
@@ -126,7 +137,16 @@ def test_decode_i8_fused_epilogues_and_routing(K_):
     assert float((got.float() - want.float()).abs().max() / want.float().abs().max()) <= 2e-3
     res2 = torch.randn((3, 2 * n), device="cuda", generator=torch.Generator(device="cuda").manual_seed(6)).half()
     assert torch.equal(K_.linear_fused(x3, pw_gu, bias=bias, residual=res2), plain + res2)   # exact: same roundings
-    for M in (5, 8, 9, 16):
+    for M in (5, 8):
+        xm = x[:M].contiguous()
+        assert torch.equal(K_.linear(xm, pw_gu, bias=bias), K_.decode_i8(xm, pw_gu, bias=bias))
+    x8 = x[:8].contiguous()
+    res8 = torch.randn((8, n), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7)).half()
+    plain8 = K_.decode_i8(x8, pw_gu, bias=bias)
+    want8 = F.silu(plain8[:, 0::2]) * plain8[:, 1::2] + res8
+    got8 = K_.linear_fused(x8, pw_gu, bias=bias, residual=res8, gated=True)
+    assert float((got8.float() - want8.float()).abs().max() / want8.float().abs().max()) <= 2e-3
+    for M in (9, 16):
         xm = x[:M].contiguous()
         assert torch.equal(K_.linear(xm, pw_gu), K_.skinny(xm, pw_gu))
     K2, N2 = 2048, 8192                                        # 8 MiB: the GEMV at every row count
