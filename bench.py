@@ -1066,8 +1066,8 @@ def run_profile_case(args, torch):
         assert q8.status() == 0
     elif args.profile_case.startswith(("gemv", "skinny", "decode")):
         # gemv / gemv16: 24 distinct 2048x12288 weights (13 MB each, 314 MB > L2), two passes
-        # gemv70b / skinny70b[_m16] / decode70b[_m4]: one 8192x57344 weight (235 MB > L2), three launches
-        M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else (4 if args.profile_case == "decode70b_m4" else 1)
+        # gemv70b / skinny70b[_m16] / decode70b[_m4, _m8]: one 8192x57344 weight (235 MB > L2), three launches
+        M = 16 if args.profile_case in ("gemv16", "skinny70b_m16") else {"decode70b_m4": 4, "decode70b_m8": 8}.get(args.profile_case, 1)
         fn = (kernels.skinny if args.profile_case.startswith("skinny") else
               kernels.decode_i8 if args.profile_case.startswith("decode") else kernels.gemv)
         K, N, copies, passes = (8192, 57344, 1, 3) if "70b" in args.profile_case else (2048, 12288, 24, 2)
@@ -1104,7 +1104,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--headline-only", action="store_true",
                     help="time the headline workload only (no qwen3_decode block, no tables): for launch-list captures")
-    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "decode70b", "decode70b_m4",
+    ap.add_argument("--profile-case", default=None, choices=["gemv", "gemv16", "gemv70b", "skinny70b", "skinny70b_m16", "decode70b", "decode70b_m4", "decode70b_m8",
                                                        "q8_decode", "q8_decode_split", "q8_prefill",
                              "gemm", "gemm_large", "gemm_m64"],
                     help="run a small fixed case of one kernel (for ncu) and exit")

@@ -1017,7 +1017,7 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
     p.world = push->world;
     if (M <= 1) return launch_decode_i8<1, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
     if (M <= 2) return launch_decode_i8<2, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-    return launch_decode_i8<4, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    return launch_decode_i8<4, true, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   }
   if (M <= 1) return launch_decode_i8<1, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   if (M <= 2) return launch_decode_i8<2, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);

@@ -238,18 +238,19 @@ def test_fused_exchange_equals_decode_then_push(K, N):
     assert kernels.gemv_status() == 0
 
 
-def test_fused_exchange_inside_a_replayed_graph():
+@pytest.mark.parametrize("M", [1, 4])          # 4 rows: the form behind the kernel that writes the activation planes
+def test_fused_exchange_inside_a_replayed_graph(M):
     from llmrqt_sdv1_b200 import kernels
     K, N = 4096, 4096
     pw = _packed(K, N, seed=9)
-    rig = _Rig(N)
-    x = [_rand((1, K), 20), _rand((1, K), 21), _rand((1, K), 22)]
+    rig = _Rig(M * N)
+    x = [_rand((M, K), 20), _rand((M, K), 21), _rand((M, K), 22)]
     mine = [kernels.decode_i8(xi, pw) for xi in x]
-    outs = [torch.empty((1, N), dtype=torch.float16, device="cuda") for _ in x]
+    outs = [torch.empty((M, N), dtype=torch.float16, device="cuda") for _ in x]
     epoch = 0
 
     def fill(seed):
-        theirs = [_rand((1, N), seed + j) for j in range(3)]
+        theirs = [_rand((M, N), seed + j) for j in range(3)]
         # three calls per replay: the third reuses the parity of the first, so the host writes it after the
         # first two slots have been consumed - here all three are written up front into distinct epochs' words
         for j, t in enumerate(theirs[:2]):
@@ -276,6 +277,15 @@ def test_fused_exchange_inside_a_replayed_graph():
         for j in range(2):
             assert torch.equal(outs[j], _fp32_sum(mine[j], theirs[j])), f"replay {rep}, call {j}"
     assert int(rig.flags[0][35].item()) == epoch and int(rig.flags[0][STATUS].item()) == 0
+
+
+def test_fused_exchange_refuses_more_than_four_rows():
+    pw = _packed(1024, 2048, seed=1)
+    rig = _Rig(8 * 2048)
+    with pytest.raises(ValueError):
+        rig.fused(_rand((5, 1024), 1), pw)
+    torch.cuda.synchronize()
+    assert int(rig.flags[0][35].item()) == 0 and int(rig.flags[0][STATUS].item()) == 0
 
 
 def test_fused_exchange_wait_runs_out_sets_status_and_reset_recovers():
