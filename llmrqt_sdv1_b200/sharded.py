@@ -227,6 +227,42 @@ class PeerSum:
         dist.barrier(self.group)
 
 
+# Rows per piece when a row-parallel linear of many rows is cut so that the all-reduce of one piece may run while
+# the GEMM of the next does; 0 = one GEMM, then one all-reduce.  Off by default: the GEMM is a persistent kernel on
+# every SM, so NCCL's kernel mostly waits for it anyway, and smaller GEMMs fill their last wave worse (70B down
+# projection, 4096 rows, 8 layers: 20.9 against 21.1 ms in pieces of 1024 rows on 2 GPUs, 7.37 against 6.94 ms on 8).
+PREFILL_CHUNK_ROWS = 0
+
+
+def linear_all_reduce(x2d: torch.Tensor, pw, bias=None, out: torch.Tensor | None = None, group=None,
+                      chunk_rows: int = PREFILL_CHUNK_ROWS) -> torch.Tensor:
+    """Row-parallel linear of many rows (prefill): y = all_reduce_sum(x2d . W_shard (+ bias)).
+
+    With `chunk_rows` > 0 the rows are cut into pieces; each piece's NCCL all-reduce is started asynchronously
+    right behind its GEMM (on NCCL's stream) and may run while the next piece's GEMM does.  `chunk_rows <= 0` or
+    fewer than two pieces: one GEMM, one all-reduce.
+    Returns after making the current stream wait for every piece."""
+    from . import kernels
+    rows, N = x2d.shape[0], pw.N
+    if out is None:
+        out = torch.empty((rows, N), dtype=torch.float16, device=x2d.device)
+    pieces = 1 if chunk_rows <= 0 else rows // chunk_rows
+    if pieces < 2:
+        kernels.linear(x2d, pw, bias=bias, out=out)
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out
+    works = []
+    for c in range(pieces):
+        r0 = c * chunk_rows
+        r1 = rows if c == pieces - 1 else r0 + chunk_rows
+        piece = out[r0:r1]
+        kernels.linear(x2d[r0:r1], pw, bias=bias, out=piece)
+        works.append(dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    return out
+
+
 class RowParallelAWQLinear(nn.Module):
     """y = all_reduce_sum( x[..., shard] . W[shard, :] ) (+ bias on rank 0)."""
 
@@ -281,6 +317,14 @@ class RowParallelAWQLinear(nn.Module):
                                overlap=overlap)
                 y = ps.reduce(rows, N)
                 return y.view(*x.shape[:-1], N) if x.dim() > 2 else y.view(1, rows, N)
+        if self.world > 1 and x.is_cuda and x.dtype == torch.float16:
+            rows = x.numel() // x.shape[-1]
+            chunk = getattr(self, "prefill_chunk_rows", PREFILL_CHUNK_ROWS)
+            if chunk > 0 and rows >= 2 * chunk:
+                pw = self.packed()
+                pw.fresh = False
+                y = linear_all_reduce(x.reshape(rows, -1), pw, bias=self.linear.bias, group=self.group, chunk_rows=chunk)
+                return y.view(*x.shape[:-1], -1) if x.dim() > 2 else y.view(1, rows, -1)
         y = self.linear(x)
         if self.world > 1:
             y = y.contiguous()

@@ -65,6 +65,22 @@ def _check_mode(mode, rank, world, dev, dist, quantize, PeerSum, RowParallelAWQL
         y_peer = mod(x)
         rel = ((y_peer.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max()).item()
         ok = ok and y_peer.shape == y_nccl.shape and rel <= 2e-3
+        # many rows (prefill), optional form: GEMM and NCCL all-reduce in pieces of rows, each piece's exchange behind
+        # the next piece's GEMM - the same bits as one GEMM followed by one all-reduce (two ranks: one addition per element)
+        if mode == "push":
+            K3, N3 = 1024 * world, 2048
+            qw, qz, sc = quantize.random_awq_tensors(K3 // world, N3, 128, seed=11 + rank, device=dev)
+            mod3 = RowParallelAWQLinear.from_local(qw, qz, sc, None, 128)
+            x3 = torch.randn((2 * 1024 + 192, K3 // world), device=dev,
+                             generator=torch.Generator(device=dev).manual_seed(30 + rank)).half()
+            mod3.prefill_chunk_rows = 1024
+            y_pieces = mod3(x3)
+            mod3.prefill_chunk_rows = 0
+            y_whole = mod3(x3)
+            ok = ok and y_pieces.shape == y_whole.shape and torch.equal(y_pieces, y_whole)
+            ys = [torch.empty_like(y_pieces) for _ in range(world)]
+            dist.all_gather(ys, y_pieces.contiguous())
+            ok = ok and all(torch.equal(ys[0], t) for t in ys)
         # the exchange inside the decode kernel's epilogue: same bits as decode kernel + push kernel, and the two
         # forms may alternate (one call counter)
         if mode == "push":
