@@ -113,10 +113,19 @@ def dequantize_packed(pw: PackedWeight) -> torch.Tensor:
 _workspaces: dict[tuple[int, int, str], torch.Tensor] = {}
 
 
+_retired_workspaces: list[torch.Tensor] = []
+
+
 def _workspace(dev: torch.device, stream: int, nbytes: int, kind: str) -> torch.Tensor:
+    """The zero-initialised scratch of one (device, stream, entry point).  When a call needs more than the buffer
+    holds, a larger one takes its place (at least 1.5 x, so few are ever made) and the old one is kept allocated:
+    a CUDA graph captured earlier still holds its address."""
     key = (dev.index, stream, kind)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+            nbytes = max(nbytes, ws.numel() * 3 // 2)
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws

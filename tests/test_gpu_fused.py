@@ -231,3 +231,41 @@ def test_graphed_step_matches_eager(K_):
         step(torch.zeros((1, 4, 512), dtype=torch.float16, device="cuda"))
     with pytest.raises(ValueError):
         step(x0, x0)
+
+
+def test_workspace_growth_keeps_a_captured_graph_valid(K_):
+    """A graph captured by the caller holds the address of the stream's workspace; a later call that needs a larger
+    workspace gets a new one, and the old one stays allocated: the replay is still correct."""
+    from llmrqt_sdv1_b200 import quantize
+    side = torch.cuda.Stream()
+    qw, qz, sc = quantize.random_awq_tensors(512, 1024, 128, seed=31, device="cuda")
+    pw = K_.make_packed(qw, qz, sc, 128)
+    x = torch.randn((2, 512), device="cuda", generator=torch.Generator(device="cuda").manual_seed(32)).half()
+    y = torch.empty((2, 1024), dtype=torch.float16, device="cuda")
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            K_.linear(x, pw, out=y)
+        side.synchronize()
+        want = y.clone()
+        key = (x.device.index, side.cuda_stream, "awq_b200_linear")
+        before = K_._workspaces[key]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            K_.linear(x, pw, out=y)
+        # a weight whose few-row kernel shares column tiles between CTAs through partial sums: a larger workspace
+        qw2, qz2, sc2 = quantize.random_awq_tensors(8192, 8192, 128, seed=33, device="cuda")
+        pw2 = K_.make_packed(qw2, qz2, sc2, 128)
+        x2 = torch.randn((64, 8192), device="cuda").half()
+        assert K_.lib.awq_b200_linear_workspace_bytes(64, 8192, 8192) > before.numel()
+        K_.linear(x2, pw2)
+        after = K_._workspaces[key]
+        assert after.data_ptr() != before.data_ptr() and any(t is before for t in K_._retired_workspaces)
+        junk = [torch.full((1 << 20,), 7, dtype=torch.uint8, device="cuda") for _ in range(8)]   # would reuse freed memory
+        y.zero_()
+        g.replay()
+        side.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    assert torch.equal(y, want)
+    del junk
+    assert K_.gemv_status() == 0
