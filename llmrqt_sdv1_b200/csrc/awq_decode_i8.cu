@@ -67,7 +67,6 @@ constexpr int kD8BN = 256;
 constexpr int kD8RawBytes = kD8BN * 64;            // [256 columns][64 bytes], 64-byte swizzle
 constexpr int kD8RawOff = 0;
 constexpr int kD8XhiOff = kD8RawOff + kD8RawBytes;
-constexpr int kD8Stages = 5;                       // per CTA; two CTAs per SM
 constexpr int kD8Windows = 2;
 constexpr int kD8AStages = 2;
 constexpr int kD8TmemCols = 256;
@@ -104,10 +103,11 @@ template <int MR> struct D8Cfg {
   static constexpr int kMetaStride = kPrepMetaBytes / 8;     // int2 entries per ring slot
   static constexpr int kCombBytes = (kD8Groups - 1) * kD8BN * MR * 4;
   static constexpr int kMetaBytes = kD8MetaSlots * kPrepMetaBytes;
-  static constexpr int kCombOff = kD8Stages * kStageBytes;
+  static constexpr int kStages = 5;                          // per CTA; two CTAs per SM (six measured no faster)
+  static constexpr int kCombOff = kStages * kStageBytes;
   static constexpr int kMetaOff = kCombOff + kCombBytes;
   static constexpr int kBarOff = kMetaOff + ((kMetaBytes + 15) / 16) * 16;
-  static constexpr int kNumBars = 3 * kD8Stages + 2 * kD8AStages + 2 * kD8Windows + kD8MetaSlots;
+  static constexpr int kNumBars = 3 * kStages + 2 * kD8AStages + 2 * kD8Windows + kD8MetaSlots;
   static constexpr int kSmemBytes = kBarOff + kNumBars * 8 + 1024 /*align*/;
 };
 
@@ -357,7 +357,7 @@ template <int MR, bool PUSH, bool PREP>
 __global__ void __launch_bounds__(PREP ? kD8Threads - kD8HelperWarps * 32 : kD8Threads, kD8CtasPerSm)
 decode_i8_kernel(const __grid_constant__ CUtensorMap map_w, const D8Params p) {
   using Cfg = D8Cfg<MR>;
-  constexpr int NT = kD8Stages, NA = kD8AStages, NW = kD8Windows, NS = kD8MetaSlots;
+  constexpr int NT = Cfg::kStages, NA = kD8AStages, NW = kD8Windows, NS = kD8MetaSlots;
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;
   __shared__ int s_last;
