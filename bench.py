@@ -840,11 +840,13 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
         yg = torch.empty((Md, ng_local), dtype=torch.float16, device=dev)
         yd = torch.empty((Md, Nd), dtype=torch.float16, device=dev)
 
+        ov = Md <= 64     # the decode batch prefetches its weights behind the previous launch, as the M = 1 step does
+
         def step_m():
             for i in range(FFN70B_LAYERS):
-                kernels.linear(xg, pw_g[i], out=yg)
+                kernels.linear(xg, pw_g[i], out=yg, overlap=ov)
                 if peer is not None and peer.fits(Md, Nd):
-                    kernels.linear(xd, pw_d[i], out=peer.partial(Md, Nd))
+                    kernels.linear(xd, pw_d[i], out=peer.partial(Md, Nd), overlap=ov)
                     peer.reduce(Md, Nd, out=yd)
                 else:
                     kernels.linear(xd, pw_d[i], out=yd)
