@@ -849,7 +849,7 @@ def run_ffn70b_tp(args, torch, peaks, rank, world, local_rank):
                     kernels.linear(xd, pw_d[i], out=peer.partial(Md, Nd), overlap=ov)
                     peer.reduce(Md, Nd, out=yd)
                 else:
-                    kernels.linear(xd, pw_d[i], out=yd)
+                    kernels.linear(xd, pw_d[i], out=yd, overlap=ov)
                     if world > 1:
                         dist.all_reduce(yd)
         if world > 1:
