@@ -315,7 +315,7 @@ AWQ_B200_API int awq_b200_peer_allreduce_push(const void* partial, void* const* 
  * recv / flags / slot_elems / rank / world (2..8) as for awq_b200_peer_allreduce_push, and the calls of the two entry
  * points may be mixed freely (they share the call counter), as long as every rank makes the same sequence of calls.
  * bias (this rank's, normally rank 0 only) is added to the partial before the exchange.  Waits on peers are bounded
- * (AWQ_B200_PEER_WAIT_LIMIT_WORD); on expiry the status word (AWQ_B200_PEER_STATUS_WORD) becomes 3.  M <= 4.
+ * (AWQ_B200_PEER_WAIT_LIMIT_WORD); on expiry the status word (AWQ_B200_PEER_STATUS_WORD) becomes 3.
  * Plays the part of the all-reduce that follows a row-parallel linear in the reference's tensor-parallel layers
  * (spec-decoding-src-code/eagle_ssd/ssd/layers/linear.py:195-199). */
 AWQ_B200_API int awq_b200_decode_i8_push(const void* x, const void* packed, const void* scales, const int32_t* qzeros,

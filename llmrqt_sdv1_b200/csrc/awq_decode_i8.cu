@@ -72,7 +72,6 @@ constexpr int kD8AStages = 2;
 constexpr int kD8TmemCols = 256;
 constexpr int kD8MetaSlots = 8;                    // ring of per-unit (sx, T) rows (see the helpers for why 8 is enough)
 constexpr int kD8MaxRows = 8;                      // beyond that the per-row fold costs more than the exact-weight kernel's unpack
-constexpr int kD8PushMaxRows = 4;                  // the epilogue that exchanges with the peers exists for 1..4 rows
 constexpr int kD8Range = 16256;                    // 127 * 128: largest |t|
 
 template <int MR> struct D8Cfg {
@@ -1007,7 +1006,6 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
   if (push != nullptr) {
     if (!push->recv || !push->flags) return AWQ_B200_ERR_NULL;
     if (push->world < 2 || push->world > 8 || push->rank < 0 || push->rank >= push->world) return AWQ_B200_ERR_SHAPE;
-    if (M > kD8PushMaxRows) return AWQ_B200_ERR_SHAPE;
     if (static_cast<size_t>(M) * N > push->slot_elems) return AWQ_B200_ERR_TOO_LARGE;
     if (epi.residual != nullptr || epi.gated) return AWQ_B200_ERR_SHAPE;      // the exchanged value is the plain sum
     p.recv = reinterpret_cast<unsigned char* const*>(push->recv);
@@ -1017,7 +1015,8 @@ static int decode_i8_run(const void* x, const void* packed, const void* scales, 
     p.world = push->world;
     if (M <= 1) return launch_decode_i8<1, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
     if (M <= 2) return launch_decode_i8<2, true, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
-    return launch_decode_i8<4, true, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    if (M <= 4) return launch_decode_i8<4, true, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
+    return launch_decode_i8<8, true, true>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   }
   if (M <= 1) return launch_decode_i8<1, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);
   if (M <= 2) return launch_decode_i8<2, false, false>(packed, p, grid, encode, stream, overlap, di.max_smem_optin);

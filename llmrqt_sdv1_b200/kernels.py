@@ -387,7 +387,7 @@ def peer_allreduce_push(partial: torch.Tensor, recv_dev: int, flags_dev: int, sl
 def decode_i8_push(x, pw: PackedWeight, recv_dev: int, flags_dev: int, slot_elems: int, rank: int, world: int,
                    bias=None, out=None, overlap: bool = False) -> torch.Tensor:
     """`decode_i8` on this rank's row shard with the push form of the peer exchange done by the kernel's epilogue:
-    returns the SUM over the ranks (see `sharded.PeerSum.linear_push`).  1 <= M <= 4, 2 <= world <= 8."""
+    returns the SUM over the ranks (see `sharded.PeerSum.linear_push`).  1 <= M <= 8, 2 <= world <= 8."""
     x = _check_x(x, pw)
     M = x.shape[0]
     _check_out(out, None, M, pw.N, x.device)

@@ -174,14 +174,16 @@ class PeerSum:
                                       M, N, self.rank, self.world, out=out, bias=bias)
 
     # The fused form: one to four rows of a shard whose weights are large enough for the integer decode kernel
-    # (about what that kernel needs to beat the GEMV plus a separate exchange launch).
-    FUSED_MAX_ROWS, FUSED_MIN_PACKED_BYTES = 4, 12 << 20
+    # (about what that kernel needs to beat the GEMV plus a separate exchange launch); five to eight rows from
+    # the size at which the dispatcher gives them to that kernel anyway.
+    FUSED_MAX_ROWS, FUSED_MIN_PACKED_BYTES = 8, 12 << 20
+    FUSED_MIN_PACKED_BYTES_5_TO_8 = 48 << 20
 
     def can_fuse(self, M: int, pw) -> bool:
         """Whether `linear_push` serves M rows of this packed shard (push mode, 2..8 ranks, group size >= 128)."""
+        need = self.FUSED_MIN_PACKED_BYTES if M <= 4 else self.FUSED_MIN_PACKED_BYTES_5_TO_8
         return (self.mode == "push" and 2 <= self.world <= 8 and 1 <= M <= self.FUSED_MAX_ROWS
-                and pw.group_size % 128 == 0 and pw.K * pw.N // 2 >= self.FUSED_MIN_PACKED_BYTES
-                and self.fits(M, pw.N))
+                and pw.group_size % 128 == 0 and pw.K * pw.N // 2 >= need and self.fits(M, pw.N))
 
     def linear_push(self, x2d: torch.Tensor, pw, bias=None, out: torch.Tensor | None = None,
                     overlap: bool = False) -> torch.Tensor:

@@ -213,9 +213,9 @@ def test_fused_exchange_equals_decode_then_push(K, N):
     this rank's partial in wire format; the call counter advances once per call; bias goes into the partial."""
     from llmrqt_sdv1_b200 import kernels
     pw = _packed(K, N, seed=K + N)
-    rig = _Rig(4 * N)
+    rig = _Rig(8 * N)
     epoch = 0
-    for call, M in enumerate((1, 2, 4, 3, 1)):
+    for call, M in enumerate((1, 2, 4, 3, 8, 5, 1)):
         epoch += 1
         x = _rand((M, K), 50 + call)
         bias = _rand((N,), 60 + call) if call % 2 else None
@@ -238,7 +238,7 @@ def test_fused_exchange_equals_decode_then_push(K, N):
     assert kernels.gemv_status() == 0
 
 
-@pytest.mark.parametrize("M", [1, 4])          # 4 rows: the form behind the kernel that writes the activation planes
+@pytest.mark.parametrize("M", [1, 4, 7])       # from 3 rows: the forms behind the kernel that writes the activation planes
 def test_fused_exchange_inside_a_replayed_graph(M):
     from llmrqt_sdv1_b200 import kernels
     K, N = 4096, 4096
@@ -279,11 +279,11 @@ def test_fused_exchange_inside_a_replayed_graph(M):
     assert int(rig.flags[0][35].item()) == epoch and int(rig.flags[0][STATUS].item()) == 0
 
 
-def test_fused_exchange_refuses_more_than_four_rows():
+def test_fused_exchange_refuses_more_than_eight_rows():
     pw = _packed(1024, 2048, seed=1)
-    rig = _Rig(8 * 2048)
+    rig = _Rig(16 * 2048)
     with pytest.raises(ValueError):
-        rig.fused(_rand((5, 1024), 1), pw)
+        rig.fused(_rand((9, 1024), 1), pw)
     torch.cuda.synchronize()
     assert int(rig.flags[0][35].item()) == 0 and int(rig.flags[0][STATUS].item()) == 0
 
