@@ -91,7 +91,9 @@ def _check_mode(mode, rank, world, dev, dist, quantize, PeerSum, RowParallelAWQL
             mod2 = RowParallelAWQLinear.from_local(qw, qz, sc, bias, 128)
             mod2.use_peer_sum(ps)
             pw2 = mod2.packed()
-            for M2 in (1, 4, 2):
+            ok = ok and not ps.can_fuse(6, pw2)                          # 5..8 rows: fused from 48 MiB per rank only
+            ps.FUSED_MIN_PACKED_BYTES_5_TO_8 = 12 << 20                  # (here: the 8-row form on this shard all the same)
+            for M2 in (1, 4, 2, 6, 8):
                 x2 = torch.randn((M2, K2 // world), device=dev, generator=torch.Generator(device=dev).manual_seed(20 + rank + M2)).half()
                 ok = ok and ps.can_fuse(M2, pw2)
                 mod2.fuse_exchange = True
