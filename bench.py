@@ -1021,6 +1021,15 @@ def config5_measure(torch, new_tokens=128):
                 "teacher_forced_logit_err_vs_hf": dec.teacher_forced_error(seq_ref, logits_fused)}
             out["decode_tok_s"] = out["graphed_decoder"]["decode_tok_s"]
             out["prefill_ms"] = prefill_ms
+            # the same step deep into a long context: attention over the cache split into chunks of positions
+            # (one CTA per head and chunk) against one CTA per head
+            del dec
+            long_ctx = {"max_len": 4096, "positions": [200, 1000, 4000]}
+            for name, split in (("ms_per_token", True), ("ms_per_token_one_cta_per_head", False)):
+                dec_l = GraphedDecoder(model, max_len=4096, attn_split=split)
+                long_ctx[name] = [round(dec_l.time_step_at(p), 4) for p in long_ctx["positions"]]
+                del dec_l
+            out["graphed_decoder"]["long_context"] = long_ctx
             out["share_of_step_in_awq_linears"] = out["graphed_decoder"]["share_of_step_in_awq_linears"]
         except Exception as exc:
             out["graphed_decoder"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}

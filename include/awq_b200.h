@@ -401,9 +401,16 @@ AWQ_B200_API int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weig
 /* out [H * D] fp16 = softmax(scale * q . K[0..*pos]^T) . V[0..*pos] for one query token of H heads against a cache
  * of KV heads (grouped-query attention, H % KV == 0); fp32 online softmax.  Stands in, at decode time, for the
  * attention call of the reference's attention block (attention.py:331-380), which is outside the quantized-linear
- * path; it exists so that a whole decode step is a fixed sequence of launches. */
+ * path; it exists so that a whole decode step is a fixed sequence of launches.
+ * workspace (optional, 16-byte aligned, awq_b200_attn_workspace_bytes(H, D) bytes, its first 256 * ceil(H / 64)
+ * bytes zero before the first use and left zero): with it, contexts beyond 256 positions are cut into chunks of
+ * about 128 positions (at most min(8, 148 / H) per head), one CTA per (head, chunk), whose partial results the
+ * last CTA of a head to finish adds in chunk order (deterministic); without it, or up to 256 positions, one CTA
+ * per head. */
+AWQ_B200_API size_t awq_b200_attn_workspace_bytes(int H, int D);
 AWQ_B200_API int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
-                         void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
+                         void* out, int H, int KV, int D, int max_len, float scale, void* workspace,
+                         size_t workspace_bytes, awq_b200_stream_t stream);
 
 /* y[M, D] fp16 = RMSNorm(x[M, D]) * weight[D]: fp32 arithmetic, one rounding (torch.nn.functional.rms_norm's); D even.
  * The norms between the linears of a decoder layer (LLMQRT/runtime_refact/nn_models/modules/nonlinear/
@@ -414,10 +421,12 @@ AWQ_B200_API int awq_b200_rmsnorm(const void* x, const void* weight, float eps, 
 /* awq_b200_qk_norm_rope_cache followed by awq_b200_attn_decode as ONE launch (one CTA per query head): qkv
  * [(H + 2 KV) * D] fp16 is the fused qkv linear's output row; every CTA normalises / rotates its query head and its
  * group's key head itself, attends over cache rows 0 .. *pos - 1 plus the fresh key / value, and the first CTA of a
- * group appends the fresh key / value to row *pos of the caches.  out [H * D] fp16; same bits as the two calls. */
+ * group appends the fresh key / value to row *pos of the caches.  out [H * D] fp16; same bits as the two calls
+ * (given the same workspace choice; workspace as for awq_b200_attn_decode). */
 AWQ_B200_API int awq_b200_attn_step(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                        const void* cos_tab, const void* sin_tab, const int64_t* pos, void* k_cache, void* v_cache,
-                       void* out, int H, int KV, int D, int max_len, float scale, awq_b200_stream_t stream);
+                       void* out, int H, int KV, int D, int max_len, float scale, void* workspace,
+                       size_t workspace_bytes, awq_b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * The reference extension's other quantized linears: FP8 (e4m3) and SmoothQuant INT8, 8-bit x 8-bit GEMMs with a

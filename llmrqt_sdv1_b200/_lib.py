@@ -55,9 +55,10 @@ SIGNATURES = {
     "awq_b200_linear_fused": (_I, _COMPUTE + [C.c_uint]),   # 5th argument: const awq_b200_epilogue*
     "awq_b200_interleave_columns": (_I, [_P, _P, _P, _I, _I, _P]),
     "awq_b200_qk_norm_rope_cache": (_I, [_P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
-    "awq_b200_attn_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P]),
+    "awq_b200_attn_workspace_bytes": (_Z, [_I, _I]),
+    "awq_b200_attn_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P, _Z, _P]),
     "awq_b200_rmsnorm": (_I, [_P, _P, C.c_float, _P, _I, _I, _P]),
-    "awq_b200_attn_step": (_I, [_P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P]),
+    "awq_b200_attn_step": (_I, [_P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, C.c_float, _P, _Z, _P]),
     "awq_b200_q8_splits": (_I, [_I, _I, _I]),
     "awq_b200_fp8_gemm_tensorwise": (_I, [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, C.c_float, _P, _P, C.c_float, _I, C.c_uint, _P, _P]),
     "awq_b200_fp8_gemm_rowwise": (_I, [_P, _I, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, C.c_uint, _P, _P]),

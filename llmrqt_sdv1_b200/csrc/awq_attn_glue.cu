@@ -92,11 +92,112 @@ __device__ __forceinline__ void load_row(const __half* p, float (&f)[V]) {
   }
 }
 
+// Long contexts: beyond kAttnSplitFrom positions the cached positions of a head are cut into chunks of about
+// kAttnChunk positions (whole batches of all warps; longer ones when the launch has too few CTAs per head), one
+// CTA per (head, chunk) - gridDim.y CTAs per head are launched, those beyond the chunks of the current position
+// leave at once.  A chunk's CTA writes its running maximum, sum and weighted values to the workspace and draws a
+// ticket; the CTA that draws the last ticket of its head adds the chunks in chunk order and writes the output
+// (deterministic; the counter is left at zero).  Up to kAttnSplitFrom positions there is one chunk, no workspace
+// traffic and no ticket: the arithmetic of the unsplit kernel (a ticket costs about what 100 positions do).
+constexpr int kAttnSplitFrom = 256;
+constexpr int kAttnChunk = 128;
+constexpr int kAttnMaxSplits = 8;
+
+struct AttnSplit {
+  float* part;          // [H][gridDim.y][2 + D]: maximum, sum, weighted values of a chunk; nullptr: never split
+  unsigned* counters;   // [H], zero between launches
+};
+
+// Chunk c of n = pos + 1 positions: [lo, hi]; returns the number of chunks (c >= chunks: nothing to do).
+__device__ __forceinline__ int attn_chunk(long long n64, int max_splits, int c, long long* lo, long long* hi) {
+  constexpr int kStep = kAttnWarps * kAttnBatch;
+  const int n = static_cast<int>(n64);                       // n <= max_len, an int
+  if (n <= kAttnSplitFrom || max_splits <= 1) {
+    *lo = 0;
+    *hi = n - 1;
+    return 1;
+  }
+  int chunks = (n + kAttnChunk - 1) / kAttnChunk;
+  if (chunks > max_splits) chunks = max_splits;
+  int len = (n + chunks - 1) / chunks;
+  len = (len + kStep - 1) / kStep * kStep;
+  chunks = (n + len - 1) / len;
+  *lo = static_cast<long long>(c) * len;
+  *hi = (c + 1) * len - 1 < n - 1 ? (c + 1) * len - 1 : n - 1;
+  return chunks;
+}
+
+// Warp 0 of a chunk's CTA: one chunk -> the output row; several -> the partial, a ticket, and for the last ticket
+// of the head the sum over the chunks.
+template <int V>
+__device__ __forceinline__ void attn_finish(const AttnSplit& sp, int head, int chunk, int chunks, int lane, float M, float L,
+                                            const float (&o)[V], __half* __restrict__ out) {
+  constexpr int D = 32 * V;
+  if (chunks == 1) {
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[static_cast<size_t>(head) * D + lane * V + i] = __float2half_rn(o[i] * inv);
+    return;
+  }
+  const int S = static_cast<int>(gridDim.y);
+  float* mine = sp.part + (static_cast<size_t>(head) * S + chunk) * (D + 2);
+  if (lane == 0) { __stcg(mine, M); __stcg(mine + 1, L); }
+#pragma unroll
+  for (int i = 0; i < V; ++i) __stcg(mine + 2 + lane * V + i, o[i]);
+  __threadfence();
+  __syncwarp();
+  unsigned ticket = 0u;
+  if (lane == 0) ticket = atomicAdd(sp.counters + head, 1u);
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
+  if (ticket != static_cast<unsigned>(chunks - 1)) return;
+  __threadfence();
+  // Eight chunks at a time: their loads first (one memory latency for the lot), then the sums in chunk order
+  // under a running maximum.
+  const float* base = sp.part + static_cast<size_t>(head) * S * (D + 2);
+  constexpr int kGroup = 8;
+  float Mt = -INFINITY, Lt = 0.f, ot[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) ot[i] = 0.f;
+  for (int c0 = 0; c0 < chunks; c0 += kGroup) {
+    float Mc[kGroup], Lc[kGroup], oc[kGroup][V];
+#pragma unroll
+    for (int c = 0; c < kGroup; ++c) {
+      const float* pc = base + static_cast<size_t>(c0 + c < chunks ? c0 + c : c0) * (D + 2);
+      Mc[c] = __ldcg(pc);
+      Lc[c] = __ldcg(pc + 1);
+#pragma unroll
+      for (int i = 0; i < V; ++i) oc[c][i] = __ldcg(pc + 2 + lane * V + i);
+    }
+    float Mn = Mt;
+#pragma unroll
+    for (int c = 0; c < kGroup; ++c)
+      if (c0 + c < chunks) Mn = fmaxf(Mn, Mc[c]);
+    const float corr = __expf(Mt - Mn);                            // Mn is finite: every chunk holds a position
+    Lt *= corr;
+#pragma unroll
+    for (int i = 0; i < V; ++i) ot[i] *= corr;
+#pragma unroll
+    for (int c = 0; c < kGroup; ++c) {
+      if (c0 + c < chunks) {                                       // warp-uniform
+        const float f = __expf(Mc[c] - Mn);
+        Lt = fmaf(Lc[c], f, Lt);
+#pragma unroll
+        for (int i = 0; i < V; ++i) ot[i] = fmaf(oc[c][i], f, ot[i]);
+      }
+    }
+    Mt = Mn;
+  }
+  const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) out[static_cast<size_t>(head) * D + lane * V + i] = __float2half_rn(ot[i] * inv);
+  if (lane == 0) sp.counters[head] = 0u;     // every chunk has drawn its ticket: leave the counter clean
+}
+
 template <int V>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
                    const long long* __restrict__ pos_ptr, __half* __restrict__ out, int H, int KV, int max_len,
-                   float scale) {
+                   float scale, AttnSplit sp) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   static_assert(V == 2 || V == 4, "head dimension 64 or 128");
@@ -108,6 +209,10 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
   const int kv = head / (H / KV);
   long long pos = *pos_ptr;
   if (pos >= max_len) pos = max_len - 1;
+  if (pos < 0) pos = 0;
+  long long lo, hi;
+  const int chunks = attn_chunk(pos + 1, static_cast<int>(gridDim.y), static_cast<int>(blockIdx.y), &lo, &hi);
+  if (static_cast<int>(blockIdx.y) >= chunks) return;              // CTA-uniform
   float qf[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) qf[i] = __half2float(q[static_cast<size_t>(head) * D + lane * V + i]) * scale;
@@ -116,44 +221,89 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
   float m = -INFINITY, l = 0.f, acc[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) acc[i] = 0.f;
-  for (long long j0 = static_cast<long long>(warp) * B; j0 <= pos; j0 += W * B) {
-    float kf[B][V], vf[B][V];
+  if (chunks == 1) {
+    // The whole context in this CTA (always so up to kAttnSplitFrom positions).  The loop is written out a
+    // second time with the chunk's bounds below: with lo / hi as its bounds the compiler schedules this loop
+    // worse (one CTA per head: 26 instead of 17 us at 1000 positions), and short contexts are the common case.
+    for (long long j0 = static_cast<long long>(warp) * B; j0 <= pos; j0 += W * B) {
+      float kf[B][V], vf[B][V];
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const long long j = (j0 + b <= pos) ? j0 + b : pos;        // a repeated row past the end; masked out below
-      load_row<V>(kb + j * D, kf[b]);
-      load_row<V>(vb + j * D, vf[b]);
+      for (int b = 0; b < B; ++b) {
+        const long long j = (j0 + b <= pos) ? j0 + b : pos;        // a repeated row past the end; masked out below
+        load_row<V>(kb + j * D, kf[b]);
+        load_row<V>(vb + j * D, vf[b]);
+      }
+      float s[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        s[b] = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
+      }
+      float m_new = m;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (j0 + b > pos) s[b] = -INFINITY;
+        m_new = fmaxf(m_new, s[b]);
+      }
+      const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
+        l += pj;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
+      }
+      m = m_new;
     }
-    float s[B];
+  } else {
+    for (long long j0 = lo + static_cast<long long>(warp) * B; j0 <= hi; j0 += W * B) {
+      float kf[B][V], vf[B][V];
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-      s[b] = 0.f;
+      for (int b = 0; b < B; ++b) {
+        const long long j = (j0 + b <= hi) ? j0 + b : hi;        // a repeated row past the end; masked out below
+        load_row<V>(kb + j * D, kf[b]);
+        load_row<V>(vb + j * D, vf[b]);
+      }
+      float s[B];
 #pragma unroll
-      for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+      for (int b = 0; b < B; ++b) {
+        s[b] = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
+      }
+      float m_new = m;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (j0 + b > hi) s[b] = -INFINITY;
+        m_new = fmaxf(m_new, s[b]);
+      }
+      const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
+        l += pj;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
+      }
+      m = m_new;
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
-    }
-    float m_new = m;
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      if (j0 + b > pos) s[b] = -INFINITY;
-      m_new = fmaxf(m_new, s[b]);
-    }
-    const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
-    l *= corr;
-#pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] *= corr;
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
-      l += pj;
-#pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
-    }
-    m = m_new;
   }
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll
@@ -173,9 +323,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_ca
 #pragma unroll
       for (int i = 0; i < V; ++i) o[i] = fmaf(s_acc[w][lane * V + i], c, o[i]);
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-#pragma unroll
-    for (int i = 0; i < V; ++i) out[static_cast<size_t>(head) * D + lane * V + i] = __float2half_rn(o[i] * inv);
+    attn_finish<V>(sp, head, static_cast<int>(blockIdx.y), chunks, lane, M, L, o, out);
   }
 }
 
@@ -221,7 +369,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_weight, const __half* __restrict__ k_weight,
                  float eps, const __half* __restrict__ cos_tab, const __half* __restrict__ sin_tab,
                  const long long* __restrict__ pos_ptr, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
-                 __half* __restrict__ out, int H, int KV, int max_len, float scale) {
+                 __half* __restrict__ out, int H, int KV, int max_len, float scale, AttnSplit sp) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may start its own prefetch
   asm volatile("griddepcontrol.wait;" ::: "memory");
   static_assert(V == 2 || V == 4, "head dimension 64 or 128");
@@ -235,6 +383,9 @@ attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_we
   const int kv = head / group;
   const long long pos = *pos_ptr;
   if (pos < 0 || pos >= max_len) return;              // out of range: leave everything untouched (CTA-uniform)
+  long long lo, hi;
+  const int chunks = attn_chunk(pos + 1, static_cast<int>(gridDim.y), static_cast<int>(blockIdx.y), &lo, &hi);
+  if (static_cast<int>(blockIdx.y) >= chunks) return;              // CTA-uniform
   if (warp < 3) {
     const __half* cs = cos_tab + static_cast<size_t>(pos) * D;
     const __half* sn = sin_tab + static_cast<size_t>(pos) * D;
@@ -250,7 +401,7 @@ attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_we
       __half* keep = is_k ? s_k : s_v;
 #pragma unroll
       for (int i = 0; i < V; ++i) keep[lane * V + i] = o[i];
-      if (head == kv * group) {                          // one CTA per group appends to the cache
+      if (head == kv * group && blockIdx.y == 0) {       // one CTA per group appends to the cache
         __half* dst = (is_k ? k_cache : v_cache) + (static_cast<size_t>(kv) * max_len + pos) * D + lane * V;
 #pragma unroll
         for (int i = 0; i < V; ++i) dst[i] = o[i];
@@ -270,49 +421,99 @@ attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_we
   float m = -INFINITY, l = 0.f, acc[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) acc[i] = 0.f;
-  for (long long j0 = static_cast<long long>(warp) * B; j0 <= pos; j0 += W * B) {
-    float kf[B][V], vf[B][V];
+  if (chunks == 1) {
+    // The whole context in this CTA (always so up to kAttnSplitFrom positions).  The loop is written out a
+    // second time with the chunk's bounds below: with lo / hi as its bounds the compiler schedules this loop
+    // worse (one CTA per head: 26 instead of 17 us at 1000 positions), and short contexts are the common case.
+    for (long long j0 = static_cast<long long>(warp) * B; j0 <= pos; j0 += W * B) {
+      float kf[B][V], vf[B][V];
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const long long j = j0 + b;
-      if (j < pos) {                                              // warp-uniform
-        load_row<V>(kb + j * D, kf[b]);
-        load_row<V>(vb + j * D, vf[b]);
-      } else {                                                    // the fresh row (and the masked slots behind it)
+      for (int b = 0; b < B; ++b) {
+        const long long j = j0 + b;
+        if (j < pos) {                                              // warp-uniform
+          load_row<V>(kb + j * D, kf[b]);
+          load_row<V>(vb + j * D, vf[b]);
+        } else {                                                    // the fresh row (and the masked slots behind it)
 #pragma unroll
-        for (int i = 0; i < V; ++i) { kf[b][i] = knew[i]; vf[b][i] = vnew[i]; }
+          for (int i = 0; i < V; ++i) { kf[b][i] = knew[i]; vf[b][i] = vnew[i]; }
+        }
       }
+      float s[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        s[b] = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
+      }
+      float m_new = m;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (j0 + b > pos) s[b] = -INFINITY;
+        m_new = fmaxf(m_new, s[b]);
+      }
+      const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
+        l += pj;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
+      }
+      m = m_new;
     }
-    float s[B];
+  } else {
+    for (long long j0 = lo + static_cast<long long>(warp) * B; j0 <= hi; j0 += W * B) {
+      float kf[B][V], vf[B][V];
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-      s[b] = 0.f;
+      for (int b = 0; b < B; ++b) {
+        const long long j = j0 + b;
+        if (j < pos) {                                              // warp-uniform
+          load_row<V>(kb + j * D, kf[b]);
+          load_row<V>(vb + j * D, vf[b]);
+        } else {                                                    // the fresh row (and the masked slots behind it)
 #pragma unroll
-      for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+          for (int i = 0; i < V; ++i) { kf[b][i] = knew[i]; vf[b][i] = vnew[i]; }
+        }
+      }
+      float s[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        s[b] = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) s[b] = fmaf(qf[i], kf[b][i], s[b]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
+      }
+      float m_new = m;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        if (j0 + b > hi) s[b] = -INFINITY;
+        m_new = fmaxf(m_new, s[b]);
+      }
+      const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] *= corr;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
+        l += pj;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
+      }
+      m = m_new;
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int b = 0; b < B; ++b) s[b] += __shfl_xor_sync(0xffffffffu, s[b], off);
-    }
-    float m_new = m;
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      if (j0 + b > pos) s[b] = -INFINITY;
-      m_new = fmaxf(m_new, s[b]);
-    }
-    const float corr = __expf(m - m_new);                        // m_new is finite: position j0 is valid
-    l *= corr;
-#pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] *= corr;
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      const float pj = __expf(s[b] - m_new);                     // 0 for masked positions
-      l += pj;
-#pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] = fmaf(pj, vf[b][i], acc[i]);
-    }
-    m = m_new;
   }
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll
@@ -332,9 +533,7 @@ attn_step_kernel(const __half* __restrict__ qkv, const __half* __restrict__ q_we
 #pragma unroll
       for (int i = 0; i < V; ++i) o[i] = fmaf(s_acc[w][lane * V + i], c, o[i]);
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-#pragma unroll
-    for (int i = 0; i < V; ++i) out[static_cast<size_t>(head) * D + lane * V + i] = __float2half_rn(o[i] * inv);
+    attn_finish<V>(sp, head, static_cast<int>(blockIdx.y), chunks, lane, M, L, o, out);
   }
 }
 
@@ -413,9 +612,37 @@ static int launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream
   return AWQ_B200_OK;
 }
 
+// Workspace of the attention kernels: [0, 256 * ceil(H / 64)) arrival counters (zero before the first use, left
+// zero), then the chunks' partial results.  CTAs per head: what one wave of one 512-thread CTA per SM holds (their
+// registers allow one per SM; with two, capped at 64 registers, the position loop ran 15-40 % slower), at most 8.
+static int attn_splits(int H) {
+  int s = 148 / H;
+  if (s < 1) s = 1;
+  if (s > kAttnMaxSplits) s = kAttnMaxSplits;
+  return s;
+}
+static size_t attn_counter_bytes(int H) { return (static_cast<size_t>(H) * sizeof(unsigned) + 255) / 256 * 256; }
+static size_t attn_workspace_bytes(int H, int D) {
+  return attn_counter_bytes(H) + static_cast<size_t>(H) * attn_splits(H) * (D + 2) * sizeof(float);
+}
+// The split a launch uses: none without a workspace of that size.
+static int attn_split_of(void* workspace, size_t workspace_bytes, int H, int D, AttnSplit* sp) {
+  sp->part = nullptr;
+  sp->counters = nullptr;
+  if (workspace == nullptr || workspace_bytes < attn_workspace_bytes(H, D)) return 1;
+  sp->counters = static_cast<unsigned*>(workspace);
+  sp->part = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + attn_counter_bytes(H));
+  return attn_splits(H);
+}
+
 }  // namespace awq
 
 extern "C" {
+
+size_t awq_b200_attn_workspace_bytes(int H, int D) {
+  if (H < 1 || (D != 64 && D != 128)) return 0;
+  return awq::attn_workspace_bytes(H, D);
+}
 
 int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weight, const void* k_weight, float eps,
                                 const void* cos_tab, const void* sin_tab, const int64_t* pos, void* q_out,
@@ -438,34 +665,42 @@ int awq_b200_qk_norm_rope_cache(const void* qkv, const void* q_weight, const voi
 }
 
 int awq_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int H,
-                         int KV, int D, int max_len, float scale, awq_b200_stream_t stream) {
+                         int KV, int D, int max_len, float scale, void* workspace, size_t workspace_bytes,
+                         awq_b200_stream_t stream) {
   using namespace awq;
   if (!q || !k_cache || !v_cache || !pos || !out) return AWQ_B200_ERR_NULL;
   if (H < 1 || KV < 1 || H % KV != 0 || max_len < 1 || (D != 64 && D != 128)) return AWQ_B200_ERR_SHAPE;
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u)) return AWQ_B200_ERR_ALIGN;
+  AttnSplit sp;
+  const dim3 grid(H, attn_split_of(workspace, workspace_bytes, H, D, &sp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const __half *qq = static_cast<const __half*>(q), *kc = static_cast<const __half*>(k_cache);
   const __half* vc = static_cast<const __half*>(v_cache);
   const long long* pp = reinterpret_cast<const long long*>(pos);
   __half* o = static_cast<__half*>(out);
-  if (D == 128) return launch_pdl(attn_decode_kernel<4>, dim3(H), dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale);
-  return launch_pdl(attn_decode_kernel<2>, dim3(H), dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale);
+  if (D == 128) return launch_pdl(attn_decode_kernel<4>, grid, dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale, sp);
+  return launch_pdl(attn_decode_kernel<2>, grid, dim3(kAttnWarps * 32), s, qq, kc, vc, pp, o, H, KV, max_len, scale, sp);
 }
 
 int awq_b200_attn_step(const void* qkv, const void* q_weight, const void* k_weight, float eps, const void* cos_tab,
                        const void* sin_tab, const int64_t* pos, void* k_cache, void* v_cache, void* out, int H, int KV,
-                       int D, int max_len, float scale, awq_b200_stream_t stream) {
+                       int D, int max_len, float scale, void* workspace, size_t workspace_bytes,
+                       awq_b200_stream_t stream) {
   using namespace awq;
   if (!qkv || !cos_tab || !sin_tab || !pos || !k_cache || !v_cache || !out) return AWQ_B200_ERR_NULL;
   if ((q_weight == nullptr) != (k_weight == nullptr)) return AWQ_B200_ERR_NULL;
   if (H < 1 || KV < 1 || H % KV != 0 || max_len < 1 || (D != 64 && D != 128)) return AWQ_B200_ERR_SHAPE;
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u)) return AWQ_B200_ERR_ALIGN;
+  AttnSplit sp;
+  const dim3 grid(H, attn_split_of(workspace, workspace_bytes, H, D, &sp));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const __half* a = static_cast<const __half*>(qkv);
   const __half *qw = static_cast<const __half*>(q_weight), *kw = static_cast<const __half*>(k_weight);
   const __half *ct = static_cast<const __half*>(cos_tab), *st = static_cast<const __half*>(sin_tab);
   const long long* pp = reinterpret_cast<const long long*>(pos);
   __half *kc = static_cast<__half*>(k_cache), *vc = static_cast<__half*>(v_cache), *o = static_cast<__half*>(out);
-  if (D == 128) return launch_pdl(attn_step_kernel<4>, dim3(H), dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale);
-  return launch_pdl(attn_step_kernel<2>, dim3(H), dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale);
+  if (D == 128) return launch_pdl(attn_step_kernel<4>, grid, dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale, sp);
+  return launch_pdl(attn_step_kernel<2>, grid, dim3(kAttnWarps * 32), s, a, qw, kw, eps, ct, st, pp, kc, vc, o, H, KV, max_len, scale, sp);
 }
 
 int awq_b200_rmsnorm(const void* x, const void* weight, float eps, void* y, int M, int D, awq_b200_stream_t stream) {

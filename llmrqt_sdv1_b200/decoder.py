@@ -47,7 +47,9 @@ def _call_linear(mod: nn.Module, x: torch.Tensor, residual: torch.Tensor | None 
 
 
 class GraphedDecoder:
-    def __init__(self, model: nn.Module, max_len: int, capture: bool | None = None):
+    def __init__(self, model: nn.Module, max_len: int, capture: bool | None = None, attn_split: bool | None = None):
+        """`attn_split`: let the attention launch cut long contexts into chunks of positions, one CTA each (None:
+        when `max_len` exceeds 512; a launch with chunk CTAs costs 0.1-0.2 us more at short contexts)."""
         core = model.model
         self.model, self.core = model, core
         self.layers = list(core.layers)
@@ -55,6 +57,7 @@ class GraphedDecoder:
         self.n_heads, self.n_kv = cfg.num_attention_heads, cfg.num_key_value_heads
         self.head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
         self.max_len = int(max_len)
+        self._attn_split = (self.max_len > 512) if attn_split is None else bool(attn_split)
         emb = core.embed_tokens.weight
         self.device, self.dtype = emb.device, emb.dtype
         dev = self.device
@@ -171,7 +174,8 @@ class GraphedDecoder:
                 # q/k norm + rope + cache append + attention of the one new token: one launch
                 kernels.attn_step(qkv, qw, kw, eps, self.cos_tab, self.sin_tab, pos, self.k_cache[li], self.v_cache[li],
                                   self._attn_buf,
-                                  layer.self_attn.scaling if hasattr(layer.self_attn, "scaling") else self.head_dim ** -0.5)
+                                  layer.self_attn.scaling if hasattr(layer.self_attn, "scaling") else self.head_dim ** -0.5,
+                                  split=self._attn_split)
                 h = self._layer_tail(layer, h, self._attn_buf)
                 continue
             q, k, v = self._qk_norm_rope(li, qkv, cos, sin_signed)
@@ -243,6 +247,29 @@ class GraphedDecoder:
         return self.out_tokens[:, :S + new_tokens].clone()
 
     # ------------------------------------------------------------------ measurements used by the benchmark
+    @torch.no_grad()
+    def time_step_at(self, position: int, iters: int = 20) -> float:
+        """ms per token of the decode step with `position` tokens in the cache (whatever the cache holds): device
+        time of the captured step alone, the position put back before every replay.  The generation state (token,
+        position, output tokens) is restored afterwards; cache row `position` is overwritten."""
+        if not 0 <= position < self.max_len - 1:
+            raise ValueError(f"position {position} outside the decoder's cache of {self.max_len}")
+        self._ensure_graph()
+        saved = (self.token.clone(), self.pos.clone(), self.out_tokens.clone())
+        run = self.graph.replay if self.graph is not None else self._step
+        total = 0.0
+        for it in range(iters + 3):
+            self.pos.fill_(position)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            run()
+            b.record()
+            b.synchronize()
+            if it >= 3:
+                total += a.elapsed_time(b)
+        self.token.copy_(saved[0]); self.pos.copy_(saved[1]); self.out_tokens.copy_(saved[2])
+        return total / iters
+
     @torch.no_grad()
     def teacher_forced_error(self, seq: torch.Tensor, logits_ref: torch.Tensor) -> float:
         """max |logits - logits_ref| / max |logits_ref| with `seq` fed as it is (no cache effects)."""

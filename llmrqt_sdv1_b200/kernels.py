@@ -422,8 +422,19 @@ def qk_norm_rope_cache(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, q_ou
         torch.cuda.current_stream(dev).cuda_stream), "awq_b200_qk_norm_rope_cache")
 
 
-def attn_decode(q, k_cache, v_cache, pos, out, scale: float) -> None:
-    """`out` [H * D] = attention of one query token `q` [H, D] over rows 0..pos of the caches [KV, max_len, D]."""
+def _attn_workspace(dev, H: int, D: int, split: bool):
+    """(pointer, bytes) of the per-stream scratch of the attention kernels; (None, 0) makes them never split."""
+    if not split:
+        return None, 0
+    need = lib.awq_b200_attn_workspace_bytes(H, D)
+    ws = _workspace(dev, torch.cuda.current_stream(dev).cuda_stream, need, "awq_b200_attn")
+    return ws.data_ptr(), ws.numel()
+
+
+def attn_decode(q, k_cache, v_cache, pos, out, scale: float, split: bool = True) -> None:
+    """`out` [H * D] = attention of one query token `q` [H, D] over rows 0..pos of the caches [KV, max_len, D].
+    `split=False`: one CTA per head whatever the position (beyond 256 positions the default cuts the positions
+    into chunks, one CTA each)."""
     KV, max_len, D = k_cache.shape[-3], k_cache.shape[-2], k_cache.shape[-1]
     H = q.numel() // D
     for t in (q, k_cache, v_cache, out):
@@ -432,8 +443,10 @@ def attn_decode(q, k_cache, v_cache, pos, out, scale: float) -> None:
     if out.numel() != H * D or v_cache.shape != k_cache.shape or pos.dtype != torch.int64:
         raise ValueError("attn_decode: inconsistent shapes")
     dev = _prep(q, k_cache, v_cache, pos, out)
+    ws, ws_bytes = _attn_workspace(dev, H, D, split)
     check(lib.awq_b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(),
-                                   H, KV, D, max_len, float(scale), torch.cuda.current_stream(dev).cuda_stream),
+                                   H, KV, D, max_len, float(scale), ws, ws_bytes,
+                                   torch.cuda.current_stream(dev).cuda_stream),
           "awq_b200_attn_decode")
 
 
@@ -453,9 +466,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return y
 
 
-def attn_step(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, k_cache, v_cache, out, scale: float) -> None:
+def attn_step(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, k_cache, v_cache, out, scale: float,
+              split: bool = True) -> None:
     """`qk_norm_rope_cache` + `attn_decode` in one launch: the fused qkv row in, the attention output [H * D] out,
-    row `pos` of the caches appended.  Same bits as the two calls."""
+    row `pos` of the caches appended.  Same bits as the two calls (with the same `split`)."""
     KV, max_len, D = k_cache.shape[-3], k_cache.shape[-2], k_cache.shape[-1]
     H = out.numel() // D
     for t in (qkv, cos_tab, sin_tab, out, k_cache, v_cache):
@@ -466,11 +480,12 @@ def attn_step(qkv, q_weight, k_weight, eps, cos_tab, sin_tab, pos, k_cache, v_ca
     if tuple(cos_tab.shape) != (max_len, D) or tuple(sin_tab.shape) != (max_len, D):
         raise ValueError(f"rotary tables must be [{max_len}, {D}]")
     dev = _prep(qkv, cos_tab, sin_tab, pos, out, k_cache, v_cache)
+    ws, ws_bytes = _attn_workspace(dev, H, D, split)
     check(lib.awq_b200_attn_step(
         qkv.data_ptr(), q_weight.data_ptr() if q_weight is not None else None,
         k_weight.data_ptr() if k_weight is not None else None, float(eps), cos_tab.data_ptr(), sin_tab.data_ptr(),
         pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), H, KV, D, max_len, float(scale),
-        torch.cuda.current_stream(dev).cuda_stream), "awq_b200_attn_step")
+        ws, ws_bytes, torch.cuda.current_stream(dev).cuda_stream), "awq_b200_attn_step")
 
 
 def gemv_status(dev: torch.device | None = None) -> int:

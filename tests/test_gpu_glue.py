@@ -82,13 +82,45 @@ def test_attn_decode(H, KV, D):
         assert err <= 2e-3, (p, float(err))
 
 
+@pytest.mark.parametrize("H,KV,D", [(16, 8, 128), (64, 8, 128), (8, 8, 64), (4, 4, 128)])
+def test_attn_decode_long_context_in_chunks(H, KV, D):
+    """Beyond 256 positions the cached positions are cut into chunks, one CTA per (head, chunk), merged by the
+    last CTA of a head: against torch's attention, against the one-CTA-per-head form, run to run identical, and
+    identical to it up to 256 positions."""
+    from llmrqt_sdv1_b200 import kernels
+    max_len = 4200
+    k_cache, v_cache = _rand((KV, max_len, D), 15), _rand((KV, max_len, D), 16)
+    q = _rand((H, D), 17, 2.0)
+    out = torch.empty((H * D,), dtype=torch.float16, device="cuda")
+    one = torch.empty_like(out)
+    scale = D ** -0.5
+    for p in (0, 200, 255, 256, 257, 511, 512, 1000, 1023, 1024, 2049, 4095, max_len - 1):
+        pos = torch.tensor([p], dtype=torch.long, device="cuda")
+        kernels.attn_decode(q, k_cache, v_cache, pos, out, scale)
+        kernels.attn_decode(q, k_cache, v_cache, pos, one, scale, split=False)
+        ref = F.scaled_dot_product_attention(q.view(1, H, 1, D).float(), k_cache[None, :, :p + 1].float(),
+                                             v_cache[None, :, :p + 1].float(), enable_gqa=(H != KV), scale=scale)
+        scale_ref = ref.abs().max()
+        assert (out.view(H, D).float() - ref.view(H, D)).abs().max() / scale_ref <= 2e-3, p
+        assert (one.view(H, D).float() - ref.view(H, D)).abs().max() / scale_ref <= 2e-3, p
+        if p < 256:
+            assert torch.equal(out, one), p
+        again = torch.empty_like(out)
+        kernels.attn_decode(q, k_cache, v_cache, pos, again, scale)
+        assert torch.equal(out, again), p
+    # the arrival counters are left at zero
+    ws = kernels._workspaces[(0, torch.cuda.current_stream().cuda_stream, "awq_b200_attn")]
+    torch.cuda.synchronize()
+    assert not ws[:256].any()
+
+
 @pytest.mark.parametrize("H,KV,D,with_norm", [(16, 8, 128, True), (32, 8, 128, False), (8, 2, 64, True), (4, 4, 128, True)])
 def test_attn_step_equals_the_two_kernel_sequence(H, KV, D, with_norm):
     """`awq_b200_attn_step` (one launch per layer) against `qk_norm_rope_cache` followed by `attn_decode`: the same
     output bits and the same cache contents, token after token, including position 0 and the last cache row; a
     position outside the cache changes nothing."""
     from llmrqt_sdv1_b200 import kernels
-    max_len, eps, scale = 160, 1e-6, D ** -0.5
+    max_len, eps, scale = 1400, 1e-6, D ** -0.5
     qw, kw = (_rand((D,), 2, 0.3) + 1.0, _rand((D,), 3, 0.3) + 1.0) if with_norm else (None, None)
     inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
     ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
@@ -98,7 +130,7 @@ def test_attn_step_equals_the_two_kernel_sequence(H, KV, D, with_norm):
     q_buf = torch.empty((H, D), dtype=torch.float16, device="cuda")
     out_a = torch.empty((H * D,), dtype=torch.float16, device="cuda")
     out_b = torch.empty_like(out_a)
-    for step, p in enumerate([0, 1, 2, 3, 4, 63, 64, 65, 128, max_len - 1]):
+    for step, p in enumerate([0, 1, 2, 3, 4, 63, 64, 65, 128, 255, 256, 257, 700, 1024, max_len - 1]):
         pos = torch.tensor([p], dtype=torch.long, device="cuda")
         qkv = _rand((1, 1, (H + 2 * KV) * D), 10 + step)
         kernels.qk_norm_rope_cache(qkv, qw, kw, eps, cos, sin, pos, q_buf, caches[0][0], caches[0][1])

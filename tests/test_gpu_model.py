@@ -147,3 +147,18 @@ def test_graphed_decoder_all_28_layers():
         if a != b:
             assert float(margin[i]) <= 2 * err, f"token {i} differs although the reference margin is clear"
             break
+
+    # a long context: the attention launch with the cached positions cut into chunks (one CTA per head and chunk)
+    # against one CTA per head - the first decode step after the same 700-token prefill
+    long_prompt = torch.randint(0, 151936, (1, 700), device="cuda", generator=g)
+    chunks = GraphedDecoder(model, max_len=1024)
+    one_cta = GraphedDecoder(model, max_len=1024, attn_split=False)
+    assert chunks._attn_split and not one_cta._attn_split and not graphed._attn_split
+    s1, s2 = chunks.generate(long_prompt, 2), one_cta.generate(long_prompt, 2)
+    torch.cuda.synchronize()
+    l1, l2 = chunks._graph_logits.float(), one_cta._graph_logits.float()
+    assert torch.equal(s1[:, :701], s2[:, :701])
+    assert float((l1 - l2).abs().max() / l2.abs().max()) <= 1e-2      # last-bit differences of 28 attention outputs, compounded
+    assert chunks.time_step_at(900, iters=3) > 0.0
+    assert torch.equal(chunks.generate(long_prompt, 2), s1)           # the timing hook restored the state
+    assert kernels.gemm_status() == 0 and kernels.gemv_status() == 0
