@@ -329,12 +329,7 @@ __global__ void __launch_bounds__((W + 1) * 32, W == 8 ? 2 : 1) gemv_stream_kern
               const int row = i / pairs;
               const int col = col0 + 2 * (i - row * pairs);
               const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
-              float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
-              for (int s = 1; s < nc; ++s) {
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * slot_stride));
-                sum.x += v.x;
-                sum.y += v.y;
-              }
+              const float2 sum = sum_partial_slots(src, slot_stride, nc);
               variant_store_pair(p, fusion, row, col, sum.x, sum.y);
             }
           }

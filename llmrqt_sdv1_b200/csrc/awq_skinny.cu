@@ -381,12 +381,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             const int row = i / pairs;
             const int col = n0 + 2 * (i - row * pairs);
             const float* src = p.partial + static_cast<size_t>(row) * p.N + col;
-            float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
-            for (int s = 1; s < nc; ++s) {
-              const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * slot_stride));
-              sum.x += v.x;
-              sum.y += v.y;
-            }
+            const float2 sum = sum_partial_slots(src, slot_stride, nc);
             epilogue_store_pair(p.y, p.epi, row, p.N, col, sum.x, sum.y);
           }
         }
