@@ -159,16 +159,18 @@ __host__ __device__ inline int stream_cta_of(long long u, long long U, long long
 __device__ __forceinline__ uint32_t half_bits_x2(uint16_t h) { return static_cast<uint32_t>(h) * 0x00010001u; }
 
 // The fp32 partial sums of one output pair in the nc slots of its contributors, added in slot (= k) order.  The
-// loads go out eight at a time before the first of them is used: a loop that adds each value as it arrives pays one
-// memory latency per slot, which is what a tile shared by 9 or 10 CTAs (tensor-parallel shards) would wait for.
+// The loads go out eight at a time before the first of them is used: a loop that adds each value as it arrives pays
+// one memory latency per slot (tiles shared by 9..16 CTAs: 3-16 % of a launch of the exact-weight kernel).
 __device__ __forceinline__ float2 sum_partial_slots(const float* src, size_t slot_stride, int nc) {
   constexpr int kBatch = 8;
   float2 sum = __ldcg(reinterpret_cast<const float2*>(src));
   for (int s0 = 1; s0 < nc; s0 += kBatch) {
     float2 v[kBatch];
 #pragma unroll
-    for (int j = 0; j < kBatch; ++j)
-      v[j] = __ldcg(reinterpret_cast<const float2*>(src + static_cast<size_t>(s0 + j < nc ? s0 + j : s0) * slot_stride));
+    for (int j = 0; j < kBatch; ++j) {
+      v[j] = make_float2(0.f, 0.f);
+      if (s0 + j < nc) v[j] = __ldcg(reinterpret_cast<const float2*>(src + static_cast<size_t>(s0 + j) * slot_stride));
+    }
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       if (s0 + j < nc) {
